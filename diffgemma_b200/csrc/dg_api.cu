@@ -1,0 +1,836 @@
+// Host side of the C ABI declared in include/dg_attn.h: context, KV cache objects, argument
+// validation, kernel selection and launch, split planning, NCCL merge.  The host mirrors what the
+// reference's step encoder does for its two attention stages (paths relative to the reference
+// project): encode_layer_qk_rope_kv_dispatch src/metal/step_kernel/enc.rs:1733-1806 and
+// encode_layer_attention_dispatch src/metal/step_kernel/enc.rs:2102-2296 (kernel choice by layer
+// geometry, buffer binding, grids).  There is no CPU fallback: without a usable GPU every call
+// returns an error.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "dg_common.cuh"
+#include "dg_kernels.h"
+
+using namespace dg;
+
+// ------------------------------------------------------------------------------------------
+// error plumbing
+// ------------------------------------------------------------------------------------------
+static thread_local std::string g_last_error;
+
+static int32_t fail_cuda(cudaError_t e, const char* what) {
+  g_last_error = std::string(what) + ": " + cudaGetErrorString(e);
+  return DG_ERR_CUDA;
+}
+#define DG_CUDA(call)                                \
+  do {                                               \
+    cudaError_t e__ = (call);                        \
+    if (e__ != cudaSuccess) return fail_cuda(e__, #call); \
+  } while (0)
+
+static int32_t fail(int32_t code, const char* msg) {
+  g_last_error = msg;
+  return code;
+}
+
+// ------------------------------------------------------------------------------------------
+// objects
+// ------------------------------------------------------------------------------------------
+struct dg_ctx {
+  int device = 0;
+  int num_sms = 0;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;
+  DevStatus* d_status = nullptr;
+  float2* rope_table = nullptr;        // [kRopeSlots][kMaxCanvas][kMaxRotHalf]
+  uint32_t* counters = nullptr;        // [kMaxQueryTiles], zero between launches
+  float* ws_o = nullptr;               // split partials
+  float* ws_ml = nullptr;
+  size_t ws_splits = 0, ws_rows = 0;   // capacity of ws_o / ws_ml: splits x rows (x 256 / x 2)
+  __nv_bfloat16* stage_q = nullptr;    // device staging for host-buffer calls / pre-normed Q
+  __nv_bfloat16* stage_k = nullptr;
+  __nv_bfloat16* stage_v = nullptr;
+  __nv_bfloat16* stage_o = nullptr;
+  size_t stage_q_elems = 0, stage_kv_elems = 0;
+  float* nccl_pay = nullptr;           // [rows][D+1] payload of the cross-rank merge
+  float* nccl_mg = nullptr;            // [rows]
+  size_t nccl_rows = 0, nccl_d = 0;
+  int force_general = 0;
+  uint32_t forced_splits = 0;
+  uint32_t last_launches = 0;
+};
+
+struct dg_kv {
+  dg_ctx* ctx = nullptr;
+  __nv_bfloat16* k = nullptr;   // [Hkv][cap][D]
+  __nv_bfloat16* v = nullptr;
+  uint64_t cap = 0;
+  uint32_t Hkv = 0, D = 0;
+  bool has_tmap = false;
+  CUtensorMap tm_k, tm_v;
+};
+
+constexpr uint32_t kRopeSlots = 8;
+constexpr uint32_t kMaxQueryTiles = 4096;
+
+// ------------------------------------------------------------------------------------------
+// driver entry point for tensor-map encoding (no link-time dependency on libcuda)
+// ------------------------------------------------------------------------------------------
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static PFN_encodeTiled get_encode_fn() {
+  static PFN_encodeTiled fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<PFN_encodeTiled>(p);
+  return fn;
+}
+
+static int32_t make_kv_tmap(CUtensorMap* tm, void* base, uint64_t cap, uint32_t Hkv) {
+  PFN_encodeTiled enc = get_encode_fn();
+  if (!enc) return fail(DG_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  const cuuint64_t dims[3] = {256, cap, Hkv};
+  const cuuint64_t strides[2] = {256 * 2, cap * 256 * 2};   // bytes, dims 1 and 2
+  const cuuint32_t box[3] = {64, 128, 1};                    // 128 B x 128 keys
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_error = "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(int(r));
+    return DG_ERR_CUDA;
+  }
+  return DG_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// validation helpers
+// ------------------------------------------------------------------------------------------
+static int32_t check_desc(const dg_layer_desc* d) {
+  if (!d) return fail(DG_ERR_INVALID_ARG, "desc is NULL");
+  if (d->n_q_heads == 0 || d->n_kv_heads == 0 || d->n_q_heads % d->n_kv_heads != 0)
+    return fail(DG_ERR_INVALID_ARG, "n_q_heads must be a positive multiple of n_kv_heads");
+  if (d->head_dim == 0 || d->head_dim % 8 != 0 || d->head_dim > kMaxHeadDim)
+    return fail(DG_ERR_UNSUPPORTED, "head_dim must be a multiple of 8, at most 512");
+  if (d->canvas == 0 || d->canvas > kMaxCanvas) return fail(DG_ERR_UNSUPPORTED, "canvas must be in 1..256");
+  if (d->rotary_dim > d->head_dim || d->rotary_dim % 2 != 0)
+    return fail(DG_ERR_INVALID_ARG, "rotary_dim must be even and <= head_dim");
+  if (d->mask_mode > DG_MASK_WINDOW_PER_ROW) return fail(DG_ERR_INVALID_ARG, "unknown mask_mode");
+  if (d->rope_pairing > DG_ROPE_PROPORTIONAL) return fail(DG_ERR_INVALID_ARG, "unknown rope_pairing");
+  if (d->rope_pairing == DG_ROPE_SPLIT_HALF && d->rotary_dim / 2 + d->rotary_dim / 2 > d->head_dim)
+    return fail(DG_ERR_INVALID_ARG, "rotary_dim too large");
+  if (d->rope_pairing == DG_ROPE_PROPORTIONAL && d->rotary_dim / 2 > d->head_dim / 2)
+    return fail(DG_ERR_INVALID_ARG, "rotary_dim too large for proportional pairing");
+  if (!(d->softmax_scale > 0.f) || !std::isfinite(d->softmax_scale))
+    return fail(DG_ERR_INVALID_ARG, "softmax_scale must be positive and finite");
+  if (!(d->rope_theta > 0.f)) return fail(DG_ERR_INVALID_ARG, "rope_theta must be positive");
+  return DG_OK;
+}
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static RopeParams make_rope(const dg_layer_desc& d) {
+  RopeParams rp;
+  rp.rot_half = d.rotary_dim / 2;
+  rp.pair_off = d.rope_pairing == DG_ROPE_SPLIT_HALF ? d.rotary_dim / 2 : d.head_dim / 2;
+  // theta^(-2i/head_dim) evaluated in f32 on the host (src/shaders/attn/cpu.rs:35); the device only
+  // multiplies by the position and takes cosf/sinf of the f32 angle.
+  for (uint32_t i = 0; i < kMaxRotHalf; ++i)
+    rp.inv_freq[i] = i < rp.rot_half ? std::pow(d.rope_theta, -2.0f * float(i) / float(d.head_dim)) : 0.f;
+  return rp;
+}
+
+static bool tensor_path_ok(const dg_layer_desc& d) { return d.head_dim == 256 && d.canvas <= kMaxCanvas; }
+// the in-kernel Q prologue covers full split-half rotary only
+static bool fused_q_prologue_ok(const dg_layer_desc& d) {
+  return d.rotary_dim == 256 && d.rope_pairing == DG_ROPE_SPLIT_HALF;
+}
+
+static uint32_t choose_splits(const dg_ctx* ctx, uint32_t q_tiles, uint32_t k_tiles) {
+  uint32_t smax = k_tiles < kSm100MaxSplits ? k_tiles : kSm100MaxSplits;
+  if (smax < 1) smax = 1;
+  if (ctx->forced_splits) return ctx->forced_splits < smax ? ctx->forced_splits : smax;
+  const uint32_t sms = ctx->num_sms > 0 ? uint32_t(ctx->num_sms) : 148u;
+  uint32_t best = 1;
+  uint64_t best_cost = ~0ull;
+  for (uint32_t s = 1; s <= smax; ++s) {
+    const uint64_t waves = (uint64_t(q_tiles) * s + sms - 1) / sms;
+    const uint64_t per = (k_tiles + s - 1) / s + 3 + (s > 1 ? 1 : 0);   // + prologue/epilogue/merge in tile units
+    const uint64_t cost = waves * per;
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;
+}
+
+static int32_t ensure_split_ws(dg_ctx* ctx, uint32_t splits, uint32_t rows) {
+  if (splits <= ctx->ws_splits && rows <= ctx->ws_rows) return DG_OK;
+  const size_t s = splits > ctx->ws_splits ? splits : ctx->ws_splits;
+  const size_t r = rows > ctx->ws_rows ? rows : ctx->ws_rows;
+  DG_CUDA(cudaStreamSynchronize(ctx->stream));
+  if (ctx->ws_o) cudaFree(ctx->ws_o);
+  if (ctx->ws_ml) cudaFree(ctx->ws_ml);
+  ctx->ws_o = ctx->ws_ml = nullptr;
+  ctx->ws_splits = ctx->ws_rows = 0;
+  DG_CUDA(cudaMalloc(&ctx->ws_o, s * r * 256 * sizeof(float)));
+  DG_CUDA(cudaMalloc(&ctx->ws_ml, s * r * 2 * sizeof(float)));
+  ctx->ws_splits = s;
+  ctx->ws_rows = r;
+  return DG_OK;
+}
+
+static int32_t ensure_stage(dg_ctx* ctx, size_t q_elems, size_t kv_elems) {
+  if (q_elems > ctx->stage_q_elems) {
+    DG_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->stage_q) cudaFree(ctx->stage_q);
+    if (ctx->stage_o) cudaFree(ctx->stage_o);
+    ctx->stage_q = ctx->stage_o = nullptr;
+    ctx->stage_q_elems = 0;
+    DG_CUDA(cudaMalloc(&ctx->stage_q, q_elems * 2));
+    DG_CUDA(cudaMalloc(&ctx->stage_o, q_elems * 2));
+    ctx->stage_q_elems = q_elems;
+  }
+  if (kv_elems > ctx->stage_kv_elems) {
+    DG_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->stage_k) cudaFree(ctx->stage_k);
+    if (ctx->stage_v) cudaFree(ctx->stage_v);
+    ctx->stage_k = ctx->stage_v = nullptr;
+    ctx->stage_kv_elems = 0;
+    DG_CUDA(cudaMalloc(&ctx->stage_k, kv_elems * 2));
+    DG_CUDA(cudaMalloc(&ctx->stage_v, kv_elems * 2));
+    ctx->stage_kv_elems = kv_elems;
+  }
+  return DG_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// context
+// ------------------------------------------------------------------------------------------
+extern "C" const char* dg_last_error_message(void) { return g_last_error.c_str(); }
+
+extern "C" const char* dg_status_str(int32_t s) {
+  switch (s) {
+    case DG_OK: return "ok";
+    case DG_ERR_INVALID_ARG: return "invalid argument";
+    case DG_ERR_UNSUPPORTED: return "unsupported geometry";
+    case DG_ERR_CAPACITY: return "kv_len + canvas exceeds the cache capacity";
+    case DG_ERR_CUDA: return "CUDA error";
+    case DG_ERR_NO_DEVICE: return "no sm_100 device";
+    case DG_ERR_NCCL: return "NCCL error";
+    case DG_ERR_ALIGNMENT: return "pointer not 16-byte aligned";
+    case DG_DEV_WAIT_TIMEOUT: return "device-side wait timed out";
+    case DG_DEV_BAD_SHAPE: return "device-side shape check failed";
+    default: return "unknown status";
+  }
+}
+
+extern "C" int32_t dg_ctx_create(int32_t device, dg_ctx** out) {
+  if (!out) return fail(DG_ERR_INVALID_ARG, "out is NULL");
+  *out = nullptr;
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
+    cudaGetLastError();
+    return fail(DG_ERR_NO_DEVICE, "no CUDA device visible; this library has no CPU path");
+  }
+  if (device < 0 || device >= n) return fail(DG_ERR_INVALID_ARG, "device index out of range");
+  cudaDeviceProp prop;
+  DG_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) return fail(DG_ERR_NO_DEVICE, "device is not sm_100 (B200); kernels are built for sm_100a only");
+  DG_CUDA(cudaSetDevice(device));
+  dg_ctx* c = new (std::nothrow) dg_ctx();
+  if (!c) return fail(DG_ERR_INVALID_ARG, "out of host memory");
+  c->device = device;
+  c->num_sms = prop.multiProcessorCount;
+  cudaError_t e = cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_status, sizeof(DevStatus));
+  if (e == cudaSuccess) e = cudaMemset(c->d_status, 0, sizeof(DevStatus));
+  if (e == cudaSuccess) e = cudaMalloc(&c->rope_table, size_t(kRopeSlots) * kMaxCanvas * kMaxRotHalf * sizeof(float2));
+  if (e == cudaSuccess) e = cudaMalloc(&c->counters, kMaxQueryTiles * sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMemset(c->counters, 0, kMaxQueryTiles * sizeof(uint32_t));
+  if (e == cudaSuccess) e = sm100_attn_configure();
+  if (e != cudaSuccess) {
+    dg_ctx_destroy(c);
+    return fail_cuda(e, "dg_ctx_create");
+  }
+  c->stream = c->own_stream;
+  *out = c;
+  return DG_OK;
+}
+
+extern "C" int32_t dg_ctx_destroy(dg_ctx* c) {
+  if (!c) return DG_OK;
+  cudaSetDevice(c->device);
+  if (c->stream) cudaStreamSynchronize(c->stream);
+  cudaFree(c->d_status);
+  cudaFree(c->rope_table);
+  cudaFree(c->counters);
+  cudaFree(c->ws_o);
+  cudaFree(c->ws_ml);
+  cudaFree(c->stage_q);
+  cudaFree(c->stage_k);
+  cudaFree(c->stage_v);
+  cudaFree(c->stage_o);
+  cudaFree(c->nccl_pay);
+  cudaFree(c->nccl_mg);
+  if (c->own_stream) cudaStreamDestroy(c->own_stream);
+  delete c;
+  return DG_OK;
+}
+
+extern "C" int32_t dg_ctx_set_stream(dg_ctx* c, void* s) {
+  if (!c) return fail(DG_ERR_INVALID_ARG, "ctx is NULL");
+  c->stream = s ? static_cast<cudaStream_t>(s) : c->own_stream;
+  return DG_OK;
+}
+extern "C" void* dg_ctx_stream(dg_ctx* c) { return c ? static_cast<void*>(c->stream) : nullptr; }
+
+static int32_t read_status(dg_ctx* c, DevStatus* h) {
+  DG_CUDA(cudaMemcpyAsync(h, c->d_status, sizeof(DevStatus), cudaMemcpyDeviceToHost, c->stream));
+  DG_CUDA(cudaStreamSynchronize(c->stream));
+  return DG_OK;
+}
+
+extern "C" int32_t dg_ctx_synchronize(dg_ctx* c) {
+  if (!c) return fail(DG_ERR_INVALID_ARG, "ctx is NULL");
+  DG_CUDA(cudaSetDevice(c->device));
+  DevStatus h;
+  const int32_t r = read_status(c, &h);
+  if (r != DG_OK) return r;
+  return int32_t(h.code);
+}
+
+extern "C" int32_t dg_ctx_last_device_status(dg_ctx* c, uint32_t out[4]) {
+  if (!c || !out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  DG_CUDA(cudaSetDevice(c->device));
+  DevStatus h;
+  const int32_t r = read_status(c, &h);
+  if (r != DG_OK) return r;
+  out[0] = h.code; out[1] = h.kernel_id; out[2] = h.cta; out[3] = h.value;
+  return DG_OK;
+}
+
+extern "C" int32_t dg_uses_tensor_path(const dg_layer_desc* d) {
+  if (check_desc(d) != DG_OK) return 0;
+  return tensor_path_ok(*d) ? 1 : 0;
+}
+extern "C" int32_t dg_ctx_force_general(dg_ctx* c, int32_t on) {
+  if (!c) return fail(DG_ERR_INVALID_ARG, "ctx is NULL");
+  c->force_general = on ? 1 : 0;
+  return DG_OK;
+}
+extern "C" int32_t dg_ctx_set_splits(dg_ctx* c, uint32_t n) {
+  if (!c) return fail(DG_ERR_INVALID_ARG, "ctx is NULL");
+  if (n > kSm100MaxSplits) return fail(DG_ERR_INVALID_ARG, "at most 32 splits");
+  c->forced_splits = n;
+  return DG_OK;
+}
+extern "C" uint32_t dg_ctx_last_launch_count(const dg_ctx* c) { return c ? c->last_launches : 0; }
+
+// ------------------------------------------------------------------------------------------
+// KV cache
+// ------------------------------------------------------------------------------------------
+extern "C" int32_t dg_kv_create(dg_ctx* c, const dg_layer_desc* d, uint64_t capacity_tokens, dg_kv** out) {
+  if (!c || !out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  *out = nullptr;
+  int32_t r = check_desc(d);
+  if (r != DG_OK) return r;
+  if (capacity_tokens == 0 || capacity_tokens > (1ull << 31)) return fail(DG_ERR_INVALID_ARG, "bad capacity");
+  DG_CUDA(cudaSetDevice(c->device));
+  dg_kv* kv = new (std::nothrow) dg_kv();
+  if (!kv) return fail(DG_ERR_INVALID_ARG, "out of host memory");
+  kv->ctx = c;
+  kv->cap = (capacity_tokens + 127) / 128 * 128;
+  kv->Hkv = d->n_kv_heads;
+  kv->D = d->head_dim;
+  const size_t bytes = size_t(kv->Hkv) * kv->cap * kv->D * 2;
+  cudaError_t e = cudaMalloc(&kv->k, bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&kv->v, bytes);
+  // rows in [T, cap) are read by whole-tile loads and masked afterwards: they must be finite
+  if (e == cudaSuccess) e = cudaMemsetAsync(kv->k, 0, bytes, c->stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(kv->v, 0, bytes, c->stream);
+  if (e != cudaSuccess) {
+    dg_kv_destroy(kv);
+    return fail_cuda(e, "dg_kv_create");
+  }
+  if (kv->D == 256) {
+    r = make_kv_tmap(&kv->tm_k, kv->k, kv->cap, kv->Hkv);
+    if (r == DG_OK) r = make_kv_tmap(&kv->tm_v, kv->v, kv->cap, kv->Hkv);
+    if (r != DG_OK) {
+      dg_kv_destroy(kv);
+      return r;
+    }
+    kv->has_tmap = true;
+  }
+  *out = kv;
+  return DG_OK;
+}
+
+extern "C" int32_t dg_kv_destroy(dg_kv* kv) {
+  if (!kv) return DG_OK;
+  if (kv->ctx) {
+    cudaSetDevice(kv->ctx->device);
+    cudaStreamSynchronize(kv->ctx->stream);
+  }
+  cudaFree(kv->k);
+  cudaFree(kv->v);
+  delete kv;
+  return DG_OK;
+}
+extern "C" uint64_t dg_kv_capacity(const dg_kv* kv) { return kv ? kv->cap : 0; }
+
+extern "C" int32_t dg_kv_load_prefix(dg_kv* kv, const void* k, const void* v, uint64_t pos0, uint64_t n) {
+  if (!kv || !k || !v) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  if (pos0 + n > kv->cap) return fail(DG_ERR_CAPACITY, "prefix does not fit the cache");
+  if (n == 0) return DG_OK;
+  DG_CUDA(cudaSetDevice(kv->ctx->device));
+  const size_t row = size_t(kv->D) * 2, spitch = size_t(kv->Hkv) * row;
+  for (uint32_t h = 0; h < kv->Hkv; ++h) {
+    DG_CUDA(cudaMemcpy2DAsync(kv->k + (size_t(h) * kv->cap + pos0) * kv->D, row,
+                              static_cast<const uint8_t*>(k) + h * row, spitch, row, n, cudaMemcpyDefault,
+                              kv->ctx->stream));
+    DG_CUDA(cudaMemcpy2DAsync(kv->v + (size_t(h) * kv->cap + pos0) * kv->D, row,
+                              static_cast<const uint8_t*>(v) + h * row, spitch, row, n, cudaMemcpyDefault,
+                              kv->ctx->stream));
+  }
+  return DG_OK;
+}
+
+extern "C" int32_t dg_kv_read(dg_kv* kv, void* k_out, void* v_out, uint64_t pos0, uint64_t n) {
+  if (!kv || !k_out || !v_out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  if (pos0 + n > kv->cap) return fail(DG_ERR_CAPACITY, "range outside the cache");
+  DG_CUDA(cudaSetDevice(kv->ctx->device));
+  const size_t row = size_t(kv->D) * 2, dpitch = size_t(kv->Hkv) * row;
+  for (uint32_t h = 0; h < kv->Hkv && n > 0; ++h) {
+    DG_CUDA(cudaMemcpy2DAsync(static_cast<uint8_t*>(k_out) + h * row, dpitch,
+                              kv->k + (size_t(h) * kv->cap + pos0) * kv->D, row, row, n, cudaMemcpyDefault,
+                              kv->ctx->stream));
+    DG_CUDA(cudaMemcpy2DAsync(static_cast<uint8_t*>(v_out) + h * row, dpitch,
+                              kv->v + (size_t(h) * kv->cap + pos0) * kv->D, row, row, n, cudaMemcpyDefault,
+                              kv->ctx->stream));
+  }
+  DG_CUDA(cudaStreamSynchronize(kv->ctx->stream));
+  return DG_OK;
+}
+
+static int32_t check_kv(const dg_layer_desc& d, const dg_kv* kv, uint64_t end_pos) {
+  if (!kv) return fail(DG_ERR_INVALID_ARG, "kv is NULL");
+  if (kv->Hkv != d.n_kv_heads || kv->D != d.head_dim) return fail(DG_ERR_INVALID_ARG, "kv geometry differs from desc");
+  if (end_pos > kv->cap) return fail(DG_ERR_CAPACITY, "kv_len + canvas exceeds the cache capacity");
+  return DG_OK;
+}
+
+// append n tokens (norm + RoPE + cache write); optionally also Q (stage 1) and the RoPE table
+static int32_t do_append(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint64_t pos0, uint32_t n, const void* q_in,
+                         void* q_out, const void* k_in, void* k_out, const void* v_in, void* v_out, const void* qw,
+                         const void* kw, float2* table) {
+  AppendParams ap;
+  ap.q_in = static_cast<const __nv_bfloat16*>(q_in);
+  ap.q_out = static_cast<__nv_bfloat16*>(q_out);
+  ap.k_in = static_cast<const __nv_bfloat16*>(k_in);
+  ap.k_out = static_cast<__nv_bfloat16*>(k_out);
+  ap.v_in = static_cast<const __nv_bfloat16*>(v_in);
+  ap.v_out = static_cast<__nv_bfloat16*>(v_out);
+  ap.qw = static_cast<const __nv_bfloat16*>(qw);
+  ap.kw = static_cast<const __nv_bfloat16*>(kw);
+  ap.cache_k = kv->k;
+  ap.cache_v = kv->v;
+  ap.rope_table = table;
+  ap.cap = kv->cap;
+  ap.pos0 = uint32_t(pos0);
+  ap.n = n;
+  ap.Hq = d.n_q_heads;
+  ap.Hkv = d.n_kv_heads;
+  ap.D = d.head_dim;
+  ap.v_norm = d.v_norm;
+  ap.eps = d.rms_eps;
+  const RopeParams rp = make_rope(d);
+  launch_append(ap, rp, c->stream);
+  DG_CUDA(cudaGetLastError());
+  c->last_launches += 1;
+  return DG_OK;
+}
+
+extern "C" int32_t dg_kv_append(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint64_t pos0, uint32_t n, const void* k,
+                                const void* v, const void* kw) {
+  if (!c || !k || !v) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  int32_t r = check_desc(d);
+  if (r != DG_OK) return r;
+  r = check_kv(*d, kv, pos0 + n);
+  if (r != DG_OK) return r;
+  if (n > 65535) return fail(DG_ERR_INVALID_ARG, "append at most 65535 tokens per call");
+  DG_CUDA(cudaSetDevice(c->device));
+  c->last_launches = 0;
+  return do_append(c, *d, kv, pos0, n, nullptr, nullptr, k, nullptr, v, nullptr, nullptr, kw, nullptr);
+}
+
+// ------------------------------------------------------------------------------------------
+// attention launch (stage 2), shared by every entry point
+// ------------------------------------------------------------------------------------------
+struct AttnCall {
+  const void* q = nullptr;       // [C][Hq][D]
+  const void* qw = nullptr;
+  const float2* table = nullptr;
+  bool q_prenormed = false;
+  const uint8_t* attend = nullptr;
+  void* out = nullptr;           // bf16, or NULL for partial
+  float* out_o = nullptr;
+  float* out_m = nullptr;
+  float* out_l = nullptr;
+  uint32_t kv_len = 0, t0 = 0, t1 = 0xffffffffu;
+  int include_canvas = 1;
+};
+
+static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const AttnCall& a) {
+  AttnParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.q = static_cast<const __nv_bfloat16*>(a.q);
+  p.qw = static_cast<const __nv_bfloat16*>(a.qw);
+  p.rope_table = a.table;
+  p.cache_k = kv->k;
+  p.cache_v = kv->v;
+  p.attend = a.attend;
+  p.out = static_cast<__nv_bfloat16*>(a.out);
+  p.out_o = a.out_o;
+  p.out_m = a.out_m;
+  p.out_l = a.out_l;
+  p.status = c->d_status;
+  p.cap = kv->cap;
+  p.mask = make_mask(d, a.kv_len, a.t0, a.t1, a.include_canvas);
+  p.C = d.canvas;
+  p.Hq = d.n_q_heads;
+  p.Hkv = d.n_kv_heads;
+  p.G = d.n_q_heads / d.n_kv_heads;
+  p.D = d.head_dim;
+  p.q_prenormed = a.q_prenormed ? 1u : 0u;
+  p.n_splits = 1;
+  p.rot_half = d.rotary_dim / 2;
+  p.pair_off = d.rope_pairing == DG_ROPE_SPLIT_HALF ? d.rotary_dim / 2 : d.head_dim / 2;
+  p.scale_log2 = d.softmax_scale * 1.4426950408889634f;
+  p.eps = d.rms_eps;
+
+  const bool tensor = tensor_path_ok(d) && kv->has_tmap && !c->force_general && a.attend == nullptr &&
+                      (a.q_prenormed || fused_q_prologue_ok(d));
+  if (!tensor) {
+    launch_attn_general(p, c->stream);
+    DG_CUDA(cudaGetLastError());
+    c->last_launches += 1;
+    return DG_OK;
+  }
+  const uint32_t q_tiles = sm100_query_tiles(p.C, p.G, p.Hkv);
+  const uint32_t k_tiles = sm100_key_tiles(p.mask);
+  if (q_tiles > kMaxQueryTiles) return fail(DG_ERR_UNSUPPORTED, "too many query tiles");
+  p.n_splits = choose_splits(c, q_tiles, k_tiles);
+  if (p.n_splits > 1) {
+    const int32_t r = ensure_split_ws(c, p.n_splits, p.C * p.Hq);
+    if (r != DG_OK) return r;
+    p.ws_o = c->ws_o;
+    p.ws_ml = c->ws_ml;
+    p.ws_counters = c->counters;
+  }
+  const cudaError_t e = launch_attn_sm100(p, kv->tm_k, kv->tm_v, c->stream);
+  if (e != cudaSuccess) return fail_cuda(e, "launch_attn_sm100");
+  c->last_launches += 1;
+  return DG_OK;
+}
+
+static int32_t check_ptrs16(std::initializer_list<const void*> ps) {
+  for (const void* p : ps)
+    if (p && !aligned16(p)) return fail(DG_ERR_ALIGNMENT, "device pointers must be 16-byte aligned");
+  return DG_OK;
+}
+
+// one canvas: stage 1 on K/V (+ table), then stage 2 with the fused Q prologue
+static int32_t denoise_one(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint32_t kv_len, uint32_t slot, const void* q,
+                           const void* k, const void* v, const void* qw, const void* kw, const uint8_t* attend,
+                           AttnCall a) {
+  int32_t r = check_kv(d, kv, uint64_t(kv_len) + d.canvas);
+  if (r != DG_OK) return r;
+  float2* table = c->rope_table + size_t(slot % kRopeSlots) * kMaxCanvas * kMaxRotHalf;
+  const bool tensor = tensor_path_ok(d) && kv->has_tmap && !c->force_general && attend == nullptr;
+  if (tensor && !fused_q_prologue_ok(d)) {
+    // partial / proportional rotary: run the stand-alone Q prologue into the staging buffer
+    r = ensure_stage(c, size_t(d.canvas) * d.n_q_heads * d.head_dim, 0);
+    if (r != DG_OK) return r;
+    r = do_append(c, d, kv, kv_len, d.canvas, q, c->stage_q, k, nullptr, v, nullptr, qw, kw, nullptr);
+    if (r != DG_OK) return r;
+    a.q = c->stage_q;
+    a.q_prenormed = true;
+  } else {
+    r = do_append(c, d, kv, kv_len, d.canvas, nullptr, nullptr, k, nullptr, v, nullptr, nullptr, kw, table);
+    if (r != DG_OK) return r;
+    a.q = q;
+    a.qw = qw;
+    a.table = table;
+    a.q_prenormed = false;
+  }
+  a.kv_len = kv_len;
+  a.attend = attend;
+  return do_attention(c, d, kv, a);
+}
+
+extern "C" int32_t dg_qk_rope_kv(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint32_t kv_len, void* q, void* k, void* v,
+                                 const void* qw, const void* kw) {
+  if (!c || !q || !k || !v) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  int32_t r = check_desc(d);
+  if (r != DG_OK) return r;
+  r = check_kv(*d, kv, uint64_t(kv_len) + d->canvas);
+  if (r != DG_OK) return r;
+  DG_CUDA(cudaSetDevice(c->device));
+  c->last_launches = 0;
+  return do_append(c, *d, kv, kv_len, d->canvas, q, q, k, k, v, d->v_norm ? v : nullptr, qw, kw, nullptr);
+}
+
+extern "C" int32_t dg_attention(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint32_t kv_len, const void* q, void* out) {
+  if (!c || !q || !out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  int32_t r = check_desc(d);
+  if (r != DG_OK) return r;
+  r = check_kv(*d, kv, uint64_t(kv_len) + d->canvas);
+  if (r != DG_OK) return r;
+  r = check_ptrs16({q, out});
+  if (r != DG_OK) return r;
+  DG_CUDA(cudaSetDevice(c->device));
+  c->last_launches = 0;
+  AttnCall a;
+  a.q = q;
+  a.q_prenormed = true;
+  a.out = out;
+  a.kv_len = kv_len;
+  return do_attention(c, *d, kv, a);
+}
+
+extern "C" int32_t dg_attn_denoise(dg_ctx* c, const dg_layer_desc* d, dg_kv* const* kv, const uint32_t* kv_len,
+                                   uint32_t batch, const void* q, const void* k, const void* v, const void* qw,
+                                   const void* kw, void* out) {
+  if (!c || !kv || !kv_len || !q || !k || !v || !out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  int32_t r = check_desc(d);
+  if (r != DG_OK) return r;
+  r = check_ptrs16({q, k, v, qw, kw, out});
+  if (r != DG_OK) return r;
+  DG_CUDA(cudaSetDevice(c->device));
+  c->last_launches = 0;
+  const size_t qe = size_t(d->canvas) * d->n_q_heads * d->head_dim, ke = size_t(d->canvas) * d->n_kv_heads * d->head_dim;
+  for (uint32_t b = 0; b < batch; ++b) {
+    AttnCall a;
+    a.out = static_cast<__nv_bfloat16*>(out) + b * qe;
+    r = denoise_one(c, *d, kv[b], kv_len[b], b, static_cast<const __nv_bfloat16*>(q) + b * qe,
+                    static_cast<const __nv_bfloat16*>(k) + b * ke, static_cast<const __nv_bfloat16*>(v) + b * ke, qw, kw,
+                    nullptr, a);
+    if (r != DG_OK) return r;
+  }
+  return DG_OK;
+}
+
+extern "C" int32_t dg_attn_denoise_host(dg_ctx* c, const dg_layer_desc* d, dg_kv* const* kv, const uint32_t* kv_len,
+                                        uint32_t batch, const void* q, const void* k, const void* v, const void* qw,
+                                        const void* kw, void* out) {
+  if (!c || !kv || !kv_len || !q || !k || !v || !out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  int32_t r = check_desc(d);
+  if (r != DG_OK) return r;
+  DG_CUDA(cudaSetDevice(c->device));
+  const size_t qe = size_t(batch) * d->canvas * d->n_q_heads * d->head_dim;
+  const size_t ke = size_t(batch) * d->canvas * d->n_kv_heads * d->head_dim;
+  r = ensure_stage(c, qe, ke);
+  if (r != DG_OK) return r;
+  DG_CUDA(cudaMemcpyAsync(c->stage_q, q, qe * 2, cudaMemcpyHostToDevice, c->stream));
+  DG_CUDA(cudaMemcpyAsync(c->stage_k, k, ke * 2, cudaMemcpyHostToDevice, c->stream));
+  DG_CUDA(cudaMemcpyAsync(c->stage_v, v, ke * 2, cudaMemcpyHostToDevice, c->stream));
+  // qw / kw are tiny and constant per layer: they stay device pointers.  When the stand-alone Q
+  // prologue runs it normalises stage_q in place, which is safe (one warp owns one head vector).
+  r = dg_attn_denoise(c, d, kv, kv_len, batch, c->stage_q, c->stage_k, c->stage_v, qw, kw, c->stage_o);
+  if (r != DG_OK) return r;
+  const uint32_t launches = c->last_launches;
+  DG_CUDA(cudaMemcpyAsync(out, c->stage_o, qe * 2, cudaMemcpyDeviceToHost, c->stream));
+  const int32_t s = dg_ctx_synchronize(c);
+  c->last_launches = launches;
+  return s;
+}
+
+extern "C" int32_t dg_attn_denoise_bitmap(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint32_t kv_len, const void* q,
+                                          const void* k, const void* v, const void* qw, const void* kw,
+                                          const uint8_t* attend, void* out) {
+  if (!c || !q || !k || !v || !attend || !out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  int32_t r = check_desc(d);
+  if (r != DG_OK) return r;
+  DG_CUDA(cudaSetDevice(c->device));
+  c->last_launches = 0;
+  AttnCall a;
+  a.out = out;
+  return denoise_one(c, *d, kv, kv_len, 0, q, k, v, qw, kw, attend, a);
+}
+
+extern "C" int32_t dg_attn_partial(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint32_t kv_len, uint32_t t0, uint32_t t1,
+                                   int32_t include_canvas, const void* q, const void* k, const void* v, const void* qw,
+                                   const void* kw, float* o_unnorm, float* m, float* l) {
+  if (!c || !q || !k || !v || !o_unnorm || !m || !l) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  int32_t r = check_desc(d);
+  if (r != DG_OK) return r;
+  r = check_ptrs16({q, k, v, qw, kw, o_unnorm});
+  if (r != DG_OK) return r;
+  DG_CUDA(cudaSetDevice(c->device));
+  c->last_launches = 0;
+  AttnCall a;
+  a.out = nullptr;
+  a.out_o = o_unnorm;
+  a.out_m = m;
+  a.out_l = l;
+  a.t0 = t0;
+  a.t1 = t1;
+  a.include_canvas = include_canvas ? 1 : 0;
+  return denoise_one(c, *d, kv, kv_len, 0, q, k, v, qw, kw, nullptr, a);
+}
+
+extern "C" int32_t dg_attn_merge_local(dg_ctx* c, uint32_t n_parts, uint32_t rows, uint32_t head_dim, const float* o,
+                                       const float* m, const float* l, void* out) {
+  if (!c || !o || !m || !l || !out || n_parts == 0) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  DG_CUDA(cudaSetDevice(c->device));
+  launch_merge_local(n_parts, rows, head_dim, o, m, l, static_cast<__nv_bfloat16*>(out), c->stream);
+  DG_CUDA(cudaGetLastError());
+  c->last_launches = 1;
+  return DG_OK;
+}
+
+extern "C" int32_t dg_attn_visibility(dg_ctx* c, const dg_layer_desc* d, uint32_t kv_len, uint32_t t0, uint32_t t1,
+                                      int32_t include_canvas, uint8_t* attend_out) {
+  if (!c || !attend_out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  const int32_t r = check_desc(d);
+  if (r != DG_OK) return r;
+  DG_CUDA(cudaSetDevice(c->device));
+  launch_visibility(make_mask(*d, kv_len, t0, t1, include_canvas), d->canvas, attend_out, c->stream);
+  DG_CUDA(cudaGetLastError());
+  return DG_OK;
+}
+
+extern "C" double dg_attn_flops(const dg_layer_desc* d, uint32_t kv_len) {
+  if (check_desc(d) != DG_OK) return 0.0;
+  const MaskParams mk = make_mask(*d, kv_len, 0, 0xffffffffu, 1);
+  double vis = 0.0;
+  for (uint32_t r = 0; r < d->canvas; ++r) {
+    const uint32_t lo = mask_row_lo(mk, r);
+    vis += double(mk.pre_hi > lo ? mk.pre_hi - lo : 0u) + double(mk.can_hi - mk.kv_len);
+  }
+  return 4.0 * d->head_dim * d->n_q_heads * vis;
+}
+
+// ------------------------------------------------------------------------------------------
+// NCCL (loaded at run time so that the library itself has no hard dependency on it)
+// ------------------------------------------------------------------------------------------
+namespace {
+struct NcclApi {
+  void* handle = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  const char* (*GetErrorString)(ncclResult_t) = nullptr;
+  bool ok = false;
+};
+NcclApi& nccl() {
+  static NcclApi api;
+  static bool tried = false;
+  if (tried) return api;
+  tried = true;
+  const char* env = getenv("DG_NCCL_LIB");
+  const char* names[] = {env, "libnccl.so.2", "libnccl.so"};
+  for (const char* n : names) {
+    if (!n) continue;
+    api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+    if (api.handle) break;
+  }
+  if (!api.handle) return api;
+  api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(api.handle, "ncclGetUniqueId"));
+  api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(api.handle, "ncclCommInitRank"));
+  api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(api.handle, "ncclCommDestroy"));
+  api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(api.handle, "ncclAllReduce"));
+  api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(api.handle, "ncclAllGather"));
+  api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(api.handle, "ncclGetErrorString"));
+  api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce && api.AllGather && api.GetErrorString;
+  return api;
+}
+int32_t fail_nccl(ncclResult_t r, const char* what) {
+  g_last_error = std::string(what) + ": " + (nccl().GetErrorString ? nccl().GetErrorString(r) : "nccl error");
+  return DG_ERR_NCCL;
+}
+}  // namespace
+#define DG_NCCL(call)                                  \
+  do {                                                 \
+    ncclResult_t r__ = (call);                         \
+    if (r__ != ncclSuccess) return fail_nccl(r__, #call); \
+  } while (0)
+
+extern "C" int32_t dg_nccl_unique_id(uint8_t id_out[128]) {
+  if (!id_out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  if (!nccl().ok) return fail(DG_ERR_NCCL, "libnccl.so.2 could not be loaded (set DG_NCCL_LIB)");
+  static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId is 128 bytes");
+  ncclUniqueId id;
+  DG_NCCL(nccl().GetUniqueId(&id));
+  std::memcpy(id_out, &id, 128);
+  return DG_OK;
+}
+extern "C" int32_t dg_nccl_comm_create(dg_ctx* c, const uint8_t id[128], int32_t world, int32_t rank, void** comm_out) {
+  if (!c || !id || !comm_out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  if (!nccl().ok) return fail(DG_ERR_NCCL, "libnccl.so.2 could not be loaded (set DG_NCCL_LIB)");
+  DG_CUDA(cudaSetDevice(c->device));
+  ncclUniqueId uid;
+  std::memcpy(&uid, id, 128);
+  ncclComm_t comm;
+  DG_NCCL(nccl().CommInitRank(&comm, world, uid, rank));
+  *comm_out = comm;
+  return DG_OK;
+}
+extern "C" int32_t dg_nccl_comm_destroy(void* comm) {
+  if (!comm) return DG_OK;
+  if (!nccl().ok) return fail(DG_ERR_NCCL, "NCCL not loaded");
+  DG_NCCL(nccl().CommDestroy(static_cast<ncclComm_t>(comm)));
+  return DG_OK;
+}
+
+extern "C" int32_t dg_attn_merge_nccl(dg_ctx* c, void* comm, float* o_unnorm, float* m, float* l, void* out, uint32_t rows,
+                                      uint32_t head_dim) {
+  if (!c || !comm || !o_unnorm || !m || !l || !out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  if (!nccl().ok) return fail(DG_ERR_NCCL, "NCCL not loaded");
+  DG_CUDA(cudaSetDevice(c->device));
+  if (rows > c->nccl_rows || head_dim > c->nccl_d) {
+    DG_CUDA(cudaStreamSynchronize(c->stream));
+    cudaFree(c->nccl_pay);
+    cudaFree(c->nccl_mg);
+    c->nccl_pay = c->nccl_mg = nullptr;
+    c->nccl_rows = c->nccl_d = 0;
+    DG_CUDA(cudaMalloc(&c->nccl_pay, size_t(rows) * (head_dim + 1) * sizeof(float)));
+    DG_CUDA(cudaMalloc(&c->nccl_mg, size_t(rows) * sizeof(float)));
+    c->nccl_rows = rows;
+    c->nccl_d = head_dim;
+  }
+  ncclComm_t cm = static_cast<ncclComm_t>(comm);
+  // 1. global reference point   2. rescale [O | l] to it   3. sum across ranks   4. normalise
+  DG_NCCL(nccl().AllReduce(m, c->nccl_mg, rows, ncclFloat32, ncclMax, cm, c->stream));
+  launch_merge_pack(rows, head_dim, o_unnorm, m, c->nccl_mg, l, c->nccl_pay, c->stream);
+  DG_CUDA(cudaGetLastError());
+  DG_NCCL(nccl().AllReduce(c->nccl_pay, c->nccl_pay, size_t(rows) * (head_dim + 1), ncclFloat32, ncclSum, cm, c->stream));
+  launch_merge_finalize(rows, head_dim, c->nccl_pay, static_cast<__nv_bfloat16*>(out), c->stream);
+  DG_CUDA(cudaGetLastError());
+  c->last_launches += 2;
+  return DG_OK;
+}
+
+extern "C" int32_t dg_nccl_all_gather(dg_ctx* c, void* comm, const void* send, void* recv, uint64_t bytes_per_rank) {
+  if (!c || !comm || !send || !recv) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  if (!nccl().ok) return fail(DG_ERR_NCCL, "NCCL not loaded");
+  DG_CUDA(cudaSetDevice(c->device));
+  DG_NCCL(nccl().AllGather(send, recv, bytes_per_rank, ncclUint8, static_cast<ncclComm_t>(comm), c->stream));
+  return DG_OK;
+}

@@ -1,0 +1,136 @@
+// Shared host/device definitions for the canvas-attention kernels: the mask predicate (one
+// definition used by every kernel and by the visibility dump, so the mask is bit-exact by
+// construction), launch parameter blocks and the device status word.
+#pragma once
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/dg_attn.h"
+
+namespace dg {
+
+constexpr uint32_t kMaxHeadDim = 512;
+constexpr uint32_t kMaxCanvas = 256;
+constexpr uint32_t kMaxRotHalf = 256;   // rotary_dim / 2 <= 256
+
+// Which keys a canvas row may attend (src/shaders/attn/attention/attention.metal:52-63 for the
+// window rule; split-KV shards intersect the prefix interval with [t0, t1)).
+//   prefix key t (t < kv_len) visible  iff  max(lo(row), t0) <= t < pre_hi
+//   canvas key t (kv_len <= t < can_hi) visible iff include_canvas
+struct MaskParams {
+  uint32_t kv_len;    // first canvas position = number of prefix keys
+  uint32_t t0;        // shard lower bound (0 when unsharded)
+  uint32_t pre_hi;    // min(t1, kv_len)
+  uint32_t can_hi;    // kv_len + canvas when canvas keys are included, else kv_len
+  uint32_t mode;      // DG_MASK_*
+  uint32_t wm1;       // window - 1 (unused when mode == NONE or window == 0)
+  uint32_t windowed;  // 1 when a window applies
+  uint32_t pad_;
+};
+
+__host__ __device__ inline MaskParams make_mask(const dg_layer_desc& d, uint32_t kv_len, uint32_t t0, uint32_t t1,
+                                                int include_canvas) {
+  MaskParams m;
+  m.kv_len = kv_len;
+  m.t0 = t0;
+  m.pre_hi = t1 < kv_len ? t1 : kv_len;
+  m.can_hi = include_canvas ? kv_len + d.canvas : kv_len;
+  m.mode = d.mask_mode;
+  m.windowed = (d.mask_mode != DG_MASK_NONE && d.window != 0) ? 1u : 0u;
+  m.wm1 = m.windowed ? d.window - 1u : 0u;
+  m.pad_ = 0;
+  return m;
+}
+
+// lowest visible prefix key of canvas row `row`
+__host__ __device__ inline uint32_t mask_row_lo(const MaskParams& m, uint32_t row) {
+  uint32_t lo = 0;
+  if (m.windowed) {
+    const uint32_t qpos = (m.mode == DG_MASK_WINDOW_PER_ROW) ? m.kv_len + row : m.kv_len;
+    lo = qpos > m.wm1 ? qpos - m.wm1 : 0u;
+  }
+  return lo > m.t0 ? lo : m.t0;
+}
+
+__host__ __device__ inline bool mask_visible_lo(const MaskParams& m, uint32_t row_lo, uint32_t t) {
+  return (t >= row_lo && t < m.pre_hi) || (t >= m.kv_len && t < m.can_hi);
+}
+__host__ __device__ inline bool mask_visible(const MaskParams& m, uint32_t row, uint32_t t) {
+  return mask_visible_lo(m, mask_row_lo(m, row), t);
+}
+
+// Device status word {code, kernel_id, cta, value}: first writer wins.
+struct DevStatus {
+  uint32_t code, kernel_id, cta, value;
+};
+__device__ inline void dev_status_set(DevStatus* s, uint32_t code, uint32_t kernel_id, uint32_t cta,
+                                      uint32_t value) {
+  if (s == nullptr) return;
+  if (atomicCAS(&s->code, 0u, code) == 0u) {
+    s->kernel_id = kernel_id;
+    s->cta = cta;
+    s->value = value;
+  }
+}
+
+enum : uint32_t { KID_APPEND = 1, KID_GENERAL = 2, KID_SM100 = 3, KID_MERGE = 4, KID_VIS = 5 };
+
+// ----------------------------------------------------------------------------------------
+// Launch parameter blocks
+// ----------------------------------------------------------------------------------------
+struct RopeParams {
+  uint32_t rot_half;     // rotary_dim / 2
+  uint32_t pair_off;     // offset of the partner element: rot_half (split-half) or D/2 (proportional)
+  float inv_freq[kMaxRotHalf];
+};
+
+// qk_rope_kv / append kernel
+struct AppendParams {
+  const __nv_bfloat16* q_in;   // [n][Hq][D] or null
+  __nv_bfloat16* q_out;        // normed + roped Q (may alias q_in) or null
+  const __nv_bfloat16* k_in;   // [n][Hkv][D]
+  __nv_bfloat16* k_out;        // normed + roped K written back (may alias k_in) or null
+  const __nv_bfloat16* v_in;   // [n][Hkv][D]
+  __nv_bfloat16* v_out;        // normed V written back or null
+  const __nv_bfloat16* qw;     // [D] or null
+  const __nv_bfloat16* kw;     // [D] or null
+  __nv_bfloat16* cache_k;      // K[Hkv][cap][D]
+  __nv_bfloat16* cache_v;
+  float2* rope_table;          // [n][rot_half] (cos, sin) of positions pos0 + i, or null
+  uint64_t cap;
+  uint32_t pos0, n;
+  uint32_t Hq, Hkv, D;
+  uint32_t v_norm;
+  float eps;
+};
+
+// attention kernels (general and sm100)
+struct AttnParams {
+  const __nv_bfloat16* q;        // [C][Hq][D]
+  const __nv_bfloat16* qw;       // [D] or null (unit)
+  const float2* rope_table;      // [C][rot_half]; only read when q_prenormed == 0
+  const __nv_bfloat16* cache_k;  // K[Hkv][cap][D]
+  const __nv_bfloat16* cache_v;
+  const uint8_t* attend;         // optional bitmap [C][kv_len+C] (general kernel only)
+  __nv_bfloat16* out;            // [C][Hq][D] or null when partial output is requested
+  float* out_o;                  // partial: [C][Hq][D] fp32 un-normalised
+  float* out_m;                  // partial: [C][Hq]
+  float* out_l;                  // partial: [C][Hq]
+  float* ws_o;                   // split workspace [n_splits][C*Hq][D]
+  float* ws_ml;                  // split workspace [n_splits][C*Hq][2]
+  uint32_t* ws_counters;         // one per query tile, zero between launches
+  DevStatus* status;
+  uint64_t cap;
+  MaskParams mask;
+  uint32_t C, Hq, Hkv, G, D;
+  uint32_t q_prenormed;
+  uint32_t n_splits;
+  uint32_t rot_half, pair_off;
+  float scale_log2;              // softmax_scale * log2(e)
+  float eps;
+};
+
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(uint32_t(b) << 16); }
+
+}  // namespace dg

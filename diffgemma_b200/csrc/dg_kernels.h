@@ -1,0 +1,29 @@
+// Host-callable launchers of the kernels in this directory.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "dg_common.cuh"
+
+namespace dg {
+
+void launch_append(const AppendParams& p, const RopeParams& rp, cudaStream_t st);
+void launch_attn_general(const AttnParams& p, cudaStream_t st);
+void launch_merge_local(uint32_t n_parts, uint32_t rows, uint32_t D, const float* o, const float* m,
+                        const float* l, __nv_bfloat16* out, cudaStream_t st);
+void launch_merge_pack(uint32_t rows, uint32_t D, const float* o, const float* m_local, const float* m_global,
+                       const float* l, float* pay, cudaStream_t st);
+void launch_merge_finalize(uint32_t rows, uint32_t D, const float* pay, __nv_bfloat16* out, cudaStream_t st);
+void launch_visibility(const MaskParams& mk, uint32_t C, uint8_t* out, cudaStream_t st);
+void launch_fill_f32(float* p, float v, size_t n, cudaStream_t st);
+
+// Tensor-core kernel (head_dim 256).  tm_k / tm_v: 3-D tensor maps {D, cap, Hkv}, box {64, 128, 1},
+// 128-byte swizzle.  Returns the CUDA error of the launch.
+constexpr uint32_t kSm100MaxSplits = 32;
+cudaError_t sm100_attn_configure();   // one-time cudaFuncSetAttribute
+cudaError_t launch_attn_sm100(const AttnParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
+                              cudaStream_t st);
+uint32_t sm100_query_tiles(uint32_t C, uint32_t G, uint32_t Hkv);   // CTAs in grid.x
+uint32_t sm100_key_tiles(const MaskParams& mk);                     // upper bound of key tiles per CTA
+
+}  // namespace dg

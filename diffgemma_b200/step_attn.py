@@ -1,0 +1,231 @@
+"""Host-side mirror of the reference's two attention stages, over the C ABI.
+
+The reference drives, per layer and per denoise step, the stages `LayerQkRopeKv` and
+`LayerAttention` (src/metal/step_kernel/enc.rs:1733-1806, 2102-2296 in the reference project) with
+the geometry in `LayerOffsets{head_dim, n_kv_heads, is_full}` and
+`AttnDims{canvas, n_q_heads, causal, window}`.  The classes below carry the same information and
+call the CUDA library; torch is used only to own device memory and streams.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from . import capi
+from .capi import LayerDesc, check
+
+
+@dataclass
+class AttnLayer:
+    """Geometry + semantics of one attention layer (dg_layer_desc)."""
+    n_q_heads: int = 16
+    n_kv_heads: int = 8
+    head_dim: int = 256
+    canvas: int = 256
+    rotary_dim: int = 256
+    rope_theta: float = 1.0e6
+    rms_eps: float = 1.0e-6
+    softmax_scale: float = 1.0 / 16.0
+    window: int = 0
+    mask_mode: int = capi.MASK_NONE
+    v_norm: int = 0
+    rope_pairing: int = capi.ROPE_SPLIT_HALF
+
+    def c_desc(self) -> LayerDesc:
+        return LayerDesc(self.n_q_heads, self.n_kv_heads, self.head_dim, self.canvas, self.rotary_dim,
+                         self.rope_theta, self.rms_eps, self.softmax_scale, self.window, self.mask_mode,
+                         self.v_norm, self.rope_pairing)
+
+    @staticmethod
+    def reference_sliding(window: int = 1024, canvas: int = 256) -> "AttnLayer":
+        """A sliding layer with the reference's own semantics: no softmax scale, V normed, uniform
+        denoise window (src/shaders/attn/attention/attention.metal:52-63)."""
+        return AttnLayer(n_kv_heads=8, rope_theta=1.0e4, softmax_scale=1.0, window=window,
+                         mask_mode=capi.MASK_WINDOW_UNIFORM, v_norm=1, canvas=canvas)
+
+    def flops(self, kv_len: int) -> float:
+        d = self.c_desc()
+        return float(capi.load().dg_attn_flops(C.byref(d), kv_len))
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    assert t.is_contiguous(), "tensors handed to the C ABI must be contiguous"
+    return C.c_void_p(t.data_ptr())
+
+
+class Context:
+    """dg_ctx: one per host thread / stream."""
+
+    def __init__(self, device: int = 0, use_torch_stream: bool = True):
+        self.lib = capi.load()
+        h = C.c_void_p()
+        check(self.lib.dg_ctx_create(device, C.byref(h)), "dg_ctx_create")
+        self.h = h
+        self.device = device
+        if use_torch_stream and torch.cuda.is_available():
+            s = torch.cuda.current_stream(device)
+            check(self.lib.dg_ctx_set_stream(self.h, C.c_void_p(s.cuda_stream)), "dg_ctx_set_stream")
+
+    def synchronize(self) -> None:
+        check(self.lib.dg_ctx_synchronize(self.h), "dg_ctx_synchronize")
+
+    def device_status(self):
+        out = (C.c_uint32 * 4)()
+        check(self.lib.dg_ctx_last_device_status(self.h, C.byref(out)), "dg_ctx_last_device_status")
+        return tuple(out)
+
+    def force_general(self, on: bool) -> None:
+        check(self.lib.dg_ctx_force_general(self.h, int(on)), "dg_ctx_force_general")
+
+    def set_splits(self, n: int) -> None:
+        check(self.lib.dg_ctx_set_splits(self.h, n), "dg_ctx_set_splits")
+
+    @property
+    def last_launch_count(self) -> int:
+        return int(self.lib.dg_ctx_last_launch_count(self.h))
+
+    def close(self) -> None:
+        if self.h:
+            self.lib.dg_ctx_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class KvCache:
+    """dg_kv: one layer's head-major bf16 cache for one canvas stream."""
+
+    def __init__(self, ctx: Context, layer: AttnLayer, capacity_tokens: int):
+        self.ctx = ctx
+        self.layer = layer
+        h = C.c_void_p()
+        d = layer.c_desc()
+        check(ctx.lib.dg_kv_create(ctx.h, C.byref(d), capacity_tokens, C.byref(h)), "dg_kv_create")
+        self.h = h
+
+    @property
+    def capacity(self) -> int:
+        return int(self.ctx.lib.dg_kv_capacity(self.h))
+
+    def load_prefix(self, k: torch.Tensor, v: torch.Tensor, pos0: int = 0) -> None:
+        """k, v: [n, Hkv, D] bf16 (host or device), K already normed + roped."""
+        assert k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16 and k.shape == v.shape
+        check(self.ctx.lib.dg_kv_load_prefix(self.h, _ptr(k), _ptr(v), pos0, k.shape[0]), "dg_kv_load_prefix")
+        if not k.is_cuda:
+            self.ctx.synchronize()   # pageable host source must outlive the copy
+
+    def append(self, k: torch.Tensor, v: torch.Tensor, pos0: int, kw: torch.Tensor | None = None) -> None:
+        """Norm + RoPE raw keys and write them (and V) at [pos0, pos0+n).  Device tensors."""
+        d = self.layer.c_desc()
+        n = k.shape[0]
+        done = 0
+        while done < n:
+            step = min(32768, n - done)
+            check(self.ctx.lib.dg_kv_append(self.ctx.h, C.byref(d), self.h, pos0 + done, step,
+                                            _ptr(k[done:done + step]), _ptr(v[done:done + step]), _ptr(kw)),
+                  "dg_kv_append")
+            done += step
+
+    def read(self, pos0: int, n: int):
+        lay = self.layer
+        k = torch.empty((n, lay.n_kv_heads, lay.head_dim), dtype=torch.bfloat16, device=f"cuda:{self.ctx.device}")
+        v = torch.empty_like(k)
+        check(self.ctx.lib.dg_kv_read(self.h, _ptr(k), _ptr(v), pos0, n), "dg_kv_read")
+        return k, v
+
+    def close(self) -> None:
+        if self.h:
+            self.ctx.lib.dg_kv_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class CanvasAttention:
+    """The hot path for one layer: stage 1 (qk_rope_kv), stage 2 (attention), or both fused."""
+
+    def __init__(self, ctx: Context, layer: AttnLayer):
+        self.ctx = ctx
+        self.layer = layer
+        self.desc = layer.c_desc()
+        self.lib = ctx.lib
+
+    @property
+    def uses_tensor_path(self) -> bool:
+        return bool(self.lib.dg_uses_tensor_path(C.byref(self.desc)))
+
+    # stage LayerQkRopeKv
+    def qk_rope_kv(self, kv: KvCache, kv_len: int, q, k, v, qw=None, kw=None) -> None:
+        check(self.lib.dg_qk_rope_kv(self.ctx.h, C.byref(self.desc), kv.h, kv_len, _ptr(q), _ptr(k), _ptr(v),
+                                     _ptr(qw), _ptr(kw)), "dg_qk_rope_kv")
+
+    # stage LayerAttention
+    def attention(self, kv: KvCache, kv_len: int, q_normed, out=None):
+        out = torch.empty_like(q_normed) if out is None else out
+        check(self.lib.dg_attention(self.ctx.h, C.byref(self.desc), kv.h, kv_len, _ptr(q_normed), _ptr(out)),
+              "dg_attention")
+        return out
+
+    def denoise(self, kvs, kv_lens, q, k, v, qw=None, kw=None, out=None):
+        """q: [B,C,Hq,D], k,v: [B,C,Hkv,D] pre-norm bf16 device tensors; kvs: list of KvCache."""
+        B = len(kvs)
+        out = torch.empty_like(q) if out is None else out
+        kv_arr = (C.c_void_p * B)(*[kv.h for kv in kvs])
+        len_arr = (C.c_uint32 * B)(*kv_lens)
+        check(self.lib.dg_attn_denoise(self.ctx.h, C.byref(self.desc), kv_arr, len_arr, B, _ptr(q), _ptr(k), _ptr(v),
+                                       _ptr(qw), _ptr(kw), _ptr(out)), "dg_attn_denoise")
+        return out
+
+    def denoise_host(self, kvs, kv_lens, q, k, v, out, qw=None, kw=None):
+        """Same with HOST tensors q, k, v, out (pinned recommended); synchronous."""
+        B = len(kvs)
+        kv_arr = (C.c_void_p * B)(*[kv.h for kv in kvs])
+        len_arr = (C.c_uint32 * B)(*kv_lens)
+        check(self.lib.dg_attn_denoise_host(self.ctx.h, C.byref(self.desc), kv_arr, len_arr, B, _ptr(q), _ptr(k),
+                                            _ptr(v), _ptr(qw), _ptr(kw), _ptr(out)), "dg_attn_denoise_host")
+        return out
+
+    def denoise_bitmap(self, kv: KvCache, kv_len: int, q, k, v, attend, qw=None, kw=None, out=None):
+        out = torch.empty_like(q) if out is None else out
+        check(self.lib.dg_attn_denoise_bitmap(self.ctx.h, C.byref(self.desc), kv.h, kv_len, _ptr(q), _ptr(k), _ptr(v),
+                                              _ptr(qw), _ptr(kw), _ptr(attend), _ptr(out)), "dg_attn_denoise_bitmap")
+        return out
+
+    def partial(self, kv: KvCache, kv_len: int, t0: int, t1: int, include_canvas: bool, q, k, v, qw=None, kw=None):
+        lay = self.layer
+        dev = q.device
+        o = torch.empty((lay.canvas, lay.n_q_heads, lay.head_dim), dtype=torch.float32, device=dev)
+        m = torch.empty((lay.canvas, lay.n_q_heads), dtype=torch.float32, device=dev)
+        l = torch.empty_like(m)
+        check(self.lib.dg_attn_partial(self.ctx.h, C.byref(self.desc), kv.h, kv_len, t0, t1, int(include_canvas),
+                                       _ptr(q), _ptr(k), _ptr(v), _ptr(qw), _ptr(kw), _ptr(o), _ptr(m), _ptr(l)),
+              "dg_attn_partial")
+        return o, m, l
+
+    def merge_local(self, o, m, l):
+        """o: [P,C,Hq,D], m,l: [P,C,Hq] fp32 -> bf16 [C,Hq,D]."""
+        P = o.shape[0]
+        rows = o.shape[1] * o.shape[2]
+        out = torch.empty(o.shape[1:], dtype=torch.bfloat16, device=o.device)
+        check(self.lib.dg_attn_merge_local(self.ctx.h, P, rows, o.shape[3], _ptr(o), _ptr(m), _ptr(l), _ptr(out)),
+              "dg_attn_merge_local")
+        return out
+
+    def visibility(self, kv_len: int, t0: int = 0, t1: int = 0xFFFFFFFF, include_canvas: bool = True):
+        T = kv_len + self.layer.canvas
+        out = torch.empty((self.layer.canvas, T), dtype=torch.uint8, device=f"cuda:{self.ctx.device}")
+        check(self.lib.dg_attn_visibility(self.ctx.h, C.byref(self.desc), kv_len, t0, t1, int(include_canvas),
+                                          _ptr(out)), "dg_attn_visibility")
+        return out

@@ -1,0 +1,199 @@
+/* dg_attn.h - C ABI of the B200 (sm_100a) denoise-step canvas attention.
+ *
+ * This is the boundary a host written in any language binds (extern "C", plain pointers
+ * and sizes).  It replaces the two per-layer dispatches the reference's step runtime issues
+ * for attention (paths relative to the reference project):
+ *
+ *   stage LayerQkRopeKv  -> kernel qk_rope_kv      src/metal/step_kernel/enc.rs:1733-1806,
+ *                                                  src/shaders/attn/qk_rope_kv/qk_rope_kv.metal:29-149
+ *   stage LayerAttention -> kernels attention*     src/metal/step_kernel/enc.rs:2102-2296,
+ *                                                  src/shaders/attn/attention/attention.metal:22-133
+ *
+ * Conventions
+ *  - Every function returns an int32 status: 0 = OK, negative = host-side validation or CUDA
+ *    error (nothing was launched, or the launch failed), positive = a device status code read
+ *    back from the kernels (only reported by the synchronising calls).  Nothing aborts or traps.
+ *  - All tensors are bf16 (IEEE bfloat16 bit patterns, round-to-nearest-even) unless stated.
+ *  - A context owns a CUDA stream and a workspace; it is thread-compatible, not thread-safe:
+ *    one context per host thread, calls on one context are ordered on its stream.  Calls are
+ *    asynchronous with respect to the host unless stated; buffers must stay valid until
+ *    dg_ctx_synchronize() (or a synchronising call) returns.
+ *  - "device pointer" = memory of the context's GPU; "host pointer" = ordinary host memory.
+ */
+#ifndef DG_ATTN_H_
+#define DG_ATTN_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ----------------------------------------------------------------------- */
+enum {
+  DG_OK = 0,
+  DG_ERR_INVALID_ARG = -1,   /* NULL pointer, bad enum, size out of range                       */
+  DG_ERR_UNSUPPORTED = -2,   /* geometry the kernels do not cover (e.g. head_dim > 512)         */
+  DG_ERR_CAPACITY = -3,      /* kv_len + canvas exceeds the cache capacity                      */
+  DG_ERR_CUDA = -4,          /* a CUDA runtime/driver call failed; see dg_last_error_message()  */
+  DG_ERR_NO_DEVICE = -5,     /* no sm_100 GPU present / wrong architecture                      */
+  DG_ERR_NCCL = -6,          /* NCCL not loadable or an NCCL call failed                        */
+  DG_ERR_ALIGNMENT = -7,     /* a device pointer is not 16-byte aligned                         */
+  DG_DEV_WAIT_TIMEOUT = 1,   /* a bounded device-side wait gave up (kernel unwound cleanly)     */
+  DG_DEV_BAD_SHAPE = 2       /* device-side shape assertion                                     */
+};
+
+/* mask modes: which PREFIX keys a canvas row sees (canvas keys are always visible to every
+ * row, bidirectionally).  src/shaders/attn/attention/attention.metal:52-63                     */
+enum {
+  DG_MASK_NONE = 0,           /* all prefix keys (global layers)                                */
+  DG_MASK_WINDOW_UNIFORM = 1, /* reference denoise rule: t >= max(0, kv_len-(window-1)), all rows */
+  DG_MASK_WINDOW_PER_ROW = 2  /* row i (position kv_len+i): t >= max(0, kv_len+i-(window-1))    */
+};
+
+/* RoPE pairings.  src/shaders/attn/cpu.rs:31-65                                                */
+enum {
+  DG_ROPE_SPLIT_HALF = 0,     /* pairs (d, d + rotary_dim/2)                                    */
+  DG_ROPE_PROPORTIONAL = 1    /* pairs (d, head_dim/2 + d), d < rotary_dim/2                    */
+};
+
+/* Per-layer geometry and semantics.  Mirrors what the reference spreads over LayerOffsets
+ * {head_dim, n_kv_heads, is_full} (src/metal/step_kernel/mod.rs:132-167) and
+ * AttnDims{canvas, n_q_heads, causal, window} (src/shaders/include/attention_device.metal:147-152). */
+typedef struct dg_layer_desc {
+  uint32_t n_q_heads;      /* 16                                                               */
+  uint32_t n_kv_heads;     /* 8 (sliding) | 2 (global); must divide n_q_heads                  */
+  uint32_t head_dim;       /* 256 on the tensor-core path; any multiple of 8 up to 512 otherwise */
+  uint32_t canvas;         /* 1..256 query rows                                                */
+  uint32_t rotary_dim;     /* <= head_dim, even                                                */
+  float rope_theta;        /* 1e6 | 1e4                                                        */
+  float rms_eps;           /* 1e-6                                                             */
+  float softmax_scale;     /* 1/16 for the benchmark configs, 1.0 = reference semantics        */
+  uint32_t window;         /* 0 = none                                                         */
+  uint32_t mask_mode;      /* DG_MASK_*                                                        */
+  uint32_t v_norm;         /* 1: V gets the no-scale RMSNorm before the cache write            */
+  uint32_t rope_pairing;   /* DG_ROPE_*                                                        */
+} dg_layer_desc;
+
+typedef struct dg_ctx dg_ctx;
+typedef struct dg_kv dg_kv;
+
+/* ---- context ---------------------------------------------------------------------------- */
+/* Replaces the reference's Metal device/queue/pipeline objects (src/metal/device.rs,
+ * src/metal/step_kernel/build.rs:303-).  Creates a stream and a workspace on `device`.         */
+int32_t dg_ctx_create(int32_t device, dg_ctx** out);
+int32_t dg_ctx_destroy(dg_ctx* ctx);
+/* Use a caller-owned CUDA stream (cudaStream_t passed as void*) instead of the internal one.   */
+int32_t dg_ctx_set_stream(dg_ctx* ctx, void* cuda_stream);
+void* dg_ctx_stream(dg_ctx* ctx);
+/* Wait for all work queued on the context, then return the first device status (0 = none).
+ * Mirrors the reference's wait + DebugStatus check (src/metal/step_kernel/runtime.rs:565-632). */
+int32_t dg_ctx_synchronize(dg_ctx* ctx);
+/* {code, kernel_id, cta, value}, first-writer-wins; same convention as the reference's
+ * DebugStatus (src/shaders/include/debug_status.metal:21-53).  Synchronises.                   */
+int32_t dg_ctx_last_device_status(dg_ctx* ctx, uint32_t out[4]);
+const char* dg_status_str(int32_t status);
+/* Text of the last CUDA/NCCL error seen by this thread ("" if none).                           */
+const char* dg_last_error_message(void);
+/* 1 when the tensor-core (tcgen05) kernel will serve this layer geometry, 0 when the general
+ * kernel will.  No launch.                                                                     */
+int32_t dg_uses_tensor_path(const dg_layer_desc* desc);
+/* Force the general (CUDA-core) kernel for every geometry (1) or restore the default (0).
+ * Used by tests to cross-check the two kernels.                                                */
+int32_t dg_ctx_force_general(dg_ctx* ctx, int32_t on);
+/* Override the number of key splits per query tile on the tensor path (0 = automatic).         */
+int32_t dg_ctx_set_splits(dg_ctx* ctx, uint32_t n_splits);
+
+/* ---- KV cache --------------------------------------------------------------------------- */
+/* One layer's cache for one canvas stream: bf16 K[Hkv][cap][D] and V[Hkv][cap][D], head-major,
+ * device-owned, zero-initialised.  Replaces the reference's per-layer kv_region inside its
+ * monolithic buffer (src/metal/step_kv/mod.rs:1-25, src/metal/step_kernel/mod.rs:506-527).
+ * `capacity_tokens` must cover prefix + canvas; it is rounded up to a multiple of 128.          */
+int32_t dg_kv_create(dg_ctx* ctx, const dg_layer_desc* desc, uint64_t capacity_tokens, dg_kv** out);
+int32_t dg_kv_destroy(dg_kv* kv);
+uint64_t dg_kv_capacity(const dg_kv* kv);
+/* Copy `n` tokens of ready-to-use keys/values (K already normed + roped) into positions
+ * [pos0, pos0+n).  k, v: token-major [n][Hkv][D] bf16, host or device pointers.                */
+int32_t dg_kv_load_prefix(dg_kv* kv, const void* k, const void* v, uint64_t pos0, uint64_t n);
+/* Read positions [pos0, pos0+n) back as token-major [n][Hkv][D] (snapshot/export; the
+ * reference's compact gather: src/metal/step_kv/mod.rs:102-151).  Synchronises.                */
+int32_t dg_kv_read(dg_kv* kv, void* k_out, void* v_out, uint64_t pos0, uint64_t n);
+/* Norm (+weight) + RoPE raw keys, optional V norm, and write `n` tokens at [pos0, pos0+n):
+ * the cache-write half of qk_rope_kv for an arbitrary run of tokens (a committed block, or a
+ * synthetic prefill).  k, v: device pointers [n][Hkv][D]; kw: [D] or NULL.                      */
+int32_t dg_kv_append(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* kv, uint64_t pos0, uint32_t n,
+                     const void* k, const void* v, const void* kw);
+
+/* ---- the hot path ----------------------------------------------------------------------- */
+/* Stage 1 alone (reference stage LayerQkRopeKv): per-head RMSNorm(+weight) + RoPE on canvas
+ * Q and K in place, V optionally normed in place, K/V written to the cache at
+ * [kv_len, kv_len+canvas).  q: [C][Hq][D], k, v: [C][Hkv][D] device pointers (read-write).      */
+int32_t dg_qk_rope_kv(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* kv, uint32_t kv_len, void* q, void* k,
+                      void* v, const void* qw, const void* kw);
+/* Stage 2 alone (reference stage LayerAttention): q is already normed + roped; the canvas
+ * K/V are already in the cache.  out: [C][Hq][D] bf16 device pointer.                           */
+int32_t dg_attention(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* kv, uint32_t kv_len, const void* q,
+                     void* out);
+/* Both stages for `batch` independent canvases, Q prologue fused into the attention kernel.
+ * q: [batch][C][Hq][D], k, v: [batch][C][Hkv][D] PRE-norm bf16 device pointers (not modified);
+ * qw, kw: norm weights [D] or NULL (= unit); kv[b], kv_len[b]: cache and prefix length of canvas b
+ * (kv_len is a host array).  Canvas K/V are written at [kv_len[b], kv_len[b]+C) (uncommitted,
+ * overwritten by the next step: src/metal/step_kernel/runtime.rs:83-98).
+ * out: [batch][C][Hq][D] bf16 device pointer.                                                   */
+int32_t dg_attn_denoise(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* const* kv, const uint32_t* kv_len,
+                        uint32_t batch, const void* q, const void* k, const void* v, const void* qw,
+                        const void* kw, void* out);
+/* Same call with HOST buffers for q, k, v and out: copies in, runs, copies out, synchronises.
+ * This is the end-to-end call a host that keeps activations in host memory makes.              */
+int32_t dg_attn_denoise_host(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* const* kv, const uint32_t* kv_len,
+                             uint32_t batch, const void* q, const void* k, const void* v, const void* qw,
+                             const void* kw, void* out);
+/* General decoder bitmap (reference DecoderAttnMask, src/model/mask.rs:4-27): attend is a
+ * device pointer to uint8 [C][kv_len+C], 1 = visible.  Served by the general kernel.            */
+int32_t dg_attn_denoise_bitmap(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* kv, uint32_t kv_len,
+                               const void* q, const void* k, const void* v, const void* qw, const void* kw,
+                               const uint8_t* attend, void* out);
+
+/* ---- split-KV building blocks (multi-GPU, and the block-continuation state of the reference:
+ * AttnBlockRange / attn_state, src/shaders/include/attention_device.metal:154-165) ------------ */
+/* Partial attention over prefix keys [t0, t1) (clipped to kv_len and to the layer's window)
+ * plus the canvas keys iff include_canvas.  Canvas K/V are appended first exactly as in
+ * dg_attn_denoise.  Outputs (device pointers, fp32): o_unnorm [C][Hq][D] = sum_t e^(s_t - m) v_t,
+ * m [C][Hq] = reference point of the exponent (-inf when the row saw no key), l [C][Hq] =
+ * sum_t e^(s_t - m); log-sum-exp = m + ln(l).                                                   */
+int32_t dg_attn_partial(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* kv, uint32_t kv_len, uint32_t t0,
+                        uint32_t t1, int32_t include_canvas, const void* q, const void* k, const void* v,
+                        const void* qw, const void* kw, float* o_unnorm, float* m, float* l);
+/* Merge `n_parts` partials that live on THIS device (o: [n_parts][rows][D], m, l: [n_parts][rows])
+ * into bf16 out [rows][D].  rows = C*Hq.                                                        */
+int32_t dg_attn_merge_local(dg_ctx* ctx, uint32_t n_parts, uint32_t rows, uint32_t head_dim, const float* o,
+                            const float* m, const float* l, void* out);
+/* Merge one partial per rank across an NCCL communicator (ncclComm_t passed as void*):
+ * all-reduce(max) of m, local rescale, all-reduce(sum) of [O | l], normalise.  Every rank
+ * receives the full bf16 out [rows][D].  o_unnorm, m, l are overwritten.                        */
+int32_t dg_attn_merge_nccl(dg_ctx* ctx, void* nccl_comm, float* o_unnorm, float* m, float* l, void* out,
+                           uint32_t rows, uint32_t head_dim);
+/* NCCL bootstrap helpers for hosts without their own NCCL binding.  The 128-byte unique id is
+ * created on rank 0 and must reach the other ranks by the host's own means.                    */
+int32_t dg_nccl_unique_id(uint8_t id_out[128]);
+int32_t dg_nccl_comm_create(dg_ctx* ctx, const uint8_t id[128], int32_t world_size, int32_t rank, void** comm_out);
+int32_t dg_nccl_comm_destroy(void* comm);
+/* All-gather of per-rank output head slices (KV-head sharding): every rank contributes
+ * `bytes_per_rank` bytes at send and receives world*bytes_per_rank at recv (device pointers).   */
+int32_t dg_nccl_all_gather(dg_ctx* ctx, void* comm, const void* send, void* recv, uint64_t bytes_per_rank);
+
+/* ---- mask introspection (bit-exact mask parity) ----------------------------------------- */
+/* Evaluate on the GPU the same visibility predicate the attention kernels use and write it as
+ * uint8 [C][kv_len+C] to the device pointer `attend_out`.                                       */
+int32_t dg_attn_visibility(dg_ctx* ctx, const dg_layer_desc* desc, uint32_t kv_len, uint32_t t0, uint32_t t1,
+                           int32_t include_canvas, uint8_t* attend_out);
+
+/* Algorithmic FLOPs of one dg_attn_denoise canvas: 4 * D * Hq * (visible (row, key) pairs).     */
+double dg_attn_flops(const dg_layer_desc* desc, uint32_t kv_len);
+/* Number of kernels the last hot-path call on this context launched.                           */
+uint32_t dg_ctx_last_launch_count(const dg_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DG_ATTN_H_ */
