@@ -1,0 +1,341 @@
+"""Benchmark of the denoise-step canvas attention.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--cfg 2]
+
+A "step" is one pass of the hot path (qk_rope_kv append + fused attention) over one canvas of the
+32k-prefix global-layer configuration (Hq=16, Hkv=2, head_dim=256, canvas 256, prefix 32768).  With
+N > 1 (launched by torchrun, one rank per GPU) the prefix is split across the ranks (split-KV) and
+the per-rank (O, m, l) partials are merged over NCCL: total work is fixed, scaling is "strong".
+
+Inputs are seeded synthetic N(0,1) bf16 tensors.  Between timed steps the working set is rotated
+over several KV caches whose total size exceeds the 126 MB L2, as the layers of a model would.
+Rank 0 prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "canvas-attn TFLOP/s @32k prefix"
+UNIT = "TFLOP/s"
+L2_BYTES = 126e6
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one attention-kernel launch of the benchmark
+# workload, from the committed ncu capture under profiles/ (None until one exists)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def _peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"bf16_tflops": float(d["bf16_tflops"]), "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._t = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                parts = [x.strip() for x in out.strip().split(",")]
+                if len(parts) >= 6:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        sm, mx, reasons = [], 0.0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx = max(mx, float(s[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, s[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def _cfg(idx: int):
+    from diffgemma_b200 import synthetic
+    c = synthetic.configs()[idx]
+    return c
+
+
+class CpuSample:
+    """The C++/OpenMP oracle port on a bounded sample of the workload: the first `rows` canvas rows
+    (all heads, all keys).  Inputs are prepared once; run() returns (TFLOP/s, seconds, flops)."""
+
+    def __init__(self, cfg_idx: int, n_threads: int = 0):
+        import numpy as np
+        import torch
+        from oracle import attn_oracle as ao
+        from oracle import c_oracle as co
+        from diffgemma_b200 import synthetic
+        self.ao, self.co = ao, co
+        cfg = _cfg(cfg_idx)
+        lay = cfg.layer
+        self.cfg, self.lay = cfg, lay
+        self.d = ao.LayerDesc(lay.n_q_heads, lay.n_kv_heads, lay.head_dim, lay.canvas, lay.rotary_dim, lay.rope_theta,
+                              lay.rms_eps, lay.softmax_scale, lay.window, lay.mask_mode, lay.v_norm, lay.rope_pairing)
+        q, kc, vc, kp, vp = synthetic.draw(lay, cfg.prefix, synthetic.config_seed(cfg_idx))
+        # the prefix keys are used as drawn (norm + RoPE of the prefix is prefill work, not this path)
+        self.t = [x.view(torch.int16).numpy().view(np.uint16) for x in (q, kc, vc, kp, vp)]
+        self.n_threads = n_threads
+        self.cores = n_threads or co.num_threads()
+        self.vis_per_row = ao.visibility(self.d, cfg.prefix).sum(axis=1)
+        self.run(1)   # warm
+
+    def run(self, rows: int):
+        q, kc, vc, kp, vp = self.t
+        P = self.cfg.prefix
+        t0 = time.perf_counter()
+        qn, kn, vn = self.co.qk_rope_kv(self.d, P, q, kc, vc)
+        self.co.attention(self.d, P, qn, kn, vn, kp, vp, row_begin=0, row_end=rows, n_threads=self.n_threads)
+        dt = time.perf_counter() - t0
+        flops = 4.0 * self.lay.head_dim * self.lay.n_q_heads * float(self.vis_per_row[:rows].sum())
+        return flops / dt / 1e12, dt, flops
+
+
+def run_reference(args):
+    """Reference arm: the reference's CPU implementation of the path (its own CPU code is Rust and
+    cannot be built in this image, so this is the C++/OpenMP port of it), all host threads, each
+    step a bounded sample of the workload sized so that the whole run takes about two minutes."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = _cfg(args.cfg)
+    smp = CpuSample(args.cfg)
+    _, dt8, _ = smp.run(8)
+    n_steps = args.warmup + args.steps
+    rows = int(max(1, min(cfg.layer.canvas, 8 * (120.0 / n_steps) / dt8)))
+    vals = []
+    for i in range(n_steps):
+        v, dt, flops = smp.run(rows)
+        if i >= args.warmup:
+            vals.append((v, dt))
+    value = sum(v for v, _ in vals) / len(vals)
+    ms = 1e3 * sum(dt for _, dt in vals) / len(vals)
+    sample = f"first {rows} of {cfg.layer.canvas} canvas rows x all 16 heads x all keys per step"
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": cfg.name, "prefix": cfg.prefix, "n_q_heads": 16, "n_kv_heads": cfg.layer.n_kv_heads,
+                       "head_dim": 256, "canvas": 256, "sample": sample},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": smp.cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from diffgemma_b200 import synthetic
+    from diffgemma_b200.step_attn import CanvasAttention, Context, KvCache
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
+    dev = torch.device("cuda", local)
+    ctx = Context(local)
+    cfg = _cfg(args.cfg)
+    lay = cfg.layer
+    P = cfg.prefix
+    flops = lay.flops(P)
+    kv_bytes = 2 * lay.n_kv_heads * (P + lay.canvas) * lay.head_dim * 2
+    n_rot = max(2, int(L2_BYTES * 2 // kv_bytes) + 1)          # rotate > 2x L2 worth of KV
+    n_rot = min(n_rot, 16)
+
+    # ---- synthetic state: n_rot independent caches ("layers"), filled through the append kernel
+    from diffgemma_b200.split_kv import SplitKvGroup, plan_shards
+    bounds = plan_shards(P, world)
+    t0s, t1s = bounds[rank], bounds[rank + 1]
+    kvs = []
+    for j in range(n_rot):
+        g = torch.Generator(device=dev).manual_seed(synthetic.config_seed(args.cfg) + 17 * j)
+        kv = KvCache(ctx, lay, P + lay.canvas)
+        n = t1s - t0s
+        kraw = torch.randn(n, lay.n_kv_heads, lay.head_dim, generator=g, device=dev).to(torch.bfloat16)
+        vraw = torch.randn(n, lay.n_kv_heads, lay.head_dim, generator=g, device=dev).to(torch.bfloat16)
+        kv.append(kraw, vraw, t0s)          # this rank's shard, at its absolute positions
+        kvs.append(kv)
+        del kraw, vraw
+    q_h, kc_h, vc_h, _, _ = synthetic.draw(lay, P, synthetic.config_seed(args.cfg), with_prefix=False)
+    q_h, kc_h, vc_h = (t[None].contiguous().pin_memory() for t in (q_h, kc_h, vc_h))
+    out_h = torch.empty_like(q_h).pin_memory()
+    q, kc, vc = q_h.to(dev), kc_h.to(dev), vc_h.to(dev)
+    out = torch.empty_like(q)
+    att = CanvasAttention(ctx, lay)
+    group = SplitKvGroup(ctx, lay) if world > 1 else None
+    stream = ctx.torch_stream
+
+    def step_dev(i):
+        kv = kvs[i % n_rot]
+        if group is None:
+            att.denoise([kv], [P], q, kc, vc, out=out)
+        else:
+            group.denoise(kv, P, q[0], kc[0], vc[0], out=out[0])
+
+    def step_host(i):
+        kv = kvs[i % n_rot]
+        if group is None:
+            att.denoise_host([kv], [P], q_h, kc_h, vc_h, out_h)
+        else:
+            q.copy_(q_h, non_blocking=True)
+            kc.copy_(kc_h, non_blocking=True)
+            vc.copy_(vc_h, non_blocking=True)
+            group.denoise(kv, P, q[0], kc[0], vc[0], out=out[0])
+            out_h.copy_(out, non_blocking=True)
+            ctx.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for i in range(warmup):
+            fn(i)
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    warm = max(3, args.warmup)
+    with ClockSampler(local) as clk:
+        # device-resident arm, with the dominant kernel timed per launch on its own stream
+        ctx.kernel_timing(True, args.steps + warm + 8)
+        for i in range(warm):
+            step_dev(i)
+        ctx.kernel_timing(True, args.steps + 8)      # restart the event ring after the warm-up
+        ms_dev = timed(step_dev, args.steps, 0)
+        k_ms, k_n = ctx.kernel_time()
+        ctx.kernel_timing(False)
+        launches_per_step = ctx.last_launch_count
+        # end-to-end arm: host buffers, H2D + kernels + D2H + sync every step
+        t_host0 = time.perf_counter()
+        ms_e2e_ev = timed(step_host, args.steps, warm)
+        _ = time.perf_counter() - t_host0
+    clocks = clk.summary()
+    st = ctx.device_status()
+    assert st[0] == 0, f"device status {st}"
+
+    if rank == 0:
+        peaks = _peaks()
+        value = flops / (ms_dev * 1e-3) / 1e12
+        e2e = flops / (ms_e2e_ev * 1e-3) / 1e12
+        k_avg_ms = k_ms / max(1, k_n)
+        shard_flops = flops if world == 1 else None
+        achieved = (flops / world) / (k_avg_ms * 1e-3) / 1e12 if k_n else None
+        if world > 1:
+            # per-rank kernel work: this rank's shard (+ canvas keys on the owner); report rank 0's
+            vis = (t1s - t0s) + (lay.canvas if rank == world - 1 else 0)
+            achieved = 4.0 * lay.head_dim * lay.n_q_heads * lay.canvas * vis / (k_avg_ms * 1e-3) / 1e12 if k_n else None
+        io_bytes = kv_bytes + 2 * lay.canvas * lay.n_q_heads * lay.head_dim * 2
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": ms_dev, "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": cfg.name, "prefix": P, "n_q_heads": lay.n_q_heads, "n_kv_heads": lay.n_kv_heads,
+                       "head_dim": lay.head_dim, "canvas": lay.canvas, "mask": "all prefix visible, canvas bidirectional",
+                       "partition": "single GPU" if world == 1 else f"split-KV over {world} GPUs + NCCL LSE merge",
+                       "l2": f"steps rotate over {n_rot} KV caches ({n_rot * kv_bytes / 1e6:.0f} MB > 126 MB L2)",
+                       "algorithmic_gflop_per_step": flops / 1e9},
+            "pct_of_measured_bf16_peak": 100.0 * value / (peaks["bf16_tflops"] * world),
+            "pct_of_nominal_bf16_peak": 100.0 * value / (2250.0 * world),
+            "achieved_hbm_gbs": io_bytes / (ms_dev * 1e-3) / 1e9,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": (achieved / peaks["bf16_tflops"]) if achieved else None,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": peaks["source"] + " burst",
+                         "kernel": "dg_attn_sm100_kernel", "kernel_ms": k_avg_ms, "kernel_launches_timed": k_n},
+            "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e_ev,
+                    "h2d_bytes_per_step": int(q_h.numel() * 2 + kc_h.numel() * 2 + vc_h.numel() * 2),
+                    "d2h_bytes_per_step": int(out_h.numel() * 2)},
+            "gpu_launches": int(launches_per_step * args.steps),
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            smp = CpuSample(args.cfg)
+            v, dt, fl = smp.run(args.ref_rows)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": smp.cores, "kind": "port",
+                                    "sample": f"first {args.ref_rows} of {lay.canvas} canvas rows x 16 heads x all keys "
+                                              f"({fl / 1e9:.1f} GFLOP in {dt:.2f} s), C++/OpenMP fp32 port"}
+        print(json.dumps(line), flush=True)
+    if group is not None:
+        group.close()
+    for kv in kvs:
+        kv.close()
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cfg", type=int, default=2, choices=[0, 1, 2, 4])
+    ap.add_argument("--ref-rows", type=int, default=256, help="canvas rows in the bounded CPU sample")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -75,6 +75,8 @@ SIGNATURES = {
     "dg_attn_visibility": (_i32, [_vp, _pd, _u32, _u32, _u32, _i32, _vp]),
     "dg_attn_flops": (C.c_double, [_pd, _u32]),
     "dg_ctx_last_launch_count": (_u32, [_vp]),
+    "dg_ctx_kernel_timing": (_i32, [_vp, _i32, _u32]),
+    "dg_ctx_kernel_time": (_i32, [_vp, C.POINTER(C.c_double), C.POINTER(_u32)]),
 }
 
 _lib = None

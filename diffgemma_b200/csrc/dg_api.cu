@@ -15,6 +15,7 @@
 #include <cstring>
 #include <new>
 #include <string>
+#include <vector>
 
 #include "dg_common.cuh"
 #include "dg_kernels.h"
@@ -66,6 +67,10 @@ struct dg_ctx {
   int force_general = 0;
   uint32_t forced_splits = 0;
   uint32_t last_launches = 0;
+  // optional per-launch timing of the attention kernel (event pairs on the launching stream)
+  bool timing = false;
+  std::vector<cudaEvent_t> ev;
+  size_t ev_used = 0;
 };
 
 struct dg_kv {
@@ -286,6 +291,7 @@ extern "C" int32_t dg_ctx_destroy(dg_ctx* c) {
   cudaFree(c->stage_o);
   cudaFree(c->nccl_pay);
   cudaFree(c->nccl_mg);
+  for (cudaEvent_t e : c->ev) cudaEventDestroy(e);
   if (c->own_stream) cudaStreamDestroy(c->own_stream);
   delete c;
   return DG_OK;
@@ -339,6 +345,34 @@ extern "C" int32_t dg_ctx_set_splits(dg_ctx* c, uint32_t n) {
   return DG_OK;
 }
 extern "C" uint32_t dg_ctx_last_launch_count(const dg_ctx* c) { return c ? c->last_launches : 0; }
+
+extern "C" int32_t dg_ctx_kernel_timing(dg_ctx* c, int32_t on, uint32_t max_launches) {
+  if (!c) return fail(DG_ERR_INVALID_ARG, "ctx is NULL");
+  DG_CUDA(cudaSetDevice(c->device));
+  c->timing = on != 0;
+  c->ev_used = 0;
+  while (on && c->ev.size() < size_t(max_launches) * 2) {
+    cudaEvent_t e;
+    DG_CUDA(cudaEventCreate(&e));
+    c->ev.push_back(e);
+  }
+  return DG_OK;
+}
+
+extern "C" int32_t dg_ctx_kernel_time(dg_ctx* c, double* total_ms, uint32_t* launches) {
+  if (!c || !total_ms || !launches) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  DG_CUDA(cudaSetDevice(c->device));
+  DG_CUDA(cudaStreamSynchronize(c->stream));
+  double sum = 0.0;
+  for (size_t i = 0; i + 1 < c->ev_used; i += 2) {
+    float ms = 0.f;
+    DG_CUDA(cudaEventElapsedTime(&ms, c->ev[i], c->ev[i + 1]));
+    sum += ms;
+  }
+  *total_ms = sum;
+  *launches = uint32_t(c->ev_used / 2);
+  return DG_OK;
+}
 
 // ------------------------------------------------------------------------------------------
 // KV cache
@@ -541,8 +575,14 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
     p.ws_ml = c->ws_ml;
     p.ws_counters = c->counters;
   }
+  const bool timed = c->timing && c->ev_used + 2 <= c->ev.size();
+  if (timed) DG_CUDA(cudaEventRecord(c->ev[c->ev_used], c->stream));
   const cudaError_t e = launch_attn_sm100(p, kv->tm_k, kv->tm_v, c->stream);
   if (e != cudaSuccess) return fail_cuda(e, "launch_attn_sm100");
+  if (timed) {
+    DG_CUDA(cudaEventRecord(c->ev[c->ev_used + 1], c->stream));
+    c->ev_used += 2;
+  }
   c->last_launches += 1;
   return DG_OK;
 }

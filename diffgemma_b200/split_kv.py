@@ -1,0 +1,94 @@
+"""Multi-GPU partitioning of the canvas attention: split-KV and KV-head sharding.
+
+One process per GPU.  torch.distributed is used only for rendezvous (to carry the NCCL unique id
+to the other ranks); the data path is the CUDA library's own NCCL communicator.
+
+Split-KV: rank r owns the contiguous prefix shard [bounds[r], bounds[r+1]) in its local cache, at
+the same absolute key positions; Q and the canvas K/V are replicated.  The canvas keys are counted
+by exactly one rank (the last one) so the log-sum-exp merge does not double-count them.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from . import capi
+from .capi import check
+from .step_attn import AttnLayer, CanvasAttention, Context, KvCache, _ptr
+
+
+def plan_shards(kv_len: int, world: int, align: int = 128) -> list[int]:
+    """Shard bounds [b_0=0, ..., b_world=kv_len]: contiguous, near-equal, tile-aligned interior cuts."""
+    assert world >= 1 and kv_len >= 0
+    bounds = [0]
+    for r in range(1, world):
+        cut = (kv_len * r) // world
+        cut = (cut // align) * align
+        bounds.append(max(cut, bounds[-1]))
+    bounds.append(kv_len)
+    return bounds
+
+
+def canvas_owner(world: int) -> int:
+    """The rank whose partial includes the canvas keys."""
+    return world - 1
+
+
+def head_shards(n_kv_heads: int, world: int) -> list[tuple[int, int]]:
+    """KV-head sharding: (first_head, n_heads) per rank; ranks beyond n_kv_heads get (0, 0)."""
+    per = max(1, n_kv_heads // world) if world <= n_kv_heads else 1
+    out = []
+    for r in range(world):
+        h0 = r * per
+        out.append((h0, per) if h0 + per <= n_kv_heads else (0, 0))
+    return out
+
+
+class SplitKvGroup:
+    """Split-KV attention over the ranks of a torch.distributed process group."""
+
+    def __init__(self, ctx: Context, layer: AttnLayer, group=None):
+        self.ctx = ctx
+        self.layer = layer
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.att = CanvasAttention(ctx, layer)
+        lib = ctx.lib
+        ident = torch.zeros(128, dtype=torch.uint8)
+        if self.rank == 0:
+            buf = (C.c_uint8 * 128)()
+            check(lib.dg_nccl_unique_id(C.cast(buf, C.c_void_p)), "dg_nccl_unique_id")
+            ident = torch.tensor(list(buf), dtype=torch.uint8)
+        # rendezvous only: carry the id over whatever backend the group has
+        dev = torch.device("cuda", ctx.device) if dist.get_backend(group) == "nccl" else torch.device("cpu")
+        ident = ident.to(dev)
+        dist.broadcast(ident, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        idb = (C.c_uint8 * 128)(*ident.cpu().tolist())
+        comm = C.c_void_p()
+        check(lib.dg_nccl_comm_create(ctx.h, C.cast(idb, C.c_void_p), self.world, self.rank, C.byref(comm)),
+              "dg_nccl_comm_create")
+        self.comm = comm
+
+    def shard_bounds(self, kv_len: int):
+        b = plan_shards(kv_len, self.world)
+        return b[self.rank], b[self.rank + 1]
+
+    def denoise(self, kv: KvCache, kv_len: int, q, k, v, qw=None, kw=None, out=None):
+        """q: [C,Hq,D], k, v: [C,Hkv,D] (replicated inputs).  Every rank gets the full bf16 output."""
+        t0, t1 = self.shard_bounds(kv_len)
+        o, m, l = self.att.partial(kv, kv_len, t0, t1, self.rank == canvas_owner(self.world), q, k, v, qw, kw)
+        out = torch.empty_like(q) if out is None else out
+        rows = self.layer.canvas * self.layer.n_q_heads
+        check(self.ctx.lib.dg_attn_merge_nccl(self.ctx.h, self.comm, _ptr(o), _ptr(m), _ptr(l), _ptr(out), rows,
+                                              self.layer.head_dim), "dg_attn_merge_nccl")
+        self._keep = (o, m, l)   # keep the partial buffers alive until the stream has consumed them
+        return out
+
+    def close(self):
+        if self.comm:
+            self.ctx.synchronize()
+            self.ctx.lib.dg_nccl_comm_destroy(self.comm)
+            self.comm = None

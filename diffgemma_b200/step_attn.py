@@ -60,15 +60,19 @@ def _ptr(t):
 class Context:
     """dg_ctx: one per host thread / stream."""
 
-    def __init__(self, device: int = 0, use_torch_stream: bool = True):
+    def __init__(self, device: int = 0, make_current: bool = True):
+        """Creates the context with its own CUDA stream.  With `make_current` that stream also
+        becomes torch's current stream on `device`, so tensor uploads, events and the library's
+        kernels are ordered on one stream (`torch_stream` wraps it either way)."""
         self.lib = capi.load()
         h = C.c_void_p()
         check(self.lib.dg_ctx_create(device, C.byref(h)), "dg_ctx_create")
         self.h = h
         self.device = device
-        if use_torch_stream and torch.cuda.is_available():
-            s = torch.cuda.current_stream(device)
-            check(self.lib.dg_ctx_set_stream(self.h, C.c_void_p(s.cuda_stream)), "dg_ctx_set_stream")
+        self.torch_stream = torch.cuda.ExternalStream(int(self.lib.dg_ctx_stream(self.h)), device=device)
+        if make_current:
+            torch.cuda.set_device(device)
+            torch.cuda.set_stream(self.torch_stream)
 
     def synchronize(self) -> None:
         check(self.lib.dg_ctx_synchronize(self.h), "dg_ctx_synchronize")
@@ -87,6 +91,16 @@ class Context:
     @property
     def last_launch_count(self) -> int:
         return int(self.lib.dg_ctx_last_launch_count(self.h))
+
+    def kernel_timing(self, on: bool, max_launches: int = 4096) -> None:
+        check(self.lib.dg_ctx_kernel_timing(self.h, int(on), max_launches), "dg_ctx_kernel_timing")
+
+    def kernel_time(self):
+        """(summed ms, launches) of the attention-kernel launches since kernel_timing(True)."""
+        ms = C.c_double()
+        n = C.c_uint32()
+        check(self.lib.dg_ctx_kernel_time(self.h, C.byref(ms), C.byref(n)), "dg_ctx_kernel_time")
+        return ms.value, n.value
 
     def close(self) -> None:
         if self.h:

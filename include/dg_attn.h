@@ -192,6 +192,12 @@ int32_t dg_attn_visibility(dg_ctx* ctx, const dg_layer_desc* desc, uint32_t kv_l
 double dg_attn_flops(const dg_layer_desc* desc, uint32_t kv_len);
 /* Number of kernels the last hot-path call on this context launched.                           */
 uint32_t dg_ctx_last_launch_count(const dg_ctx* ctx);
+/* Measurement aid (the reference's per-stage profile: LayerEncodeSubProfile,
+ * src/metal/step_kernel/mod.rs:399-429): with on = 1 every tensor-path attention launch is
+ * bracketed by a CUDA event pair on the launching stream, up to max_launches launches;
+ * dg_ctx_kernel_time synchronises and returns their summed duration and count.                  */
+int32_t dg_ctx_kernel_timing(dg_ctx* ctx, int32_t on, uint32_t max_launches);
+int32_t dg_ctx_kernel_time(dg_ctx* ctx, double* total_ms, uint32_t* launches);
 
 #ifdef __cplusplus
 }

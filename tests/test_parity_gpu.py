@@ -1,0 +1,371 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI (all tests need a B200).
+
+Tolerances: bf16 outputs vs the fp32 oracle on identical seeded inputs must satisfy max-abs <= 2e-2
+and mean-abs <= 2e-3 (tests/util.py); masks and integer outputs are compared bit-exactly."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import util
+from diffgemma_b200 import capi
+from diffgemma_b200.step_attn import AttnLayer, CanvasAttention, KvCache
+from oracle import attn_oracle as ao
+from test_oracle_pins import REF_FIXTURES, _ref_fixture
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+# ------------------------------------------------------------------------------------------
+# stage 1: qk_rope_kv  (reference fixtures: src/shaders/attn/qk_rope_kv/mod.rs:82-185)
+# ------------------------------------------------------------------------------------------
+def _bits(t):
+    return t.detach().cpu().view(torch.int16).numpy().astype(np.int32) & 0xFFFF
+
+
+def _assert_bf16_close(got_t, want_f32, what):
+    got = util.t2f(got_t)
+    want = ao.round_bf16(want_f32)
+    ulp = np.abs(_bits(got_t) - ao.f32_to_bf16_bits(want).astype(np.int32))
+    ok = (ulp <= 1) | (np.abs(got - want) <= 2e-6)
+    assert ok.all(), f"{what}: {np.count_nonzero(~ok)} values differ by more than one bf16 ulp"
+    assert (ulp != 0).mean() < 5e-3, f"{what}: too many one-ulp differences"
+
+
+@pytest.mark.parametrize("canvas,hq,hkv,hd,kv_len,rot,pairing,vnorm,weights", [
+    (2, 4, 2, 32, 2, 32, 0, 1, False),        # tiny
+    (2, 4, 2, 64, 2, 16, 1, 1, False),        # full_layer: rotary = hd/4, proportional pairing
+    (1, 16, 2, 512, 22, 128, 1, 1, True),     # full_hd512 with non-unit weights
+    (256, 16, 8, 256, 8192, 256, 0, 0, True),
+    (256, 16, 2, 256, 131072, 256, 0, 1, False),
+])
+def test_qk_rope_kv_stage(ctx, canvas, hq, hkv, hd, kv_len, rot, pairing, vnorm, weights):
+    layer = AttnLayer(n_q_heads=hq, n_kv_heads=hkv, head_dim=hd, canvas=canvas, rotary_dim=rot,
+                      rope_theta=1e6 if pairing else 1e4, v_norm=vnorm, rope_pairing=pairing)
+    d = util.oracle_desc(layer)
+    g = torch.Generator().manual_seed(hd + kv_len)
+    q = torch.randn(canvas, hq, hd, generator=g).to(torch.bfloat16)
+    k = torch.randn(canvas, hkv, hd, generator=g).to(torch.bfloat16)
+    v = torch.randn(canvas, hkv, hd, generator=g).to(torch.bfloat16)
+    qw = (1 + 0.1 * torch.randn(hd, generator=g)).to(torch.bfloat16) if weights else None
+    kw = (1 + 0.1 * torch.randn(hd, generator=g)).to(torch.bfloat16) if weights else None
+    qn, kn, vn = ao.qk_rope_kv(util.t2f(q), util.t2f(k), util.t2f(v), None if qw is None else util.t2f(qw),
+                               None if kw is None else util.t2f(kw), d, kv_len, round_out=False)
+    kv = KvCache(ctx, layer, kv_len + canvas)
+    att = CanvasAttention(ctx, layer)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    att.qk_rope_kv(kv, kv_len, qd, kd, vd, None if qw is None else qw.to(DEV), None if kw is None else kw.to(DEV))
+    ctx.synchronize()
+    _assert_bf16_close(qd, qn, "q")
+    _assert_bf16_close(kd, kn, "k")
+    ck, cv = kv.read(kv_len, canvas)
+    _assert_bf16_close(ck, kn, "cache k")
+    _assert_bf16_close(cv, vn, "cache v")
+    if vnorm:
+        _assert_bf16_close(vd, vn, "v written back")
+    kv.close()
+
+
+# ------------------------------------------------------------------------------------------
+# stage 2 on the reference's closed-form fixtures (src/shaders/attn/attention/mod.rs:59-184);
+# tolerance of the reference's own GPU-vs-CPU gate: max-abs 2e-2, cosine >= 0.9999 (:842-946)
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", list(REF_FIXTURES))
+def test_attention_stage_reference_fixtures(ctx, name):
+    canvas, hq, hkv, hd, kv_len, kind = REF_FIXTURES[name]
+    q, K, V = _ref_fixture(canvas, hq, hkv, hd, kv_len, kind)
+    layer = AttnLayer(n_q_heads=hq, n_kv_heads=hkv, head_dim=hd, canvas=canvas, rotary_dim=hd, softmax_scale=1.0)
+    kv = KvCache(ctx, layer, kv_len + canvas)
+    kv.load_prefix(util.f2t(K, DEV), util.f2t(V, DEV), 0)
+    att = CanvasAttention(ctx, layer)
+    out = att.attention(kv, kv_len, util.f2t(q, DEV))
+    ctx.synchronize()
+    got = util.t2f(out)
+    want = np.load(os.path.join(os.path.dirname(__file__), "golden", "attn_golden.npz"))[name]
+    assert np.abs(got - want).max() <= 2e-2
+    cos = float((got * want).sum() / (np.linalg.norm(got) * np.linalg.norm(want)))
+    assert cos >= 0.9999
+    kv.close()
+
+
+# ------------------------------------------------------------------------------------------
+# the fused hot path vs the oracle
+# ------------------------------------------------------------------------------------------
+PARITY_CASES = [
+    # prefix, Hkv, window, mask_mode, scale, canvas, weights, v_norm
+    (0, 8, 0, 0, 1 / 16, 256, False, 0),        # empty prefix
+    (1, 8, 0, 0, 1 / 16, 256, False, 0),
+    (100, 8, 0, 0, 1 / 16, 256, False, 0),      # below one key tile
+    (127, 2, 0, 0, 1 / 16, 256, False, 0),
+    (128, 2, 0, 0, 1 / 16, 256, True, 0),       # exactly one tile
+    (129, 2, 0, 0, 1 / 16, 256, False, 1),      # tile + 1
+    (1000, 8, 0, 0, 1.0, 256, True, 1),         # reference semantics: no scale, V normed
+    (2048, 8, 0, 0, 1 / 16, 256, False, 0),     # configuration 0
+    (700, 8, 1024, 1, 1 / 16, 256, False, 0),   # kv_len < window
+    (1023, 8, 1024, 1, 1 / 16, 256, False, 0),  # kv_len = window - 1
+    (1024, 8, 1024, 2, 1 / 16, 256, False, 0),  # kv_len = window
+    (3000, 8, 1024, 1, 1.0, 256, False, 1),     # uniform window (reference rule), > window
+    (3000, 8, 1024, 2, 1 / 16, 256, False, 0),  # per-row window
+    (8192, 8, 1024, 2, 1 / 16, 256, False, 0),  # configuration 1
+    (8192, 8, 1024, 1, 1 / 16, 256, False, 0),
+    (500, 16, 0, 0, 1 / 16, 256, False, 0),     # GQA group 1
+    (500, 4, 0, 0, 1 / 16, 256, False, 0),      # GQA group 4
+    (500, 8, 0, 0, 1 / 16, 128, False, 0),      # narrower active canvases
+    (500, 2, 0, 0, 1 / 16, 64, True, 0),
+    (333, 8, 64, 2, 1 / 16, 100, False, 0),     # ragged canvas, tiny window
+]
+
+
+@pytest.mark.parametrize("P,Hkv,W,mode,scale,canvas,weights,vnorm", PARITY_CASES)
+def test_denoise_parity(ctx, P, Hkv, W, mode, scale, canvas, weights, vnorm):
+    layer = AttnLayer(n_kv_heads=Hkv, window=W, mask_mode=mode, softmax_scale=scale, canvas=canvas,
+                      rope_theta=1e4 if W else 1e6, v_norm=vnorm)
+    case = util.make_case(layer, P, seed=P * 7 + Hkv, weights=weights)
+    ref = util.run_oracle(case)
+    assert CanvasAttention(ctx, layer).uses_tensor_path
+    ctx.force_general(False)
+    for splits in (0, 1, 3):
+        ctx.set_splits(splits)
+        got = util.run_gpu(ctx, case)
+        util.assert_close(got, ref, f"tensor path splits={splits}")
+    ctx.set_splits(0)
+    ctx.force_general(True)
+    got = util.run_gpu(ctx, case)
+    ctx.force_general(False)
+    util.assert_close(got, ref, "general path")
+    assert ctx.device_status()[0] == 0
+
+
+@pytest.mark.parametrize("cfg_prefix,Hkv", [(32768, 2), (131072, 2)])
+def test_full_size_parity_and_split_invariance(ctx, cfg_prefix, Hkv):
+    """Configurations 2 and 4 at full size against the oracle, plus properties that do not depend
+    on the size: the result must not depend on the number of key splits, rows of softmax weights sum
+    to one (V = 1 gives O = 1), and the output is linear in V."""
+    layer = AttnLayer(n_kv_heads=Hkv, rope_theta=1e6)
+    case = util.make_case(layer, cfg_prefix, seed=20261125 + cfg_prefix)
+    ref = util.run_oracle(case)
+    kv, att = util.gpu_setup(ctx, case)
+    q, kc, vc = util.dev(case, "q")[None], util.dev(case, "kc")[None], util.dev(case, "vc")[None]
+    outs = {}
+    for splits in (0, 1, 4, 7):
+        ctx.set_splits(splits)
+        outs[splits] = util.t2f(att.denoise([kv], [cfg_prefix], q, kc, vc)[0])
+        util.assert_close(outs[splits], ref, f"P={cfg_prefix} splits={splits}")
+    ctx.set_splits(0)
+    assert np.abs(outs[1] - outs[4]).max() <= 2e-3 and np.abs(outs[1] - outs[7]).max() <= 2e-3
+    # V = 1 everywhere -> every output element is exactly the sum of the weights = 1
+    ones_p = torch.ones_like(case["vp"]).to(DEV)
+    kv.load_prefix(case["kp"].to(DEV), ones_p, 0)
+    o1 = util.t2f(att.denoise([kv], [cfg_prefix], q, kc, torch.ones_like(vc))[0])
+    assert np.abs(o1 - 1.0).max() <= 8e-3
+    # linearity in V: O(V) + O(1) == O(V + 1) up to bf16 rounding of the outputs
+    kv.load_prefix(case["kp"].to(DEV), (case["vp"].float() + 1).to(torch.bfloat16).to(DEV), 0)
+    o2 = util.t2f(att.denoise([kv], [cfg_prefix], q, kc, (vc.float() + 1).to(torch.bfloat16))[0])
+    assert np.abs(o2 - (outs[0] + 1.0)).max() <= 3e-2
+    assert np.abs(o2 - (outs[0] + 1.0)).mean() <= 4e-3
+    kv.close()
+
+
+def test_run_twice_is_bitwise_identical(ctx):
+    layer = AttnLayer(n_kv_heads=2)
+    case = util.make_case(layer, 5000, seed=11)
+    kv, att = util.gpu_setup(ctx, case)
+    q, kc, vc = util.dev(case, "q")[None], util.dev(case, "kc")[None], util.dev(case, "vc")[None]
+    a = att.denoise([kv], [5000], q, kc, vc).clone()
+    b = att.denoise([kv], [5000], q, kc, vc).clone()
+    ctx.synchronize()
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    kv.close()
+
+
+def test_batch_of_independent_canvases(ctx):
+    """Four canvases with their own caches and ragged prefix lengths (configuration 3's shape)."""
+    layer = AttnLayer(n_kv_heads=8, window=1024, mask_mode=capi.MASK_WINDOW_UNIFORM, rope_theta=1e4)
+    lens = [2048 - 64 * b for b in range(4)]
+    cases = [util.make_case(layer, lens[b], seed=300 + b) for b in range(4)]
+    kvs = []
+    for c in cases:
+        kv, att = util.gpu_setup(ctx, c)
+        kvs.append(kv)
+    q = torch.stack([c["q"] for c in cases]).to(DEV)
+    k = torch.stack([c["kc"] for c in cases]).to(DEV)
+    v = torch.stack([c["vc"] for c in cases]).to(DEV)
+    out = att.denoise(kvs, lens, q, k, v)
+    ctx.synchronize()
+    for b, c in enumerate(cases):
+        util.assert_close(util.t2f(out[b]), util.run_oracle(c), f"canvas {b}")
+    for kv in kvs:
+        kv.close()
+
+
+def test_host_buffer_call_matches_device_call(ctx):
+    layer = AttnLayer(n_kv_heads=8)
+    case = util.make_case(layer, 777, seed=5)
+    kv, att = util.gpu_setup(ctx, case)
+    dev_out = att.denoise([kv], [777], util.dev(case, "q")[None], util.dev(case, "kc")[None], util.dev(case, "vc")[None])
+    q, k, v = (case[n][None].contiguous().pin_memory() for n in ("q", "kc", "vc"))
+    host_out = torch.empty_like(q).pin_memory()
+    att.denoise_host([kv], [777], q, k, v, host_out)
+    assert torch.equal(host_out.view(torch.int16), dev_out.cpu().view(torch.int16))
+    assert ctx.last_launch_count == 2
+    kv.close()
+
+
+# ------------------------------------------------------------------------------------------
+# masks: bit-exact
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("P,W,mode,canvas", [(0, 0, 0, 256), (300, 0, 0, 256), (700, 1024, 1, 256), (1023, 1024, 2, 256),
+                                             (1024, 1024, 2, 256), (1025, 1024, 1, 256), (3000, 1024, 2, 256),
+                                             (8192, 1024, 2, 256), (8192, 1024, 1, 256), (333, 64, 2, 100)])
+def test_visibility_bitmap_bit_exact(ctx, P, W, mode, canvas):
+    layer = AttnLayer(window=W, mask_mode=mode, canvas=canvas)
+    att = CanvasAttention(ctx, layer)
+    d = util.oracle_desc(layer)
+    shards = [(0, P, True), (0, P // 2, False), (P // 2, P, True), (P // 3, P // 3, True)]
+    for t0, t1, inc in shards:
+        got = att.visibility(P, t0, t1, inc).cpu().numpy().astype(bool)
+        np.testing.assert_array_equal(got, ao.visibility(d, P, t0, t1, inc))
+
+
+@pytest.mark.parametrize("force_general", [False, True])
+@pytest.mark.parametrize("P,W,mode,t0,t1,inc", [
+    (100, 0, 0, 0, 100, True), (100, 64, 1, 0, 100, True), (100, 64, 2, 0, 100, True),
+    (100, 64, 2, 30, 80, False), (100, 0, 0, 50, 50, True), (90, 32, 2, 0, 90, True),
+])
+def test_kernel_mask_bit_exact_through_indicator_values(ctx, force_general, P, W, mode, t0, t1, inc):
+    """With Q = 0 every visible key has weight exactly 1, so l counts the visible keys of a row and,
+    with V[t] = one-hot(t), the un-normalised output IS the row of the visibility bitmap.  T <= 256
+    so each key has its own output column: the kernels' mask is compared bit for bit."""
+    canvas = 256 - P if P >= 100 else 128
+    canvas = min(canvas, 256 - P)
+    layer = AttnLayer(n_kv_heads=8, window=W, mask_mode=mode, canvas=canvas)
+    T = P + canvas
+    assert T <= 256
+    onehot = torch.zeros(T, 8, 256, dtype=torch.bfloat16)
+    for t in range(T):
+        onehot[t, :, t] = 1.0
+    kv = KvCache(ctx, layer, T)
+    kv.load_prefix(torch.zeros(P, 8, 256, dtype=torch.bfloat16).to(DEV), onehot[:P].to(DEV), 0)
+    att = CanvasAttention(ctx, layer)
+    q = torch.zeros(canvas, 16, 256, dtype=torch.bfloat16, device=DEV)
+    kc = torch.zeros(canvas, 8, 256, dtype=torch.bfloat16, device=DEV)
+    vc = onehot[P:].to(DEV).contiguous()
+    ctx.force_general(force_general)
+    o, m, l = att.partial(kv, P, t0, t1, inc, q, kc, vc)
+    ctx.synchronize()
+    ctx.force_general(False)
+    want = ao.visibility(util.oracle_desc(layer), P, t0, t1, inc)        # [canvas, T]
+    o = o.cpu().numpy()
+    l = l.cpu().numpy()
+    for h in (0, 7, 15):
+        np.testing.assert_array_equal(o[:, h, :T] != 0, want)
+        np.testing.assert_array_equal(o[:, h, :T][want], 1.0)
+        np.testing.assert_array_equal(l[:, h], want.sum(axis=1).astype(np.float32))
+    kv.close()
+
+
+def test_sparse_decoder_bitmap(ctx):
+    """Shape of the reference's sparse decoder-bitmap fixture (src/shaders/attn/gqa_attention/mod.rs:
+    181-232): 32 canvas rows, 14 prefix keys, 16Q/8KV, head_dim 256; canvas keys with (q+k)%5==0
+    masked and rows q%7==0 blind to the prefix."""
+    layer = AttnLayer(n_kv_heads=8, canvas=32, softmax_scale=1.0)
+    P = 14
+    case = util.make_case(layer, P, seed=99)
+    att_map = np.ones((32, P + 32), bool)
+    for qi in range(32):
+        for k in range(P, P + 32):
+            if (qi + k) % 5 == 0:
+                att_map[qi, k] = False
+        if qi % 7 == 0:
+            att_map[qi, :P] = False
+    ref = util.run_oracle(case, attend=att_map)
+    kv, att = util.gpu_setup(ctx, case)
+    out = att.denoise_bitmap(kv, P, util.dev(case, "q"), util.dev(case, "kc"), util.dev(case, "vc"),
+                             torch.from_numpy(att_map.astype(np.uint8)).to(DEV))
+    ctx.synchronize()
+    util.assert_close(util.t2f(out), ref, "bitmap")
+    kv.close()
+
+
+# ------------------------------------------------------------------------------------------
+# split-KV partials and merges
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("P,W,mode,cuts", [(5000, 0, 0, [0, 1280, 2560, 5000]), (3000, 1024, 1, [0, 1024, 2048, 3000]),
+                                           (3000, 1024, 2, [0, 1500, 3000])])
+def test_partials_merge_to_single_shot(ctx, P, W, mode, cuts):
+    layer = AttnLayer(n_kv_heads=2, window=W, mask_mode=mode)
+    case = util.make_case(layer, P, seed=P + W)
+    ref = util.run_oracle(case)
+    kv, att = util.gpu_setup(ctx, case)
+    q, kc, vc = util.dev(case, "q"), util.dev(case, "kc"), util.dev(case, "vc")
+    parts = []
+    for i in range(len(cuts) - 1):
+        inc = i == len(cuts) - 2
+        o, m, l = att.partial(kv, P, cuts[i], cuts[i + 1], inc, q, kc, vc)
+        want_o, want_m, want_l = util.run_oracle(case, partial=(cuts[i], cuts[i + 1], inc))
+        # same log-sum-exp and same normalised partial output as the oracle's shard
+        lse = (m + torch.log(l)).cpu().numpy()
+        want_lse = want_m + np.log(np.where(want_l > 0, want_l, 1.0))
+        seen = want_l > 0
+        assert np.abs(lse[seen] - want_lse[seen]).max() <= 2e-3
+        assert np.all(np.isneginf(m.cpu().numpy()[~seen])) and np.all(l.cpu().numpy()[~seen] == 0)
+        norm = (o / torch.where(l > 0, l, torch.ones_like(l))[..., None]).cpu().numpy()
+        want_norm = want_o / np.where(want_l > 0, want_l, 1.0)[..., None]
+        assert np.abs(norm - want_norm).max() <= 2e-2
+        parts.append((o, m, l))
+    merged = att.merge_local(torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts]),
+                             torch.stack([p[2] for p in parts]))
+    ctx.synchronize()
+    util.assert_close(util.t2f(merged), ref, "merged partials")
+    kv.close()
+
+
+# ------------------------------------------------------------------------------------------
+# errors: reported, never raised as faults
+# ------------------------------------------------------------------------------------------
+def test_argument_errors(ctx):
+    layer = AttnLayer(n_kv_heads=8)
+    att = CanvasAttention(ctx, layer)
+    kv = KvCache(ctx, layer, 512)
+    q = torch.zeros(1, 256, 16, 256, dtype=torch.bfloat16, device=DEV)
+    k = torch.zeros(1, 256, 8, 256, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(capi.DgError) as e:
+        att.denoise([kv], [400], q, k, k)              # 400 + 256 > capacity 512
+    assert e.value.status == capi.DG_ERR_CAPACITY
+    lib = ctx.lib
+    arr = (C.c_void_p * 1)(kv.h)
+    lens = (C.c_uint32 * 1)(0)
+    st = lib.dg_attn_denoise(ctx.h, C.byref(att.desc), arr, lens, 1, C.c_void_p(q.data_ptr() + 2), C.c_void_p(k.data_ptr()),
+                             C.c_void_p(k.data_ptr()), None, None, C.c_void_p(q.data_ptr()))
+    assert st == capi.DG_ERR_ALIGNMENT
+    st = lib.dg_attn_denoise(ctx.h, C.byref(att.desc), arr, lens, 1, None, None, None, None, None, None)
+    assert st == capi.DG_ERR_INVALID_ARG
+    other = AttnLayer(n_kv_heads=2)
+    with pytest.raises(capi.DgError) as e:
+        CanvasAttention(ctx, other).denoise([kv], [0], q, k[:, :, :2].contiguous(), k[:, :, :2].contiguous())
+    assert e.value.status == capi.DG_ERR_INVALID_ARG   # cache geometry differs from the layer
+    assert ctx.device_status()[0] == 0
+    kv.close()
+
+
+def test_output_guard_rows_untouched(ctx):
+    """Canary rows before and after the output must survive (no out-of-bounds stores), also for a
+    ragged canvas whose last query tile is partly padding."""
+    layer = AttnLayer(n_kv_heads=8, canvas=100)
+    case = util.make_case(layer, 300, seed=8)
+    kv, att = util.gpu_setup(ctx, case)
+    n = 100 * 16 * 256
+    guard = 4096
+    buf = torch.full((n + 2 * guard,), 7.0, dtype=torch.bfloat16, device=DEV)
+    out = buf[guard:guard + n].view(1, 100, 16, 256)
+    for splits in (1, 3):
+        ctx.set_splits(splits)
+        att.denoise([kv], [300], util.dev(case, "q")[None], util.dev(case, "kc")[None], util.dev(case, "vc")[None], out=out)
+    ctx.set_splits(0)
+    ctx.synchronize()
+    assert torch.all(buf[:guard] == 7.0) and torch.all(buf[guard + n:] == 7.0)
+    util.assert_close(util.t2f(out[0]), util.run_oracle(case), "ragged canvas")
+    kv.close()
