@@ -172,7 +172,8 @@ static uint32_t choose_splits(const dg_ctx* ctx, uint32_t q_tiles, uint32_t k_ti
   uint64_t best_cost = ~0ull;
   for (uint32_t s = 1; s <= smax; ++s) {
     const uint64_t waves = (uint64_t(q_tiles) * s + sms - 1) / sms;
-    const uint64_t per = (k_tiles + s - 1) / s + 3 + (s > 1 ? 1 : 0);   // + prologue/epilogue/merge in tile units
+    // fixed cost of a CTA (set-up, Q prologue, epilogue) and of the merge, in key-tile units
+    const uint64_t per = (k_tiles + s - 1) / s + 8 + (s > 1 ? 2 + s / 2 : 0);
     const uint64_t cost = waves * per;
     if (cost < best_cost) {
       best_cost = cost;

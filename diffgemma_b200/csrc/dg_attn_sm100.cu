@@ -54,8 +54,9 @@ enum : uint32_t {
   BAR_V_EMPTY = 4,
   BAR_S_FULL0 = 5,   // +1 for buffer 1
   BAR_P_FULL0 = 7,   // +1 for buffer 1
-  BAR_PV_DONE = 9,
-  N_BARS = 10
+  BAR_PV_DONE = 9,   // one phase per key tile; only waited on when O must be rescaled
+  BAR_O_FINAL = 10,  // single phase: every PV of this CTA has completed
+  N_BARS = 11
 };
 
 struct TileSched {
@@ -125,6 +126,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
     mbar_init(bar_addr(bar_base, BAR_P_FULL0), 128);
     mbar_init(bar_addr(bar_base, BAR_P_FULL0 + 1), 128);
     mbar_init(bar_addr(bar_base, BAR_PV_DONE), 1);
+    mbar_init(bar_addr(bar_base, BAR_O_FINAL), 1);
     ctl[1] = 0u;
     ctl[2] = 0u;
     fence_mbar_init();
@@ -145,63 +147,83 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
 
   if (warp < 4) {
     // ---------------------------------------------------------------- Q prologue (warp per row)
-    for (uint32_t it = 0; it < 32; ++it) {
-      const uint32_t r = warp * 32 + it;
-      const uint32_t R = mt * BM + r;
-      const bool valid = R < rows_per_head;
-      const uint32_t i = valid ? R / p.G : 0u;
-      const uint32_t h = kvh * p.G + (valid ? R % p.G : 0u);
-      float x[8];
-      if (valid) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(p.q + (size_t(i) * p.Hq + h) * HD + lane * 8);
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    // Rows are processed in batches of QB with every global load of a batch (raw row chunk and
+    // RoPE table entries) issued before the first use, so a warp pays one memory round trip per
+    // batch instead of one per row.
+    constexpr int QB = 4;
+    float wq[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) wq[e] = 1.0f;
+    if (!p.q_prenormed && p.qw) {
+      const uint4 wr = *reinterpret_cast<const uint4*>(p.qw + lane * 8);
+      const uint32_t w[4] = {wr.x, wr.y, wr.z, wr.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        wq[2 * e] = __uint_as_float(w[e] << 16);
+        wq[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+      }
+    }
+#pragma unroll 1
+    for (uint32_t batch = 0; batch < 32 / QB; ++batch) {
+      uint4 raw[QB];
+      float2 cs[QB][8];
+#pragma unroll
+      for (int b = 0; b < QB; ++b) {
+        const uint32_t r = warp * 32 + batch * QB + b;
+        const uint32_t R = mt * BM + r;
+        const bool valid = R < rows_per_head;
+        const uint32_t i = valid ? R / p.G : 0u;
+        const uint32_t h = kvh * p.G + (valid ? R % p.G : 0u);
+        raw[b] = valid ? *reinterpret_cast<const uint4*>(p.q + (size_t(i) * p.Hq + h) * HD + lane * 8)
+                       : make_uint4(0u, 0u, 0u, 0u);
+        if (!p.q_prenormed) {
+          const float4* tab = reinterpret_cast<const float4*>(p.rope_table + size_t(i) * 128 + (lane & 15) * 8);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float4 t4 = tab[e];
+            cs[b][2 * e] = make_float2(t4.x, t4.y);
+            cs[b][2 * e + 1] = make_float2(t4.z, t4.w);
+          }
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < QB; ++b) {
+        const uint32_t r = warp * 32 + batch * QB + b;
+        float x[8];
+        const uint32_t w[4] = {raw[b].x, raw[b].y, raw[b].z, raw[b].w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           x[2 * e] = __uint_as_float(w[e] << 16);
           x[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
         }
-      } else {
+        if (!p.q_prenormed) {
+          float ss = 0.f;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) x[e] = 0.f;
-      }
-      if (!p.q_prenormed) {
-        float ss = 0.f;
+          for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+          for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+          const float inv = 1.0f / sqrtf(ss / float(HD) + p.eps);
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        const float inv = 1.0f / sqrtf(ss / float(HD) + p.eps);
-        if (p.qw) {
-          const uint4 wr = *reinterpret_cast<const uint4*>(p.qw + lane * 8);
-          const uint32_t w[4] = {wr.x, wr.y, wr.z, wr.w};
+          for (int e = 0; e < 8; ++e) x[e] *= inv * wq[e];
+          // split-half RoPE: element d pairs with d + 128, i.e. lane l pairs with lane l ^ 16
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            x[2 * e] *= inv * __uint_as_float(w[e] << 16);
-            x[2 * e + 1] *= inv * __uint_as_float(w[e] & 0xffff0000u);
+          for (int e = 0; e < 8; ++e) {
+            const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
+            const float2 c2 = cs[b][e];
+            x[e] = (lane < 16) ? (x[e] * c2.x - other * c2.y) : (other * c2.y + x[e] * c2.x);
           }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) x[e] *= inv;
         }
-        // split-half RoPE: element d pairs with d + 128, i.e. lane l pairs with lane l ^ 16
-        const float2* tab = p.rope_table + size_t(i) * 128 + (lane & 15) * 8;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
-          const float2 cs = tab[e];
-          x[e] = (lane < 16) ? (x[e] * cs.x - other * cs.y) : (other * cs.y + x[e] * cs.x);
-        }
+        uint4 packed;
+        packed.x = pack_bf16x2(x[0], x[1]);
+        packed.y = pack_bf16x2(x[2], x[3]);
+        packed.z = pack_bf16x2(x[4], x[5]);
+        packed.w = pack_bf16x2(x[6], x[7]);
+        // K-major 128-byte-swizzled layout: atom = 64-element column block, 16-byte chunk index
+        // XORed with (row & 7)
+        const uint32_t atom = lane >> 3, cc = lane & 7;
+        const uint32_t off = OFF_Q + atom * ATOM_BYTES + r * 128u + ((cc ^ (r & 7u)) << 4);
+        *reinterpret_cast<uint4*>(smem + off) = packed;
       }
-      uint4 packed;
-      packed.x = pack_bf16x2(x[0], x[1]);
-      packed.y = pack_bf16x2(x[2], x[3]);
-      packed.z = pack_bf16x2(x[4], x[5]);
-      packed.w = pack_bf16x2(x[6], x[7]);
-      // K-major 128-byte-swizzled layout: atom = 64-element column block, 16-byte chunk index
-      // XORed with (row & 7)
-      const uint32_t atom = lane >> 3, cc = lane & 7;
-      const uint32_t off = OFF_Q + atom * ATOM_BYTES + r * 128u + ((cc ^ (r & 7u)) << 4);
-      *reinterpret_cast<uint4*>(smem + off) = packed;
     }
     fence_proxy_async_smem();
     mbar_arrive(bar_addr(bar_base, BAR_Q));
@@ -354,6 +376,9 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
         }
         umma_commit(bar_addr(bar_base, BAR_V_EMPTY));
         umma_commit(bar_addr(bar_base, BAR_PV_DONE));
+        // The epilogue must not reuse BAR_PV_DONE: when the last S tile is ready only PV(n-3) is
+        // known to be complete, so a parity wait on that barrier could alias by two phases.
+        if (n + 1 == n_local) umma_commit(bar_addr(bar_base, BAR_O_FINAL));
       }
     }
   }
@@ -370,7 +395,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
     const uint32_t t_lane = tmem + ((warp * 32u) << 16);
     bool have_o = __all_sync(0xffffffffu, n_local > 0 && !*abort_flag);
     if (have_o) {
-      have_o = __all_sync(0xffffffffu, mbar_wait(bar_addr(bar_base, BAR_PV_DONE), (n_local - 1) & 1u, abort_flag));
+      have_o = __all_sync(0xffffffffu, mbar_wait(bar_addr(bar_base, BAR_O_FINAL), 0u, abort_flag));
       tc_fence_after();
     }
     const bool direct = (p.n_splits == 1);
@@ -443,44 +468,75 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       __threadfence();
       const uint32_t S = p.n_splits;
       const float2* ml_all = reinterpret_cast<const float2*>(p.ws_ml);
-      for (uint32_t r = warp; r < BM; r += N_THREADS / 32) {
-        const uint32_t R = mt * BM + r;
-        if (R >= rows_per_head) break;
-        const size_t orow = size_t(R / p.G) * p.Hq + kvh * p.G + R % p.G;
-        float2 ml = make_float2(-INFINITY, 0.f);
-        if (lane < S) ml = ml_all[size_t(lane) * rows_total + orow];
-        float mg = ml.x;
+      // Each warp merges two rows per iteration and keeps up to 2 x 4 x 2 16-byte loads in flight,
+      // so the merge is bound by L2 bandwidth rather than by one round trip per row and split.
+      constexpr uint32_t NW = N_THREADS / 32;
+      for (uint32_t r0 = warp * 2; r0 < BM; r0 += NW * 2) {
+        size_t orow[2];
+        bool live[2];
+        float2 ml[2];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, o));
-        const float w_mine = (ml.x == -INFINITY) ? 0.f : fast_exp2(ml.x - mg);
-        float lg = w_mine * ml.y;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) lg += __shfl_xor_sync(0xffffffffu, lg, o);
-        float acc[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-        for (uint32_t s = 0; s < S; ++s) {
-          const float w = __shfl_sync(0xffffffffu, w_mine, int(s));
-          const float4* src = reinterpret_cast<const float4*>(p.ws_o + (size_t(s) * rows_total + orow) * HD + lane * 8);
-          const float4 a = src[0], bq = src[1];
-          acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * a.z; acc[3] += w * a.w;
-          acc[4] += w * bq.x; acc[5] += w * bq.y; acc[6] += w * bq.z; acc[7] += w * bq.w;
+        for (int k = 0; k < 2; ++k) {
+          const uint32_t R = mt * BM + r0 + k;
+          live[k] = (r0 + k < BM) && (R < rows_per_head);
+          const uint32_t Rc = live[k] ? R : mt * BM;
+          orow[k] = size_t(Rc / p.G) * p.Hq + kvh * p.G + Rc % p.G;
+          ml[k] = make_float2(-INFINITY, 0.f);
+          if (lane < S) ml[k] = ml_all[size_t(lane) * rows_total + orow[k]];
         }
-        if (p.out) {
-          const float inv = lg > 0.f ? 1.0f / lg : 0.f;
-          uint4 w4;
-          w4.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
-          w4.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
-          w4.z = pack_bf16x2(acc[4] * inv, acc[5] * inv);
-          w4.w = pack_bf16x2(acc[6] * inv, acc[7] * inv);
-          *reinterpret_cast<uint4*>(p.out + orow * HD + lane * 8) = w4;
-        } else {
-          float4* dst = reinterpret_cast<float4*>(p.out_o + orow * HD + lane * 8);
-          dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-          dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-          if (lane == 0) {
-            p.out_m[orow] = mg * 0.6931471805599453f;
-            p.out_l[orow] = lg;
+        float mg[2], lg[2], w_mine[2], acc[2][8];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          mg[k] = ml[k].x;
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) mg[k] = fmaxf(mg[k], __shfl_xor_sync(0xffffffffu, mg[k], o));
+          w_mine[k] = (ml[k].x == -INFINITY) ? 0.f : fast_exp2(ml[k].x - mg[k]);
+          lg[k] = w_mine[k] * ml[k].y;
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) lg[k] += __shfl_xor_sync(0xffffffffu, lg[k], o);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
+        }
+        for (uint32_t s0 = 0; s0 < S; s0 += 4) {
+          float4 a[2][4], bq[2][4];
+#pragma unroll
+          for (int k = 0; k < 2; ++k)
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+              const uint32_t sidx = (s0 + j < S) ? s0 + j : S - 1;   // clamped; its weight is zeroed below
+              const float4* src = reinterpret_cast<const float4*>(p.ws_o + (size_t(sidx) * rows_total + orow[k]) * HD + lane * 8);
+              a[k][j] = src[0];
+              bq[k][j] = src[1];
+            }
+#pragma unroll
+          for (int k = 0; k < 2; ++k)
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+              float w = __shfl_sync(0xffffffffu, w_mine[k], int((s0 + j) & 31u));
+              if (s0 + j >= S) w = 0.f;
+              acc[k][0] += w * a[k][j].x; acc[k][1] += w * a[k][j].y; acc[k][2] += w * a[k][j].z; acc[k][3] += w * a[k][j].w;
+              acc[k][4] += w * bq[k][j].x; acc[k][5] += w * bq[k][j].y; acc[k][6] += w * bq[k][j].z; acc[k][7] += w * bq[k][j].w;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          if (!live[k]) continue;
+          if (p.out) {
+            const float inv = lg[k] > 0.f ? 1.0f / lg[k] : 0.f;
+            uint4 w4;
+            w4.x = pack_bf16x2(acc[k][0] * inv, acc[k][1] * inv);
+            w4.y = pack_bf16x2(acc[k][2] * inv, acc[k][3] * inv);
+            w4.z = pack_bf16x2(acc[k][4] * inv, acc[k][5] * inv);
+            w4.w = pack_bf16x2(acc[k][6] * inv, acc[k][7] * inv);
+            *reinterpret_cast<uint4*>(p.out + orow[k] * HD + lane * 8) = w4;
+          } else {
+            float4* dst = reinterpret_cast<float4*>(p.out_o + orow[k] * HD + lane * 8);
+            dst[0] = make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
+            dst[1] = make_float4(acc[k][4], acc[k][5], acc[k][6], acc[k][7]);
+            if (lane == 0) {
+              p.out_m[orow[k]] = mg[k] * 0.6931471805599453f;
+              p.out_l[orow[k]] = lg[k];
+            }
           }
         }
       }

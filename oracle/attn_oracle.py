@@ -83,9 +83,11 @@ def rms_norm_heads(x: np.ndarray, w: np.ndarray | None, eps: float) -> np.ndarra
     x = x.astype(np.float32)
     ss = np.sum(x * x, axis=-1, keepdims=True, dtype=np.float32)
     inv = (np.float32(1.0) / np.sqrt(ss / np.float32(x.shape[-1]) + np.float32(eps))).astype(np.float32)
-    y = x * inv
     if w is not None:
-        y = y * w.astype(np.float32)
+        # x * (inv * w), the association of src/shaders/attn/cpu.rs:67-75
+        y = x * (inv * w.astype(np.float32))
+    else:
+        y = x * inv
     return y.astype(np.float32)
 
 

@@ -310,7 +310,8 @@ def test_partials_merge_to_single_shot(ctx, P, W, mode, cuts):
         lse = (m + torch.log(l)).cpu().numpy()
         want_lse = want_m + np.log(np.where(want_l > 0, want_l, 1.0))
         seen = want_l > 0
-        assert np.abs(lse[seen] - want_lse[seen]).max() <= 2e-3
+        if seen.any():
+            assert np.abs(lse[seen] - want_lse[seen]).max() <= 2e-3
         assert np.all(np.isneginf(m.cpu().numpy()[~seen])) and np.all(l.cpu().numpy()[~seen] == 0)
         norm = (o / torch.where(l > 0, l, torch.ones_like(l))[..., None]).cpu().numpy()
         want_norm = want_o / np.where(want_l > 0, want_l, 1.0)[..., None]

@@ -86,8 +86,17 @@ def errors(got: np.ndarray, ref: np.ndarray):
     return float(diff.max()), float(diff.mean())
 
 
+def max_abs_tol(ref: np.ndarray) -> float:
+    """2e-2 for outputs of magnitude <= 2 (every benchmark configuration).  bf16 has 8 significant
+    bits, so rounding the OUTPUT alone costs up to 2^-9 * 2^ceil(log2|o|): 7.8e-3 below 2, 1.6e-2 in
+    [2, 4), 3.1e-2 in [4, 8).  The unscaled-logit stress cases reach |o| > 4, so the bound grows in
+    proportion to the largest reference magnitude beyond 2."""
+    return MAX_ABS_TOL * max(1.0, float(np.abs(ref).max()) / 2.0)
+
+
 def assert_close(got, ref, what=""):
     mx, mean = errors(got, ref)
     assert np.isfinite(got).all(), f"{what}: non-finite output"
-    assert mx <= MAX_ABS_TOL and mean <= MEAN_ABS_TOL, f"{what}: max-abs {mx:.3e} mean-abs {mean:.3e}"
+    tol = max_abs_tol(ref)
+    assert mx <= tol and mean <= MEAN_ABS_TOL, f"{what}: max-abs {mx:.3e} (tol {tol:.2e}) mean-abs {mean:.3e}"
     return mx, mean
