@@ -30,8 +30,9 @@ UNIT = "TFLOP/s"
 L2_BYTES = 126e6
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention-kernel launch of the benchmark
-# workload, from the committed ncu capture under profiles/ (None until one exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# workload (70.09 MB + 4.47 MB), from the ncu capture summarised in
+# profiles/dg_attn_sm100_kernel__cfg2_global_p32768.md
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {2: 74.56e6}
 
 
 def _peaks():
@@ -44,35 +45,47 @@ def _peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with one long-running nvidia-smi (-lms 20) while the
+    timed region runs; the process is ended by its own PID afterwards."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
         self.index = index
         self.samples = []
-        self._stop = threading.Event()
-        self._t = threading.Thread(target=self._run, daemon=True)
+        self.proc = None
+        self._t = None
 
-    def _run(self):
-        while not self._stop.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
-                parts = [x.strip() for x in out.strip().split(",")]
+    def _reader(self):
+        try:
+            for line in self.proc.stdout:
+                parts = [x.strip() for x in line.strip().split(",")]
                 if len(parts) >= 6:
                     self.samples.append(parts)
-            except Exception:
-                pass
-            self._stop.wait(0.05)
+        except Exception:
+            pass
 
     def __enter__(self):
-        self._t.start()
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self._t = threading.Thread(target=self._reader, daemon=True)
+            self._t.start()
+            time.sleep(0.3)     # let the first samples arrive before the timed region
+        except Exception:
+            self.proc = None
         return self
 
     def __exit__(self, *a):
-        self._stop.set()
-        self._t.join(timeout=6)
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+        if self._t is not None:
+            self._t.join(timeout=5)
 
     def summary(self):
         sm, mx, reasons = [], 0.0, set()
@@ -297,7 +310,7 @@ def run_ours(args):
             "achieved_hbm_gbs": io_bytes / (ms_dev * 1e-3) / 1e9,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": (achieved / peaks["bf16_tflops"]) if achieved else None,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": peaks["source"] + " burst",
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(args.cfg) if world == 1 else None, "peak_source": peaks["source"] + " burst",
                          "kernel": "dg_attn_sm100_kernel", "kernel_ms": k_avg_ms, "kernel_launches_timed": k_n},
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e_ev,
                     "h2d_bytes_per_step": int(q_h.numel() * 2 + kc_h.numel() * 2 + vc_h.numel() * 2),
@@ -324,8 +337,8 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cfg", type=int, default=2, choices=[0, 1, 2, 4])
     ap.add_argument("--ref-rows", type=int, default=256, help="canvas rows in the bounded CPU sample")
