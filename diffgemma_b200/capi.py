@@ -62,6 +62,7 @@ SIGNATURES = {
     "dg_kv_append": (_i32, [_vp, _pd, _vp, _u64, _u32, _vp, _vp, _vp]),
     "dg_qk_rope_kv": (_i32, [_vp, _pd, _vp, _u32, _vp, _vp, _vp, _vp, _vp]),
     "dg_attention": (_i32, [_vp, _pd, _vp, _u32, _vp, _vp]),
+    "dg_attention_static_scratch": (_i32, [_vp, _pd, _vp, _u32, _vp, _vp]),
     "dg_attn_denoise": (_i32, [_vp, _pd, C.POINTER(_vp), C.POINTER(_u32), _u32, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dg_attn_denoise_host": (_i32, [_vp, _pd, C.POINTER(_vp), C.POINTER(_u32), _u32, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dg_attn_denoise_bitmap": (_i32, [_vp, _pd, _vp, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),

@@ -13,6 +13,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <string>
 #include <vector>
@@ -873,5 +874,118 @@ extern "C" int32_t dg_nccl_all_gather(dg_ctx* c, void* comm, const void* send, v
   if (!nccl().ok) return fail(DG_ERR_NCCL, "NCCL not loaded");
   DG_CUDA(cudaSetDevice(c->device));
   DG_NCCL(nccl().AllGather(send, recv, bytes_per_rank, ncclUint8, static_cast<ncclComm_t>(comm), c->stream));
+  return DG_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Stage 2 without any allocation
+// ------------------------------------------------------------------------------------------
+// Some hosts may not allocate device memory once they are running: a serving loop that has handed
+// every free byte of HBM to its own pool, a step that is being recorded into a CUDA graph (stream
+// capture forbids cudaMalloc), or a real-time thread that must not enter the allocator.  The regular
+// entry points grow the split workspace with cudaMalloc the first time a launch needs more of it.
+// dg_attention_static_scratch never does: its split workspace is the fixed array below, which every
+// GPU that loads this library holds from module load until process exit.
+//
+// Layout of the array (floats): [partial O: kStaticSplits x kStaticRows x 256]
+//                               [partial (m, l): kStaticSplits x kStaticRows x 2]
+//                               [one counter per query tile: kStaticTiles words]
+// = 4 x 4096 x 256 + 4 x 4096 x 2 + 128 floats = 16.13 MiB.
+namespace {
+constexpr uint32_t kStaticSplits = 4;      // at most 4 key splits per query tile
+constexpr uint32_t kStaticRows = 4096;     // canvas * n_q_heads, e.g. 256 x 16
+constexpr uint32_t kStaticTiles = 128;     // query tiles (counters)
+constexpr size_t kStaticOFloats = size_t(kStaticSplits) * kStaticRows * 256;
+constexpr size_t kStaticMlFloats = size_t(kStaticSplits) * kStaticRows * 2;
+constexpr size_t kStaticFloats = kStaticOFloats + kStaticMlFloats + kStaticTiles;
+constexpr int kMaxDevices = 64;
+}  // namespace
+
+static __device__ __align__(256) float g_static_scratch[kStaticFloats];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address; the address
+// the kernels need comes from cudaGetSymbolAddress, asked once per device with that device current.
+static float* g_static_scratch_addr[kMaxDevices] = {};
+static std::mutex g_static_scratch_mutex;
+
+static int32_t static_scratch_for_device(int device, float** out) {
+  if (device < 0 || device >= kMaxDevices) return fail(DG_ERR_INVALID_ARG, "device index out of range");
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_addr[device] == nullptr) {
+    DG_CUDA(cudaSetDevice(device));
+    void* ptr = nullptr;
+    DG_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    if (ptr == nullptr) return fail(DG_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    g_static_scratch_addr[device] = static_cast<float*>(ptr);
+  }
+  *out = g_static_scratch_addr[device];
+  return DG_OK;
+}
+
+extern "C" int32_t dg_attention_static_scratch(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint32_t kv_len, const void* q,
+                                               void* out) {
+  if (!c || !q || !out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  int32_t r = check_desc(d);
+  if (r != DG_OK) return r;
+  r = check_kv(*d, kv, uint64_t(kv_len) + d->canvas);
+  if (r != DG_OK) return r;
+  r = check_ptrs16({q, out});
+  if (r != DG_OK) return r;
+  DG_CUDA(cudaSetDevice(c->device));
+  c->last_launches = 0;
+
+  AttnParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.cache_k = kv->k;
+  p.cache_v = kv->v;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.status = c->d_status;
+  p.cap = kv->cap;
+  p.mask = make_mask(*d, kv_len, 0, 0xffffffffu, 1);
+  p.C = d->canvas;
+  p.Hq = d->n_q_heads;
+  p.Hkv = d->n_kv_heads;
+  p.G = d->n_q_heads / d->n_kv_heads;
+  p.D = d->head_dim;
+  p.q_prenormed = 1u;
+  p.n_splits = 1;
+  p.rot_half = d->rotary_dim / 2;
+  p.pair_off = d->rope_pairing == DG_ROPE_SPLIT_HALF ? d->rotary_dim / 2 : d->head_dim / 2;
+  p.scale_log2 = d->softmax_scale * 1.4426950408889634f;
+  p.eps = d->rms_eps;
+
+  if (!(tensor_path_ok(*d) && kv->has_tmap)) {
+    // the general kernel keeps all of its state in registers and shared memory: nothing to provide
+    launch_attn_general(p, c->stream);
+    DG_CUDA(cudaGetLastError());
+    c->last_launches = 1;
+    return DG_OK;
+  }
+  const uint32_t rows = p.C * p.Hq;
+  const uint32_t q_tiles = sm100_query_tiles(p.C, p.G, p.Hkv);
+  if (rows > kStaticRows || q_tiles > kStaticTiles) {
+    g_last_error = "dg_attention_static_scratch: canvas * n_q_heads = " + std::to_string(rows) + " rows (" +
+                   std::to_string(q_tiles) + " query tiles) exceeds the built-in scratch of " +
+                   std::to_string(kStaticRows) + " rows / " + std::to_string(kStaticTiles) +
+                   " tiles; use dg_attention, which allocates its workspace";
+    return DG_ERR_UNSUPPORTED;
+  }
+  float* scratch = nullptr;
+  r = static_scratch_for_device(c->device, &scratch);
+  if (r != DG_OK) return r;
+  uint32_t splits = choose_splits(c, q_tiles, sm100_key_tiles(p.mask));
+  if (splits > kStaticSplits) splits = kStaticSplits;
+  p.n_splits = splits;
+  p.ws_o = scratch;
+  p.ws_ml = scratch + kStaticOFloats;
+  p.ws_counters = reinterpret_cast<uint32_t*>(scratch + kStaticOFloats + kStaticMlFloats);
+  // The array keeps whatever the previous call left.  Partials are fully rewritten before they are
+  // read, but the per-tile arrival counters must start at zero (a call that was cut short could have
+  // left them half-counted), so they are cleared on the stream ahead of the launch.
+  DG_CUDA(cudaMemsetAsync(p.ws_counters, 0, kStaticTiles * sizeof(uint32_t), c->stream));
+  const cudaError_t e = launch_attn_sm100(p, kv->tm_k, kv->tm_v, c->stream);
+  if (e != cudaSuccess) return fail_cuda(e, "launch_attn_sm100");
+  c->last_launches = 1;
   return DG_OK;
 }

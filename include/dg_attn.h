@@ -134,6 +134,20 @@ int32_t dg_qk_rope_kv(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* kv, uint32_
  * K/V are already in the cache.  out: [C][Hq][D] bf16 device pointer.                           */
 int32_t dg_attention(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* kv, uint32_t kv_len, const void* q,
                      void* out);
+/* Stage 2 for hosts that must not allocate device memory while they run (all HBM already given to
+ * the host's own pool, a step being captured into a CUDA graph, a thread barred from the allocator).
+ * Same arguments and result as dg_attention, but the key-split workspace is a 16.13 MiB array built
+ * into the library (every GPU that loads the library holds it until the process exits) and the call
+ * performs no cudaMalloc / cudaFree.  Limits: canvas * n_q_heads <= 4096 rows, at most 128 query
+ * tiles, at most 4 key splits (more are clamped); beyond the row/tile limits the call returns
+ * DG_ERR_UNSUPPORTED with an explanatory message.  The first call on each device looks up the
+ * array's device address; make that first call before starting any stream capture.  All calls on a
+ * device share the one array and it keeps the previous call's contents (the call clears the part
+ * that must start at zero): two calls whose kernels overlap on the GPU (different streams, or
+ * different contexts on one device) race on it and must be serialised by the caller.
+ * This entry point has no counterpart in the reference.                                          */
+int32_t dg_attention_static_scratch(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* kv, uint32_t kv_len,
+                                    const void* q, void* out);
 /* Both stages for `batch` independent canvases, Q prologue fused into the attention kernel.
  * q: [batch][C][Hq][D], k, v: [batch][C][Hkv][D] PRE-norm bf16 device pointers (not modified);
  * qw, kw: norm weights [D] or NULL (= unit); kv[b], kv_len[b]: cache and prefix length of canvas b
