@@ -70,6 +70,7 @@ class Context:
         self.h = h
         self.device = device
         self.torch_stream = torch.cuda.ExternalStream(int(self.lib.dg_ctx_stream(self.h)), device=device)
+        self._made_current = make_current
         if make_current:
             torch.cuda.set_device(device)
             torch.cuda.set_stream(self.torch_stream)
@@ -104,6 +105,10 @@ class Context:
 
     def close(self) -> None:
         if self.h:
+            if self._made_current:
+                # hand torch its default stream back before the context's stream is destroyed
+                torch.cuda.synchronize(self.device)
+                torch.cuda.set_stream(torch.cuda.default_stream(self.device))
             self.lib.dg_ctx_destroy(self.h)
             self.h = None
 

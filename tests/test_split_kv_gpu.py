@@ -1,0 +1,61 @@
+"""Split-KV across GPUs over NCCL: every rank holds one prefix shard, the per-rank (O, m, l) partials
+are merged by dg_attn_merge_nccl, and the result must equal the single-GPU oracle.  Needs >= 2 GPUs
+(skipped otherwise); ranks are child processes, one per GPU."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _rank_main(rank, world, port, P, W, mode, ret):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import util
+    from diffgemma_b200.split_kv import SplitKvGroup, plan_shards
+    from diffgemma_b200.step_attn import AttnLayer, Context, KvCache
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        ctx = Context(rank)
+        layer = AttnLayer(n_kv_heads=2, window=W, mask_mode=mode)
+        case = util.make_case(layer, P, seed=77)          # same seed on every rank: replicated inputs
+        dev = f"cuda:{rank}"
+        b = plan_shards(P, world)
+        kv = KvCache(ctx, layer, P + layer.canvas)
+        t0, t1 = b[rank], b[rank + 1]
+        if t1 > t0:                                        # only this rank's shard is resident
+            kv.load_prefix(case["kp"][t0:t1].contiguous().to(dev), case["vp"][t0:t1].contiguous().to(dev), t0)
+        grp = SplitKvGroup(ctx, layer)
+        out = None
+        for _ in range(2):                                 # twice: workspace reuse across steps
+            out = grp.denoise(kv, P, case["q"].to(dev), case["kc"].to(dev), case["vc"].to(dev))
+        ctx.synchronize()
+        ref = util.run_oracle(case)
+        ret[rank] = util.errors(util.t2f(out), ref) + (float(util.max_abs_tol(ref)),)
+        grp.close()
+        kv.close()
+        ctx.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("P,W,mode,port", [(6000, 0, 0, 29721), (3000, 1024, 1, 29722)])
+def test_split_kv_nccl_matches_oracle(P, W, mode, port):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_rank_main, args=(world, port, P, W, mode, ret), nprocs=world, join=True)
+    assert len(ret) == world
+    for rank, (mx, mean, tol) in ret.items():
+        assert mx <= tol and mean <= 2e-3, (rank, mx, mean)
