@@ -77,6 +77,7 @@ SIGNATURES = {
     "dg_attn_flops": (C.c_double, [_pd, _u32]),
     "dg_ctx_last_launch_count": (_u32, [_vp]),
     "dg_ctx_kernel_timing": (_i32, [_vp, _i32, _u32]),
+    "dg_ctx_phase_stamps": (_i32, [_vp, _vp]),
     "dg_ctx_kernel_time": (_i32, [_vp, C.POINTER(C.c_double), C.POINTER(_u32)]),
 }
 

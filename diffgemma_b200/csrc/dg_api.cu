@@ -69,6 +69,7 @@ struct dg_ctx {
   uint32_t forced_splits = 0;
   uint32_t last_launches = 0;
   // optional per-launch timing of the attention kernel (event pairs on the launching stream)
+  unsigned long long* stamps = nullptr;   // caller-owned device buffer for per-CTA phase stamps
   bool timing = false;
   std::vector<cudaEvent_t> ev;
   size_t ev_used = 0;
@@ -348,6 +349,12 @@ extern "C" int32_t dg_ctx_set_splits(dg_ctx* c, uint32_t n) {
 }
 extern "C" uint32_t dg_ctx_last_launch_count(const dg_ctx* c) { return c ? c->last_launches : 0; }
 
+extern "C" int32_t dg_ctx_phase_stamps(dg_ctx* c, void* device_buffer) {
+  if (!c) return fail(DG_ERR_INVALID_ARG, "ctx is NULL");
+  c->stamps = static_cast<unsigned long long*>(device_buffer);
+  return DG_OK;
+}
+
 extern "C" int32_t dg_ctx_kernel_timing(dg_ctx* c, int32_t on, uint32_t max_launches) {
   if (!c) return fail(DG_ERR_INVALID_ARG, "ctx is NULL");
   DG_CUDA(cudaSetDevice(c->device));
@@ -544,6 +551,7 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
   p.out_m = a.out_m;
   p.out_l = a.out_l;
   p.status = c->d_status;
+  p.stamps = c->stamps;
   p.cap = kv->cap;
   p.mask = make_mask(d, a.kv_len, a.t0, a.t1, a.include_canvas);
   p.C = d.canvas;

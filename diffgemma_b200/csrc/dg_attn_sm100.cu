@@ -7,8 +7,9 @@
 //   * S = Q K^T and O += P V run on tcgen05.mma with fp32 accumulators in tensor memory:
 //     TMEM columns [0,128) and [128,256) double-buffer S, [256,512) hold O; P (bf16) overwrites
 //     the first 64 columns of its S buffer and is consumed from TMEM as the A operand.
-//   * online softmax in registers, one thread per query row, with lazy rescaling of O (only when
-//     the running maximum grows by more than 2^8).
+//   * online softmax in registers, two threads per query row (64 key columns each, so that every
+//     scheduler has two softmax warps to hide instruction latency), with lazy rescaling of O (only
+//     when the running maximum grows by more than 2^8).
 //   * intra-GPU split-KV: grid.y CTAs share one query tile, each writes an (O, m, l) partial and
 //     the last one to finish merges them (log-sum-exp) - no second launch.
 //
@@ -38,11 +39,17 @@ constexpr uint32_t OFF_Q = 0;
 constexpr uint32_t OFF_K = TILE_BYTES;
 constexpr uint32_t OFF_V = 2 * TILE_BYTES;
 constexpr uint32_t OFF_BAR = 3 * TILE_BYTES;
-constexpr uint32_t SMEM_BYTES = OFF_BAR + 256 + 1024;   // + barrier block + alignment slack
+constexpr uint32_t OFF_XCH = OFF_BAR + 256;             // pair-exchange scratch (4 KB)
+constexpr uint32_t SMEM_BYTES = OFF_XCH + 4096 + 1024;  // + alignment slack
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TM_S = 0;            // two S buffers of 128 columns
 constexpr uint32_t TM_O = 256;          // O accumulator, 256 columns
-constexpr uint32_t N_THREADS = 224;     // warps 0-3 softmax, 4 K loader, 5 V loader, 6 MMA issuer
+// warps 0-7: two softmax warpgroups (warp w and w+4 share the 32 query rows of TMEM quadrant w & 3;
+// the first handles key columns 0-63 of every tile, the second 64-127), 8: K loader, 9: V loader,
+// 10: TMEM allocation + the MMA-issuing thread
+constexpr uint32_t N_SM_WARPS = 8;
+constexpr uint32_t WARP_K = 8, WARP_V = 9, WARP_MMA = 10;
+constexpr uint32_t N_THREADS = 352;
 constexpr float RESCALE_THRESHOLD = 8.0f;   // log2 units
 
 // barrier slots (8 bytes each) inside the barrier block
@@ -86,7 +93,22 @@ __host__ __device__ inline TileSched tile_sched(const MaskParams& mk, uint32_t r
 
 __device__ __forceinline__ uint32_t bar_addr(uint32_t bar_base, uint32_t idx) { return bar_base + idx * 8u; }
 
+// Phase time stamps (globaltimer, ns) of one CTA, written by thread 0 when a stamp buffer is given:
+// 0 start, 1 set-up done, 2 Q prologue done, 3 main loop done, 4 epilogue done, 5 merge done.
+__device__ __forceinline__ void stamp(const AttnParams& p, uint32_t slot) {
+  if (p.stamps != nullptr && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    p.stamps[(size_t(blockIdx.y) * gridDim.x + blockIdx.x) * 8 + slot] = t;
+  }
+}
+
 }  // namespace
+
+// named barrier shared by the two warps that own the same 32 query rows
+__device__ __forceinline__ void pair_sync(uint32_t smw) {
+  asm volatile("bar.sync %0, 64;" ::"r"(smw + 1u) : "memory");
+}
 
 __global__ void __launch_bounds__(N_THREADS, 1)
 dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_k,
@@ -98,6 +120,9 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   const uint32_t bar_base = smem_base + OFF_BAR;
   volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + N_BARS * 8);
   // ctl[0] = TMEM base address, ctl[1] = abort flag, ctl[2] = "this CTA merges" flag
+  float* xch_max = reinterpret_cast<float*>(smem + OFF_XCH);   // [2 tile parities][BM][2 halves]
+  float* xch_misc = xch_max + 2 * BM * 2;                       // [BM][2]: prologue sums of squares
+  float* xch_l = xch_misc + BM * 2;                             // [BM][2]: final softmax denominators
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t tiles_per_head = (p.C * p.G + BM - 1) / BM;
@@ -114,126 +139,128 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   const uint32_t v_end = uint32_t((uint64_t(split + 1) * n_tiles) / p.n_splits);
   const uint32_t n_local = v_end - v_begin;
 
+  stamp(p, 0);
   // ------------------------------------------------------------------ set-up
   if (tid == 0) {
-    mbar_init(bar_addr(bar_base, BAR_Q), 128);
+    mbar_init(bar_addr(bar_base, BAR_Q), N_SM_WARPS * 32);
     mbar_init(bar_addr(bar_base, BAR_K_FULL), 1);
     mbar_init(bar_addr(bar_base, BAR_K_EMPTY), 1);
     mbar_init(bar_addr(bar_base, BAR_V_FULL), 1);
     mbar_init(bar_addr(bar_base, BAR_V_EMPTY), 1);
     mbar_init(bar_addr(bar_base, BAR_S_FULL0), 1);
     mbar_init(bar_addr(bar_base, BAR_S_FULL0 + 1), 1);
-    mbar_init(bar_addr(bar_base, BAR_P_FULL0), 128);
-    mbar_init(bar_addr(bar_base, BAR_P_FULL0 + 1), 128);
+    mbar_init(bar_addr(bar_base, BAR_P_FULL0), N_SM_WARPS * 32);
+    mbar_init(bar_addr(bar_base, BAR_P_FULL0 + 1), N_SM_WARPS * 32);
     mbar_init(bar_addr(bar_base, BAR_PV_DONE), 1);
     mbar_init(bar_addr(bar_base, BAR_O_FINAL), 1);
     ctl[1] = 0u;
     ctl[2] = 0u;
     fence_mbar_init();
   }
-  if (warp == 6) {
+  if (warp == WARP_MMA) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(&ctl[0])), TMEM_COLS);
     tmem_relinquish();
   }
-  if ((warp == 4 || warp == 5) && lane == 0) tma_prefetch_desc(warp == 4 ? &tm_k : &tm_v);
+  if ((warp == WARP_K || warp == WARP_V) && lane == 0) tma_prefetch_desc(warp == WARP_K ? &tm_k : &tm_v);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = ctl[0];
+  stamp(p, 1);
   volatile uint32_t* abort_flag = &ctl[1];
 
-  // per-row softmax state lives in the softmax threads across the main loop and the epilogue
+  // softmax-thread geometry: TMEM quadrant smw, row r of the query tile, column half
+  const uint32_t smw = warp & 3u, half = (warp >> 2) & 1u;
+  const uint32_t r = smw * 32 + lane;
+  // per-row softmax state (identical in both threads of a row, except l_run which is per half)
   float m_used = -INFINITY, l_run = 0.f;
 
-  if (warp < 4) {
-    // ---------------------------------------------------------------- Q prologue (warp per row)
-    // Rows are processed in batches of QB with every global load of a batch (raw row chunk and
-    // RoPE table entries) issued before the first use, so a warp pays one memory round trip per
-    // batch instead of one per row.
-    constexpr int QB = 4;
-    float wq[8];
+  if (warp < N_SM_WARPS) {
+    // ---------------------------------------------------------------- Q prologue (two threads per row)
+    // Thread (row, half) owns the RoPE pairs (d, d+128) with d in [64*half, 64*half + 64): eight
+    // 16-byte chunks from each half of the row.  No shuffles; the two partial sums of squares meet
+    // through shared memory.
+    {
+      const uint32_t R = mt * BM + r;
+      const bool valid = R < rows_per_head;
+      const uint32_t i = valid ? R / p.G : 0u;
+      const uint32_t h = kvh * p.G + (valid ? R % p.G : 0u);
+      const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t(i) * p.Hq + h) * HD);
+      const bool do_norm = !p.q_prenormed;
+      uint4 lo[8], hi[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) wq[e] = 1.0f;
-    if (!p.q_prenormed && p.qw) {
-      const uint4 wr = *reinterpret_cast<const uint4*>(p.qw + lane * 8);
-      const uint32_t w[4] = {wr.x, wr.y, wr.z, wr.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        wq[2 * e] = __uint_as_float(w[e] << 16);
-        wq[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+      for (int j = 0; j < 8; ++j) {
+        lo[j] = src[half * 8 + j];
+        hi[j] = src[16 + half * 8 + j];
       }
-    }
-#pragma unroll 1
-    for (uint32_t batch = 0; batch < 32 / QB; ++batch) {
-      uint4 raw[QB];
-      float2 cs[QB][8];
+      if (!valid) {
 #pragma unroll
-      for (int b = 0; b < QB; ++b) {
-        const uint32_t r = warp * 32 + batch * QB + b;
-        const uint32_t R = mt * BM + r;
-        const bool valid = R < rows_per_head;
-        const uint32_t i = valid ? R / p.G : 0u;
-        const uint32_t h = kvh * p.G + (valid ? R % p.G : 0u);
-        raw[b] = valid ? *reinterpret_cast<const uint4*>(p.q + (size_t(i) * p.Hq + h) * HD + lane * 8)
-                       : make_uint4(0u, 0u, 0u, 0u);
-        if (!p.q_prenormed) {
-          const float4* tab = reinterpret_cast<const float4*>(p.rope_table + size_t(i) * 128 + (lane & 15) * 8);
+        for (int j = 0; j < 8; ++j) lo[j] = hi[j] = make_uint4(0u, 0u, 0u, 0u);
+      }
+      float inv = 1.0f;
+      if (do_norm) {
+        float ss0 = 0.f, ss1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t a[4] = {lo[j].x, lo[j].y, lo[j].z, lo[j].w};
+          const uint32_t b[4] = {hi[j].x, hi[j].y, hi[j].z, hi[j].w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float4 t4 = tab[e];
-            cs[b][2 * e] = make_float2(t4.x, t4.y);
-            cs[b][2 * e + 1] = make_float2(t4.z, t4.w);
+            const float a0 = __uint_as_float(a[e] << 16), a1 = __uint_as_float(a[e] & 0xffff0000u);
+            const float b0 = __uint_as_float(b[e] << 16), b1 = __uint_as_float(b[e] & 0xffff0000u);
+            ss0 += a0 * a0 + a1 * a1;
+            ss1 += b0 * b0 + b1 * b1;
           }
         }
+        xch_misc[r * 2 + half] = ss0 + ss1;
+        pair_sync(smw);
+        const float ss = xch_misc[r * 2 + 0] + xch_misc[r * 2 + 1];
+        inv = 1.0f / sqrtf(ss / float(HD) + p.eps);
       }
+      const float4* tab = reinterpret_cast<const float4*>(p.rope_table + size_t(i) * 128 + half * 64);
 #pragma unroll
-      for (int b = 0; b < QB; ++b) {
-        const uint32_t r = warp * 32 + batch * QB + b;
-        float x[8];
-        const uint32_t w[4] = {raw[b].x, raw[b].y, raw[b].z, raw[b].w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          x[2 * e] = __uint_as_float(w[e] << 16);
-          x[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
-        }
-        if (!p.q_prenormed) {
-          float ss = 0.f;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-          const float inv = 1.0f / sqrtf(ss / float(HD) + p.eps);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) x[e] *= inv * wq[e];
-          // split-half RoPE: element d pairs with d + 128, i.e. lane l pairs with lane l ^ 16
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
-            const float2 c2 = cs[b][e];
-            x[e] = (lane < 16) ? (x[e] * c2.x - other * c2.y) : (other * c2.y + x[e] * c2.x);
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t c_lo = half * 8 + j, c_hi = c_lo + 16;
+        uint4 out_lo = lo[j], out_hi = hi[j];
+        if (do_norm) {
+          uint4 wl4 = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u), wh4 = wl4;   // bf16 1.0
+          if (p.qw) {
+            wl4 = reinterpret_cast<const uint4*>(p.qw)[c_lo];
+            wh4 = reinterpret_cast<const uint4*>(p.qw)[c_hi];
           }
+          const uint32_t a[4] = {lo[j].x, lo[j].y, lo[j].z, lo[j].w};
+          const uint32_t b[4] = {hi[j].x, hi[j].y, hi[j].z, hi[j].w};
+          const uint32_t wa[4] = {wl4.x, wl4.y, wl4.z, wl4.w};
+          const uint32_t wb[4] = {wh4.x, wh4.y, wh4.z, wh4.w};
+          uint32_t ya[4], yb[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float4 cs = tab[j * 4 + e];   // (cos, sin) of pairs 8*c_lo + 2e and + 2e + 1
+            const float a0 = __uint_as_float(a[e] << 16) * (inv * __uint_as_float(wa[e] << 16));
+            const float a1 = __uint_as_float(a[e] & 0xffff0000u) * (inv * __uint_as_float(wa[e] & 0xffff0000u));
+            const float b0 = __uint_as_float(b[e] << 16) * (inv * __uint_as_float(wb[e] << 16));
+            const float b1 = __uint_as_float(b[e] & 0xffff0000u) * (inv * __uint_as_float(wb[e] & 0xffff0000u));
+            ya[e] = pack_bf16x2(a0 * cs.x - b0 * cs.y, a1 * cs.z - b1 * cs.w);
+            yb[e] = pack_bf16x2(a0 * cs.y + b0 * cs.x, a1 * cs.w + b1 * cs.z);
+          }
+          out_lo = make_uint4(ya[0], ya[1], ya[2], ya[3]);
+          out_hi = make_uint4(yb[0], yb[1], yb[2], yb[3]);
         }
-        uint4 packed;
-        packed.x = pack_bf16x2(x[0], x[1]);
-        packed.y = pack_bf16x2(x[2], x[3]);
-        packed.z = pack_bf16x2(x[4], x[5]);
-        packed.w = pack_bf16x2(x[6], x[7]);
         // K-major 128-byte-swizzled layout: atom = 64-element column block, 16-byte chunk index
         // XORed with (row & 7)
-        const uint32_t atom = lane >> 3, cc = lane & 7;
-        const uint32_t off = OFF_Q + atom * ATOM_BYTES + r * 128u + ((cc ^ (r & 7u)) << 4);
-        *reinterpret_cast<uint4*>(smem + off) = packed;
+        *reinterpret_cast<uint4*>(smem + OFF_Q + (c_lo >> 3) * ATOM_BYTES + r * 128u + (((c_lo & 7u) ^ (r & 7u)) << 4)) = out_lo;
+        *reinterpret_cast<uint4*>(smem + OFF_Q + (c_hi >> 3) * ATOM_BYTES + r * 128u + (((c_hi & 7u) ^ (r & 7u)) << 4)) = out_hi;
       }
     }
     fence_proxy_async_smem();
     mbar_arrive(bar_addr(bar_base, BAR_Q));
+    stamp(p, 2);
 
     // ---------------------------------------------------------------- softmax main loop
-    const uint32_t r = warp * 32 + lane;
     const uint32_t R = mt * BM + r;
     const uint32_t i_row = (R < rows_per_head) ? R / p.G : p.C - 1;
     const uint32_t row_lo = mask_row_lo(mk, i_row);
-    const uint32_t t_lane = tmem + ((warp * 32u) << 16);
+    const uint32_t t_lane = tmem + ((smw * 32u) << 16);
     const bool contiguous = (mk.pre_hi == mk.kv_len) && (mk.can_hi > mk.kv_len);
     const float sc = p.scale_log2;
 
@@ -245,41 +272,48 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       // warp-uniform outcome: the TMEM instructions below need the whole warp
       if (!__all_sync(0xffffffffu, mbar_wait(bar_addr(bar_base, BAR_S_FULL0 + b), (n >> 1) & 1u, abort_flag))) break;
       tc_fence_after();
-      uint32_t sraw[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(t_lane + TM_S + b * 128u + c * 32u, sraw[c]);
+      uint32_t sraw[2][32];
+      tmem_ld32(t_lane + TM_S + b * 128u + half * 64u, sraw[0]);
+      tmem_ld32(t_lane + TM_S + b * 128u + half * 64u + 32u, sraw[1]);
       tmem_wait_ld();
 
       const bool full = (k0 >= row_lo && k0 + BN <= mk.pre_hi) || (k0 >= mk.kv_len && k0 + BN <= mk.can_hi) ||
                         (contiguous && k0 >= row_lo && k0 + BN <= mk.can_hi);
       if (!full) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int e = 0; e < 32; ++e)
-            if (!mask_visible_lo(mk, row_lo, k0 + c * 32 + e)) sraw[c][e] = 0xff800000u;  // -inf
+            if (!mask_visible_lo(mk, row_lo, k0 + half * 64 + c * 32 + e)) sraw[c][e] = 0xff800000u;  // -inf
       }
-      float mx = -INFINITY;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(sraw[c][e]));
+        for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sraw[c][e]));
+      const float mx_half = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // the two halves of a row agree on the row maximum through shared memory; after this barrier
+      // both have their S columns in registers, so P may overwrite either half's S columns
+      xch_max[(b * BM + r) * 2 + half] = mx_half;
+      pair_sync(smw);
+      const float mx = fmaxf(mx_half, xch_max[(b * BM + r) * 2 + (half ^ 1u)]);
       const float m_new = mx * sc;   // sc > 0; -inf stays -inf
       const bool first = (n == 0);
       const bool need = first || (m_new > m_used + RESCALE_THRESHOLD);
       if (!first && __any_sync(0xffffffffu, need)) {
-        // O holds sum p v relative to m_used: bring it to the new reference point
+        // O holds sum p v relative to m_used: bring it to the new reference point (each half of
+        // the row rescales its own 128 columns of O)
         if (!__all_sync(0xffffffffu, mbar_wait(bar_addr(bar_base, BAR_PV_DONE), (n - 1) & 1u, abort_flag))) break;
         tc_fence_after();
         const float alpha = need ? fast_exp2(m_used - m_new) : 1.0f;
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < 4; ++c) {
           uint32_t o[32];
-          tmem_ld32(t_lane + TM_O + c * 32u, o);
+          tmem_ld32(t_lane + TM_O + half * 128u + c * 32u, o);
           tmem_wait_ld();
 #pragma unroll
           for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-          tmem_st32(t_lane + TM_O + c * 32u, o);
+          tmem_st32(t_lane + TM_O + half * 128u + c * 32u, o);
         }
         tmem_wait_st();
         l_run *= alpha;
@@ -287,29 +321,26 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       if (need) m_used = m_new;
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
       const float neg_m = -m_eff;
-      float lsum = 0.f;
-      // P column j (32 bit) = keys (2j, 2j+1) as bf16x2; 64 columns overwrite the head of S
+      float ls0 = 0.f, ls1 = 0.f;
+      // P column j (32 bit) = keys (2j, 2j+1) as bf16x2: this half's 64 keys are 32 columns
+      uint32_t pk[32];
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t pk[32];
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc)
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const int c = hf * 2 + cc;
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sraw[c][e]), sc, neg_m));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sraw[c][e + 1]), sc, neg_m));
-            lsum += p0 + p1;
-            pk[cc * 16 + (e >> 1)] = pack_bf16x2(p0, p1);
-          }
-        tmem_st32(t_lane + TM_S + b * 128u + hf * 32u, pk);
-      }
-      l_run += lsum;
+        for (int e = 0; e < 32; e += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sraw[c][e]), sc, neg_m));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sraw[c][e + 1]), sc, neg_m));
+          ls0 += p0;
+          ls1 += p1;
+          pk[c * 16 + (e >> 1)] = pack_bf16x2(p0, p1);
+        }
+      l_run += ls0 + ls1;
+      tmem_st32(t_lane + TM_S + b * 128u + half * 32u, pk);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar_addr(bar_base, BAR_P_FULL0 + b));
     }
-  } else if (warp == 4) {
+  } else if (warp == WARP_K) {
     // ---------------------------------------------------------------- K loader
     if (lane == 0) {
       for (uint32_t n = 0; n < n_local; ++n) {
@@ -323,7 +354,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
           tma_load_3d(sK + a * ATOM_BYTES, &tm_k, full, int32_t(a * 64), int32_t(jt * BN), int32_t(kvh));
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == WARP_V) {
     // ---------------------------------------------------------------- V loader
     if (lane == 0) {
       for (uint32_t n = 0; n < n_local; ++n) {
@@ -383,78 +414,100 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
     }
   }
 
+  stamp(p, 3);
   // ------------------------------------------------------------------ epilogue (softmax warps)
   const uint32_t rows_total = p.C * p.Hq;
-  if (warp < 4) {
-    const uint32_t r = warp * 32 + lane;
+  if (warp < N_SM_WARPS) {
     const uint32_t R = mt * BM + r;
     const bool valid = R < rows_per_head;
     const uint32_t i_row = valid ? R / p.G : 0u;
     const uint32_t h = kvh * p.G + (valid ? R % p.G : 0u);
     const size_t orow = size_t(i_row) * p.Hq + h;
-    const uint32_t t_lane = tmem + ((warp * 32u) << 16);
+    const uint32_t t_lane = tmem + ((smw * 32u) << 16);
     bool have_o = __all_sync(0xffffffffu, n_local > 0 && !*abort_flag);
     if (have_o) {
       have_o = __all_sync(0xffffffffu, mbar_wait(bar_addr(bar_base, BAR_O_FINAL), 0u, abort_flag));
       tc_fence_after();
     }
+    // the row's denominator is the sum of the two halves' partial sums
+    xch_l[r * 2 + half] = l_run;
+    pair_sync(smw);
+    const float l_tot = xch_l[r * 2 + 0] + xch_l[r * 2 + 1];
     const bool direct = (p.n_splits == 1);
     const bool to_bf16 = direct && p.out != nullptr;
-    const float inv_l = l_run > 0.f ? 1.0f / l_run : 0.f;
+    const float inv_l = l_tot > 0.f ? 1.0f / l_tot : 0.f;
     const float mul = to_bf16 ? inv_l : 1.0f;
     float* dst_o = direct ? p.out_o : p.ws_o + size_t(split) * rows_total * HD;
+    // Each thread owns (half of) one row in TMEM, but rows are 1 KB apart in memory.  A 32 x 32
+    // chunk goes through a padded per-warp tile in shared memory (the Q tile is dead by now) so that
+    // every store instruction of the warp writes four full 128-byte lines (64-byte for bf16).
+    float* tile = reinterpret_cast<float*>(smem + OFF_Q) + warp * (32 * 36);
+    size_t orow_k[8];
+    bool valid_k[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t Rk = mt * BM + smw * 32 + k * 4 + (lane >> 3);
+      valid_k[k] = Rk < rows_per_head;
+      const uint32_t Rc = valid_k[k] ? Rk : 0u;
+      orow_k[k] = size_t(Rc / p.G) * p.Hq + kvh * p.G + Rc % p.G;
+    }
 #pragma unroll 1
-    for (int c = 0; c < 8; ++c) {
+    for (int c = 0; c < 4; ++c) {
+      const uint32_t col0 = half * 128u + c * 32u;
       uint32_t o[32];
       if (have_o) {
-        tmem_ld32(t_lane + TM_O + c * 32u, o);
+        tmem_ld32(t_lane + TM_O + col0, o);
         tmem_wait_ld();
       } else {
 #pragma unroll
         for (int e = 0; e < 32; ++e) o[e] = 0u;
       }
-      if (!valid) continue;
-      if (to_bf16) {
-        uint4* d4 = reinterpret_cast<uint4*>(p.out + orow * HD + c * 32);
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint4 w;
-          w.x = pack_bf16x2(__uint_as_float(o[q4 * 8 + 0]) * mul, __uint_as_float(o[q4 * 8 + 1]) * mul);
-          w.y = pack_bf16x2(__uint_as_float(o[q4 * 8 + 2]) * mul, __uint_as_float(o[q4 * 8 + 3]) * mul);
-          w.z = pack_bf16x2(__uint_as_float(o[q4 * 8 + 4]) * mul, __uint_as_float(o[q4 * 8 + 5]) * mul);
-          w.w = pack_bf16x2(__uint_as_float(o[q4 * 8 + 6]) * mul, __uint_as_float(o[q4 * 8 + 7]) * mul);
-          d4[q4] = w;
+      for (int q4 = 0; q4 < 8; ++q4)
+        *reinterpret_cast<float4*>(tile + lane * 36 + q4 * 4) =
+            make_float4(__uint_as_float(o[q4 * 4]) * mul, __uint_as_float(o[q4 * 4 + 1]) * mul,
+                        __uint_as_float(o[q4 * 4 + 2]) * mul, __uint_as_float(o[q4 * 4 + 3]) * mul);
+      __syncwarp();
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float4 v4 = *reinterpret_cast<const float4*>(tile + (k * 4 + (lane >> 3)) * 36 + (lane & 7) * 4);
+        if (!valid_k[k]) continue;
+        if (to_bf16) {
+          uint2 w2;
+          w2.x = pack_bf16x2(v4.x, v4.y);
+          w2.y = pack_bf16x2(v4.z, v4.w);
+          *reinterpret_cast<uint2*>(p.out + orow_k[k] * HD + col0 + (lane & 7) * 4) = w2;
+        } else {
+          *reinterpret_cast<float4*>(dst_o + orow_k[k] * HD + col0 + (lane & 7) * 4) = v4;
         }
-      } else {
-        uint4* d4 = reinterpret_cast<uint4*>(dst_o + orow * HD + c * 32);
-#pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) d4[q4] = make_uint4(o[q4 * 4], o[q4 * 4 + 1], o[q4 * 4 + 2], o[q4 * 4 + 3]);
       }
+      __syncwarp();
     }
-    if (valid && !to_bf16) {
+    if (valid && !to_bf16 && half == 0) {
       if (direct) {
         p.out_m[orow] = m_used * 0.6931471805599453f;   // log2 units -> natural units
-        p.out_l[orow] = l_run;
+        p.out_l[orow] = l_tot;
       } else {
         float2* ml = reinterpret_cast<float2*>(p.ws_ml) + size_t(split) * rows_total + orow;
-        *ml = make_float2(m_used, l_run);   // log2 units inside the workspace
+        *ml = make_float2(m_used, l_tot);   // log2 units inside the workspace
       }
     }
     if (!direct) __threadfence();
   }
 
+  stamp(p, 4);
   // ------------------------------------------------------------------ teardown
   if (*abort_flag) {
     // a bounded wait gave up: report, let our own TMA traffic land, then leave
     if (tid == 0) dev_status_set(p.status, DG_DEV_WAIT_TIMEOUT, KID_SM100, blockIdx.x + gridDim.x * blockIdx.y, n_local);
-    if (warp == 4 && lane == 0 && n_local > 0) {
+    if (warp == WARP_K && lane == 0 && n_local > 0) {
       const long long t0 = clock64();
       while (clock64() - t0 < 2000000ll) {}   // ~1 ms: far longer than any tile load in flight
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 6) tmem_dealloc(tmem, TMEM_COLS);
+  if (warp == WARP_MMA) tmem_dealloc(tmem, TMEM_COLS);
 
   // ------------------------------------------------------------------ split merge by the last CTA
   if (p.n_splits > 1) {
@@ -468,39 +521,65 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       __threadfence();
       const uint32_t S = p.n_splits;
       const float2* ml_all = reinterpret_cast<const float2*>(p.ws_ml);
-      // Each warp merges two rows per iteration and keeps up to 2 x 4 x 2 16-byte loads in flight,
-      // so the merge is bound by L2 bandwidth rather than by one round trip per row and split.
-      constexpr uint32_t NW = N_THREADS / 32;
-      for (uint32_t r0 = warp * 2; r0 < BM; r0 += NW * 2) {
-        size_t orow[2];
-        bool live[2];
-        float2 ml[2];
+      // Phase A: one thread per row turns the S (m, l) pairs into merge weights, kept in shared
+      // memory (the Q tile is dead): wsm[row][s] = 2^(m_s - m_g), plus m_g and l_g per row.
+      float* wsm = reinterpret_cast<float*>(smem + OFF_Q);            // [BM][32]
+      float* wl = wsm + BM * 32;                                        // [BM][32]
+      float* row_mg = wl + BM * 32;                                     // [BM]
+      float* row_lg = row_mg + BM;                                      // [BM]
+      if (tid < BM) {
+        const uint32_t R = mt * BM + tid;
+        const bool live = R < rows_per_head;
+        const uint32_t Rc = live ? R : mt * BM;
+        const size_t orow = size_t(Rc / p.G) * p.Hq + kvh * p.G + Rc % p.G;
+        float mg = -INFINITY;
+        for (uint32_t s0 = 0; s0 < S; s0 += 8) {
+          float2 v[8];
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
+          for (uint32_t j = 0; j < 8; ++j) {
+            const uint32_t sidx = (s0 + j < S) ? s0 + j : S - 1;
+            v[j] = ml_all[size_t(sidx) * rows_total + orow];
+          }
+#pragma unroll
+          for (uint32_t j = 0; j < 8; ++j)
+            if (s0 + j < S) {
+              wsm[tid * 32 + s0 + j] = v[j].x;                          // m_s for now
+              wl[tid * 32 + s0 + j] = v[j].y;
+              mg = fmaxf(mg, v[j].x);
+            }
+        }
+        float lg = 0.f;
+        for (uint32_t s = 0; s < S; ++s) {
+          const float ms = wsm[tid * 32 + s];
+          const float w = (ms == -INFINITY) ? 0.f : fast_exp2(ms - mg);
+          wsm[tid * 32 + s] = w;
+          lg += w * wl[tid * 32 + s];
+        }
+        row_mg[tid] = mg;
+        row_lg[tid] = lg;
+      }
+      __syncthreads();
+      // Phase B: each warp merges four rows per iteration with up to 4 x 4 x 2 16-byte loads in
+      // flight, so the pass is bound by L2 bandwidth rather than by a round trip per row and split.
+      constexpr uint32_t NW = N_THREADS / 32;
+      constexpr uint32_t RK = 4;
+      for (uint32_t r0 = warp * RK; r0 < BM; r0 += NW * RK) {
+        size_t orow[RK];
+        bool live[RK];
+        float acc[RK][8];
+#pragma unroll
+        for (uint32_t k = 0; k < RK; ++k) {
           const uint32_t R = mt * BM + r0 + k;
           live[k] = (r0 + k < BM) && (R < rows_per_head);
           const uint32_t Rc = live[k] ? R : mt * BM;
           orow[k] = size_t(Rc / p.G) * p.Hq + kvh * p.G + Rc % p.G;
-          ml[k] = make_float2(-INFINITY, 0.f);
-          if (lane < S) ml[k] = ml_all[size_t(lane) * rows_total + orow[k]];
-        }
-        float mg[2], lg[2], w_mine[2], acc[2][8];
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          mg[k] = ml[k].x;
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) mg[k] = fmaxf(mg[k], __shfl_xor_sync(0xffffffffu, mg[k], o));
-          w_mine[k] = (ml[k].x == -INFINITY) ? 0.f : fast_exp2(ml[k].x - mg[k]);
-          lg[k] = w_mine[k] * ml[k].y;
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) lg[k] += __shfl_xor_sync(0xffffffffu, lg[k], o);
 #pragma unroll
           for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
         }
         for (uint32_t s0 = 0; s0 < S; s0 += 4) {
-          float4 a[2][4], bq[2][4];
+          float4 a[RK][4], bq[RK][4];
 #pragma unroll
-          for (int k = 0; k < 2; ++k)
+          for (uint32_t k = 0; k < RK; ++k)
 #pragma unroll
             for (uint32_t j = 0; j < 4; ++j) {
               const uint32_t sidx = (s0 + j < S) ? s0 + j : S - 1;   // clamped; its weight is zeroed below
@@ -509,20 +588,21 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
               bq[k][j] = src[1];
             }
 #pragma unroll
-          for (int k = 0; k < 2; ++k)
+          for (uint32_t k = 0; k < RK; ++k)
 #pragma unroll
             for (uint32_t j = 0; j < 4; ++j) {
-              float w = __shfl_sync(0xffffffffu, w_mine[k], int((s0 + j) & 31u));
-              if (s0 + j >= S) w = 0.f;
+              const uint32_t rr = (r0 + k < BM) ? r0 + k : BM - 1;
+              const float w = (s0 + j < S) ? wsm[rr * 32 + s0 + j] : 0.f;
               acc[k][0] += w * a[k][j].x; acc[k][1] += w * a[k][j].y; acc[k][2] += w * a[k][j].z; acc[k][3] += w * a[k][j].w;
               acc[k][4] += w * bq[k][j].x; acc[k][5] += w * bq[k][j].y; acc[k][6] += w * bq[k][j].z; acc[k][7] += w * bq[k][j].w;
             }
         }
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
+        for (uint32_t k = 0; k < RK; ++k) {
           if (!live[k]) continue;
+          const float lg = row_lg[r0 + k], mg = row_mg[r0 + k];
           if (p.out) {
-            const float inv = lg[k] > 0.f ? 1.0f / lg[k] : 0.f;
+            const float inv = lg > 0.f ? 1.0f / lg : 0.f;
             uint4 w4;
             w4.x = pack_bf16x2(acc[k][0] * inv, acc[k][1] * inv);
             w4.y = pack_bf16x2(acc[k][2] * inv, acc[k][3] * inv);
@@ -534,8 +614,8 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
             dst[0] = make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
             dst[1] = make_float4(acc[k][4], acc[k][5], acc[k][6], acc[k][7]);
             if (lane == 0) {
-              p.out_m[orow[k]] = mg[k] * 0.6931471805599453f;
-              p.out_l[orow[k]] = lg[k];
+              p.out_m[orow[k]] = mg * 0.6931471805599453f;
+              p.out_l[orow[k]] = lg;
             }
           }
         }
@@ -543,6 +623,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       if (tid == 0) p.ws_counters[blockIdx.x] = 0u;   // ready for the next launch
     }
   }
+  stamp(p, 5);
 }
 
 cudaError_t sm100_attn_configure() {

@@ -121,6 +121,7 @@ struct AttnParams {
   float* ws_ml;                  // split workspace [n_splits][C*Hq][2]
   uint32_t* ws_counters;         // one per query tile, zero between launches
   DevStatus* status;
+  unsigned long long* stamps;    // optional per-CTA phase time stamps [CTAs][8] (ns), null = off
   uint64_t cap;
   MaskParams mask;
   uint32_t C, Hq, Hkv, G, D;

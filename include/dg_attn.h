@@ -211,6 +211,10 @@ uint32_t dg_ctx_last_launch_count(const dg_ctx* ctx);
  * bracketed by a CUDA event pair on the launching stream, up to max_launches launches;
  * dg_ctx_kernel_time synchronises and returns their summed duration and count.                  */
 int32_t dg_ctx_kernel_timing(dg_ctx* ctx, int32_t on, uint32_t max_launches);
+/* Measurement aid: with a non-NULL device buffer of CTAs x 8 uint64, thread 0 of every CTA of the
+ * tensor-path kernel stores globaltimer stamps (ns) at its phase boundaries: 0 start, 1 set-up done,
+ * 2 Q prologue done, 3 key loop done, 4 epilogue done, 5 merge done.  NULL switches it off.       */
+int32_t dg_ctx_phase_stamps(dg_ctx* ctx, void* device_buffer);
 int32_t dg_ctx_kernel_time(dg_ctx* ctx, double* total_ms, uint32_t* launches);
 
 #ifdef __cplusplus
