@@ -172,10 +172,11 @@ static uint32_t choose_splits(const dg_ctx* ctx, uint32_t q_tiles, uint32_t k_ti
   const uint32_t sms = ctx->num_sms > 0 ? uint32_t(ctx->num_sms) : 148u;
   uint32_t best = 1;
   uint64_t best_cost = ~0ull;
-  for (uint32_t s = 1; s <= smax; ++s) {
+  // automatic choice: powers of two up to 8, the split counts that merge inside a cluster
+  for (uint32_t s = 1; s <= smax && s <= 8; s *= 2) {
     const uint64_t waves = (uint64_t(q_tiles) * s + sms - 1) / sms;
     // fixed cost of a CTA (set-up, Q prologue, epilogue) and of the merge, in key-tile units
-    const uint64_t per = (k_tiles + s - 1) / s + 8 + (s > 1 ? 2 + s / 2 : 0);
+    const uint64_t per = (k_tiles + s - 1) / s + 6 + (s > 1 ? 2 : 0);
     const uint64_t cost = waves * per;
     if (cost < best_cost) {
       best_cost = cost;
@@ -578,7 +579,8 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
   const uint32_t k_tiles = sm100_key_tiles(p.mask);
   if (q_tiles > kMaxQueryTiles) return fail(DG_ERR_UNSUPPORTED, "too many query tiles");
   p.n_splits = choose_splits(c, q_tiles, k_tiles);
-  if (p.n_splits > 1) {
+  p.cluster_merge = (p.n_splits == 2 || p.n_splits == 4 || p.n_splits == 8) ? 1u : 0u;
+  if (p.n_splits > 1 && !p.cluster_merge) {
     const int32_t r = ensure_split_ws(c, p.n_splits, p.C * p.Hq);
     if (r != DG_OK) return r;
     p.ws_o = c->ws_o;

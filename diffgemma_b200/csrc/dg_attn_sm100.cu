@@ -10,8 +10,11 @@
 //   * online softmax in registers, two threads per query row (64 key columns each, so that every
 //     scheduler has two softmax warps to hide instruction latency), with lazy rescaling of O (only
 //     when the running maximum grows by more than 2^8).
-//   * intra-GPU split-KV: grid.y CTAs share one query tile, each writes an (O, m, l) partial and
-//     the last one to finish merges them (log-sum-exp) - no second launch.
+//   * intra-GPU split-KV: grid.y CTAs share one query tile.  For 2, 4 or 8 splits they form a
+//     thread-block cluster: each keeps its (O, m, l) partial in shared memory and, after a cluster
+//     barrier, merges its share of the rows by reading the peers' partials through distributed
+//     shared memory.  Other split counts write partials to a global workspace and the last CTA to
+//     finish merges them.  Either way there is no second launch.
 //
 // Query rows are the GQA-stacked rows of one KV head: stacked row R -> canvas row R / G, query
 // head kvh*G + R % G, so all 128 rows of a CTA reuse the same K/V tiles.
@@ -40,6 +43,7 @@ constexpr uint32_t OFF_K = TILE_BYTES;
 constexpr uint32_t OFF_V = 2 * TILE_BYTES;
 constexpr uint32_t OFF_BAR = 3 * TILE_BYTES;
 constexpr uint32_t OFF_XCH = OFF_BAR + 256;             // pair-exchange scratch (4 KB)
+constexpr uint32_t OBUF_LD = 260;                       // floats per row of the on-chip partial (padded 256)
 constexpr uint32_t SMEM_BYTES = OFF_XCH + 4096 + 1024;  // + alignment slack
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TM_S = 0;            // two S buffers of 128 columns
@@ -166,6 +170,10 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = ctl[0];
+  // Programmatic dependent launch: everything above overlapped the tail of the preceding kernel
+  // on the stream (the canvas K/V append, which also writes the RoPE table); its results are
+  // needed from here on.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   stamp(p, 1);
   volatile uint32_t* abort_flag = &ctl[1];
 
@@ -434,6 +442,29 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
     pair_sync(smw);
     const float l_tot = xch_l[r * 2 + 0] + xch_l[r * 2 + 1];
     const bool direct = (p.n_splits == 1);
+    const bool via_dsmem = (p.cluster_merge != 0u) && !direct;
+    if (via_dsmem) {
+      // The partial stays on chip: un-normalised O rows go to a padded tile in this CTA's shared
+      // memory (Q, K and V tiles are dead) and (m, l) beside it; the cluster merges them below.
+      float* obuf = reinterpret_cast<float*>(smem + OFF_Q);           // [BM][OBUF_LD]
+      float2* mlbuf = reinterpret_cast<float2*>(smem + OFF_XCH);      // [BM] (pair-exchange scratch is dead)
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        const uint32_t col0 = half * 128u + c * 32u;
+        uint32_t o[32];
+        if (have_o) {
+          tmem_ld32(t_lane + TM_O + col0, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = 0u;
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4)
+          *reinterpret_cast<uint4*>(obuf + r * OBUF_LD + col0 + q4 * 4) = make_uint4(o[q4 * 4], o[q4 * 4 + 1], o[q4 * 4 + 2], o[q4 * 4 + 3]);
+      }
+      if (half == 0) mlbuf[r] = make_float2(m_used, l_tot);
+    } else {
     const bool to_bf16 = direct && p.out != nullptr;
     const float inv_l = l_tot > 0.f ? 1.0f / l_tot : 0.f;
     const float mul = to_bf16 ? inv_l : 1.0f;
@@ -493,6 +524,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       }
     }
     if (!direct) __threadfence();
+    }   // !via_dsmem
   }
 
   stamp(p, 4);
@@ -509,8 +541,73 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   __syncthreads();
   if (warp == WARP_MMA) tmem_dealloc(tmem, TMEM_COLS);
 
-  // ------------------------------------------------------------------ split merge by the last CTA
-  if (p.n_splits > 1) {
+  // ------------------------------------------------------------------ split merge inside the cluster
+  if (p.n_splits > 1 && p.cluster_merge) {
+    // The n_splits CTAs of this query tile are one thread-block cluster (cluster dims (1, S, 1)).
+    // Each holds its partial in shared memory; after the cluster barrier CTA k merges rows
+    // [k*BM/S, (k+1)*BM/S), reading the S partial rows through distributed shared memory.
+    const uint32_t S = p.n_splits;
+    cluster_sync_all();
+    const uint32_t rank = cluster_ctarank();
+    const uint32_t rpc = BM / S;
+    const uint32_t obuf_s = smem_base + OFF_Q, ml_s = smem_base + OFF_XCH;
+    for (uint32_t rl = warp; rl < rpc; rl += N_THREADS / 32) {
+      const uint32_t rr = rank * rpc + rl;
+      const uint32_t R = mt * BM + rr;
+      if (R >= rows_per_head) continue;
+      const size_t orow = size_t(R / p.G) * p.Hq + kvh * p.G + R % p.G;
+      float2 ml = make_float2(-INFINITY, 0.f);
+      if (lane < S) ml = dsmem_ld_f2(dsmem_addr(ml_s + rr * 8u, lane));
+      float mg = ml.x;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, o));
+      const float w_mine = (ml.x == -INFINITY) ? 0.f : fast_exp2(ml.x - mg);
+      float lg = w_mine * ml.y;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) lg += __shfl_xor_sync(0xffffffffu, lg, o);
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      const uint32_t row_off = obuf_s + (rr * OBUF_LD + lane * 8u) * 4u;
+      for (uint32_t s0 = 0; s0 < S; s0 += 4) {
+        float4 a[4], bq[4];
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {
+          const uint32_t src = (s0 + j < S) ? s0 + j : S - 1;
+          const uint32_t ra = dsmem_addr(row_off, src);
+          a[j] = dsmem_ld_f4(ra);
+          bq[j] = dsmem_ld_f4(ra + 16u);
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {
+          float w = __shfl_sync(0xffffffffu, w_mine, int((s0 + j) & 31u));
+          if (s0 + j >= S) w = 0.f;
+          acc[0] += w * a[j].x; acc[1] += w * a[j].y; acc[2] += w * a[j].z; acc[3] += w * a[j].w;
+          acc[4] += w * bq[j].x; acc[5] += w * bq[j].y; acc[6] += w * bq[j].z; acc[7] += w * bq[j].w;
+        }
+      }
+      if (p.out) {
+        const float inv = lg > 0.f ? 1.0f / lg : 0.f;
+        uint4 w4;
+        w4.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
+        w4.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
+        w4.z = pack_bf16x2(acc[4] * inv, acc[5] * inv);
+        w4.w = pack_bf16x2(acc[6] * inv, acc[7] * inv);
+        *reinterpret_cast<uint4*>(p.out + orow * HD + lane * 8) = w4;
+      } else {
+        float4* dst = reinterpret_cast<float4*>(p.out_o + orow * HD + lane * 8);
+        dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        if (lane == 0) {
+          p.out_m[orow] = mg * 0.6931471805599453f;
+          p.out_l[orow] = lg;
+        }
+      }
+    }
+    // no CTA may leave while a peer can still read its shared memory
+    cluster_sync_all();
+  } else if (p.n_splits > 1) {
+    // ---------------------------------------------------------------- split merge by the last CTA
     if (tid == 0) {
       __threadfence();
       const uint32_t old = atomicAdd(p.ws_counters + blockIdx.x, 1u);
@@ -640,8 +737,28 @@ uint32_t sm100_key_tiles(const MaskParams& mk) {
 cudaError_t launch_attn_sm100(const AttnParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
                               cudaStream_t st) {
   const dim3 grid(sm100_query_tiles(p.C, p.G, p.Hkv), p.n_splits);
-  dg_attn_sm100_kernel<<<grid, N_THREADS, SMEM_BYTES, st>>>(p, tm_k, tm_v);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(N_THREADS);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  unsigned n_attr = 0;
+  // start while the preceding kernel on the stream drains; the kernel waits (griddepcontrol.wait)
+  // before it touches anything that kernel wrote
+  attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+  ++n_attr;
+  if (p.cluster_merge && p.n_splits > 1) {
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = 1;
+    attr[n_attr].val.clusterDim.y = p.n_splits;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n_attr;
+  return cudaLaunchKernelEx(&cfg, dg_attn_sm100_kernel, p, tm_k, tm_v);
 }
 
 }  // namespace dg

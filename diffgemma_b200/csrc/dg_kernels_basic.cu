@@ -27,6 +27,9 @@ __device__ __forceinline__ float warp_max(float v) {
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(32) dg_append_kernel(const AppendParams p, const RopeParams rp) {
   __shared__ float xs[kMaxHeadDim];
+  // let a dependent kernel (the attention launch that follows on the stream) begin its set-up now;
+  // it synchronises on this grid's completion before it reads the cache or the RoPE table
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const uint32_t tok = blockIdx.x, slot = blockIdx.y, lane = threadIdx.x;
   const uint32_t D = p.D;
   const uint32_t pos = p.pos0 + tok;
