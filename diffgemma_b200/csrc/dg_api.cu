@@ -66,6 +66,7 @@ struct dg_ctx {
   float* nccl_mg = nullptr;            // [rows]
   size_t nccl_rows = 0, nccl_d = 0;
   int force_general = 0;
+  int pair_mode = 0;                   // 1: CTA-pair (cta_group::2) kernel on the tensor path
   uint32_t forced_splits = 0;
   uint32_t last_launches = 0;
   // optional per-launch timing of the attention kernel (event pairs on the launching stream)
@@ -83,6 +84,7 @@ struct dg_kv {
   uint32_t Hkv = 0, D = 0;
   bool has_tmap = false;
   CUtensorMap tm_k, tm_v;
+  CUtensorMap tm_k64;   // K with 64-key boxes (CTA-pair kernel: each CTA stages half of a key tile)
 };
 
 constexpr uint32_t kRopeSlots = 8;
@@ -106,12 +108,12 @@ static PFN_encodeTiled get_encode_fn() {
   return fn;
 }
 
-static int32_t make_kv_tmap(CUtensorMap* tm, void* base, uint64_t cap, uint32_t Hkv) {
+static int32_t make_kv_tmap(CUtensorMap* tm, void* base, uint64_t cap, uint32_t Hkv, uint32_t box_keys = 128) {
   PFN_encodeTiled enc = get_encode_fn();
   if (!enc) return fail(DG_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
   const cuuint64_t dims[3] = {256, cap, Hkv};
   const cuuint64_t strides[2] = {256 * 2, cap * 256 * 2};   // bytes, dims 1 and 2
-  const cuuint32_t box[3] = {64, 128, 1};                    // 128 B x 128 keys
+  const cuuint32_t box[3] = {64, box_keys, 1};               // 128 B x box_keys keys
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -173,7 +175,8 @@ static uint32_t choose_splits(const dg_ctx* ctx, uint32_t q_tiles, uint32_t k_ti
   uint32_t best = 1;
   uint64_t best_cost = ~0ull;
   // automatic choice: powers of two up to 8, the split counts that merge inside a cluster
-  for (uint32_t s = 1; s <= smax && s <= 8; s *= 2) {
+  const uint32_t auto_max = ctx->pair_mode ? 4u : 8u;   // cluster = pair x splits must stay <= 8 CTAs
+  for (uint32_t s = 1; s <= smax && s <= auto_max; s *= 2) {
     const uint64_t waves = (uint64_t(q_tiles) * s + sms - 1) / sms;
     // fixed cost of a CTA (set-up, Q prologue, epilogue) and of the merge, in key-tile units
     const uint64_t per = (k_tiles + s - 1) / s + 6 + (s > 1 ? 2 : 0);
@@ -271,6 +274,7 @@ extern "C" int32_t dg_ctx_create(int32_t device, dg_ctx** out) {
   if (e == cudaSuccess) e = cudaMalloc(&c->counters, kMaxQueryTiles * sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaMemset(c->counters, 0, kMaxQueryTiles * sizeof(uint32_t));
   if (e == cudaSuccess) e = sm100_attn_configure();
+  if (e == cudaSuccess) e = sm100_pair_configure();
   if (e != cudaSuccess) {
     dg_ctx_destroy(c);
     return fail_cuda(e, "dg_ctx_create");
@@ -340,6 +344,16 @@ extern "C" int32_t dg_uses_tensor_path(const dg_layer_desc* d) {
 extern "C" int32_t dg_ctx_force_general(dg_ctx* c, int32_t on) {
   if (!c) return fail(DG_ERR_INVALID_ARG, "ctx is NULL");
   c->force_general = on ? 1 : 0;
+  return DG_OK;
+}
+extern "C" int32_t dg_ctx_max_active_clusters(dg_ctx* c, int32_t pair, uint32_t cluster_y) {
+  if (!c) return fail(DG_ERR_INVALID_ARG, "ctx is NULL");
+  cudaSetDevice(c->device);
+  return pair ? sm100_pair_max_active_clusters(cluster_y) : sm100_max_active_clusters(cluster_y);
+}
+extern "C" int32_t dg_ctx_set_pair_mode(dg_ctx* c, int32_t on) {
+  if (!c) return fail(DG_ERR_INVALID_ARG, "ctx is NULL");
+  c->pair_mode = on ? 1 : 0;
   return DG_OK;
 }
 extern "C" int32_t dg_ctx_set_splits(dg_ctx* c, uint32_t n) {
@@ -413,6 +427,7 @@ extern "C" int32_t dg_kv_create(dg_ctx* c, const dg_layer_desc* d, uint64_t capa
   if (kv->D == 256) {
     r = make_kv_tmap(&kv->tm_k, kv->k, kv->cap, kv->Hkv);
     if (r == DG_OK) r = make_kv_tmap(&kv->tm_v, kv->v, kv->cap, kv->Hkv);
+    if (r == DG_OK) r = make_kv_tmap(&kv->tm_k64, kv->k, kv->cap, kv->Hkv, 64);
     if (r != DG_OK) {
       dg_kv_destroy(kv);
       return r;
@@ -575,11 +590,12 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
     c->last_launches += 1;
     return DG_OK;
   }
-  const uint32_t q_tiles = sm100_query_tiles(p.C, p.G, p.Hkv);
+  const bool pair = c->pair_mode != 0;
+  const uint32_t q_tiles = pair ? sm100_pair_query_tiles(p.C, p.G, p.Hkv) : sm100_query_tiles(p.C, p.G, p.Hkv);
   const uint32_t k_tiles = sm100_key_tiles(p.mask);
   if (q_tiles > kMaxQueryTiles) return fail(DG_ERR_UNSUPPORTED, "too many query tiles");
   p.n_splits = choose_splits(c, q_tiles, k_tiles);
-  p.cluster_merge = (p.n_splits == 2 || p.n_splits == 4 || p.n_splits == 8) ? 1u : 0u;
+  p.cluster_merge = (p.n_splits == 2 || p.n_splits == 4 || (!pair && p.n_splits == 8)) ? 1u : 0u;
   if (p.n_splits > 1 && !p.cluster_merge) {
     const int32_t r = ensure_split_ws(c, p.n_splits, p.C * p.Hq);
     if (r != DG_OK) return r;
@@ -589,7 +605,8 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
   }
   const bool timed = c->timing && c->ev_used + 2 <= c->ev.size();
   if (timed) DG_CUDA(cudaEventRecord(c->ev[c->ev_used], c->stream));
-  const cudaError_t e = launch_attn_sm100(p, kv->tm_k, kv->tm_v, c->stream);
+  const cudaError_t e = pair ? launch_attn_sm100_pair(p, kv->tm_k64, kv->tm_v, c->stream)
+                             : launch_attn_sm100(p, kv->tm_k, kv->tm_v, c->stream);
   if (e != cudaSuccess) return fail_cuda(e, "launch_attn_sm100");
   if (timed) {
     DG_CUDA(cudaEventRecord(c->ev[c->ev_used + 1], c->stream));

@@ -24,6 +24,13 @@ cudaError_t sm100_attn_configure();   // one-time cudaFuncSetAttribute
 cudaError_t launch_attn_sm100(const AttnParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
                               cudaStream_t st);
 uint32_t sm100_query_tiles(uint32_t C, uint32_t G, uint32_t Hkv);   // CTAs in grid.x
+// CTA-pair variant (cta_group::2): tm_k64 is the K tensor map with box {64, 64, 1}
+cudaError_t sm100_pair_configure();
+cudaError_t launch_attn_sm100_pair(const AttnParams& p, const CUtensorMap& tm_k64, const CUtensorMap& tm_v,
+                                   cudaStream_t st);
+uint32_t sm100_pair_query_tiles(uint32_t C, uint32_t G, uint32_t Hkv);
+int sm100_max_active_clusters(uint32_t cluster_y);        // single-CTA kernel, clusters (1, y, 1)
+int sm100_pair_max_active_clusters(uint32_t cluster_y);   // pair kernel, clusters (2, y, 1)
 uint32_t sm100_key_tiles(const MaskParams& mk);                     // upper bound of key tiles per CTA
 
 }  // namespace dg

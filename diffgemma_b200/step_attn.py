@@ -86,6 +86,9 @@ class Context:
     def force_general(self, on: bool) -> None:
         check(self.lib.dg_ctx_force_general(self.h, int(on)), "dg_ctx_force_general")
 
+    def set_pair_mode(self, on: bool) -> None:
+        check(self.lib.dg_ctx_set_pair_mode(self.h, int(on)), "dg_ctx_set_pair_mode")
+
     def set_splits(self, n: int) -> None:
         check(self.lib.dg_ctx_set_splits(self.h, n), "dg_ctx_set_splits")
 

@@ -101,6 +101,12 @@ int32_t dg_uses_tensor_path(const dg_layer_desc* desc);
 /* Force the general (CUDA-core) kernel for every geometry (1) or restore the default (0).
  * Used by tests to cross-check the two kernels.                                                */
 int32_t dg_ctx_force_general(dg_ctx* ctx, int32_t on);
+/* Select the tensor-path kernel variant: 0 = one CTA per query tile, 1 = CTA pairs
+ * (tcgen05 cta_group::2: two query tiles share every staged K/V tile).                          */
+int32_t dg_ctx_set_pair_mode(dg_ctx* ctx, int32_t on);
+/* Number of thread-block clusters of the tensor-path kernel (pair = 0: (1, cluster_y, 1) CTAs,
+ * pair = 1: (2, cluster_y, 1) CTAs) that can be resident on the device at once; negative on error. */
+int32_t dg_ctx_max_active_clusters(dg_ctx* ctx, int32_t pair, uint32_t cluster_y);
 /* Override the number of key splits per query tile on the tensor path (0 = automatic).         */
 int32_t dg_ctx_set_splits(dg_ctx* ctx, uint32_t n_splits);
 
