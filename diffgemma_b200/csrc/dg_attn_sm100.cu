@@ -32,9 +32,27 @@ namespace dg {
 
 using namespace sm100;
 
-__global__ void __launch_bounds__(N_THREADS, 1)
+// Single-CTA kernel: four softmax warpgroups.  Warps w, w+4, w+8, w+12 share the 32 query rows of
+// TMEM quadrant w & 3; warpgroup q = w >> 2 handles key columns [32 q, 32 q + 32) of every tile, so
+// each scheduler has four softmax warps in flight to hide TMEM, MUFU and barrier latency.
+namespace one {
+constexpr uint32_t NTR = 4;                       // threads per query row
+constexpr uint32_t SM_WARPS = 4 * NTR;            // 16 softmax warps
+constexpr uint32_t W_K = SM_WARPS, W_V = SM_WARPS + 1, W_MMA = SM_WARPS + 2;
+constexpr uint32_t THREADS = (SM_WARPS + 3) * 32;   // 608
+constexpr uint32_t CPT = BN / NTR;                // 32 key columns per thread
+constexpr uint32_t OPT = HD / NTR;                // 64 output columns per thread
+}  // namespace one
+
+// named barrier of the NTR warps that own the same 32 query rows
+__device__ __forceinline__ void row_group_sync(uint32_t smw) {
+  asm volatile("bar.sync %0, %1;" ::"r"(smw + 1u), "n"(one::NTR * 32) : "memory");
+}
+
+__global__ void __launch_bounds__(one::THREADS, 1)
 dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v) {
+  using namespace one;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -42,9 +60,9 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   const uint32_t bar_base = smem_base + OFF_BAR;
   volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + N_BARS * 8);
   // ctl[0] = TMEM base address, ctl[1] = abort flag, ctl[2] = "this CTA merges" flag
-  float* xch_max = reinterpret_cast<float*>(smem + OFF_XCH);   // [2 tile parities][BM][2 halves]
-  float* xch_misc = xch_max + 2 * BM * 2;                       // [BM][2]: prologue sums of squares
-  float* xch_l = xch_misc + BM * 2;                             // [BM][2]: final softmax denominators
+  float* xch_max = reinterpret_cast<float*>(smem + OFF_XCH);   // [2 tile parities][BM][NTR]
+  float* xch_misc = xch_max + 2 * BM * NTR;                     // [BM][NTR]: prologue sums of squares
+  float* xch_l = xch_misc + BM * NTR;                           // [BM][NTR]: final softmax denominators
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t tiles_per_head = (p.C * p.G + BM - 1) / BM;
@@ -64,26 +82,26 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   stamp(p, 0);
   // ------------------------------------------------------------------ set-up
   if (tid == 0) {
-    mbar_init(bar_addr(bar_base, BAR_Q), N_SM_WARPS);          // one arrival per softmax warp
+    mbar_init(bar_addr(bar_base, BAR_Q), SM_WARPS);          // one arrival per softmax warp
     mbar_init(bar_addr(bar_base, BAR_K_FULL), 1);
     mbar_init(bar_addr(bar_base, BAR_K_EMPTY), 1);
     mbar_init(bar_addr(bar_base, BAR_V_FULL), 1);
     mbar_init(bar_addr(bar_base, BAR_V_EMPTY), 1);
     mbar_init(bar_addr(bar_base, BAR_S_FULL0), 1);
     mbar_init(bar_addr(bar_base, BAR_S_FULL0 + 1), 1);
-    mbar_init(bar_addr(bar_base, BAR_P_FULL0), N_SM_WARPS);
-    mbar_init(bar_addr(bar_base, BAR_P_FULL0 + 1), N_SM_WARPS);
+    mbar_init(bar_addr(bar_base, BAR_P_FULL0), SM_WARPS);
+    mbar_init(bar_addr(bar_base, BAR_P_FULL0 + 1), SM_WARPS);
     mbar_init(bar_addr(bar_base, BAR_PV_DONE), 1);
     mbar_init(bar_addr(bar_base, BAR_O_FINAL), 1);
     ctl[1] = 0u;
     ctl[2] = 0u;
     fence_mbar_init();
   }
-  if (warp == WARP_MMA) {
+  if (warp == W_MMA) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(&ctl[0])), TMEM_COLS);
     tmem_relinquish();
   }
-  if ((warp == WARP_K || warp == WARP_V) && lane == 0) tma_prefetch_desc(warp == WARP_K ? &tm_k : &tm_v);
+  if ((warp == W_K || warp == W_V) && lane == 0) tma_prefetch_desc(warp == W_K ? &tm_k : &tm_v);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -95,39 +113,40 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   stamp(p, 1);
   volatile uint32_t* abort_flag = &ctl[1];
 
-  // softmax-thread geometry: TMEM quadrant smw, row r of the query tile, column half
-  const uint32_t smw = warp & 3u, half = (warp >> 2) & 1u;
+  // softmax-thread geometry: TMEM quadrant smw, row r of the query tile, column quarter qd
+  const uint32_t smw = warp & 3u, qd = (warp >> 2) & (NTR - 1u);
   const uint32_t r = smw * 32 + lane;
-  // per-row softmax state (identical in both threads of a row, except l_run which is per half)
+  // per-row softmax state (identical in every thread of a row, except l_run which is per quarter)
   float m_used = -INFINITY, l_run = 0.f;
 
-  if (warp < N_SM_WARPS) {
-    // ---------------------------------------------------------------- Q prologue (two threads per row)
-    // Thread (row, half) owns the RoPE pairs (d, d+128) with d in [64*half, 64*half + 64): eight
-    // 16-byte chunks from each half of the row.  No shuffles; the two partial sums of squares meet
-    // through shared memory.
+  if (warp < SM_WARPS) {
+    // ---------------------------------------------------------------- Q prologue (four threads per row)
+    // Thread (row, qd) owns the RoPE pairs (d, d+128) with d in [32 qd, 32 qd + 32): four 16-byte
+    // chunks from each half of the row.  No shuffles; the partial sums of squares meet through
+    // shared memory.
     {
+      constexpr int NJ = 16 / NTR;
       const uint32_t R = mt * BM + r;
       const bool valid = R < rows_per_head;
       const uint32_t i = valid ? R / p.G : 0u;
       const uint32_t h = kvh * p.G + (valid ? R % p.G : 0u);
       const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t(i) * p.Hq + h) * HD);
       const bool do_norm = !p.q_prenormed;
-      uint4 lo[8], hi[8];
+      uint4 lo[NJ], hi[NJ];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        lo[j] = src[half * 8 + j];
-        hi[j] = src[16 + half * 8 + j];
+      for (int j = 0; j < NJ; ++j) {
+        lo[j] = src[qd * NJ + j];
+        hi[j] = src[16 + qd * NJ + j];
       }
       if (!valid) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) lo[j] = hi[j] = make_uint4(0u, 0u, 0u, 0u);
+        for (int j = 0; j < NJ; ++j) lo[j] = hi[j] = make_uint4(0u, 0u, 0u, 0u);
       }
       float inv = 1.0f;
       if (do_norm) {
         float ss0 = 0.f, ss1 = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < NJ; ++j) {
           const uint32_t a[4] = {lo[j].x, lo[j].y, lo[j].z, lo[j].w};
           const uint32_t b[4] = {hi[j].x, hi[j].y, hi[j].z, hi[j].w};
 #pragma unroll
@@ -138,15 +157,17 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
             ss1 += b0 * b0 + b1 * b1;
           }
         }
-        xch_misc[r * 2 + half] = ss0 + ss1;
-        pair_sync(smw);
-        const float ss = xch_misc[r * 2 + 0] + xch_misc[r * 2 + 1];
+        xch_misc[r * NTR + qd] = ss0 + ss1;
+        row_group_sync(smw);
+        float ss = 0.f;
+#pragma unroll
+        for (uint32_t k = 0; k < NTR; ++k) ss += xch_misc[r * NTR + k];   // same order in every thread
         inv = 1.0f / sqrtf(ss / float(HD) + p.eps);
       }
-      const float4* tab = reinterpret_cast<const float4*>(p.rope_table + size_t(i) * 128 + half * 64);
+      const float4* tab = reinterpret_cast<const float4*>(p.rope_table + size_t(i) * 128 + qd * (8 * NJ));
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint32_t c_lo = half * 8 + j, c_hi = c_lo + 16;
+      for (int j = 0; j < NJ; ++j) {
+        const uint32_t c_lo = qd * NJ + j, c_hi = c_lo + 16;
         uint4 out_lo = lo[j], out_hi = hi[j];
         if (do_norm) {
           uint4 wl4 = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u), wh4 = wl4;   // bf16 1.0
@@ -200,48 +221,45 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       // warp-uniform outcome: the TMEM instructions below need the whole warp
       if (!__all_sync(0xffffffffu, mbar_wait(bar_addr(bar_base, BAR_S_FULL0 + b), (n >> 1) & 1u, abort_flag))) break;
       tc_fence_after();
-      uint32_t sraw[2][32];
-      tmem_ld32(t_lane + TM_S + b * 128u + half * 64u, sraw[0]);
-      tmem_ld32(t_lane + TM_S + b * 128u + half * 64u + 32u, sraw[1]);
+      uint32_t sraw[32];
+      tmem_ld32(t_lane + TM_S + b * 128u + qd * CPT, sraw);
       tmem_wait_ld();
 
       const bool full = (k0 >= row_lo && k0 + BN <= mk.pre_hi) || (k0 >= mk.kv_len && k0 + BN <= mk.can_hi) ||
                         (contiguous && k0 >= row_lo && k0 + BN <= mk.can_hi);
       if (!full) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (!mask_visible_lo(mk, row_lo, k0 + half * 64 + c * 32 + e)) sraw[c][e] = 0xff800000u;  // -inf
+        for (int e = 0; e < 32; ++e)
+          if (!mask_visible_lo(mk, row_lo, k0 + qd * CPT + e)) sraw[e] = 0xff800000u;  // -inf
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
+      for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sraw[e]));
+      const float mx_part = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // the threads of a row agree on the row maximum through shared memory; after this barrier
+      // all of them have their S columns in registers, so P may overwrite any S column
+      xch_max[(b * BM + r) * NTR + qd] = mx_part;
+      row_group_sync(smw);
+      float mx = mx_part;
 #pragma unroll
-        for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sraw[c][e]));
-      const float mx_half = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // the two halves of a row agree on the row maximum through shared memory; after this barrier
-      // both have their S columns in registers, so P may overwrite either half's S columns
-      xch_max[(b * BM + r) * 2 + half] = mx_half;
-      pair_sync(smw);
-      const float mx = fmaxf(mx_half, xch_max[(b * BM + r) * 2 + (half ^ 1u)]);
+      for (uint32_t k = 0; k < NTR; ++k) mx = fmaxf(mx, xch_max[(b * BM + r) * NTR + k]);
       const float m_new = mx * sc;   // sc > 0; -inf stays -inf
       const bool first = (n == 0);
       const bool need = first || (m_new > m_used + RESCALE_THRESHOLD);
       if (!first && __any_sync(0xffffffffu, need)) {
-        // O holds sum p v relative to m_used: bring it to the new reference point (each half of
-        // the row rescales its own 128 columns of O)
+        // O holds sum p v relative to m_used: bring it to the new reference point (each thread of
+        // the row rescales its own 64 columns of O)
         if (!__all_sync(0xffffffffu, mbar_wait(bar_addr(bar_base, BAR_PV_DONE), (n - 1) & 1u, abort_flag))) break;
         tc_fence_after();
         const float alpha = need ? fast_exp2(m_used - m_new) : 1.0f;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (uint32_t c = 0; c < OPT / 32; ++c) {
           uint32_t o[32];
-          tmem_ld32(t_lane + TM_O + half * 128u + c * 32u, o);
+          tmem_ld32(t_lane + TM_O + qd * OPT + c * 32u, o);
           tmem_wait_ld();
 #pragma unroll
           for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-          tmem_st32(t_lane + TM_O + half * 128u + c * 32u, o);
+          tmem_st32(t_lane + TM_O + qd * OPT + c * 32u, o);
         }
         tmem_wait_st();
         l_run *= alpha;
@@ -250,26 +268,24 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
       const float neg_m = -m_eff;
       float ls0 = 0.f, ls1 = 0.f;
-      // P column j (32 bit) = keys (2j, 2j+1) as bf16x2: this half's 64 keys are 32 columns
-      uint32_t pk[32];
+      // P column j (32 bit) = keys (2j, 2j+1) as bf16x2: this thread's 32 keys are 16 columns
+      uint32_t pk[16];
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sraw[c][e]), sc, neg_m));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sraw[c][e + 1]), sc, neg_m));
-          ls0 += p0;
-          ls1 += p1;
-          pk[c * 16 + (e >> 1)] = pack_bf16x2(p0, p1);
-        }
+      for (int e = 0; e < 32; e += 2) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(sraw[e]), sc, neg_m));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(sraw[e + 1]), sc, neg_m));
+        ls0 += p0;
+        ls1 += p1;
+        pk[e >> 1] = pack_bf16x2(p0, p1);
+      }
       l_run += ls0 + ls1;
-      tmem_st32(t_lane + TM_S + b * 128u + half * 32u, pk);
+      tmem_st16(t_lane + TM_S + b * 128u + qd * (CPT / 2), pk);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_addr(bar_base, BAR_P_FULL0 + b));
     }
-  } else if (warp == WARP_K) {
+  } else if (warp == W_K) {
     // ---------------------------------------------------------------- K loader
     if (lane == 0) {
       for (uint32_t n = 0; n < n_local; ++n) {
@@ -283,7 +299,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
           tma_load_3d(sK + a * ATOM_BYTES, &tm_k, full, int32_t(a * 64), int32_t(jt * BN), int32_t(kvh));
       }
     }
-  } else if (warp == WARP_V) {
+  } else if (warp == W_V) {
     // ---------------------------------------------------------------- V loader
     if (lane == 0) {
       for (uint32_t n = 0; n < n_local; ++n) {
@@ -346,7 +362,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   stamp(p, 3);
   // ------------------------------------------------------------------ epilogue (softmax warps)
   const uint32_t rows_total = p.C * p.Hq;
-  if (warp < N_SM_WARPS) {
+  if (warp < SM_WARPS) {
     const uint32_t R = mt * BM + r;
     const bool valid = R < rows_per_head;
     const uint32_t i_row = valid ? R / p.G : 0u;
@@ -358,20 +374,22 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       have_o = __all_sync(0xffffffffu, mbar_wait(bar_addr(bar_base, BAR_O_FINAL), 0u, abort_flag));
       tc_fence_after();
     }
-    // the row's denominator is the sum of the two halves' partial sums
-    xch_l[r * 2 + half] = l_run;
-    pair_sync(smw);
-    const float l_tot = xch_l[r * 2 + 0] + xch_l[r * 2 + 1];
+    // the row's denominator is the sum of its threads' partial sums
+    xch_l[r * NTR + qd] = l_run;
+    row_group_sync(smw);
+    float l_tot = 0.f;
+#pragma unroll
+    for (uint32_t k = 0; k < NTR; ++k) l_tot += xch_l[r * NTR + k];
     const bool direct = (p.n_splits == 1);
     const bool via_dsmem = (p.cluster_merge != 0u) && !direct;
     if (via_dsmem) {
       // The partial stays on chip: un-normalised O rows go to a padded tile in this CTA's shared
       // memory (Q, K and V tiles are dead) and (m, l) beside it; the cluster merges them below.
       float* obuf = reinterpret_cast<float*>(smem + OFF_Q);           // [BM][OBUF_LD]
-      float2* mlbuf = reinterpret_cast<float2*>(smem + OFF_XCH);      // [BM] (pair-exchange scratch is dead)
+      float2* mlbuf = reinterpret_cast<float2*>(smem + OFF_ML);       // [BM]
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        const uint32_t col0 = half * 128u + c * 32u;
+      for (uint32_t c = 0; c < OPT / 32; ++c) {
+        const uint32_t col0 = qd * OPT + c * 32u;
         uint32_t o[32];
         if (have_o) {
           tmem_ld32(t_lane + TM_O + col0, o);
@@ -384,13 +402,13 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
         for (int q4 = 0; q4 < 8; ++q4)
           *reinterpret_cast<uint4*>(obuf + r * OBUF_LD + col0 + q4 * 4) = make_uint4(o[q4 * 4], o[q4 * 4 + 1], o[q4 * 4 + 2], o[q4 * 4 + 3]);
       }
-      if (half == 0) mlbuf[r] = make_float2(m_used, l_tot);
+      if (qd == 0) mlbuf[r] = make_float2(m_used, l_tot);
     } else {
     const bool to_bf16 = direct && p.out != nullptr;
     const float inv_l = l_tot > 0.f ? 1.0f / l_tot : 0.f;
     const float mul = to_bf16 ? inv_l : 1.0f;
     float* dst_o = direct ? p.out_o : p.ws_o + size_t(split) * rows_total * HD;
-    // Each thread owns (half of) one row in TMEM, but rows are 1 KB apart in memory.  A 32 x 32
+    // Each thread owns a quarter of one row in TMEM, but rows are 1 KB apart in memory.  A 32 x 32
     // chunk goes through a padded per-warp tile in shared memory (the Q tile is dead by now) so that
     // every store instruction of the warp writes four full 128-byte lines (64-byte for bf16).
     float* tile = reinterpret_cast<float*>(smem + OFF_Q) + warp * (32 * 36);
@@ -404,8 +422,8 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       orow_k[k] = size_t(Rc / p.G) * p.Hq + kvh * p.G + Rc % p.G;
     }
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-      const uint32_t col0 = half * 128u + c * 32u;
+    for (uint32_t c = 0; c < OPT / 32; ++c) {
+      const uint32_t col0 = qd * OPT + c * 32u;
       uint32_t o[32];
       if (have_o) {
         tmem_ld32(t_lane + TM_O + col0, o);
@@ -435,7 +453,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       }
       __syncwarp();
     }
-    if (valid && !to_bf16 && half == 0) {
+    if (valid && !to_bf16 && qd == 0) {
       if (direct) {
         p.out_m[orow] = m_used * 0.6931471805599453f;   // log2 units -> natural units
         p.out_l[orow] = l_tot;
@@ -453,14 +471,14 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   if (*abort_flag) {
     // a bounded wait gave up: report, let our own TMA traffic land, then leave
     if (tid == 0) dev_status_set(p.status, DG_DEV_WAIT_TIMEOUT, KID_SM100, blockIdx.x + gridDim.x * blockIdx.y, n_local);
-    if (warp == WARP_K && lane == 0 && n_local > 0) {
+    if (warp == W_K && lane == 0 && n_local > 0) {
       const long long t0 = clock64();
       while (clock64() - t0 < 2000000ll) {}   // ~1 ms: far longer than any tile load in flight
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == WARP_MMA) tmem_dealloc(tmem, TMEM_COLS);
+  if (warp == W_MMA) tmem_dealloc(tmem, TMEM_COLS);
 
   // ------------------------------------------------------------------ split merge inside the cluster
   if (p.n_splits > 1 && p.cluster_merge) {
@@ -471,8 +489,8 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
     cluster_sync_all();
     const uint32_t rank = cluster_ctarank();
     const uint32_t rpc = BM / S;
-    const uint32_t obuf_s = smem_base + OFF_Q, ml_s = smem_base + OFF_XCH;
-    for (uint32_t rl = warp; rl < rpc; rl += N_THREADS / 32) {
+    const uint32_t obuf_s = smem_base + OFF_Q, ml_s = smem_base + OFF_ML;
+    for (uint32_t rl = warp; rl < rpc; rl += THREADS / 32) {
       const uint32_t rr = rank * rpc + rl;
       const uint32_t R = mt * BM + rr;
       if (R >= rows_per_head) continue;
@@ -579,8 +597,8 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       __syncthreads();
       // Phase B: each warp merges four rows per iteration with up to 4 x 4 x 2 16-byte loads in
       // flight, so the pass is bound by L2 bandwidth rather than by a round trip per row and split.
-      constexpr uint32_t NW = N_THREADS / 32;
-      constexpr uint32_t RK = 4;
+      constexpr uint32_t NW = THREADS / 32;
+      constexpr uint32_t RK = 2;
       for (uint32_t r0 = warp * RK; r0 < BM; r0 += NW * RK) {
         size_t orow[RK];
         bool live[RK];
@@ -652,7 +670,7 @@ cudaError_t sm100_attn_configure() {
 int sm100_max_active_clusters(uint32_t cluster_y) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(1, cluster_y, 148);
-  cfg.blockDim = dim3(N_THREADS);
+  cfg.blockDim = dim3(one::THREADS);
   cfg.dynamicSmemBytes = SMEM_BYTES;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -681,7 +699,7 @@ cudaError_t launch_attn_sm100(const AttnParams& p, const CUtensorMap& tm_k, cons
   const dim3 grid(sm100_query_tiles(p.C, p.G, p.Hkv), p.n_splits);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(N_THREADS);
+  cfg.blockDim = dim3(one::THREADS);
   cfg.dynamicSmemBytes = SMEM_BYTES;
   cfg.stream = st;
   cudaLaunchAttribute attr[2];

@@ -19,15 +19,16 @@ constexpr uint32_t OFF_Q = 0;
 constexpr uint32_t OFF_K = TILE_BYTES;
 constexpr uint32_t OFF_V = 2 * TILE_BYTES;
 constexpr uint32_t OFF_BAR = 3 * TILE_BYTES;
-constexpr uint32_t OFF_XCH = OFF_BAR + 256;             // pair-exchange scratch (4 KB)
+constexpr uint32_t OFF_XCH = OFF_BAR + 256;             // row-group exchange scratch (8 KB)
+constexpr uint32_t OFF_ML = OFF_XCH + 8192;             // (m, l) of the on-chip partial, [BM] float2
 constexpr uint32_t OBUF_LD = 260;                       // floats per row of the on-chip partial (padded 256)
-constexpr uint32_t SMEM_BYTES = OFF_XCH + 4096 + 1024;  // + alignment slack
+constexpr uint32_t SMEM_BYTES = OFF_ML + 1024 + 1024;   // + alignment slack
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TM_S = 0;            // two S buffers of 128 columns
 constexpr uint32_t TM_O = 256;          // O accumulator, 256 columns
-// warps 0-7: two softmax warpgroups (warp w and w+4 share the 32 query rows of TMEM quadrant w & 3;
-// the first handles key columns 0-63 of every tile, the second 64-127), 8: K loader, 9: V loader,
-// 10: TMEM allocation + the MMA-issuing thread
+// CTA-pair variant: warps 0-7 = two softmax warpgroups (warp w and w+4 share the 32 query rows of
+// TMEM quadrant w & 3; the first handles key columns 0-63 of every tile, the second 64-127),
+// 8: K loader, 9: V loader, 10: TMEM allocation + the MMA-issuing thread
 constexpr uint32_t N_SM_WARPS = 8;
 constexpr uint32_t WARP_K = 8, WARP_V = 9, WARP_MMA = 10;
 constexpr uint32_t N_THREADS = 352;
