@@ -142,6 +142,14 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
 #pragma unroll
         for (int j = 0; j < NJ; ++j) lo[j] = hi[j] = make_uint4(0u, 0u, 0u, 0u);
       }
+      // RoPE-table entries of this thread's pairs: issued now so that they arrive while the sums of
+      // squares are reduced
+      float4 tabv[NJ * 4];
+      if (do_norm) {
+        const float4* tab = reinterpret_cast<const float4*>(p.rope_table + size_t(i) * 128 + qd * (8 * NJ));
+#pragma unroll
+        for (int t = 0; t < NJ * 4; ++t) tabv[t] = tab[t];
+      }
       float inv = 1.0f;
       if (do_norm) {
         float ss0 = 0.f, ss1 = 0.f;
@@ -164,7 +172,6 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
         for (uint32_t k = 0; k < NTR; ++k) ss += xch_misc[r * NTR + k];   // same order in every thread
         inv = 1.0f / sqrtf(ss / float(HD) + p.eps);
       }
-      const float4* tab = reinterpret_cast<const float4*>(p.rope_table + size_t(i) * 128 + qd * (8 * NJ));
 #pragma unroll
       for (int j = 0; j < NJ; ++j) {
         const uint32_t c_lo = qd * NJ + j, c_hi = c_lo + 16;
@@ -182,7 +189,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
           uint32_t ya[4], yb[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float4 cs = tab[j * 4 + e];   // (cos, sin) of pairs 8*c_lo + 2e and + 2e + 1
+            const float4 cs = tabv[j * 4 + e];   // (cos, sin) of pairs 8*c_lo + 2e and + 2e + 1
             const float a0 = __uint_as_float(a[e] << 16) * (inv * __uint_as_float(wa[e] << 16));
             const float a1 = __uint_as_float(a[e] & 0xffff0000u) * (inv * __uint_as_float(wa[e] & 0xffff0000u));
             const float b0 = __uint_as_float(b[e] << 16) * (inv * __uint_as_float(wb[e] << 16));
@@ -362,6 +369,18 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   stamp(p, 3);
   // ------------------------------------------------------------------ epilogue (softmax warps)
   const uint32_t rows_total = p.C * p.Hq;
+  bool have_o = false;
+  if (warp < SM_WARPS) {
+    have_o = __all_sync(0xffffffffu, n_local > 0 && !*abort_flag);
+    if (have_o) {
+      have_o = __all_sync(0xffffffffu, mbar_wait(bar_addr(bar_base, BAR_O_FINAL), 0u, abort_flag));
+      tc_fence_after();
+    }
+  }
+  // Cluster merge: partial rows are pushed into the owner CTA's Q/K/V region, which must be dead
+  // in EVERY CTA of the cluster first - all of this CTA's MMAs are complete once its softmax
+  // warps have seen O_FINAL, and this barrier collects that from all CTAs.
+  if (p.cluster_merge && p.n_splits > 1) cluster_sync_all();
   if (warp < SM_WARPS) {
     const uint32_t R = mt * BM + r;
     const bool valid = R < rows_per_head;
@@ -369,11 +388,6 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
     const uint32_t h = kvh * p.G + (valid ? R % p.G : 0u);
     const size_t orow = size_t(i_row) * p.Hq + h;
     const uint32_t t_lane = tmem + ((smw * 32u) << 16);
-    bool have_o = __all_sync(0xffffffffu, n_local > 0 && !*abort_flag);
-    if (have_o) {
-      have_o = __all_sync(0xffffffffu, mbar_wait(bar_addr(bar_base, BAR_O_FINAL), 0u, abort_flag));
-      tc_fence_after();
-    }
     // the row's denominator is the sum of its threads' partial sums
     xch_l[r * NTR + qd] = l_run;
     row_group_sync(smw);
@@ -383,10 +397,15 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
     const bool direct = (p.n_splits == 1);
     const bool via_dsmem = (p.cluster_merge != 0u) && !direct;
     if (via_dsmem) {
-      // The partial stays on chip: un-normalised O rows go to a padded tile in this CTA's shared
-      // memory (Q, K and V tiles are dead) and (m, l) beside it; the cluster merges them below.
-      float* obuf = reinterpret_cast<float*>(smem + OFF_Q);           // [BM][OBUF_LD]
-      float2* mlbuf = reinterpret_cast<float2*>(smem + OFF_ML);       // [BM]
+      // The partial stays on chip.  Row r of the query tile is merged by CTA r / (BM / S) of the
+      // cluster, so each thread pushes its columns of the un-normalised O row (and one thread the
+      // (m, l) pair) straight into that CTA's receive buffer with remote shared-memory stores:
+      // recv[source CTA][row within the owner's share][OBUF_LD floats] in the dead Q/K/V region.
+      const uint32_t S = p.n_splits;
+      const uint32_t rpc = BM / S;
+      const uint32_t src_rank = cluster_ctarank();
+      const uint32_t owner = r / rpc, rl = r % rpc;
+      const uint32_t dst_row = dsmem_addr(smem_base + OFF_Q + ((src_rank * rpc + rl) * OBUF_LD) * 4u, owner);
 #pragma unroll 1
       for (uint32_t c = 0; c < OPT / 32; ++c) {
         const uint32_t col0 = qd * OPT + c * 32u;
@@ -400,9 +419,9 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
         }
 #pragma unroll
         for (int q4 = 0; q4 < 8; ++q4)
-          *reinterpret_cast<uint4*>(obuf + r * OBUF_LD + col0 + q4 * 4) = make_uint4(o[q4 * 4], o[q4 * 4 + 1], o[q4 * 4 + 2], o[q4 * 4 + 3]);
+          dsmem_st_u4(dst_row + (col0 + q4 * 4) * 4u, make_uint4(o[q4 * 4], o[q4 * 4 + 1], o[q4 * 4 + 2], o[q4 * 4 + 3]));
       }
-      if (qd == 0) mlbuf[r] = make_float2(m_used, l_tot);
+      if (qd == 0) dsmem_st_f2(dsmem_addr(smem_base + OFF_ML + (src_rank * rpc + rl) * 8u, owner), make_float2(m_used, l_tot));
     } else {
     const bool to_bf16 = direct && p.out != nullptr;
     const float inv_l = l_tot > 0.f ? 1.0f / l_tot : 0.f;
@@ -483,20 +502,22 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   // ------------------------------------------------------------------ split merge inside the cluster
   if (p.n_splits > 1 && p.cluster_merge) {
     // The n_splits CTAs of this query tile are one thread-block cluster (cluster dims (1, S, 1)).
-    // Each holds its partial in shared memory; after the cluster barrier CTA k merges rows
-    // [k*BM/S, (k+1)*BM/S), reading the S partial rows through distributed shared memory.
+    // Every CTA has pushed each partial row to the CTA that owns it; after the cluster barrier CTA k
+    // holds all S partials of rows [k*BM/S, (k+1)*BM/S) in its own shared memory and merges them.
+    // Nothing touches remote shared memory after the barrier, so no second barrier is needed.
     const uint32_t S = p.n_splits;
     cluster_sync_all();
     const uint32_t rank = cluster_ctarank();
     const uint32_t rpc = BM / S;
-    const uint32_t obuf_s = smem_base + OFF_Q, ml_s = smem_base + OFF_ML;
+    const float* recv = reinterpret_cast<const float*>(smem + OFF_Q);        // [S][rpc][OBUF_LD]
+    const float2* recv_ml = reinterpret_cast<const float2*>(smem + OFF_ML);  // [S][rpc]
     for (uint32_t rl = warp; rl < rpc; rl += THREADS / 32) {
       const uint32_t rr = rank * rpc + rl;
       const uint32_t R = mt * BM + rr;
       if (R >= rows_per_head) continue;
       const size_t orow = size_t(R / p.G) * p.Hq + kvh * p.G + R % p.G;
       float2 ml = make_float2(-INFINITY, 0.f);
-      if (lane < S) ml = dsmem_ld_f2(dsmem_addr(ml_s + rr * 8u, lane));
+      if (lane < S) ml = recv_ml[lane * rpc + rl];
       float mg = ml.x;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, o));
@@ -507,23 +528,12 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       float acc[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-      const uint32_t row_off = obuf_s + (rr * OBUF_LD + lane * 8u) * 4u;
-      for (uint32_t s0 = 0; s0 < S; s0 += 4) {
-        float4 a[4], bq[4];
-#pragma unroll
-        for (uint32_t j = 0; j < 4; ++j) {
-          const uint32_t src = (s0 + j < S) ? s0 + j : S - 1;
-          const uint32_t ra = dsmem_addr(row_off, src);
-          a[j] = dsmem_ld_f4(ra);
-          bq[j] = dsmem_ld_f4(ra + 16u);
-        }
-#pragma unroll
-        for (uint32_t j = 0; j < 4; ++j) {
-          float w = __shfl_sync(0xffffffffu, w_mine, int((s0 + j) & 31u));
-          if (s0 + j >= S) w = 0.f;
-          acc[0] += w * a[j].x; acc[1] += w * a[j].y; acc[2] += w * a[j].z; acc[3] += w * a[j].w;
-          acc[4] += w * bq[j].x; acc[5] += w * bq[j].y; acc[6] += w * bq[j].z; acc[7] += w * bq[j].w;
-        }
+      for (uint32_t s2 = 0; s2 < S; ++s2) {
+        const float w = __shfl_sync(0xffffffffu, w_mine, int(s2));
+        const float4* src = reinterpret_cast<const float4*>(recv + (s2 * rpc + rl) * OBUF_LD + lane * 8);
+        const float4 a = src[0], bq = src[1];
+        acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * a.z; acc[3] += w * a.w;
+        acc[4] += w * bq.x; acc[5] += w * bq.y; acc[6] += w * bq.z; acc[7] += w * bq.w;
       }
       if (p.out) {
         const float inv = lg > 0.f ? 1.0f / lg : 0.f;
@@ -543,8 +553,6 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
         }
       }
     }
-    // no CTA may leave while a peer can still read its shared memory
-    cluster_sync_all();
   } else if (p.n_splits > 1) {
     // ---------------------------------------------------------------- split merge by the last CTA
     if (tid == 0) {

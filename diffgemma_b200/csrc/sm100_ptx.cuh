@@ -101,6 +101,13 @@ __device__ __forceinline__ float4 dsmem_ld_f4(uint32_t addr) {
                : "memory");
   return v;
 }
+__device__ __forceinline__ void dsmem_st_u4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void dsmem_st_f2(uint32_t addr, float2 v) {
+  asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(v.x), "f"(v.y) : "memory");
+}
 __device__ __forceinline__ float2 dsmem_ld_f2(uint32_t addr) {
   float2 v;
   asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
