@@ -220,7 +220,7 @@ def run_ours(args):
     q, kc, vc = q_h.to(dev), kc_h.to(dev), vc_h.to(dev)
     out = torch.empty_like(q)
     att = CanvasAttention(ctx, lay)
-    group = SplitKvGroup(ctx, lay) if world > 1 else None
+    group = SplitKvGroup(ctx, lay, exchange=args.exchange) if world > 1 else None
     stream = ctx.torch_stream
 
     def step_dev(i):
@@ -302,7 +302,9 @@ def run_ours(args):
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": cfg.name, "prefix": P, "n_q_heads": lay.n_q_heads, "n_kv_heads": lay.n_kv_heads,
                        "head_dim": lay.head_dim, "canvas": lay.canvas, "mask": "all prefix visible, canvas bidirectional",
-                       "partition": "single GPU" if world == 1 else f"split-KV over {world} GPUs + NCCL LSE merge",
+                       "partition": "single GPU" if world == 1 else
+                       (f"split-KV over {world} GPUs + LSE merge over peer memory (NVLink)" if args.exchange == "p2p"
+                        else f"split-KV over {world} GPUs + NCCL LSE merge"),
                        "l2": f"steps rotate over {n_rot} KV caches ({n_rot * kv_bytes / 1e6:.0f} MB > 126 MB L2)",
                        "algorithmic_gflop_per_step": flops / 1e9},
             "pct_of_measured_bf16_peak": 100.0 * value / (peaks["bf16_tflops"] * world),
@@ -343,6 +345,7 @@ def main():
     ap.add_argument("--cfg", type=int, default=2, choices=[0, 1, 2, 4])
     ap.add_argument("--ref-rows", type=int, default=256, help="canvas rows in the bounded CPU sample")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="multi-GPU partial exchange")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

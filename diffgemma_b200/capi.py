@@ -49,6 +49,8 @@ SIGNATURES = {
     "dg_ctx_stream": (_vp, [_vp]),
     "dg_ctx_synchronize": (_i32, [_vp]),
     "dg_ctx_last_device_status": (_i32, [_vp, C.POINTER(_u32 * 4)]),
+    "dg_ctx_clear_device_status": (_i32, [_vp]),
+    "dg_ctx_selftest_wait_timeout": (_i32, [_vp, _u64]),
     "dg_status_str": (C.c_char_p, [_i32]),
     "dg_last_error_message": (C.c_char_p, []),
     "dg_uses_tensor_path": (_i32, [_pd]),
@@ -75,6 +77,11 @@ SIGNATURES = {
     "dg_nccl_comm_create": (_i32, [_vp, _vp, _i32, _i32, C.POINTER(_vp)]),
     "dg_nccl_comm_destroy": (_i32, [_vp]),
     "dg_nccl_all_gather": (_i32, [_vp, _vp, _vp, _vp, _u64]),
+    "dg_p2p_create": (_i32, [_vp, _u32, _u32, _i32, _i32, C.POINTER(_vp)]),
+    "dg_p2p_handle": (_i32, [_vp, _vp]),
+    "dg_p2p_connect": (_i32, [_vp, _vp]),
+    "dg_p2p_destroy": (_i32, [_vp]),
+    "dg_attn_denoise_split_p2p": (_i32, [_vp, _pd, _vp, _u32, _u32, _u32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dg_attn_visibility": (_i32, [_vp, _pd, _u32, _u32, _u32, _i32, _vp]),
     "dg_attn_flops": (C.c_double, [_pd, _u32]),
     "dg_ctx_last_launch_count": (_u32, [_vp]),

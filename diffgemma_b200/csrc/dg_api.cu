@@ -337,6 +337,23 @@ extern "C" int32_t dg_ctx_last_device_status(dg_ctx* c, uint32_t out[4]) {
   return DG_OK;
 }
 
+extern "C" int32_t dg_ctx_clear_device_status(dg_ctx* c) {
+  if (!c) return fail(DG_ERR_INVALID_ARG, "ctx is NULL");
+  DG_CUDA(cudaSetDevice(c->device));
+  DG_CUDA(cudaMemsetAsync(c->d_status, 0, sizeof(DevStatus), c->stream));
+  return DG_OK;
+}
+
+extern "C" int32_t dg_ctx_selftest_wait_timeout(dg_ctx* c, uint64_t limit_cycles) {
+  if (!c) return fail(DG_ERR_INVALID_ARG, "ctx is NULL");
+  if (limit_cycles == 0 || limit_cycles > 2000000000ull) return fail(DG_ERR_INVALID_ARG, "limit must be in 1..2e9 cycles");
+  DG_CUDA(cudaSetDevice(c->device));
+  // the flag is one of the (always zero between launches) query-tile counters: nothing sets it
+  launch_selftest_wait(c->counters + (kMaxQueryTiles - 1), (long long)limit_cycles, c->d_status, c->stream);
+  DG_CUDA(cudaGetLastError());
+  return DG_OK;
+}
+
 extern "C" int32_t dg_uses_tensor_path(const dg_layer_desc* d) {
   if (check_desc(d) != DG_OK) return 0;
   return tensor_path_ok(*d) ? 1 : 0;
@@ -1014,5 +1031,140 @@ extern "C" int32_t dg_attention_static_scratch(dg_ctx* c, const dg_layer_desc* d
   const cudaError_t e = launch_attn_sm100(p, kv->tm_k, kv->tm_v, c->stream);
   if (e != cudaSuccess) return fail_cuda(e, "launch_attn_sm100");
   c->last_launches = 1;
+  return DG_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Split-KV over peer memory (one process per GPU, buffers shared through CUDA IPC)
+// ------------------------------------------------------------------------------------------
+struct dg_p2p {
+  dg_ctx* ctx = nullptr;
+  uint32_t world = 0, rank = 0, rows = 0, D = 0;
+  uint8_t* local = nullptr;
+  size_t bytes = 0;
+  uint8_t* peer[8] = {};
+  bool opened[8] = {};
+  bool connected = false;
+  uint32_t step = 0;
+  P2pParams layout;
+};
+
+static void p2p_layout(dg_p2p* x) {
+  P2pParams& L = x->layout;
+  std::memset(&L, 0, sizeof(L));
+  size_t off = 0;
+  auto take = [&](size_t n) { const size_t o = off; off = (off + n + 255) & ~size_t(255); return o; };
+  for (int p = 0; p < 2; ++p) {
+    L.off_o[p] = take(size_t(x->rows) * x->D * 4);
+    L.off_m[p] = take(size_t(x->rows) * 4);
+    L.off_l[p] = take(size_t(x->rows) * 4);
+    L.off_res[p] = take(size_t(x->rows) * x->D * 2);
+  }
+  L.off_pflag = take(2 * 4);
+  L.off_rflag = take(2 * 8 * 4);
+  L.off_done = take(2 * 4);
+  x->bytes = off;
+  L.world = x->world;
+  L.rank = x->rank;
+  L.rows = x->rows;
+  L.D = x->D;
+  L.status = x->ctx->d_status;
+  L.wait_limit = 1000000000ll;
+}
+
+extern "C" int32_t dg_p2p_create(dg_ctx* c, uint32_t rows, uint32_t head_dim, int32_t world, int32_t rank, dg_p2p** out) {
+  if (!c || !out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  *out = nullptr;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(DG_ERR_INVALID_ARG, "world must be 1..8 and rank inside it");
+  if (rows == 0 || head_dim == 0 || head_dim % 8 != 0) return fail(DG_ERR_INVALID_ARG, "bad rows / head_dim");
+  DG_CUDA(cudaSetDevice(c->device));
+  dg_p2p* x = new (std::nothrow) dg_p2p();
+  if (!x) return fail(DG_ERR_INVALID_ARG, "out of host memory");
+  x->ctx = c;
+  x->world = uint32_t(world);
+  x->rank = uint32_t(rank);
+  x->rows = rows;
+  x->D = head_dim;
+  p2p_layout(x);
+  cudaError_t e = cudaMalloc(&x->local, x->bytes);
+  if (e == cudaSuccess) e = cudaMemset(x->local, 0, x->bytes);
+  if (e != cudaSuccess) {
+    delete x;
+    return fail_cuda(e, "dg_p2p_create");
+  }
+  x->peer[rank] = x->local;
+  *out = x;
+  return DG_OK;
+}
+
+extern "C" int32_t dg_p2p_handle(dg_p2p* x, uint8_t handle_out[64]) {
+  if (!x || !handle_out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "cudaIpcMemHandle_t is 64 bytes");
+  DG_CUDA(cudaSetDevice(x->ctx->device));
+  cudaIpcMemHandle_t h;
+  DG_CUDA(cudaIpcGetMemHandle(&h, x->local));
+  std::memcpy(handle_out, &h, 64);
+  return DG_OK;
+}
+
+extern "C" int32_t dg_p2p_connect(dg_p2p* x, const uint8_t* handles) {
+  if (!x || !handles) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  DG_CUDA(cudaSetDevice(x->ctx->device));
+  for (uint32_t w = 0; w < x->world; ++w) {
+    if (w == x->rank) continue;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handles + size_t(w) * 64, 64);
+    void* ptr = nullptr;
+    DG_CUDA(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    x->peer[w] = static_cast<uint8_t*>(ptr);
+    x->opened[w] = true;
+  }
+  for (uint32_t w = 0; w < 8; ++w) x->layout.peer[w] = x->peer[w < x->world ? w : x->rank];
+  x->connected = true;
+  return DG_OK;
+}
+
+extern "C" int32_t dg_p2p_destroy(dg_p2p* x) {
+  if (!x) return DG_OK;
+  cudaSetDevice(x->ctx->device);
+  cudaStreamSynchronize(x->ctx->stream);
+  for (uint32_t w = 0; w < x->world; ++w)
+    if (x->opened[w]) cudaIpcCloseMemHandle(x->peer[w]);
+  cudaFree(x->local);
+  delete x;
+  return DG_OK;
+}
+
+extern "C" int32_t dg_attn_denoise_split_p2p(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint32_t kv_len, uint32_t t0,
+                                             uint32_t t1, int32_t include_canvas, dg_p2p* x, const void* q, const void* k,
+                                             const void* v, const void* qw, const void* kw, void* out) {
+  if (!c || !x || !q || !k || !v || !out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  if (!x->connected && x->world > 1) return fail(DG_ERR_INVALID_ARG, "dg_p2p_connect has not been called");
+  int32_t r = check_desc(d);
+  if (r != DG_OK) return r;
+  if (x->rows != d->canvas * d->n_q_heads || x->D != d->head_dim) return fail(DG_ERR_INVALID_ARG, "exchange buffer geometry differs from desc");
+  r = check_ptrs16({q, k, v, qw, kw, out});
+  if (r != DG_OK) return r;
+  DG_CUDA(cudaSetDevice(c->device));
+  c->last_launches = 0;
+  x->step += 1;
+  const uint32_t par = x->step & 1u;
+  if (x->world == 1) x->layout.peer[0] = x->local;
+  AttnCall a;
+  a.out = nullptr;
+  a.out_o = reinterpret_cast<float*>(x->local + x->layout.off_o[par]);
+  a.out_m = reinterpret_cast<float*>(x->local + x->layout.off_m[par]);
+  a.out_l = reinterpret_cast<float*>(x->local + x->layout.off_l[par]);
+  a.t0 = t0;
+  a.t1 = t1;
+  a.include_canvas = include_canvas ? 1 : 0;
+  r = denoise_one(c, *d, kv, kv_len, 0, q, k, v, qw, kw, nullptr, a);
+  if (r != DG_OK) return r;
+  P2pParams pp = x->layout;
+  pp.step = x->step;
+  pp.parity = par;
+  launch_p2p_merge(pp, out, c->num_sms, c->stream);
+  DG_CUDA(cudaGetLastError());
+  c->last_launches += 1;
   return DG_OK;
 }

@@ -74,7 +74,7 @@ __device__ inline void dev_status_set(DevStatus* s, uint32_t code, uint32_t kern
   }
 }
 
-enum : uint32_t { KID_APPEND = 1, KID_GENERAL = 2, KID_SM100 = 3, KID_MERGE = 4, KID_VIS = 5 };
+enum : uint32_t { KID_APPEND = 1, KID_GENERAL = 2, KID_SM100 = 3, KID_MERGE = 4, KID_VIS = 5, KID_SELFTEST = 6 };
 
 // ----------------------------------------------------------------------------------------
 // Launch parameter blocks
@@ -131,6 +131,16 @@ struct AttnParams {
   uint32_t rot_half, pair_off;
   float scale_log2;              // softmax_scale * log2(e)
   float eps;
+};
+
+// peer-to-peer split-KV merge (dg_p2p_merge.cu)
+struct P2pParams {
+  uint8_t* peer[8];        // exchange buffer of every rank, as mapped into this process
+  size_t off_o[2], off_m[2], off_l[2], off_res[2];   // per parity
+  size_t off_pflag, off_rflag, off_done;             // u32 pflag[2], rflag[2][8], done[2]
+  DevStatus* status;
+  long long wait_limit;    // cycles
+  uint32_t world, rank, rows, D, step, parity;
 };
 
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(uint32_t(b) << 16); }

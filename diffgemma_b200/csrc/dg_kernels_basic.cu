@@ -336,6 +336,24 @@ void launch_visibility(const MaskParams& mk, uint32_t C, uint8_t* out, cudaStrea
   dg_visibility_kernel<<<dim3(gx, C), 256, 0, st>>>(mk, C, out);
 }
 
+// ------------------------------------------------------------------------------------------
+// Self-test of the bounded-wait / device-status path: one thread waits on a flag that nothing
+// sets, gives up after `limit_cycles`, and reports DG_DEV_WAIT_TIMEOUT exactly like a kernel whose
+// barrier wait ran out.  The context stays usable.
+// ------------------------------------------------------------------------------------------
+__global__ void dg_selftest_wait_kernel(volatile uint32_t* flag, long long limit_cycles, DevStatus* status) {
+  const long long t0 = clock64();
+  while (*flag == 0u) {
+    if (clock64() - t0 > limit_cycles) {
+      dev_status_set(status, DG_DEV_WAIT_TIMEOUT, KID_SELFTEST, blockIdx.x, 0u);
+      return;
+    }
+  }
+}
+void launch_selftest_wait(uint32_t* flag, long long limit_cycles, DevStatus* status, cudaStream_t st) {
+  dg_selftest_wait_kernel<<<1, 1, 0, st>>>(flag, limit_cycles, status);
+}
+
 // fill helpers for degenerate launches
 __global__ void dg_fill_f32_kernel(float* p, float v, size_t n) {
   for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) p[i] = v;

@@ -1,0 +1,161 @@
+// Split-KV merge over peer memory (NVLink / NVSwitch), one process per GPU.
+//
+// Every rank owns an exchange buffer that the other ranks have mapped (CUDA IPC).  After its
+// partial attention kernel a rank publishes "partial ready"; the merge kernel of rank r then reads
+// the W partial rows of ITS slice of the query rows straight from the peers' buffers (plain
+// loads over NVLink, no TMA, no multicast), merges them by log-sum-exp and stores the bf16 result
+// rows into every rank's result area, publishes "slice r done" to every rank, and - once all W
+// slices have landed locally - copies the result to the caller's output.  Two parities
+// of every buffer and flag alternate between steps; flags carry a monotonically increasing step id.
+//
+// All waits are bounded: a flag that does not arrive within the limit records DG_DEV_WAIT_TIMEOUT
+// and the kernel carries on without it.
+#include "dg_common.cuh"
+#include "dg_kernels.h"
+
+namespace dg {
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float4 ld_sys_f4(const float4* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_sys_f(const float* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// wait until *flag >= want (step ids only grow); false on timeout
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want, long long limit_cycles) {
+  const long long t0 = clock64();
+  while (int32_t(ld_acquire_sys(flag) - want) < 0) {
+    if (clock64() - t0 > limit_cycles) return false;
+  }
+  return true;
+}
+
+__global__ void __launch_bounds__(256) dg_p2p_merge_kernel(const P2pParams q, uint4* __restrict__ out) {
+  __shared__ uint32_t s_ok;
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t par = q.parity;
+  uint8_t* mine = q.peer[q.rank];
+  if (tid == 0) s_ok = 1u;
+  // 1. publish this rank's partial (written by the preceding kernel on the stream)
+  if (blockIdx.x == 0 && tid == 0) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(mine + q.off_pflag) + par, q.step);
+  }
+  __syncthreads();
+  // 2. every CTA waits for every peer's partial
+  if (tid < q.world) {
+    const uint32_t* f = reinterpret_cast<const uint32_t*>(q.peer[tid] + q.off_pflag) + par;
+    if (!wait_flag(f, q.step, q.wait_limit)) {
+      s_ok = 0u;
+      dev_status_set(q.status, DG_DEV_WAIT_TIMEOUT, KID_MERGE, blockIdx.x, tid);
+    }
+  }
+  __syncthreads();
+  // 3. merge this rank's slice of the rows
+  const uint32_t r0 = uint32_t((uint64_t(q.rank) * q.rows) / q.world);
+  const uint32_t r1 = uint32_t((uint64_t(q.rank + 1) * q.rows) / q.world);
+  const uint32_t D = q.D, W = q.world;
+  if (s_ok) {
+    for (uint32_t row = r0 + blockIdx.x * 8 + warp; row < r1; row += gridDim.x * 8) {
+      float mw = -INFINITY, lw = 0.f;
+      if (lane < W) {
+        mw = ld_sys_f(reinterpret_cast<const float*>(q.peer[lane] + q.off_m[par]) + row);
+        lw = ld_sys_f(reinterpret_cast<const float*>(q.peer[lane] + q.off_l[par]) + row);
+      }
+      float mg = mw;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, o));
+      const float w_mine = (mw == -INFINITY) ? 0.f : expf(mw - mg);
+      float lg = w_mine * lw;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) lg += __shfl_xor_sync(0xffffffffu, lg, o);
+      const float inv = lg > 0.f ? 1.0f / lg : 0.f;
+      for (uint32_t c0 = lane * 8; c0 < D; c0 += 256) {
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+        float4 a[8], b[8];
+#pragma unroll
+        for (uint32_t w = 0; w < 8; ++w) {
+          a[w] = b[w] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (w < W) {   // uniform: only the W real partials cross the link, all issued before first use
+            const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(q.peer[w] + q.off_o[par]) + size_t(row) * D + c0);
+            a[w] = ld_sys_f4(src);
+            b[w] = ld_sys_f4(src + 1);
+          }
+        }
+#pragma unroll
+        for (uint32_t w = 0; w < 8; ++w) {
+          float wt = __shfl_sync(0xffffffffu, w_mine, int(w));
+          if (w >= W) wt = 0.f;
+          acc[0] += wt * a[w].x; acc[1] += wt * a[w].y; acc[2] += wt * a[w].z; acc[3] += wt * a[w].w;
+          acc[4] += wt * b[w].x; acc[5] += wt * b[w].y; acc[6] += wt * b[w].z; acc[7] += wt * b[w].w;
+        }
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv), h1 = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(acc[4] * inv, acc[5] * inv), h3 = __floats2bfloat162_rn(acc[6] * inv, acc[7] * inv);
+        uint4 o4;
+        o4.x = *reinterpret_cast<uint32_t*>(&h0);
+        o4.y = *reinterpret_cast<uint32_t*>(&h1);
+        o4.z = *reinterpret_cast<uint32_t*>(&h2);
+        o4.w = *reinterpret_cast<uint32_t*>(&h3);
+        for (uint32_t w = 0; w < W; ++w)
+          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(q.peer[w] + q.off_res[par]) + size_t(row) * D + c0) = o4;
+      }
+    }
+  }
+  // 4. the last CTA to finish tells every rank that this rank's slice has landed.  One
+  //    system-scope fence per CTA, issued after the CTA barrier, covers the stores of all its threads.
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence_system();
+    uint32_t* done = reinterpret_cast<uint32_t*>(mine + q.off_done) + par;
+    const uint32_t old = atomicAdd(done, 1u);
+    if (old == gridDim.x - 1) {
+      *done = 0u;
+      __threadfence_system();
+      for (uint32_t w = 0; w < W; ++w)
+        st_release_sys(reinterpret_cast<uint32_t*>(q.peer[w] + q.off_rflag) + par * 8 + q.rank, q.step);
+    }
+  }
+  // 5. once every rank's slice has landed here, copy the result to the caller's output.  Every CTA
+  //    of this grid is resident (at most one per SM), so waiting here cannot starve the CTA that
+  //    publishes this rank's own flag.
+  if (tid < W) {
+    const uint32_t* f = reinterpret_cast<const uint32_t*>(mine + q.off_rflag) + par * 8 + tid;
+    if (!wait_flag(f, q.step, q.wait_limit)) {
+      s_ok = 0u;
+      dev_status_set(q.status, DG_DEV_WAIT_TIMEOUT, KID_MERGE, blockIdx.x, 100u + tid);
+    }
+  }
+  __syncthreads();
+  if (!s_ok) return;   // a slice never arrived: the status word says so, the output is left alone
+  const uint4* src = reinterpret_cast<const uint4*>(mine + q.off_res[par]);
+  const size_t n = size_t(q.rows) * q.D / 8;   // 16-byte units
+  for (size_t i = size_t(blockIdx.x) * 256 + tid; i < n; i += size_t(gridDim.x) * 256) out[i] = src[i];
+}
+
+void launch_p2p_merge(const P2pParams& q, void* out, int num_sms, cudaStream_t st) {
+  const uint32_t slice = (q.rows + q.world - 1) / q.world;
+  uint32_t grid = (slice + 7) / 8;
+  if (grid > uint32_t(num_sms)) grid = uint32_t(num_sms);
+  if (grid == 0) grid = 1;
+  dg_p2p_merge_kernel<<<grid, 256, 0, st>>>(q, static_cast<uint4*>(out));
+}
+
+}  // namespace dg

@@ -47,16 +47,40 @@ def head_shards(n_kv_heads: int, world: int) -> list[tuple[int, int]]:
 
 
 class SplitKvGroup:
-    """Split-KV attention over the ranks of a torch.distributed process group."""
+    """Split-KV attention over the ranks of a torch.distributed process group.
 
-    def __init__(self, ctx: Context, layer: AttnLayer, group=None):
+    exchange="p2p" (default): partials are merged by a kernel that reads the peers' exchange buffers
+    over NVLink (CUDA IPC mappings); exchange="nccl": two NCCL all-reduces (max of m, sum of [O | l]).
+    """
+
+    def __init__(self, ctx: Context, layer: AttnLayer, group=None, exchange: str = "p2p"):
+        assert exchange in ("p2p", "nccl")
         self.ctx = ctx
         self.layer = layer
         self.group = group
+        self.exchange = exchange
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self.att = CanvasAttention(ctx, layer)
+        self.comm = None
+        self.p2p = None
         lib = ctx.lib
+        on_gpu = dist.get_backend(group) == "nccl"
+        xdev = torch.device("cuda", ctx.device) if on_gpu else torch.device("cpu")
+        if exchange == "p2p":
+            h = C.c_void_p()
+            rows = layer.canvas * layer.n_q_heads
+            check(lib.dg_p2p_create(ctx.h, rows, layer.head_dim, self.world, self.rank, C.byref(h)), "dg_p2p_create")
+            self.p2p = h
+            buf = (C.c_uint8 * 64)()
+            check(lib.dg_p2p_handle(h, C.cast(buf, C.c_void_p)), "dg_p2p_handle")
+            mine = torch.tensor(list(buf), dtype=torch.uint8, device=xdev)
+            gathered = [torch.zeros(64, dtype=torch.uint8, device=xdev) for _ in range(self.world)]
+            dist.all_gather(gathered, mine, group=group)   # rendezvous only: carries the IPC handles
+            flat = (C.c_uint8 * (64 * self.world))(*[int(b) for t in gathered for b in t.cpu().tolist()])
+            check(lib.dg_p2p_connect(h, C.cast(flat, C.c_void_p)), "dg_p2p_connect")
+            dist.barrier(group=group)
+            return
         ident = torch.zeros(128, dtype=torch.uint8)
         if self.rank == 0:
             buf = (C.c_uint8 * 128)()
@@ -79,8 +103,14 @@ class SplitKvGroup:
     def denoise(self, kv: KvCache, kv_len: int, q, k, v, qw=None, kw=None, out=None):
         """q: [C,Hq,D], k, v: [C,Hkv,D] (replicated inputs).  Every rank gets the full bf16 output."""
         t0, t1 = self.shard_bounds(kv_len)
-        o, m, l = self.att.partial(kv, kv_len, t0, t1, self.rank == canvas_owner(self.world), q, k, v, qw, kw)
         out = torch.empty_like(q) if out is None else out
+        if self.exchange == "p2p":
+            check(self.ctx.lib.dg_attn_denoise_split_p2p(self.ctx.h, C.byref(self.att.desc), kv.h, kv_len, t0, t1,
+                                                         int(self.rank == canvas_owner(self.world)), self.p2p,
+                                                         _ptr(q), _ptr(k), _ptr(v), _ptr(qw), _ptr(kw), _ptr(out)),
+                  "dg_attn_denoise_split_p2p")
+            return out
+        o, m, l = self.att.partial(kv, kv_len, t0, t1, self.rank == canvas_owner(self.world), q, k, v, qw, kw)
         rows = self.layer.canvas * self.layer.n_q_heads
         check(self.ctx.lib.dg_attn_merge_nccl(self.ctx.h, self.comm, _ptr(o), _ptr(m), _ptr(l), _ptr(out), rows,
                                               self.layer.head_dim), "dg_attn_merge_nccl")
@@ -88,6 +118,12 @@ class SplitKvGroup:
         return out
 
     def close(self):
+        if self.p2p:
+            self.ctx.synchronize()
+            if dist.is_initialized():
+                dist.barrier(group=self.group)   # nobody unmaps a buffer a peer's kernel may still read
+            self.ctx.lib.dg_p2p_destroy(self.p2p)
+            self.p2p = None
         if self.comm:
             self.ctx.synchronize()
             self.ctx.lib.dg_nccl_comm_destroy(self.comm)

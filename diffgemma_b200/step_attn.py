@@ -61,19 +61,25 @@ class Context:
     """dg_ctx: one per host thread / stream."""
 
     def __init__(self, device: int = 0, make_current: bool = True):
-        """Creates the context with its own CUDA stream.  With `make_current` that stream also
-        becomes torch's current stream on `device`, so tensor uploads, events and the library's
-        kernels are ordered on one stream (`torch_stream` wraps it either way)."""
+        """With `make_current` a new torch stream becomes both torch's current stream on `device`
+        and the context's launch stream, so tensor uploads, events and the library's kernels are
+        ordered on one stream; otherwise the context keeps its own stream, wrapped by
+        `torch_stream`."""
         self.lib = capi.load()
         h = C.c_void_p()
         check(self.lib.dg_ctx_create(device, C.byref(h)), "dg_ctx_create")
         self.h = h
         self.device = device
-        self.torch_stream = torch.cuda.ExternalStream(int(self.lib.dg_ctx_stream(self.h)), device=device)
         self._made_current = make_current
         if make_current:
+            # torch owns the stream (so that nothing torch remembers about it can outlive it); the
+            # context is told to launch on it
             torch.cuda.set_device(device)
+            self.torch_stream = torch.cuda.Stream(device=device)
+            check(self.lib.dg_ctx_set_stream(self.h, C.c_void_p(self.torch_stream.cuda_stream)), "dg_ctx_set_stream")
             torch.cuda.set_stream(self.torch_stream)
+        else:
+            self.torch_stream = torch.cuda.ExternalStream(int(self.lib.dg_ctx_stream(self.h)), device=device)
 
     def synchronize(self) -> None:
         check(self.lib.dg_ctx_synchronize(self.h), "dg_ctx_synchronize")

@@ -92,6 +92,12 @@ int32_t dg_ctx_synchronize(dg_ctx* ctx);
 /* {code, kernel_id, cta, value}, first-writer-wins; same convention as the reference's
  * DebugStatus (src/shaders/include/debug_status.metal:21-53).  Synchronises.                   */
 int32_t dg_ctx_last_device_status(dg_ctx* ctx, uint32_t out[4]);
+/* Reset the device status word to "no error" (ordered on the context's stream).                 */
+int32_t dg_ctx_clear_device_status(dg_ctx* ctx);
+/* Self-test of the failure path: launches a one-thread kernel that waits, with the given cycle
+ * limit, on a flag nothing sets; it gives up and records DG_DEV_WAIT_TIMEOUT the way an attention
+ * kernel whose barrier wait ran out does.  The context stays usable afterwards.                  */
+int32_t dg_ctx_selftest_wait_timeout(dg_ctx* ctx, uint64_t limit_cycles);
 const char* dg_status_str(int32_t status);
 /* Text of the last CUDA/NCCL error seen by this thread ("" if none).                           */
 const char* dg_last_error_message(void);
@@ -201,6 +207,23 @@ int32_t dg_nccl_comm_destroy(void* comm);
 /* All-gather of per-rank output head slices (KV-head sharding): every rank contributes
  * `bytes_per_rank` bytes at send and receives world*bytes_per_rank at recv (device pointers).   */
 int32_t dg_nccl_all_gather(dg_ctx* ctx, void* comm, const void* send, void* recv, uint64_t bytes_per_rank);
+
+/* ---- split-KV over peer memory (NVLink), one process per GPU ------------------------------ */
+/* The exchange of the per-rank (O, m, l) partials without NCCL: every rank owns an exchange buffer,
+ * exports it with dg_p2p_handle (a 64-byte CUDA IPC handle the host carries to the other ranks),
+ * maps the others with dg_p2p_connect (handles: [world][64] bytes, own entry ignored), and then
+ * dg_attn_denoise_split_p2p = dg_attn_partial on this rank's shard + a merge kernel that reads the
+ * partial rows of this rank's slice from the peers over NVLink, merges them and stores the bf16
+ * result into every rank's buffer + a copy to `out` once all slices have arrived.  world <= 8;
+ * every rank must make the same sequence of calls.  All device-side waits are bounded.          */
+typedef struct dg_p2p dg_p2p;
+int32_t dg_p2p_create(dg_ctx* ctx, uint32_t rows, uint32_t head_dim, int32_t world, int32_t rank, dg_p2p** out);
+int32_t dg_p2p_handle(dg_p2p* x, uint8_t handle_out[64]);
+int32_t dg_p2p_connect(dg_p2p* x, const uint8_t* handles);
+int32_t dg_p2p_destroy(dg_p2p* x);
+int32_t dg_attn_denoise_split_p2p(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* kv, uint32_t kv_len, uint32_t t0,
+                                  uint32_t t1, int32_t include_canvas, dg_p2p* x, const void* q, const void* k,
+                                  const void* v, const void* qw, const void* kw, void* out);
 
 /* ---- mask introspection (bit-exact mask parity) ----------------------------------------- */
 /* Evaluate on the GPU the same visibility predicate the attention kernels use and write it as

@@ -370,3 +370,42 @@ def test_output_guard_rows_untouched(ctx):
     assert torch.all(buf[:guard] == 7.0) and torch.all(buf[guard + n:] == 7.0)
     util.assert_close(util.t2f(out[0]), util.run_oracle(case), "ragged canvas")
     kv.close()
+
+
+# ------------------------------------------------------------------------------------------
+# CTA-pair kernel variant (tcgen05 cta_group::2)
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("P,Hkv,W,mode,scale,canvas", [(300, 8, 0, 0, 1 / 16, 256), (1000, 2, 0, 0, 1 / 16, 256),
+                                                       (3000, 8, 1024, 2, 1 / 16, 256), (3000, 8, 1024, 1, 1.0, 256),
+                                                       (500, 8, 0, 0, 1 / 16, 100), (500, 2, 0, 0, 1 / 16, 64)])
+def test_pair_kernel_parity(ctx, P, Hkv, W, mode, scale, canvas):
+    layer = AttnLayer(n_kv_heads=Hkv, window=W, mask_mode=mode, softmax_scale=scale, canvas=canvas,
+                      rope_theta=1e4 if W else 1e6, v_norm=1 if scale == 1.0 else 0)
+    case = util.make_case(layer, P, seed=P + 13 * Hkv)
+    ref = util.run_oracle(case)
+    ctx.set_pair_mode(True)
+    try:
+        for splits in (0, 1, 2, 3):
+            ctx.set_splits(splits)
+            util.assert_close(util.run_gpu(ctx, case), ref, f"pair kernel splits={splits}")
+    finally:
+        ctx.set_splits(0)
+        ctx.set_pair_mode(False)
+    assert ctx.device_status()[0] == 0
+
+
+# ------------------------------------------------------------------------------------------
+# failure path: a bounded wait that runs out is reported through the status word, nothing faults
+# ------------------------------------------------------------------------------------------
+def test_wait_timeout_is_reported_and_context_survives(ctx):
+    lib = ctx.lib
+    assert lib.dg_ctx_selftest_wait_timeout(ctx.h, 200000) == capi.DG_OK      # ~0.1 ms
+    assert lib.dg_ctx_synchronize(ctx.h) == capi.DG_DEV_WAIT_TIMEOUT
+    st = ctx.device_status()
+    assert st[0] == capi.DG_DEV_WAIT_TIMEOUT and st[1] == 6
+    assert lib.dg_ctx_clear_device_status(ctx.h) == capi.DG_OK
+    assert lib.dg_ctx_synchronize(ctx.h) == capi.DG_OK
+    # the context still computes correctly
+    layer = AttnLayer(n_kv_heads=8)
+    case = util.make_case(layer, 300, seed=21)
+    util.assert_close(util.run_gpu(ctx, case), util.run_oracle(case), "after a reported timeout")

@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _rank_main(rank, world, port, P, W, mode, ret):
+def _rank_main(rank, world, port, P, W, mode, exchange, ret):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import util
@@ -34,9 +34,9 @@ def _rank_main(rank, world, port, P, W, mode, ret):
         t0, t1 = b[rank], b[rank + 1]
         if t1 > t0:                                        # only this rank's shard is resident
             kv.load_prefix(case["kp"][t0:t1].contiguous().to(dev), case["vp"][t0:t1].contiguous().to(dev), t0)
-        grp = SplitKvGroup(ctx, layer)
+        grp = SplitKvGroup(ctx, layer, exchange=exchange)
         out = None
-        for _ in range(2):                                 # twice: workspace reuse across steps
+        for _ in range(3):                                 # several steps: buffer parities and flags are reused
             out = grp.denoise(kv, P, case["q"].to(dev), case["kc"].to(dev), case["vc"].to(dev))
         ctx.synchronize()
         ref = util.run_oracle(case)
@@ -48,14 +48,16 @@ def _rank_main(rank, world, port, P, W, mode, ret):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("exchange", ["p2p", "nccl"])
 @pytest.mark.parametrize("P,W,mode,port", [(6000, 0, 0, 29721), (3000, 1024, 1, 29722)])
-def test_split_kv_nccl_matches_oracle(P, W, mode, port):
+def test_split_kv_matches_oracle(P, W, mode, port, exchange):
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least 2 GPUs")
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_rank_main, args=(world, port, P, W, mode, ret), nprocs=world, join=True)
+    port += 10 if exchange == "nccl" else 0
+    mp.spawn(_rank_main, args=(world, port, P, W, mode, exchange, ret), nprocs=world, join=True)
     assert len(ret) == world
     for rank, (mx, mean, tol) in ret.items():
         assert mx <= tol and mean <= 2e-3, (rank, mx, mean)
