@@ -30,9 +30,9 @@ UNIT = "TFLOP/s"
 L2_BYTES = 126e6
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention-kernel launch of the benchmark
-# workload (70.09 MB + 4.47 MB), from the ncu capture summarised in
+# workload (70.07 MB + 8.97 MB), from the ncu capture summarised in
 # profiles/dg_attn_sm100_kernel__cfg2_global_p32768.md
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {2: 74.56e6}
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {2: 79.04e6}
 
 
 def _peaks():
