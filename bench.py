@@ -153,7 +153,9 @@ def run_reference(args):
     if rank != 0:
         return
     cfg = _cfg(args.cfg)
-    smp = CpuSample(args.cfg)
+    # all host threads this process may use: the launcher of a multi-rank run exports
+    # OMP_NUM_THREADS=1, which must not shrink the CPU arm to one core
+    smp = CpuSample(args.cfg, n_threads=len(os.sched_getaffinity(0)))
     _, dt8, _ = smp.run(8)
     n_steps = args.warmup + args.steps
     rows = int(max(1, min(cfg.layer.canvas, 8 * (120.0 / n_steps) / dt8)))
