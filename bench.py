@@ -194,6 +194,8 @@ def run_ours(args):
     assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
     dev = torch.device("cuda", local)
     ctx = Context(local)
+    if args.kernel_form != "auto":
+        ctx.set_pair_mode(args.kernel_form == "pair")
     cfg = _cfg(args.cfg)
     lay = cfg.layer
     P = cfg.prefix
@@ -348,6 +350,8 @@ def main():
     ap.add_argument("--ref-rows", type=int, default=256, help="canvas rows in the bounded CPU sample")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="multi-GPU partial exchange")
+    ap.add_argument("--kernel-form", default="auto", choices=["auto", "pair", "single"],
+                    help="tensor-kernel form: CTA pairs, one CTA per query tile, or the library's choice")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

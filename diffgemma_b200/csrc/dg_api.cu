@@ -66,7 +66,7 @@ struct dg_ctx {
   float* nccl_mg = nullptr;            // [rows]
   size_t nccl_rows = 0, nccl_d = 0;
   int force_general = 0;
-  int pair_mode = 0;                   // 1: CTA-pair (cta_group::2) kernel on the tensor path
+  int pair_mode = 2;                   // tensor path: 0 single-CTA kernel, 1 CTA-pair (cta_group::2) kernel, 2 automatic
   uint32_t forced_splits = 0;
   uint32_t last_launches = 0;
   // optional per-launch timing of the attention kernel (event pairs on the launching stream)
@@ -175,8 +175,7 @@ static uint32_t choose_splits(const dg_ctx* ctx, uint32_t q_tiles, uint32_t k_ti
   uint32_t best = 1;
   uint64_t best_cost = ~0ull;
   // automatic choice: powers of two up to 8, the split counts that merge inside a cluster
-  const uint32_t auto_max = ctx->pair_mode ? 4u : 8u;   // cluster = pair x splits must stay <= 8 CTAs
-  for (uint32_t s = 1; s <= smax && s <= auto_max; s *= 2) {
+  for (uint32_t s = 1; s <= smax && s <= 8u; s *= 2) {
     const uint64_t waves = (uint64_t(q_tiles) * s + sms - 1) / sms;
     // fixed cost of a CTA (set-up, Q prologue, epilogue) and of the merge, in key-tile units
     const uint64_t per = (k_tiles + s - 1) / s + 6 + (s > 1 ? 2 : 0);
@@ -368,9 +367,10 @@ extern "C" int32_t dg_ctx_max_active_clusters(dg_ctx* c, int32_t pair, uint32_t 
   cudaSetDevice(c->device);
   return pair ? sm100_pair_max_active_clusters(cluster_y) : sm100_max_active_clusters(cluster_y);
 }
-extern "C" int32_t dg_ctx_set_pair_mode(dg_ctx* c, int32_t on) {
+extern "C" int32_t dg_ctx_set_pair_mode(dg_ctx* c, int32_t mode) {
   if (!c) return fail(DG_ERR_INVALID_ARG, "ctx is NULL");
-  c->pair_mode = on ? 1 : 0;
+  if (mode < 0 || mode > 2) return fail(DG_ERR_INVALID_ARG, "pair mode must be 0 (single), 1 (pair) or 2 (automatic)");
+  c->pair_mode = mode;
   return DG_OK;
 }
 extern "C" int32_t dg_ctx_set_splits(dg_ctx* c, uint32_t n) {
@@ -607,12 +607,19 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
     c->last_launches += 1;
     return DG_OK;
   }
-  const bool pair = c->pair_mode != 0;
-  const uint32_t q_tiles = pair ? sm100_pair_query_tiles(p.C, p.G, p.Hkv) : sm100_query_tiles(p.C, p.G, p.Hkv);
+  // CTA pairs halve the shared-memory traffic per query tile (the kernel's limiter); they need two
+  // query tiles of one KV head to share a key schedule, so a head with a single tile runs unpaired
+  // Short key ranges stay unpaired too: the pair form's longer set-up and its workspace merge cost
+  // more than the per-tile saving returns below about a hundred key tiles.
+  const uint32_t tiles_per_head = sm100_query_tiles(p.C, p.G, 1);
   const uint32_t k_tiles = sm100_key_tiles(p.mask);
+  const bool pair = c->pair_mode == 1 || (c->pair_mode == 2 && tiles_per_head >= 2 && k_tiles >= 96);
+  const uint32_t q_tiles = pair ? sm100_pair_query_tiles(p.C, p.G, p.Hkv) : sm100_query_tiles(p.C, p.G, p.Hkv);
   if (q_tiles > kMaxQueryTiles) return fail(DG_ERR_UNSUPPORTED, "too many query tiles");
   p.n_splits = choose_splits(c, q_tiles, k_tiles);
-  p.cluster_merge = (p.n_splits == 2 || p.n_splits == 4 || (!pair && p.n_splits == 8)) ? 1u : 0u;
+  // cluster merge only for the single-CTA form: pairs x 4 splits would need clusters of 8 CTAs, of
+  // which too few are co-resident
+  p.cluster_merge = (!pair && (p.n_splits == 2 || p.n_splits == 4 || p.n_splits == 8)) ? 1u : 0u;
   if (p.n_splits > 1 && !p.cluster_merge) {
     const int32_t r = ensure_split_ws(c, p.n_splits, p.C * p.Hq);
     if (r != DG_OK) return r;

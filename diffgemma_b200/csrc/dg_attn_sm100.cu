@@ -7,14 +7,20 @@
 //   * S = Q K^T and O += P V run on tcgen05.mma with fp32 accumulators in tensor memory:
 //     TMEM columns [0,128) and [128,256) double-buffer S, [256,512) hold O; P (bf16) overwrites
 //     the first 64 columns of its S buffer and is consumed from TMEM as the A operand.
-//   * online softmax in registers, two threads per query row (64 key columns each, so that every
-//     scheduler has two softmax warps to hide instruction latency), with lazy rescaling of O (only
-//     when the running maximum grows by more than 2^8).
-//   * intra-GPU split-KV: grid.y CTAs share one query tile.  For 2, 4 or 8 splits they form a
-//     thread-block cluster: each keeps its (O, m, l) partial in shared memory and, after a cluster
-//     barrier, merges its share of the rows by reading the peers' partials through distributed
-//     shared memory.  Other split counts write partials to a global workspace and the last CTA to
-//     finish merges them.  Either way there is no second launch.
+//   * online softmax in registers, four threads per query row (32 key columns each), packed
+//     fp32x2 arithmetic, lazy rescaling of O (only when the running maximum grows by more than 2^8).
+//   * two forms of the same kernel (template parameter PAIR): one CTA per query tile, or CTA pairs
+//     (tcgen05 cta_group::2, M = 256) where every CTA stages only half of each K/V tile in two
+//     stages.  The single-CTA form is bound by shared-memory bandwidth (per 128-key tile it reads
+//     Q 64 KB + K 64 KB + V 64 KB as MMA operands and takes 128 KB of TMA writes = 320 KB against
+//     128 B/clk = 2,560 cycles, the MMAs alone need 2,048); the pair form moves 192 KB per tile.
+//   * intra-GPU split-KV: grid.y CTAs share one query tile and merge their (O, m, l) partials either
+//     through distributed shared memory (single-CTA form, 2 / 4 / 8 splits: one thread-block cluster
+//     per query tile) or through a global workspace with the last CTA to finish doing the merge.
+//     Either way there is no second launch.
+//   * the MMA-issuing thread is the critical resource: it shares a scheduler with four softmax
+//     warps, so its instruction stream is kept short (rolled loops, descriptor adds, one commit per
+//     MMA group - S_FULL doubles as "K stage free", V_EMPTY as "PV done") and nothing is polled.
 //
 // Query rows are the GQA-stacked rows of one KV head: stacked row R -> canvas row R / G, query
 // head kvh*G + R % G, so all 128 rows of a CTA reuse the same K/V tiles.
@@ -32,7 +38,7 @@ namespace dg {
 
 using namespace sm100;
 
-// Single-CTA kernel: four softmax warpgroups.  Warps w, w+4, w+8, w+12 share the 32 query rows of
+// Four softmax warpgroups.  Warps w, w+4, w+8, w+12 share the 32 query rows of
 // TMEM quadrant w & 3; warpgroup q = w >> 2 handles key columns [32 q, 32 q + 32) of every tile, so
 // each scheduler has four softmax warps in flight to hide TMEM, MUFU and barrier latency.
 namespace one {
@@ -42,6 +48,21 @@ constexpr uint32_t W_K = SM_WARPS, W_V = SM_WARPS + 1, W_MMA = SM_WARPS + 2;
 constexpr uint32_t THREADS = (SM_WARPS + 3) * 32;   // 608
 constexpr uint32_t CPT = BN / NTR;                // 32 key columns per thread
 constexpr uint32_t OPT = HD / NTR;                // 64 output columns per thread
+// CTA-pair form: every CTA stages half of each tile - 64 keys of K (4 atoms of 64 rows x 128 B),
+// 128 value columns of V (2 atoms of 128 rows x 128 B) - in two stages each
+constexpr uint32_t K_STAGE = 32768, K_ATOM = 8192, V_STAGE = 32768;
+// barrier slots.  In the pair form Q, K_FULL, V_FULL and P_FULL are used in the pair's leader only
+// (arrivals and byte counts of both CTAs land there); the others exist in both CTAs.
+enum : uint32_t {
+  B_Q = 0,
+  B_K_FULL = 1,    // +stage
+  B_V_FULL = 3,    // +stage
+  B_V_EMPTY = 7,   // +(tile & 1): PV of the tile complete -> its V stage is free, O may be rescaled
+  B_S_FULL = 9,    // +(tile & 1): QK of the tile complete -> S is ready, its K stage is free
+  B_P_FULL = 11,   // +buffer
+  B_O_FINAL = 14,  // single phase: every PV of this CTA has completed
+  B_COUNT = 15
+};
 }  // namespace one
 
 // named barrier of the NTR warps that own the same 32 query rows
@@ -49,6 +70,14 @@ __device__ __forceinline__ void row_group_sync(uint32_t smw) {
   asm volatile("bar.sync %0, %1;" ::"r"(smw + 1u), "n"(one::NTR * 32) : "memory");
 }
 
+// PAIR = false: one CTA per (query tile, key split), tm_k / tm_v with boxes {64 d, 128 keys}.
+// PAIR = true: two CTAs on the two SMs of a TPC own two adjacent query tiles of one KV head; one
+// thread of the pair's leader issues M = 256 MMAs (cta_group::2) that span both: each CTA supplies
+// its own 128 query rows and HALF of every K/V tile from its own shared memory (64 of the 128 keys
+// for S, 128 of the 256 value columns for O), so every K/V byte enters an SM's shared memory once
+// per pair and is read from it half as often.  tm_k then has boxes {64 d, 64 keys}.  No load uses
+// multicast.
+template <bool PAIR>
 __global__ void __launch_bounds__(one::THREADS, 1)
 dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v) {
@@ -58,7 +87,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t sQ = smem_base + OFF_Q, sK = smem_base + OFF_K, sV = smem_base + OFF_V;
   const uint32_t bar_base = smem_base + OFF_BAR;
-  volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + N_BARS * 8);
+  volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + B_COUNT * 8);
   // ctl[0] = TMEM base address, ctl[1] = abort flag, ctl[2] = "this CTA merges" flag
   float* xch_max = reinterpret_cast<float*>(smem + OFF_XCH);   // [2 tile parities][BM][NTR]
   float* xch_misc = xch_max + 2 * BM * NTR;                     // [BM][NTR]: prologue sums of squares
@@ -66,13 +95,31 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t tiles_per_head = (p.C * p.G + BM - 1) / BM;
-  const uint32_t kvh = blockIdx.x / tiles_per_head;
-  const uint32_t mt = blockIdx.x % tiles_per_head;
+  // pair form: tiles per head rounded up to whole pairs; a padding tile has only invalid rows
+  const uint32_t tiles_x = PAIR ? ((tiles_per_head + 1u) & ~1u) : tiles_per_head;
+  const uint32_t kvh = blockIdx.x / tiles_x;
+  const uint32_t mt = blockIdx.x % tiles_x;
   const uint32_t split = blockIdx.y;
   const uint32_t rows_per_head = p.C * p.G;
   const MaskParams mk = p.mask;
 
-  const uint32_t row_first = (mt * BM) / p.G;
+  // position in the cluster: (1, S, 1) or, in the pair form, (2, S, 1) with x fastest
+  const uint32_t crank = (PAIR || (p.cluster_merge && p.n_splits > 1)) ? cluster_ctarank() : 0u;
+  const uint32_t xi = PAIR ? (crank & 1u) : 0u;          // position inside the pair
+  const uint32_t leader = crank & ~1u;                    // pair form: cluster rank of the pair's leader
+  const bool is_leader = xi == 0u;
+  auto lead_bar = [&](uint32_t idx) { return dsmem_addr(bar_addr(bar_base, idx), leader); };
+  auto peer_bar = [&](uint32_t idx) { return dsmem_addr(bar_addr(bar_base, idx), leader | 1u); };
+  // bounded wait on one of this CTA's own barriers.  Only the Q barrier orders ordinary shared
+  // memory written by the other CTA of a pair and needs cluster scope; the others order TMA bytes
+  // or tensor-memory contents, which carry their own fences.
+  auto wait_bar = [&](uint32_t idx, uint32_t parity, volatile uint32_t* flag) -> bool {
+    return (PAIR && idx == B_Q) ? mbar_wait_cluster(bar_addr(bar_base, idx), parity, flag)
+                                : mbar_wait(bar_addr(bar_base, idx), parity, flag);
+  };
+
+  // both CTAs of a pair walk the same key tiles: schedule from the pair's first canvas row
+  const uint32_t row_first = ((PAIR ? (mt & ~1u) : mt) * BM) / p.G;
   const TileSched ts = tile_sched(mk, row_first < p.C ? row_first : p.C - 1);
   const uint32_t n_tiles = ts.nA + ts.nB;
   const uint32_t v_begin = uint32_t((uint64_t(split) * n_tiles) / p.n_splits);
@@ -82,28 +129,33 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   stamp(p, 0);
   // ------------------------------------------------------------------ set-up
   if (tid == 0) {
-    mbar_init(bar_addr(bar_base, BAR_Q), SM_WARPS);          // one arrival per softmax warp
-    mbar_init(bar_addr(bar_base, BAR_K_FULL), 1);
-    mbar_init(bar_addr(bar_base, BAR_K_EMPTY), 1);
-    mbar_init(bar_addr(bar_base, BAR_V_FULL), 1);
-    mbar_init(bar_addr(bar_base, BAR_V_EMPTY), 1);
-    mbar_init(bar_addr(bar_base, BAR_S_FULL0), 1);
-    mbar_init(bar_addr(bar_base, BAR_S_FULL0 + 1), 1);
-    mbar_init(bar_addr(bar_base, BAR_P_FULL0), SM_WARPS);
-    mbar_init(bar_addr(bar_base, BAR_P_FULL0 + 1), SM_WARPS);
-    mbar_init(bar_addr(bar_base, BAR_PV_DONE), 1);
-    mbar_init(bar_addr(bar_base, BAR_O_FINAL), 1);
+    mbar_init(bar_addr(bar_base, B_Q), (PAIR ? 2u : 1u) * SM_WARPS);   // one arrival per softmax warp
+    for (uint32_t st = 0; st < 2; ++st) {
+      mbar_init(bar_addr(bar_base, B_K_FULL + st), 1);
+      mbar_init(bar_addr(bar_base, B_V_FULL + st), 1);
+      mbar_init(bar_addr(bar_base, B_V_EMPTY + st), 1);
+      mbar_init(bar_addr(bar_base, B_S_FULL + st), 1);
+      mbar_init(bar_addr(bar_base, B_P_FULL + st), (PAIR ? 2u : 1u) * SM_WARPS);
+    }
+    mbar_init(bar_addr(bar_base, B_O_FINAL), 1);
     ctl[1] = 0u;
     ctl[2] = 0u;
     fence_mbar_init();
   }
   if (warp == W_MMA) {
-    tmem_alloc(smem_u32(const_cast<uint32_t*>(&ctl[0])), TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(&ctl[0])), TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(const_cast<uint32_t*>(&ctl[0])), TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   if ((warp == W_K || warp == W_V) && lane == 0) tma_prefetch_desc(warp == W_K ? &tm_k : &tm_v);
   tc_fence_before();
   __syncthreads();
+  // pair form: the peer's barriers must exist before anything of ours can signal them
+  if (PAIR) cluster_sync_all();
   tc_fence_after();
   const uint32_t tmem = ctl[0];
   // Programmatic dependent launch: everything above overlapped the tail of the preceding kernel
@@ -112,6 +164,8 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   asm volatile("griddepcontrol.wait;" ::: "memory");
   stamp(p, 1);
   volatile uint32_t* abort_flag = &ctl[1];
+  const bool prof = p.stamps != nullptr;
+  long long w_s = 0, w_r = 0;
 
   // softmax-thread geometry: TMEM quadrant smw, row r of the query tile, column quarter qd
   const uint32_t smw = warp & 3u, qd = (warp >> 2) & (NTR - 1u);
@@ -206,10 +260,13 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
         *reinterpret_cast<uint4*>(smem + OFF_Q + (c_hi >> 3) * ATOM_BYTES + r * 128u + (((c_hi & 7u) ^ (r & 7u)) << 4)) = out_hi;
       }
     }
-    // every lane publishes its own stores, then one lane arrives for the warp
-    fence_proxy_async_smem();
+    // every lane publishes its own stores (in the pair form the leader's MMA thread reads this
+    // tile through the async proxy from the other SM), then one lane arrives for the warp
+    if (PAIR) fence_proxy_async_all(); else fence_proxy_async_smem();
     __syncwarp();
-    if (lane == 0) mbar_arrive(bar_addr(bar_base, BAR_Q));
+    if (lane == 0) {
+      if (PAIR) mbar_arrive_cluster(lead_bar(B_Q)); else mbar_arrive(bar_addr(bar_base, B_Q));
+    }
     stamp(p, 2);
 
     // ---------------------------------------------------------------- softmax main loop
@@ -219,6 +276,8 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
     const uint32_t t_lane = tmem + ((smw * 32u) << 16);
     const bool contiguous = (mk.pre_hi == mk.kv_len) && (mk.can_hi > mk.kv_len);
     const float sc = p.scale_log2;
+    const uint32_t p_full0 = PAIR ? lead_bar(B_P_FULL) : bar_addr(bar_base, B_P_FULL);
+    const uint32_t p_full1 = PAIR ? lead_bar(B_P_FULL + 1) : bar_addr(bar_base, B_P_FULL + 1);
 
     for (uint32_t n = 0; n < n_local; ++n) {
       const uint32_t v = v_begin + n;
@@ -226,7 +285,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       const uint32_t k0 = jt * BN;
       const uint32_t b = n & 1u;
       // warp-uniform outcome: the TMEM instructions below need the whole warp
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_addr(bar_base, BAR_S_FULL0 + b), (n >> 1) & 1u, abort_flag))) break;
+      if (!__all_sync(0xffffffffu, timed_wait(prof, w_s, [&] { return wait_bar(B_S_FULL + b, (n >> 1) & 1u, abort_flag); }))) break;
       tc_fence_after();
       uint32_t sraw[32];
       tmem_ld32(t_lane + TM_S + b * 128u + qd * CPT, sraw);
@@ -241,8 +300,9 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sraw[e]));
-      const float mx_part = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      for (int e = 0; e < 32; e += 2)
+        mx4[(e >> 1) & 3] = max3_f32(mx4[(e >> 1) & 3], __uint_as_float(sraw[e]), __uint_as_float(sraw[e + 1]));
+      const float mx_part = max3_f32(max3_f32(mx4[0], mx4[1], mx4[2]), mx4[3], -INFINITY);
       // the threads of a row agree on the row maximum through shared memory; after this barrier
       // all of them have their S columns in registers, so P may overwrite any S column
       xch_max[(b * BM + r) * NTR + qd] = mx_part;
@@ -256,7 +316,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       if (!first && __any_sync(0xffffffffu, need)) {
         // O holds sum p v relative to m_used: bring it to the new reference point (each thread of
         // the row rescales its own 64 columns of O)
-        if (!__all_sync(0xffffffffu, mbar_wait(bar_addr(bar_base, BAR_PV_DONE), (n - 1) & 1u, abort_flag))) break;
+        if (!__all_sync(0xffffffffu, timed_wait(prof, w_r, [&] { return wait_bar(B_V_EMPTY + ((n - 1) & 1u), ((n - 1) >> 1) & 1u, abort_flag); }))) break;
         tc_fence_after();
         const float alpha = need ? fast_exp2(m_used - m_new) : 1.0f;
 #pragma unroll 1
@@ -274,23 +334,35 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       if (need) m_used = m_new;
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
       const float neg_m = -m_eff;
-      float ls0 = 0.f, ls1 = 0.f;
-      // P column j (32 bit) = keys (2j, 2j+1) as bf16x2: this thread's 32 keys are 16 columns
+      // P column j (32 bit) = keys (2j, 2j+1) as bf16x2: this thread's 32 keys are 16 columns.
+      // Scale/shift and row sums run on packed fp32 pairs.
+      const uint64_t sc2 = pack_f32x2(sc, sc), nm2 = pack_f32x2(neg_m, neg_m);
+      uint64_t ls2[2] = {0ull, 0ull};   // (0.f, 0.f)
       uint32_t pk[16];
 #pragma unroll
       for (int e = 0; e < 32; e += 2) {
-        const float p0 = fast_exp2(fmaf(__uint_as_float(sraw[e]), sc, neg_m));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(sraw[e + 1]), sc, neg_m));
-        ls0 += p0;
-        ls1 += p1;
+        float x0, x1;
+        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sraw[e]), __uint_as_float(sraw[e + 1])), sc2, nm2), x0, x1);
+        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+        ls2[(e >> 1) & 1] = add_f32x2(ls2[(e >> 1) & 1], pack_f32x2(p0, p1));
         pk[e >> 1] = pack_bf16x2(p0, p1);
       }
-      l_run += ls0 + ls1;
+      {
+        float s0, s1;
+        unpack_f32x2(add_f32x2(ls2[0], ls2[1]), s0, s1);
+        l_run += s0 + s1;
+      }
       tmem_st16(t_lane + TM_S + b * 128u + qd * (CPT / 2), pk);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_addr(bar_base, BAR_P_FULL0 + b));
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_remote(b ? p_full1 : p_full0); else mbar_arrive(b ? p_full1 : p_full0);
+      }
+    }
+    if (prof && tid == 0) {
+      stamp_cycles(p, 10, w_s);
+      stamp_cycles(p, 11, w_r);
     }
   } else if (warp == W_K) {
     // ---------------------------------------------------------------- K loader
@@ -298,12 +370,24 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       for (uint32_t n = 0; n < n_local; ++n) {
         const uint32_t v = v_begin + n;
         const uint32_t jt = v < ts.nA ? ts.a0 + v : ts.b0 + (v - ts.nA);
-        if (n > 0 && !mbar_wait(bar_addr(bar_base, BAR_K_EMPTY), (n - 1) & 1u, abort_flag)) break;
-        const uint32_t full = bar_addr(bar_base, BAR_K_FULL);
-        mbar_expect_tx(full, TILE_BYTES);
+        if (PAIR) {
+          // this CTA's 64 keys of the tile into stage n & 1
+          const uint32_t st = n & 1u, u = n >> 1;
+          if (u > 0 && !wait_bar(B_S_FULL + st, (u - 1) & 1u, abort_flag)) break;   // QK(n - 2) complete
+          if (is_leader) mbar_expect_tx(bar_addr(bar_base, B_K_FULL + st), 2 * K_STAGE);
+          const uint32_t full = lead_bar(B_K_FULL + st);
 #pragma unroll
-        for (uint32_t a = 0; a < 4; ++a)
-          tma_load_3d(sK + a * ATOM_BYTES, &tm_k, full, int32_t(a * 64), int32_t(jt * BN), int32_t(kvh));
+          for (uint32_t a = 0; a < 4; ++a)
+            tma_load_3d_pair(sK + st * K_STAGE + a * K_ATOM, &tm_k, full, int32_t(a * 64), int32_t(jt * BN + xi * 64),
+                             int32_t(kvh));
+        } else {
+          if (n > 0 && !wait_bar(B_S_FULL + ((n - 1) & 1u), ((n - 1) >> 1) & 1u, abort_flag)) break;   // QK(n - 1) complete
+          const uint32_t full = bar_addr(bar_base, B_K_FULL);
+          mbar_expect_tx(full, TILE_BYTES);
+#pragma unroll
+          for (uint32_t a = 0; a < 4; ++a)
+            tma_load_3d(sK + a * ATOM_BYTES, &tm_k, full, int32_t(a * 64), int32_t(jt * BN), int32_t(kvh));
+        }
       }
     }
   } else if (warp == W_V) {
@@ -312,56 +396,115 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       for (uint32_t n = 0; n < n_local; ++n) {
         const uint32_t v = v_begin + n;
         const uint32_t jt = v < ts.nA ? ts.a0 + v : ts.b0 + (v - ts.nA);
-        if (n > 0 && !mbar_wait(bar_addr(bar_base, BAR_V_EMPTY), (n - 1) & 1u, abort_flag)) break;
-        const uint32_t full = bar_addr(bar_base, BAR_V_FULL);
-        mbar_expect_tx(full, TILE_BYTES);
+        if (PAIR) {
+          // this CTA's 128 value columns of the tile into stage n & 1
+          const uint32_t st = n & 1u, u = n >> 1;
+          if (u > 0 && !wait_bar(B_V_EMPTY + st, (u - 1) & 1u, abort_flag)) break;
+          if (is_leader) mbar_expect_tx(bar_addr(bar_base, B_V_FULL + st), 2 * V_STAGE);
+          const uint32_t full = lead_bar(B_V_FULL + st);
 #pragma unroll
-        for (uint32_t a = 0; a < 4; ++a)
-          tma_load_3d(sV + a * ATOM_BYTES, &tm_v, full, int32_t(a * 64), int32_t(jt * BN), int32_t(kvh));
+          for (uint32_t a = 0; a < 2; ++a)
+            tma_load_3d_pair(sV + st * V_STAGE + a * ATOM_BYTES, &tm_v, full, int32_t(xi * 128 + a * 64),
+                             int32_t(jt * BN), int32_t(kvh));
+        } else {
+          if (n > 0 && !wait_bar(B_V_EMPTY + ((n - 1) & 1u), ((n - 1) >> 1) & 1u, abort_flag)) break;   // PV(n - 1) complete
+          const uint32_t full = bar_addr(bar_base, B_V_FULL);
+          mbar_expect_tx(full, TILE_BYTES);
+#pragma unroll
+          for (uint32_t a = 0; a < 4; ++a)
+            tma_load_3d(sV + a * ATOM_BYTES, &tm_v, full, int32_t(a * 64), int32_t(jt * BN), int32_t(kvh));
+        }
       }
     }
   } else {
-    // ---------------------------------------------------------------- MMA issuer (one thread)
-    if (lane == 0 && n_local > 0) {
-      constexpr uint32_t IDESC_QK = umma_idesc_bf16(BM, BN, 0, 0);   // A, B K-major
-      constexpr uint32_t IDESC_PV = umma_idesc_bf16(BM, HD, 0, 1);   // B (= V) MN-major
-      bool ok = mbar_wait(bar_addr(bar_base, BAR_Q), 0u, abort_flag);
-      auto issue_qk = [&](uint32_t n) -> bool {
-        if (!mbar_wait(bar_addr(bar_base, BAR_K_FULL), n & 1u, abort_flag)) return false;
+    // ---------------------------------------------------------------- MMA issuer (one thread; pair form: of the leader)
+    if (lane == 0 && n_local > 0 && is_leader) {
+      constexpr uint32_t IDESC_QK = umma_idesc_bf16(PAIR ? 2 * BM : BM, BN, 0, 0);   // A, B K-major
+      constexpr uint32_t IDESC_PV = umma_idesc_bf16(PAIR ? 2 * BM : BM, HD, 0, 1);   // B (= V) MN-major
+      // completion signal: pair form -> the same barrier slot in both CTAs
+      auto commit = [&](uint32_t idx) {
+        if (PAIR) {
+          umma_commit_pair(lead_bar(idx));
+          umma_commit_pair(peer_bar(idx));
+        } else {
+          umma_commit(bar_addr(bar_base, idx));
+        }
+      };
+      bool ok = wait_bar(B_Q, 0u, abort_flag);
+      long long w_k = 0, w_v = 0, w_p = 0;
+      const long long t_loop = prof ? clock64() : 0;
+      // Descriptors are advanced with adds on their low word (start address >> 4; every operand
+      // lives below 256 KB, so the 14-bit field cannot carry), and the MMA loops are kept rolled: the
+      // issuing thread shares its scheduler with four softmax warps, so its instruction stream must
+      // stay short to keep the tensor pipe fed.
+      constexpr uint32_t HI_KMAJ = (1024u >> 4) | (1u << 14) | (2u << 29);          // SBO 1024, version 1, 128B swizzle
+      constexpr uint32_t HI_MNMAJ = HI_KMAJ;                                          // same SBO for V
+      const uint32_t q_lo = ((sQ >> 4) & 0x3FFFu) | ((16u >> 4) << 16);              // LBO 16 (unused for K-major)
+      const uint32_t k_lo0 = ((sK >> 4) & 0x3FFFu) | ((16u >> 4) << 16);
+      const uint32_t v_lo0 = ((sV >> 4) & 0x3FFFu) | ((ATOM_BYTES >> 4) << 16);      // LBO = 64-column chunk stride
+      auto mkdesc = [](uint32_t lo, uint32_t hi) { return (uint64_t(hi) << 32) | uint64_t(lo); };
+      // The issuing thread polls (without blocking) for what the NEXT group of MMAs needs while the
+      // tensor pipe still has queued work, so that the blocking wait in front of that group normally
+      // finds the phase complete and the pipe does not drain at the S / O hand-over.
+      //   issue_qk(n, pv): S(n) = Q K(n)^T; polls P_FULL / V_FULL of tile pv (the PV issued next)
+      bool p_ready = false, v_ready = false, k_ready = false;
+      auto issue_qk = [&](uint32_t n, uint32_t pv, bool poll) -> bool {
+        // stage and phase of tile n: pair form two stages, else one
+        const uint32_t st = PAIR ? (n & 1u) : 0u, ph = PAIR ? ((n >> 1) & 1u) : (n & 1u);
+        if (!k_ready && !timed_wait(prof, w_k, [&] { return wait_bar(B_K_FULL + st, ph, abort_flag); })) return false;
+        k_ready = false;
         tc_fence_after();
         const uint32_t d_tmem = tmem + TM_S + (n & 1u) * 128u;
-#pragma unroll
-        for (uint32_t a = 0; a < 4; ++a)
+        uint32_t qa = q_lo, kb = k_lo0 + (PAIR ? st * (K_STAGE >> 4) : 0u);
+        constexpr uint32_t k_atom16 = (PAIR ? K_ATOM : ATOM_BYTES) >> 4;
+#pragma unroll 1
+        for (uint32_t a = 0; a < 4; ++a) {
 #pragma unroll
           for (uint32_t kk = 0; kk < 4; ++kk) {
-            const uint64_t da = umma_smem_desc(sQ + a * ATOM_BYTES + kk * 32u, 16u, 1024u);
-            const uint64_t db = umma_smem_desc(sK + a * ATOM_BYTES + kk * 32u, 16u, 1024u);
-            umma_ss(d_tmem, da, db, IDESC_QK, (a | kk) != 0u);
+            const uint64_t da = mkdesc(qa + kk * 2u, HI_KMAJ), db = mkdesc(kb + kk * 2u, HI_KMAJ);
+            if (PAIR) umma_ss_pair(d_tmem, da, db, IDESC_QK, (a | kk) != 0u);
+            else umma_ss(d_tmem, da, db, IDESC_QK, (a | kk) != 0u);
           }
-        umma_commit(bar_addr(bar_base, BAR_K_EMPTY));
-        umma_commit(bar_addr(bar_base, BAR_S_FULL0 + (n & 1u)));
+          qa += ATOM_BYTES >> 4;
+          kb += k_atom16;
+        }
+        commit(B_S_FULL + (n & 1u));
         return true;
       };
-      ok = ok && issue_qk(0);
+      ok = ok && issue_qk(0, 0, false);
       for (uint32_t n = 0; ok && n < n_local; ++n) {
         if (n + 1 < n_local) {
-          ok = issue_qk(n + 1);
+          ok = issue_qk(n + 1, n, true);
           if (!ok) break;
         }
-        if (!mbar_wait(bar_addr(bar_base, BAR_P_FULL0 + (n & 1u)), (n >> 1) & 1u, abort_flag)) break;
-        if (!mbar_wait(bar_addr(bar_base, BAR_V_FULL), n & 1u, abort_flag)) break;
+        const uint32_t st = PAIR ? (n & 1u) : 0u, ph = PAIR ? ((n >> 1) & 1u) : (n & 1u);
+        if (!p_ready && !timed_wait(prof, w_p, [&] { return wait_bar(B_P_FULL + (n & 1u), (n >> 1) & 1u, abort_flag); })) break;
+        if (!v_ready && !timed_wait(prof, w_v, [&] { return wait_bar(B_V_FULL + st, ph, abort_flag); })) break;
+        p_ready = v_ready = false;
         tc_fence_after();
-        const uint32_t p_tmem = tmem + TM_S + (n & 1u) * 128u;
+        uint32_t p_tmem = tmem + TM_S + (n & 1u) * 128u;
+        uint32_t vb = v_lo0 + (PAIR ? st * (V_STAGE >> 4) : 0u);
+#pragma unroll 1
+        for (uint32_t ks = 0; ks < 8; ks += 2) {
 #pragma unroll
-        for (uint32_t ks = 0; ks < 8; ++ks) {
-          const uint64_t db = umma_smem_desc(sV + ks * 2048u, ATOM_BYTES, 1024u);
-          umma_ts(tmem + TM_O, p_tmem + ks * 8u, db, IDESC_PV, (n | ks) != 0u);
+          for (uint32_t j = 0; j < 2; ++j) {
+            const uint64_t db = mkdesc(vb + j * (2048u >> 4), HI_MNMAJ);
+            if (PAIR) umma_ts_pair(tmem + TM_O, p_tmem + j * 8u, db, IDESC_PV, (n | ks | j) != 0u);
+            else umma_ts(tmem + TM_O, p_tmem + j * 8u, db, IDESC_PV, (n | ks | j) != 0u);
+          }
+          vb += 2u * (2048u >> 4);
+          p_tmem += 16u;
         }
-        umma_commit(bar_addr(bar_base, BAR_V_EMPTY));
-        umma_commit(bar_addr(bar_base, BAR_PV_DONE));
-        // The epilogue must not reuse BAR_PV_DONE: when the last S tile is ready only PV(n-3) is
+        commit(B_V_EMPTY + (n & 1u));
+        // The epilogue must not reuse B_V_EMPTY: when the last S tile is ready only PV(n-3) is
         // known to be complete, so a parity wait on that barrier could alias by two phases.
-        if (n + 1 == n_local) umma_commit(bar_addr(bar_base, BAR_O_FINAL));
+        if (n + 1 == n_local) commit(B_O_FINAL);
+      }
+      if (prof) {
+        stamp_cycles(p, 6, w_k);
+        stamp_cycles(p, 7, w_v);
+        stamp_cycles(p, 8, w_p);
+        stamp_cycles(p, 9, clock64() - t_loop);
       }
     }
   }
@@ -373,7 +516,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   if (warp < SM_WARPS) {
     have_o = __all_sync(0xffffffffu, n_local > 0 && !*abort_flag);
     if (have_o) {
-      have_o = __all_sync(0xffffffffu, mbar_wait(bar_addr(bar_base, BAR_O_FINAL), 0u, abort_flag));
+      have_o = __all_sync(0xffffffffu, wait_bar(B_O_FINAL, 0u, abort_flag));
       tc_fence_after();
     }
   }
@@ -403,8 +546,11 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       // recv[source CTA][row within the owner's share][OBUF_LD floats] in the dead Q/K/V region.
       const uint32_t S = p.n_splits;
       const uint32_t rpc = BM / S;
-      const uint32_t src_rank = cluster_ctarank();
-      const uint32_t owner = r / rpc, rl = r % rpc;
+      // split index of this CTA inside the cluster and cluster rank of the CTA that owns row r
+      // (pair form: the CTA with the same position in its pair)
+      const uint32_t src_rank = PAIR ? (crank >> 1) : crank;
+      const uint32_t owner_split = r / rpc, rl = r % rpc;
+      const uint32_t owner = PAIR ? ((owner_split << 1) | xi) : owner_split;
       const uint32_t dst_row = dsmem_addr(smem_base + OFF_Q + ((src_rank * rpc + rl) * OBUF_LD) * 4u, owner);
 #pragma unroll 1
       for (uint32_t c = 0; c < OPT / 32; ++c) {
@@ -497,7 +643,15 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == W_MMA) tmem_dealloc(tmem, TMEM_COLS);
+  if (PAIR) {
+    // Neither CTA of the pair may free tensor memory or leave while the other can still be the
+    // target of a pair-wide MMA or commit; in cluster-merge mode this barrier also closes the
+    // exchange of partial rows.
+    cluster_sync_all();
+    if (warp == W_MMA) tmem_dealloc_pair(tmem, TMEM_COLS);
+  } else if (warp == W_MMA) {
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
 
   // ------------------------------------------------------------------ split merge inside the cluster
   if (p.n_splits > 1 && p.cluster_merge) {
@@ -506,8 +660,8 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
     // holds all S partials of rows [k*BM/S, (k+1)*BM/S) in its own shared memory and merges them.
     // Nothing touches remote shared memory after the barrier, so no second barrier is needed.
     const uint32_t S = p.n_splits;
-    cluster_sync_all();
-    const uint32_t rank = cluster_ctarank();
+    if (!PAIR) cluster_sync_all();
+    const uint32_t rank = PAIR ? (crank >> 1) : crank;
     const uint32_t rpc = BM / S;
     const float* recv = reinterpret_cast<const float*>(smem + OFF_Q);        // [S][rpc][OBUF_LD]
     const float2* recv_ml = reinterpret_cast<const float2*>(smem + OFF_ML);  // [S][rpc]
@@ -671,40 +825,50 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
 }
 
 cudaError_t sm100_attn_configure() {
-  return cudaFuncSetAttribute(dg_attn_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES));
+  return cudaFuncSetAttribute(dg_attn_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES));
+}
+cudaError_t sm100_pair_configure() {
+  return cudaFuncSetAttribute(dg_attn_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES));
 }
 
-// How many clusters of (1, cluster_y, 1) CTAs of the single-CTA kernel the device can hold at once.
-int sm100_max_active_clusters(uint32_t cluster_y) {
+// How many clusters of (cluster_x, cluster_y, 1) CTAs of the kernel the device can hold at once.
+template <bool PAIR>
+static int max_active_clusters(uint32_t cluster_y) {
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(1, cluster_y, 148);
+  cfg.gridDim = dim3(PAIR ? 2 : 1, cluster_y, 148);
   cfg.blockDim = dim3(one::THREADS);
   cfg.dynamicSmemBytes = SMEM_BYTES;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.x = PAIR ? 2 : 1;
   attr[0].val.clusterDim.y = cluster_y;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, dg_attn_sm100_kernel, &cfg) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&n, dg_attn_sm100_kernel<PAIR>, &cfg) != cudaSuccess) {
     cudaGetLastError();
     return -1;
   }
   return n;
 }
+int sm100_max_active_clusters(uint32_t cluster_y) { return max_active_clusters<false>(cluster_y); }
+int sm100_pair_max_active_clusters(uint32_t cluster_y) { return max_active_clusters<true>(cluster_y); }
 
 uint32_t sm100_query_tiles(uint32_t C, uint32_t G, uint32_t Hkv) { return Hkv * ((C * G + BM - 1) / BM); }
+uint32_t sm100_pair_query_tiles(uint32_t C, uint32_t G, uint32_t Hkv) {
+  const uint32_t tph = (C * G + BM - 1) / BM;
+  return Hkv * ((tph + 1u) & ~1u);
+}
 
 uint32_t sm100_key_tiles(const MaskParams& mk) {
   const TileSched t = tile_sched(mk, 0);
   return t.nA + t.nB;
 }
 
-cudaError_t launch_attn_sm100(const AttnParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
-                              cudaStream_t st) {
-  const dim3 grid(sm100_query_tiles(p.C, p.G, p.Hkv), p.n_splits);
+template <bool PAIR>
+static cudaError_t launch(const AttnParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, cudaStream_t st) {
+  const dim3 grid(PAIR ? sm100_pair_query_tiles(p.C, p.G, p.Hkv) : sm100_query_tiles(p.C, p.G, p.Hkv), p.n_splits);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(one::THREADS);
@@ -717,16 +881,27 @@ cudaError_t launch_attn_sm100(const AttnParams& p, const CUtensorMap& tm_k, cons
   attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
   ++n_attr;
-  if (p.cluster_merge && p.n_splits > 1) {
+  const bool clustered_splits = p.cluster_merge && p.n_splits > 1;
+  if (PAIR || clustered_splits) {
     attr[n_attr].id = cudaLaunchAttributeClusterDimension;
-    attr[n_attr].val.clusterDim.x = 1;
-    attr[n_attr].val.clusterDim.y = p.n_splits;
+    attr[n_attr].val.clusterDim.x = PAIR ? 2 : 1;
+    attr[n_attr].val.clusterDim.y = clustered_splits ? p.n_splits : 1;
     attr[n_attr].val.clusterDim.z = 1;
     ++n_attr;
   }
   cfg.attrs = attr;
   cfg.numAttrs = n_attr;
-  return cudaLaunchKernelEx(&cfg, dg_attn_sm100_kernel, p, tm_k, tm_v);
+  return cudaLaunchKernelEx(&cfg, dg_attn_sm100_kernel<PAIR>, p, tm_k, tm_v);
+}
+
+cudaError_t launch_attn_sm100(const AttnParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
+                              cudaStream_t st) {
+  return launch<false>(p, tm_k, tm_v, st);
+}
+// tm_k64: K tensor map with boxes {64 d, 64 keys, 1}
+cudaError_t launch_attn_sm100_pair(const AttnParams& p, const CUtensorMap& tm_k64, const CUtensorMap& tm_v,
+                                   cudaStream_t st) {
+  return launch<true>(p, tm_k64, tm_v, st);
 }
 
 }  // namespace dg

@@ -1,5 +1,5 @@
-// Definitions shared by the single-CTA and the CTA-pair variants of the head_dim-256 attention
-// kernel: tile geometry, key-tile schedule, barrier slots, phase stamps.
+// Definitions of the head_dim-256 attention kernel that the host side shares: tile geometry,
+// shared-memory map, key-tile schedule, phase stamps.
 #pragma once
 #include <cuda.h>
 
@@ -26,27 +26,7 @@ constexpr uint32_t SMEM_BYTES = OFF_ML + 1024 + 1024;   // + alignment slack
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TM_S = 0;            // two S buffers of 128 columns
 constexpr uint32_t TM_O = 256;          // O accumulator, 256 columns
-// CTA-pair variant: warps 0-7 = two softmax warpgroups (warp w and w+4 share the 32 query rows of
-// TMEM quadrant w & 3; the first handles key columns 0-63 of every tile, the second 64-127),
-// 8: K loader, 9: V loader, 10: TMEM allocation + the MMA-issuing thread
-constexpr uint32_t N_SM_WARPS = 8;
-constexpr uint32_t WARP_K = 8, WARP_V = 9, WARP_MMA = 10;
-constexpr uint32_t N_THREADS = 352;
 constexpr float RESCALE_THRESHOLD = 8.0f;   // log2 units
-
-// barrier slots (8 bytes each) inside the barrier block
-enum : uint32_t {
-  BAR_Q = 0,
-  BAR_K_FULL = 1,
-  BAR_K_EMPTY = 2,
-  BAR_V_FULL = 3,
-  BAR_V_EMPTY = 4,
-  BAR_S_FULL0 = 5,   // +1 for buffer 1
-  BAR_P_FULL0 = 7,   // +1 for buffer 1
-  BAR_PV_DONE = 9,   // one phase per key tile; only waited on when O must be rescaled
-  BAR_O_FINAL = 10,  // single phase: every PV of this CTA has completed
-  N_BARS = 11
-};
 
 struct TileSched {
   uint32_t a0, nA, b0, nB;
@@ -77,18 +57,29 @@ __device__ __forceinline__ uint32_t bar_addr(uint32_t bar_base, uint32_t idx) { 
 
 // Phase time stamps (globaltimer, ns) of one CTA, written by thread 0 when a stamp buffer is given:
 // 0 start, 1 set-up done, 2 Q prologue done, 3 main loop done, 4 epilogue done, 5 merge done.
+// Slots 6-11 hold SM-clock cycles that single threads spent waiting inside the key loop:
+// 6 MMA issuer on K tiles, 7 on V tiles, 8 on P (softmax output), 9 its whole loop,
+// 10 softmax thread 0 on S (scores), 11 softmax thread 0 on the rescale barrier.
+constexpr uint32_t STAMP_SLOTS = 16;
 __device__ __forceinline__ void stamp(const AttnParams& p, uint32_t slot) {
   if (p.stamps != nullptr && threadIdx.x == 0) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    p.stamps[(size_t(blockIdx.y) * gridDim.x + blockIdx.x) * 8 + slot] = t;
+    p.stamps[(size_t(blockIdx.y) * gridDim.x + blockIdx.x) * STAMP_SLOTS + slot] = t;
   }
 }
-
-
-// named barrier shared by the two warps that own the same 32 query rows
-__device__ __forceinline__ void pair_sync(uint32_t smw) {
-  asm volatile("bar.sync %0, 64;" ::"r"(smw + 1u) : "memory");
+__device__ __forceinline__ void stamp_cycles(const AttnParams& p, uint32_t slot, long long cycles) {
+  if (p.stamps != nullptr)
+    p.stamps[(size_t(blockIdx.y) * gridDim.x + blockIdx.x) * STAMP_SLOTS + slot] = (unsigned long long)cycles;
+}
+// runs a wait and, when profiling, adds the cycles it took to acc
+template <class F>
+__device__ __forceinline__ bool timed_wait(bool prof, long long& acc, F f) {
+  if (!prof) return f();
+  const long long t = clock64();
+  const bool r = f();
+  acc += clock64() - t;
+  return r;
 }
 
 

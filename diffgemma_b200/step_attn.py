@@ -92,8 +92,9 @@ class Context:
     def force_general(self, on: bool) -> None:
         check(self.lib.dg_ctx_force_general(self.h, int(on)), "dg_ctx_force_general")
 
-    def set_pair_mode(self, on: bool) -> None:
-        check(self.lib.dg_ctx_set_pair_mode(self.h, int(on)), "dg_ctx_set_pair_mode")
+    def set_pair_mode(self, on: bool | None) -> None:
+        """True: CTA-pair form of the tensor kernel, False: single-CTA form, None: automatic (default)."""
+        check(self.lib.dg_ctx_set_pair_mode(self.h, 2 if on is None else int(bool(on))), "dg_ctx_set_pair_mode")
 
     def set_splits(self, n: int) -> None:
         check(self.lib.dg_ctx_set_splits(self.h, n), "dg_ctx_set_splits")

@@ -107,9 +107,11 @@ int32_t dg_uses_tensor_path(const dg_layer_desc* desc);
 /* Force the general (CUDA-core) kernel for every geometry (1) or restore the default (0).
  * Used by tests to cross-check the two kernels.                                                */
 int32_t dg_ctx_force_general(dg_ctx* ctx, int32_t on);
-/* Select the tensor-path kernel variant: 0 = one CTA per query tile, 1 = CTA pairs
- * (tcgen05 cta_group::2: two query tiles share every staged K/V tile).                          */
-int32_t dg_ctx_set_pair_mode(dg_ctx* ctx, int32_t on);
+/* Select the tensor-path kernel form: 0 = one CTA per query tile, 1 = CTA pairs (tcgen05
+ * cta_group::2: two query tiles of one KV head share every staged K/V tile, each CTA staging half
+ * of it), 2 = automatic (default: pairs when a KV head has at least two query tiles and the key
+ * range is at least 96 tiles of 128 keys).                                                        */
+int32_t dg_ctx_set_pair_mode(dg_ctx* ctx, int32_t mode);
 /* Number of thread-block clusters of the tensor-path kernel (pair = 0: (1, cluster_y, 1) CTAs,
  * pair = 1: (2, cluster_y, 1) CTAs) that can be resident on the device at once; negative on error. */
 int32_t dg_ctx_max_active_clusters(dg_ctx* ctx, int32_t pair, uint32_t cluster_y);
@@ -240,9 +242,12 @@ uint32_t dg_ctx_last_launch_count(const dg_ctx* ctx);
  * bracketed by a CUDA event pair on the launching stream, up to max_launches launches;
  * dg_ctx_kernel_time synchronises and returns their summed duration and count.                  */
 int32_t dg_ctx_kernel_timing(dg_ctx* ctx, int32_t on, uint32_t max_launches);
-/* Measurement aid: with a non-NULL device buffer of CTAs x 8 uint64, thread 0 of every CTA of the
+/* Measurement aid: with a non-NULL device buffer of CTAs x 16 uint64, thread 0 of every CTA of the
  * tensor-path kernel stores globaltimer stamps (ns) at its phase boundaries: 0 start, 1 set-up done,
- * 2 Q prologue done, 3 key loop done, 4 epilogue done, 5 merge done.  NULL switches it off.       */
+ * 2 Q prologue done, 3 key loop done, 4 epilogue done, 5 merge done; slots 6-11 hold SM-clock
+ * cycles single threads spent waiting inside the key loop (6 MMA issuer on K, 7 on V, 8 on P,
+ * 9 the issuer's whole loop, 10 softmax thread 0 on S, 11 on the rescale barrier).  The stamps
+ * cost time; NULL switches them off.                                                             */
 int32_t dg_ctx_phase_stamps(dg_ctx* ctx, void* device_buffer);
 int32_t dg_ctx_kernel_time(dg_ctx* ctx, double* total_ms, uint32_t* launches);
 

@@ -127,11 +127,16 @@ def test_denoise_parity(ctx, P, Hkv, W, mode, scale, canvas, weights, vnorm):
     ref = util.run_oracle(case)
     assert CanvasAttention(ctx, layer).uses_tensor_path
     ctx.force_general(False)
-    for splits in (0, 1, 3):
-        ctx.set_splits(splits)
-        got = util.run_gpu(ctx, case)
-        util.assert_close(got, ref, f"tensor path splits={splits}")
-    ctx.set_splits(0)
+    try:
+        for pair in (None, False):   # automatic choice (CTA pairs where they apply), then the single-CTA form
+            ctx.set_pair_mode(pair)
+            for splits in (0, 1, 3):
+                ctx.set_splits(splits)
+                got = util.run_gpu(ctx, case)
+                util.assert_close(got, ref, f"tensor path pair={pair} splits={splits}")
+    finally:
+        ctx.set_splits(0)
+        ctx.set_pair_mode(None)
     ctx.force_general(True)
     got = util.run_gpu(ctx, case)
     ctx.force_general(False)
@@ -385,12 +390,12 @@ def test_pair_kernel_parity(ctx, P, Hkv, W, mode, scale, canvas):
     ref = util.run_oracle(case)
     ctx.set_pair_mode(True)
     try:
-        for splits in (0, 1, 2, 3):
+        for splits in (0, 1, 2, 3, 4):
             ctx.set_splits(splits)
             util.assert_close(util.run_gpu(ctx, case), ref, f"pair kernel splits={splits}")
     finally:
         ctx.set_splits(0)
-        ctx.set_pair_mode(False)
+        ctx.set_pair_mode(None)
     assert ctx.device_status()[0] == 0
 
 
