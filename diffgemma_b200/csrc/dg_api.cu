@@ -53,7 +53,7 @@ struct dg_ctx {
   cudaStream_t stream = nullptr;
   DevStatus* d_status = nullptr;
   float2* rope_table = nullptr;        // [kRopeSlots][kMaxCanvas][kMaxRotHalf]
-  uint32_t* counters = nullptr;        // [kMaxQueryTiles], zero between launches
+  uint32_t* counters = nullptr;        // [kCounterSlots], zero between launches
   float* ws_o = nullptr;               // split partials
   float* ws_ml = nullptr;
   size_t ws_splits = 0, ws_rows = 0;   // capacity of ws_o / ws_ml: splits x rows (x 256 / x 2)
@@ -89,6 +89,7 @@ struct dg_kv {
 
 constexpr uint32_t kRopeSlots = 8;
 constexpr uint32_t kMaxQueryTiles = 4096;
+constexpr uint32_t kCounterSlots = kMaxQueryTiles * 8 + 1;   // (query tile, row slice) arrival counters + the self-test flag
 
 // ------------------------------------------------------------------------------------------
 // driver entry point for tensor-map encoding (no link-time dependency on libcuda)
@@ -270,8 +271,8 @@ extern "C" int32_t dg_ctx_create(int32_t device, dg_ctx** out) {
   if (e == cudaSuccess) e = cudaMalloc(&c->d_status, sizeof(DevStatus));
   if (e == cudaSuccess) e = cudaMemset(c->d_status, 0, sizeof(DevStatus));
   if (e == cudaSuccess) e = cudaMalloc(&c->rope_table, size_t(kRopeSlots) * kMaxCanvas * kMaxRotHalf * sizeof(float2));
-  if (e == cudaSuccess) e = cudaMalloc(&c->counters, kMaxQueryTiles * sizeof(uint32_t));
-  if (e == cudaSuccess) e = cudaMemset(c->counters, 0, kMaxQueryTiles * sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMalloc(&c->counters, kCounterSlots * sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMemset(c->counters, 0, kCounterSlots * sizeof(uint32_t));
   if (e == cudaSuccess) e = sm100_attn_configure();
   if (e == cudaSuccess) e = sm100_pair_configure();
   if (e != cudaSuccess) {
@@ -348,7 +349,7 @@ extern "C" int32_t dg_ctx_selftest_wait_timeout(dg_ctx* c, uint64_t limit_cycles
   if (limit_cycles == 0 || limit_cycles > 2000000000ull) return fail(DG_ERR_INVALID_ARG, "limit must be in 1..2e9 cycles");
   DG_CUDA(cudaSetDevice(c->device));
   // the flag is one of the (always zero between launches) query-tile counters: nothing sets it
-  launch_selftest_wait(c->counters + (kMaxQueryTiles - 1), (long long)limit_cycles, c->d_status, c->stream);
+  launch_selftest_wait(c->counters + (kCounterSlots - 1), (long long)limit_cycles, c->d_status, c->stream);
   DG_CUDA(cudaGetLastError());
   return DG_OK;
 }
@@ -617,10 +618,15 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
   const uint32_t q_tiles = pair ? sm100_pair_query_tiles(p.C, p.G, p.Hkv) : sm100_query_tiles(p.C, p.G, p.Hkv);
   if (q_tiles > kMaxQueryTiles) return fail(DG_ERR_UNSUPPORTED, "too many query tiles");
   p.n_splits = choose_splits(c, q_tiles, k_tiles);
-  // cluster merge only for the single-CTA form: pairs x 4 splits would need clusters of 8 CTAs, of
-  // which too few are co-resident
-  p.cluster_merge = (!pair && (p.n_splits == 2 || p.n_splits == 4 || p.n_splits == 8)) ? 1u : 0u;
-  if (p.n_splits > 1 && !p.cluster_merge) {
+  // Split merge: consecutive splits of a query tile form a thread-block cluster and merge through
+  // shared memory; what is left meets in the workspace.  Clusters stay at 4 CTAs in the pair form
+  // (2 x 2): too few clusters of 8 are co-resident on the device.
+  p.cluster_splits = 1;
+  if (p.n_splits % 2 == 0) {
+    if (pair) p.cluster_splits = 2;
+    else if (p.n_splits == 2 || p.n_splits == 4 || p.n_splits == 8) p.cluster_splits = p.n_splits;
+  }
+  if (p.n_splits / p.cluster_splits > 1) {
     const int32_t r = ensure_split_ws(c, p.n_splits, p.C * p.Hq);
     if (r != DG_OK) return r;
     p.ws_o = c->ws_o;
@@ -1028,6 +1034,7 @@ extern "C" int32_t dg_attention_static_scratch(dg_ctx* c, const dg_layer_desc* d
   uint32_t splits = choose_splits(c, q_tiles, sm100_key_tiles(p.mask));
   if (splits > kStaticSplits) splits = kStaticSplits;
   p.n_splits = splits;
+  p.cluster_splits = 1;   // every split meets in the scratch array
   p.ws_o = scratch;
   p.ws_ml = scratch + kStaticOFloats;
   p.ws_counters = reinterpret_cast<uint32_t*>(scratch + kStaticOFloats + kStaticMlFloats);

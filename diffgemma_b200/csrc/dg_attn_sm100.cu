@@ -104,7 +104,10 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   const MaskParams mk = p.mask;
 
   // position in the cluster: (1, S, 1) or, in the pair form, (2, S, 1) with x fastest
-  const uint32_t crank = (PAIR || (p.cluster_merge && p.n_splits > 1)) ? cluster_ctarank() : 0u;
+  const uint32_t crank = (PAIR || p.cluster_splits > 1) ? cluster_ctarank() : 0u;
+  // split merge, level 1: cs consecutive splits form a cluster and merge through shared memory;
+  // level 2: the n_splits / cs groups meet in the global workspace
+  const uint32_t cs = p.cluster_splits, n_groups = p.n_splits / cs, grp = split / cs;
   const uint32_t xi = PAIR ? (crank & 1u) : 0u;          // position inside the pair
   const uint32_t leader = crank & ~1u;                    // pair form: cluster rank of the pair's leader
   const bool is_leader = xi == 0u;
@@ -523,7 +526,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   // Cluster merge: partial rows are pushed into the owner CTA's Q/K/V region, which must be dead
   // in EVERY CTA of the cluster first - all of this CTA's MMAs are complete once its softmax
   // warps have seen O_FINAL, and this barrier collects that from all CTAs.
-  if (p.cluster_merge && p.n_splits > 1) cluster_sync_all();
+  if (cs > 1) cluster_sync_all();
   if (warp < SM_WARPS) {
     const uint32_t R = mt * BM + r;
     const bool valid = R < rows_per_head;
@@ -538,14 +541,13 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
 #pragma unroll
     for (uint32_t k = 0; k < NTR; ++k) l_tot += xch_l[r * NTR + k];
     const bool direct = (p.n_splits == 1);
-    const bool via_dsmem = (p.cluster_merge != 0u) && !direct;
+    const bool via_dsmem = cs > 1;
     if (via_dsmem) {
       // The partial stays on chip.  Row r of the query tile is merged by CTA r / (BM / S) of the
       // cluster, so each thread pushes its columns of the un-normalised O row (and one thread the
       // (m, l) pair) straight into that CTA's receive buffer with remote shared-memory stores:
       // recv[source CTA][row within the owner's share][OBUF_LD floats] in the dead Q/K/V region.
-      const uint32_t S = p.n_splits;
-      const uint32_t rpc = BM / S;
+      const uint32_t rpc = BM / cs;
       // split index of this CTA inside the cluster and cluster rank of the CTA that owns row r
       // (pair form: the CTA with the same position in its pair)
       const uint32_t src_rank = PAIR ? (crank >> 1) : crank;
@@ -653,25 +655,29 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
     tmem_dealloc(tmem, TMEM_COLS);
   }
 
-  // ------------------------------------------------------------------ split merge inside the cluster
-  if (p.n_splits > 1 && p.cluster_merge) {
-    // The n_splits CTAs of this query tile are one thread-block cluster (cluster dims (1, S, 1)).
-    // Every CTA has pushed each partial row to the CTA that owns it; after the cluster barrier CTA k
-    // holds all S partials of rows [k*BM/S, (k+1)*BM/S) in its own shared memory and merges them.
-    // Nothing touches remote shared memory after the barrier, so no second barrier is needed.
-    const uint32_t S = p.n_splits;
+  // ------------------------------------------------------------------ split merge, level 1: inside the cluster
+  // rows of the query tile this CTA is responsible for in level 2 (all of them without clusters)
+  uint32_t row0 = 0, n_rows = BM;
+  if (cs > 1) {
+    // The cs CTAs that hold consecutive splits of this query tile are one thread-block cluster
+    // (cluster dims (1, cs, 1), pair form (2, cs, 1)).  Every CTA has pushed each partial row to the
+    // CTA that owns it; after the cluster barrier CTA k holds all cs partials of rows
+    // [k*BM/cs, (k+1)*BM/cs) in its own shared memory and merges them.  Nothing touches remote
+    // shared memory after the barrier, so no second barrier is needed.
     if (!PAIR) cluster_sync_all();
     const uint32_t rank = PAIR ? (crank >> 1) : crank;
-    const uint32_t rpc = BM / S;
-    const float* recv = reinterpret_cast<const float*>(smem + OFF_Q);        // [S][rpc][OBUF_LD]
-    const float2* recv_ml = reinterpret_cast<const float2*>(smem + OFF_ML);  // [S][rpc]
+    const uint32_t rpc = BM / cs;
+    row0 = rank * rpc;
+    n_rows = rpc;
+    const float* recv = reinterpret_cast<const float*>(smem + OFF_Q);        // [cs][rpc][OBUF_LD]
+    const float2* recv_ml = reinterpret_cast<const float2*>(smem + OFF_ML);  // [cs][rpc]
     for (uint32_t rl = warp; rl < rpc; rl += THREADS / 32) {
       const uint32_t rr = rank * rpc + rl;
       const uint32_t R = mt * BM + rr;
       if (R >= rows_per_head) continue;
       const size_t orow = size_t(R / p.G) * p.Hq + kvh * p.G + R % p.G;
       float2 ml = make_float2(-INFINITY, 0.f);
-      if (lane < S) ml = recv_ml[lane * rpc + rl];
+      if (lane < cs) ml = recv_ml[lane * rpc + rl];
       float mg = ml.x;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, o));
@@ -682,14 +688,20 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       float acc[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-      for (uint32_t s2 = 0; s2 < S; ++s2) {
+      for (uint32_t s2 = 0; s2 < cs; ++s2) {
         const float w = __shfl_sync(0xffffffffu, w_mine, int(s2));
         const float4* src = reinterpret_cast<const float4*>(recv + (s2 * rpc + rl) * OBUF_LD + lane * 8);
         const float4 a = src[0], bq = src[1];
         acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * a.z; acc[3] += w * a.w;
         acc[4] += w * bq.x; acc[5] += w * bq.y; acc[6] += w * bq.z; acc[7] += w * bq.w;
       }
-      if (p.out) {
+      if (n_groups > 1) {
+        // the group's merged partial (still un-normalised, relative to mg) goes to the workspace
+        float4* dst = reinterpret_cast<float4*>(p.ws_o + (size_t(grp) * rows_total + orow) * HD + lane * 8);
+        dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        if (lane == 0) reinterpret_cast<float2*>(p.ws_ml)[size_t(grp) * rows_total + orow] = make_float2(mg, lg);
+      } else if (p.out) {
         const float inv = lg > 0.f ? 1.0f / lg : 0.f;
         uint4 w4;
         w4.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
@@ -707,17 +719,23 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
         }
       }
     }
-  } else if (p.n_splits > 1) {
-    // ---------------------------------------------------------------- split merge by the last CTA
+    if (n_groups > 1) __threadfence();
+  }
+  if (n_groups > 1) {
+    // ---------------------------------------------------------------- level 2: the last group to arrive merges
+    // one arrival counter per (query tile, row slice); the partials of the n_groups groups are in
+    // the workspace
+    const uint32_t S = n_groups;
+    uint32_t* counter = p.ws_counters + blockIdx.x * cs + (cs > 1 ? (PAIR ? (crank >> 1) : crank) : 0u);
+    __syncthreads();
     if (tid == 0) {
       __threadfence();
-      const uint32_t old = atomicAdd(p.ws_counters + blockIdx.x, 1u);
-      ctl[2] = (old == p.n_splits - 1u) ? 1u : 0u;
+      const uint32_t old = atomicAdd(counter, 1u);
+      ctl[2] = (old == S - 1u) ? 1u : 0u;
     }
     __syncthreads();
     if (ctl[2]) {
       __threadfence();
-      const uint32_t S = p.n_splits;
       const float2* ml_all = reinterpret_cast<const float2*>(p.ws_ml);
       // Phase A: one thread per row turns the S (m, l) pairs into merge weights, kept in shared
       // memory (the Q tile is dead): wsm[row][s] = 2^(m_s - m_g), plus m_g and l_g per row.
@@ -725,8 +743,8 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       float* wl = wsm + BM * 32;                                        // [BM][32]
       float* row_mg = wl + BM * 32;                                     // [BM]
       float* row_lg = row_mg + BM;                                      // [BM]
-      if (tid < BM) {
-        const uint32_t R = mt * BM + tid;
+      if (tid < n_rows) {
+        const uint32_t R = mt * BM + row0 + tid;
         const bool live = R < rows_per_head;
         const uint32_t Rc = live ? R : mt * BM;
         const size_t orow = size_t(Rc / p.G) * p.Hq + kvh * p.G + Rc % p.G;
@@ -761,14 +779,14 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       // flight, so the pass is bound by L2 bandwidth rather than by a round trip per row and split.
       constexpr uint32_t NW = THREADS / 32;
       constexpr uint32_t RK = 2;
-      for (uint32_t r0 = warp * RK; r0 < BM; r0 += NW * RK) {
+      for (uint32_t r0 = warp * RK; r0 < n_rows; r0 += NW * RK) {
         size_t orow[RK];
         bool live[RK];
         float acc[RK][8];
 #pragma unroll
         for (uint32_t k = 0; k < RK; ++k) {
-          const uint32_t R = mt * BM + r0 + k;
-          live[k] = (r0 + k < BM) && (R < rows_per_head);
+          const uint32_t R = mt * BM + row0 + r0 + k;
+          live[k] = (r0 + k < n_rows) && (R < rows_per_head);
           const uint32_t Rc = live[k] ? R : mt * BM;
           orow[k] = size_t(Rc / p.G) * p.Hq + kvh * p.G + Rc % p.G;
 #pragma unroll
@@ -789,7 +807,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
           for (uint32_t k = 0; k < RK; ++k)
 #pragma unroll
             for (uint32_t j = 0; j < 4; ++j) {
-              const uint32_t rr = (r0 + k < BM) ? r0 + k : BM - 1;
+              const uint32_t rr = (r0 + k < n_rows) ? r0 + k : n_rows - 1;
               const float w = (s0 + j < S) ? wsm[rr * 32 + s0 + j] : 0.f;
               acc[k][0] += w * a[k][j].x; acc[k][1] += w * a[k][j].y; acc[k][2] += w * a[k][j].z; acc[k][3] += w * a[k][j].w;
               acc[k][4] += w * bq[k][j].x; acc[k][5] += w * bq[k][j].y; acc[k][6] += w * bq[k][j].z; acc[k][7] += w * bq[k][j].w;
@@ -818,7 +836,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
           }
         }
       }
-      if (tid == 0) p.ws_counters[blockIdx.x] = 0u;   // ready for the next launch
+      if (tid == 0) *counter = 0u;   // ready for the next launch
     }
   }
   stamp(p, 5);
@@ -881,11 +899,11 @@ static cudaError_t launch(const AttnParams& p, const CUtensorMap& tm_k, const CU
   attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
   ++n_attr;
-  const bool clustered_splits = p.cluster_merge && p.n_splits > 1;
+  const bool clustered_splits = p.cluster_splits > 1;
   if (PAIR || clustered_splits) {
     attr[n_attr].id = cudaLaunchAttributeClusterDimension;
     attr[n_attr].val.clusterDim.x = PAIR ? 2 : 1;
-    attr[n_attr].val.clusterDim.y = clustered_splits ? p.n_splits : 1;
+    attr[n_attr].val.clusterDim.y = p.cluster_splits;
     attr[n_attr].val.clusterDim.z = 1;
     ++n_attr;
   }

@@ -127,7 +127,7 @@ struct AttnParams {
   uint32_t C, Hq, Hkv, G, D;
   uint32_t q_prenormed;
   uint32_t n_splits;
-  uint32_t cluster_merge;        // 1: the n_splits CTAs of a query tile form a cluster and merge through DSMEM
+  uint32_t cluster_splits;       // consecutive splits per thread-block cluster (divides n_splits; 1 = no cluster merge)
   uint32_t rot_half, pair_off;
   float scale_log2;              // softmax_scale * log2(e)
   float eps;
