@@ -53,6 +53,13 @@ struct dg_ctx {
   cudaStream_t stream = nullptr;
   DevStatus* d_status = nullptr;
   float2* rope_table = nullptr;        // [kRopeSlots][kMaxCanvas][kMaxRotHalf]
+  // what each table slot currently holds: denoise steps repeat at the same positions, so the table
+  // of a slot is rewritten only when this key changes
+  struct RopeKey {
+    bool valid = false;
+    uint32_t kv_len = 0, canvas = 0, rotary_dim = 0, pairing = 0, head_dim = 0;
+    float theta = 0.f;
+  } rope_key[8];
   uint32_t* counters = nullptr;        // [kCounterSlots], zero between launches
   float* ws_o = nullptr;               // split partials
   float* ws_ml = nullptr;
@@ -562,6 +569,7 @@ struct AttnCall {
   const void* qw = nullptr;
   const float2* table = nullptr;
   bool q_prenormed = false;
+  bool early_q = false;          // the table was not written by the append launched just before
   const uint8_t* attend = nullptr;
   void* out = nullptr;           // bf16, or NULL for partial
   float* out_o = nullptr;
@@ -577,6 +585,7 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
   p.q = static_cast<const __nv_bfloat16*>(a.q);
   p.qw = static_cast<const __nv_bfloat16*>(a.qw);
   p.rope_table = a.table;
+  p.early_q = a.early_q ? 1u : 0u;
   p.cache_k = kv->k;
   p.cache_v = kv->v;
   p.attend = a.attend;
@@ -669,12 +678,25 @@ static int32_t denoise_one(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint32_
     a.q = c->stage_q;
     a.q_prenormed = true;
   } else {
-    r = do_append(c, d, kv, kv_len, d.canvas, nullptr, nullptr, k, nullptr, v, nullptr, nullptr, kw, table);
+    dg_ctx::RopeKey& key = c->rope_key[slot % kRopeSlots];
+    const bool cached = key.valid && key.kv_len == kv_len && key.canvas == d.canvas && key.rotary_dim == d.rotary_dim &&
+                        key.pairing == d.rope_pairing && key.head_dim == d.head_dim && key.theta == d.rope_theta;
+    r = do_append(c, d, kv, kv_len, d.canvas, nullptr, nullptr, k, nullptr, v, nullptr, nullptr, kw, cached ? nullptr : table);
     if (r != DG_OK) return r;
+    if (!cached) {
+      key.valid = true;
+      key.kv_len = kv_len;
+      key.canvas = d.canvas;
+      key.rotary_dim = d.rotary_dim;
+      key.pairing = d.rope_pairing;
+      key.head_dim = d.head_dim;
+      key.theta = d.rope_theta;
+    }
     a.q = q;
     a.qw = qw;
     a.table = table;
     a.q_prenormed = false;
+    a.early_q = cached;
   }
   a.kv_len = kv_len;
   a.attend = attend;

@@ -164,7 +164,10 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   // Programmatic dependent launch: everything above overlapped the tail of the preceding kernel
   // on the stream (the canvas K/V append, which also writes the RoPE table); its results are
   // needed from here on.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // The softmax warps read Q, its norm weight and the RoPE table: when none of those comes from
+  // that kernel (the table is cached across steps at the same positions) they skip the wait, so the
+  // whole Q prologue overlaps the append; the loaders always wait before they touch the cache.
+  if (!(p.early_q && warp < SM_WARPS)) asm volatile("griddepcontrol.wait;" ::: "memory");
   stamp(p, 1);
   volatile uint32_t* abort_flag = &ctl[1];
   const bool prof = p.stamps != nullptr;

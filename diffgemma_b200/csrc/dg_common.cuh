@@ -126,6 +126,7 @@ struct AttnParams {
   MaskParams mask;
   uint32_t C, Hq, Hkv, G, D;
   uint32_t q_prenormed;
+  uint32_t early_q;              // 1: nothing the Q prologue reads is written by the preceding kernel on the stream
   uint32_t n_splits;
   uint32_t cluster_splits;       // consecutive splits per thread-block cluster (divides n_splits; 1 = no cluster merge)
   uint32_t rot_half, pair_off;
