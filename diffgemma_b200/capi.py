@@ -59,11 +59,14 @@ SIGNATURES = {
     "dg_ctx_set_pair_mode": (_i32, [_vp, _i32]),
     "dg_ctx_max_active_clusters": (_i32, [_vp, _i32, _u32]),
     "dg_kv_create": (_i32, [_vp, _pd, _u64, C.POINTER(_vp)]),
+    "dg_kv_create_ring": (_i32, [_vp, _pd, _u32, C.POINTER(_vp)]),
+    "dg_kv_ring_mask": (_u32, [_vp]),
     "dg_kv_destroy": (_i32, [_vp]),
     "dg_kv_capacity": (_u64, [_vp]),
     "dg_kv_load_prefix": (_i32, [_vp, _vp, _vp, _u64, _u64]),
     "dg_kv_read": (_i32, [_vp, _vp, _vp, _u64, _u64]),
     "dg_kv_append": (_i32, [_vp, _pd, _vp, _u64, _u32, _vp, _vp, _vp]),
+    "dg_kv_append_guarded": (_i32, [_vp, _pd, _vp, _u64, _u32, _vp, _vp, _vp, _u32]),
     "dg_qk_rope_kv": (_i32, [_vp, _pd, _vp, _u32, _vp, _vp, _vp, _vp, _vp]),
     "dg_attention": (_i32, [_vp, _pd, _vp, _u32, _vp, _vp]),
     "dg_attention_static_scratch": (_i32, [_vp, _pd, _vp, _u32, _vp, _vp]),

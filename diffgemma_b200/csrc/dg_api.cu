@@ -88,6 +88,7 @@ struct dg_kv {
   __nv_bfloat16* k = nullptr;   // [Hkv][cap][D]
   __nv_bfloat16* v = nullptr;
   uint64_t cap = 0;
+  uint32_t ring_mask = 0;       // 0: linear cache; else slots - 1 of a ring (slot = pos & ring_mask)
   uint32_t Hkv = 0, D = 0;
   bool has_tmap = false;
   CUtensorMap tm_k, tm_v;
@@ -426,7 +427,7 @@ extern "C" int32_t dg_ctx_kernel_time(dg_ctx* c, double* total_ms, uint32_t* lau
 // ------------------------------------------------------------------------------------------
 // KV cache
 // ------------------------------------------------------------------------------------------
-extern "C" int32_t dg_kv_create(dg_ctx* c, const dg_layer_desc* d, uint64_t capacity_tokens, dg_kv** out) {
+static int32_t kv_create(dg_ctx* c, const dg_layer_desc* d, uint64_t capacity_tokens, uint32_t ring_mask, dg_kv** out) {
   if (!c || !out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
   *out = nullptr;
   int32_t r = check_desc(d);
@@ -437,6 +438,7 @@ extern "C" int32_t dg_kv_create(dg_ctx* c, const dg_layer_desc* d, uint64_t capa
   if (!kv) return fail(DG_ERR_INVALID_ARG, "out of host memory");
   kv->ctx = c;
   kv->cap = (capacity_tokens + 127) / 128 * 128;
+  kv->ring_mask = ring_mask;
   kv->Hkv = d->n_kv_heads;
   kv->D = d->head_dim;
   const size_t bytes = size_t(kv->Hkv) * kv->cap * kv->D * 2;
@@ -462,6 +464,15 @@ extern "C" int32_t dg_kv_create(dg_ctx* c, const dg_layer_desc* d, uint64_t capa
   *out = kv;
   return DG_OK;
 }
+extern "C" int32_t dg_kv_create(dg_ctx* c, const dg_layer_desc* d, uint64_t capacity_tokens, dg_kv** out) {
+  return kv_create(c, d, capacity_tokens, 0u, out);
+}
+extern "C" int32_t dg_kv_create_ring(dg_ctx* c, const dg_layer_desc* d, uint32_t ring_slots, dg_kv** out) {
+  if (ring_slots < 256 || (ring_slots & (ring_slots - 1)) != 0)
+    return fail(DG_ERR_INVALID_ARG, "ring_slots must be a power of two, at least 256");
+  return kv_create(c, d, ring_slots, ring_slots - 1u, out);
+}
+extern "C" uint32_t dg_kv_ring_mask(const dg_kv* kv) { return kv ? kv->ring_mask : 0u; }
 
 extern "C" int32_t dg_kv_destroy(dg_kv* kv) {
   if (!kv) return DG_OK;
@@ -476,35 +487,74 @@ extern "C" int32_t dg_kv_destroy(dg_kv* kv) {
 }
 extern "C" uint64_t dg_kv_capacity(const dg_kv* kv) { return kv ? kv->cap : 0; }
 
+// A run of positions [pos0, pos0 + n) as at most two runs of contiguous cache slots.  In a ring only the
+// last `cap` positions of the run still have a slot (older ones were overwritten by them).
+struct SlotRuns {
+  uint64_t skip = 0;                 // leading positions of the run that no longer have a slot
+  uint64_t slot[2] = {0, 0}, len[2] = {0, 0};
+};
+static SlotRuns slot_runs(const dg_kv* kv, uint64_t pos0, uint64_t n) {
+  SlotRuns r;
+  if (kv->ring_mask == 0) {
+    r.slot[0] = pos0;
+    r.len[0] = n;
+    return r;
+  }
+  if (n > kv->cap) {
+    r.skip = n - kv->cap;
+    pos0 += r.skip;
+    n = kv->cap;
+  }
+  const uint64_t s0 = pos0 & kv->ring_mask;
+  r.slot[0] = s0;
+  r.len[0] = (s0 + n <= kv->cap) ? n : kv->cap - s0;
+  r.slot[1] = 0;
+  r.len[1] = n - r.len[0];
+  return r;
+}
+
 extern "C" int32_t dg_kv_load_prefix(dg_kv* kv, const void* k, const void* v, uint64_t pos0, uint64_t n) {
   if (!kv || !k || !v) return fail(DG_ERR_INVALID_ARG, "NULL argument");
-  if (pos0 + n > kv->cap) return fail(DG_ERR_CAPACITY, "prefix does not fit the cache");
+  if (kv->ring_mask == 0 && pos0 + n > kv->cap) return fail(DG_ERR_CAPACITY, "prefix does not fit the cache");
   if (n == 0) return DG_OK;
   DG_CUDA(cudaSetDevice(kv->ctx->device));
   const size_t row = size_t(kv->D) * 2, spitch = size_t(kv->Hkv) * row;
-  for (uint32_t h = 0; h < kv->Hkv; ++h) {
-    DG_CUDA(cudaMemcpy2DAsync(kv->k + (size_t(h) * kv->cap + pos0) * kv->D, row,
-                              static_cast<const uint8_t*>(k) + h * row, spitch, row, n, cudaMemcpyDefault,
-                              kv->ctx->stream));
-    DG_CUDA(cudaMemcpy2DAsync(kv->v + (size_t(h) * kv->cap + pos0) * kv->D, row,
-                              static_cast<const uint8_t*>(v) + h * row, spitch, row, n, cudaMemcpyDefault,
-                              kv->ctx->stream));
+  const SlotRuns runs = slot_runs(kv, pos0, n);
+  uint64_t done = runs.skip;
+  for (int s = 0; s < 2; ++s) {
+    if (runs.len[s] == 0) continue;
+    for (uint32_t h = 0; h < kv->Hkv; ++h) {
+      DG_CUDA(cudaMemcpy2DAsync(kv->k + (size_t(h) * kv->cap + runs.slot[s]) * kv->D, row,
+                                static_cast<const uint8_t*>(k) + done * spitch + h * row, spitch, row, runs.len[s],
+                                cudaMemcpyDefault, kv->ctx->stream));
+      DG_CUDA(cudaMemcpy2DAsync(kv->v + (size_t(h) * kv->cap + runs.slot[s]) * kv->D, row,
+                                static_cast<const uint8_t*>(v) + done * spitch + h * row, spitch, row, runs.len[s],
+                                cudaMemcpyDefault, kv->ctx->stream));
+    }
+    done += runs.len[s];
   }
   return DG_OK;
 }
 
 extern "C" int32_t dg_kv_read(dg_kv* kv, void* k_out, void* v_out, uint64_t pos0, uint64_t n) {
   if (!kv || !k_out || !v_out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
-  if (pos0 + n > kv->cap) return fail(DG_ERR_CAPACITY, "range outside the cache");
+  if (kv->ring_mask == 0 ? (pos0 + n > kv->cap) : (n > kv->cap))
+    return fail(DG_ERR_CAPACITY, "range outside the cache");
   DG_CUDA(cudaSetDevice(kv->ctx->device));
   const size_t row = size_t(kv->D) * 2, dpitch = size_t(kv->Hkv) * row;
-  for (uint32_t h = 0; h < kv->Hkv && n > 0; ++h) {
-    DG_CUDA(cudaMemcpy2DAsync(static_cast<uint8_t*>(k_out) + h * row, dpitch,
-                              kv->k + (size_t(h) * kv->cap + pos0) * kv->D, row, row, n, cudaMemcpyDefault,
-                              kv->ctx->stream));
-    DG_CUDA(cudaMemcpy2DAsync(static_cast<uint8_t*>(v_out) + h * row, dpitch,
-                              kv->v + (size_t(h) * kv->cap + pos0) * kv->D, row, row, n, cudaMemcpyDefault,
-                              kv->ctx->stream));
+  const SlotRuns runs = slot_runs(kv, pos0, n);
+  uint64_t done = 0;
+  for (int s = 0; s < 2; ++s) {
+    if (runs.len[s] == 0) continue;
+    for (uint32_t h = 0; h < kv->Hkv; ++h) {
+      DG_CUDA(cudaMemcpy2DAsync(static_cast<uint8_t*>(k_out) + done * dpitch + h * row, dpitch,
+                                kv->k + (size_t(h) * kv->cap + runs.slot[s]) * kv->D, row, row, runs.len[s],
+                                cudaMemcpyDefault, kv->ctx->stream));
+      DG_CUDA(cudaMemcpy2DAsync(static_cast<uint8_t*>(v_out) + done * dpitch + h * row, dpitch,
+                                kv->v + (size_t(h) * kv->cap + runs.slot[s]) * kv->D, row, row, runs.len[s],
+                                cudaMemcpyDefault, kv->ctx->stream));
+    }
+    done += runs.len[s];
   }
   DG_CUDA(cudaStreamSynchronize(kv->ctx->stream));
   return DG_OK;
@@ -513,14 +563,25 @@ extern "C" int32_t dg_kv_read(dg_kv* kv, void* k_out, void* v_out, uint64_t pos0
 static int32_t check_kv(const dg_layer_desc& d, const dg_kv* kv, uint64_t end_pos) {
   if (!kv) return fail(DG_ERR_INVALID_ARG, "kv is NULL");
   if (kv->Hkv != d.n_kv_heads || kv->D != d.head_dim) return fail(DG_ERR_INVALID_ARG, "kv geometry differs from desc");
-  if (end_pos > kv->cap) return fail(DG_ERR_CAPACITY, "kv_len + canvas exceeds the cache capacity");
+  if (kv->ring_mask == 0 && end_pos > kv->cap) return fail(DG_ERR_CAPACITY, "kv_len + canvas exceeds the cache capacity");
+  if (end_pos > (1ull << 31)) return fail(DG_ERR_CAPACITY, "position beyond 2^31");
+  return DG_OK;
+}
+// A ring holds the last `cap` positions: every key an attention call can load (whole 128-key tiles
+// from the first visible position of canvas row 0 to the end of the canvas) must still be in it.
+static int32_t check_ring_span(const dg_kv* kv, const MaskParams& mk, uint32_t canvas) {
+  if (kv->ring_mask == 0) return DG_OK;
+  const uint32_t lo = mask_row_lo(mk, 0) / 128u * 128u;
+  const uint64_t end = uint64_t(mk.kv_len) + canvas;
+  if (end - lo > kv->cap)
+    return fail(DG_ERR_CAPACITY, "the visible key range (window + canvas, tile aligned) exceeds the ring");
   return DG_OK;
 }
 
 // append n tokens (norm + RoPE + cache write); optionally also Q (stage 1) and the RoPE table
 static int32_t do_append(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint64_t pos0, uint32_t n, const void* q_in,
                          void* q_out, const void* k_in, void* k_out, const void* v_in, void* v_out, const void* qw,
-                         const void* kw, float2* table) {
+                         const void* kw, float2* table, uint32_t write_end = 0xffffffffu) {
   AppendParams ap;
   ap.q_in = static_cast<const __nv_bfloat16*>(q_in);
   ap.q_out = static_cast<__nv_bfloat16*>(q_out);
@@ -541,6 +602,8 @@ static int32_t do_append(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint64_t 
   ap.D = d.head_dim;
   ap.v_norm = d.v_norm;
   ap.eps = d.rms_eps;
+  ap.ring_mask = kv->ring_mask ? kv->ring_mask : 0xffffffffu;
+  ap.write_end = write_end;
   const RopeParams rp = make_rope(d);
   launch_append(ap, rp, c->stream);
   DG_CUDA(cudaGetLastError());
@@ -548,17 +611,23 @@ static int32_t do_append(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint64_t 
   return DG_OK;
 }
 
+extern "C" int32_t dg_kv_append_guarded(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint64_t pos0, uint32_t n,
+                                        const void* k, const void* v, const void* kw, uint32_t write_end);
 extern "C" int32_t dg_kv_append(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint64_t pos0, uint32_t n, const void* k,
                                 const void* v, const void* kw) {
+  return dg_kv_append_guarded(c, d, kv, pos0, n, k, v, kw, 0xffffffffu);
+}
+extern "C" int32_t dg_kv_append_guarded(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint64_t pos0, uint32_t n,
+                                        const void* k, const void* v, const void* kw, uint32_t write_end) {
   if (!c || !k || !v) return fail(DG_ERR_INVALID_ARG, "NULL argument");
   int32_t r = check_desc(d);
   if (r != DG_OK) return r;
-  r = check_kv(*d, kv, pos0 + n);
+  r = check_kv(*d, kv, (pos0 + n < write_end) ? pos0 + n : (write_end > pos0 ? uint64_t(write_end) : pos0));
   if (r != DG_OK) return r;
   if (n > 65535) return fail(DG_ERR_INVALID_ARG, "append at most 65535 tokens per call");
   DG_CUDA(cudaSetDevice(c->device));
   c->last_launches = 0;
-  return do_append(c, *d, kv, pos0, n, nullptr, nullptr, k, nullptr, v, nullptr, nullptr, kw, nullptr);
+  return do_append(c, *d, kv, pos0, n, nullptr, nullptr, k, nullptr, v, nullptr, nullptr, kw, nullptr, write_end);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -597,6 +666,11 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
   p.stamps = c->stamps;
   p.cap = kv->cap;
   p.mask = make_mask(d, a.kv_len, a.t0, a.t1, a.include_canvas);
+  p.ring_mask = kv->ring_mask ? kv->ring_mask : 0xffffffffu;
+  {
+    const int32_t rr = check_ring_span(kv, p.mask, d.canvas);
+    if (rr != DG_OK) return rr;
+  }
   p.C = d.canvas;
   p.Hq = d.n_q_heads;
   p.Hkv = d.n_kv_heads;
@@ -1028,6 +1102,7 @@ extern "C" int32_t dg_attention_static_scratch(dg_ctx* c, const dg_layer_desc* d
   p.G = d->n_q_heads / d->n_kv_heads;
   p.D = d->head_dim;
   p.q_prenormed = 1u;
+  p.ring_mask = kv->ring_mask ? kv->ring_mask : 0xffffffffu;
   p.n_splits = 1;
   p.rot_half = d->rotary_dim / 2;
   p.pair_off = d->rope_pairing == DG_ROPE_SPLIT_HALF ? d->rotary_dim / 2 : d->head_dim / 2;

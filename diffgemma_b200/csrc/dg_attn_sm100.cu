@@ -3,7 +3,9 @@
 //   * Q prologue in the kernel: per-head RMSNorm(+weight) + split-half RoPE on the CTA's 128
 //     query rows, rounded to bf16 and written straight into the UMMA shared-memory layout.
 //   * K/V tiles of 128 keys are TMA-staged (3-D tiled loads, 128-byte swizzle, no multicast) from
-//     the head-major bf16 cache K[Hkv][cap][256], V[Hkv][cap][256].
+//     the head-major bf16 cache K[Hkv][cap][256], V[Hkv][cap][256]; a ring cache (sliding layers) keeps
+//     key position t in slot t & ring_mask, and because the ring is a multiple of 128 slots a key
+//     tile stays one contiguous box.
 //   * S = Q K^T and O += P V run on tcgen05.mma with fp32 accumulators in tensor memory:
 //     TMEM columns [0,128) and [128,256) double-buffer S, [256,512) hold O; P (bf16) overwrites
 //     the first 64 columns of its S buffer and is consumed from TMEM as the A operand.
@@ -384,7 +386,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
           const uint32_t full = lead_bar(B_K_FULL + st);
 #pragma unroll
           for (uint32_t a = 0; a < 4; ++a)
-            tma_load_3d_pair(sK + st * K_STAGE + a * K_ATOM, &tm_k, full, int32_t(a * 64), int32_t(jt * BN + xi * 64),
+            tma_load_3d_pair(sK + st * K_STAGE + a * K_ATOM, &tm_k, full, int32_t(a * 64), int32_t((jt * BN + xi * 64) & p.ring_mask),
                              int32_t(kvh));
         } else {
           if (n > 0 && !wait_bar(B_S_FULL + ((n - 1) & 1u), ((n - 1) >> 1) & 1u, abort_flag)) break;   // QK(n - 1) complete
@@ -392,7 +394,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
           mbar_expect_tx(full, TILE_BYTES);
 #pragma unroll
           for (uint32_t a = 0; a < 4; ++a)
-            tma_load_3d(sK + a * ATOM_BYTES, &tm_k, full, int32_t(a * 64), int32_t(jt * BN), int32_t(kvh));
+            tma_load_3d(sK + a * ATOM_BYTES, &tm_k, full, int32_t(a * 64), int32_t((jt * BN) & p.ring_mask), int32_t(kvh));
         }
       }
     }
@@ -411,14 +413,14 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
 #pragma unroll
           for (uint32_t a = 0; a < 2; ++a)
             tma_load_3d_pair(sV + st * V_STAGE + a * ATOM_BYTES, &tm_v, full, int32_t(xi * 128 + a * 64),
-                             int32_t(jt * BN), int32_t(kvh));
+                             int32_t((jt * BN) & p.ring_mask), int32_t(kvh));
         } else {
           if (n > 0 && !wait_bar(B_V_EMPTY + ((n - 1) & 1u), ((n - 1) >> 1) & 1u, abort_flag)) break;   // PV(n - 1) complete
           const uint32_t full = bar_addr(bar_base, B_V_FULL);
           mbar_expect_tx(full, TILE_BYTES);
 #pragma unroll
           for (uint32_t a = 0; a < 4; ++a)
-            tma_load_3d(sV + a * ATOM_BYTES, &tm_v, full, int32_t(a * 64), int32_t(jt * BN), int32_t(kvh));
+            tma_load_3d(sV + a * ATOM_BYTES, &tm_v, full, int32_t(a * 64), int32_t((jt * BN) & p.ring_mask), int32_t(kvh));
         }
       }
     }

@@ -103,6 +103,8 @@ struct AppendParams {
   uint32_t Hq, Hkv, D;
   uint32_t v_norm;
   float eps;
+  uint32_t ring_mask;          // cache slot of position pos = pos & ring_mask (0xffffffff: linear cache)
+  uint32_t write_end;          // positions >= write_end are not written to the cache (0xffffffff: none)
 };
 
 // attention kernels (general and sm100)
@@ -126,6 +128,7 @@ struct AttnParams {
   MaskParams mask;
   uint32_t C, Hq, Hkv, G, D;
   uint32_t q_prenormed;
+  uint32_t ring_mask;            // cache slot of key position t = t & ring_mask (0xffffffff: linear cache)
   uint32_t early_q;              // 1: nothing the Q prologue reads is written by the preceding kernel on the stream
   uint32_t n_splits;
   uint32_t cluster_splits;       // consecutive splits per thread-block cluster (divides n_splits; 1 = no cluster merge)

@@ -51,7 +51,11 @@ __global__ void __launch_bounds__(32) dg_append_kernel(const AppendParams p, con
   const __nv_bfloat16* src = (is_q ? p.q_in : (is_k ? p.k_in : p.v_in)) + (size_t(tok) * H + h) * D;
   __nv_bfloat16* wb = (is_q ? p.q_out : (is_k ? p.k_out : p.v_out));
   if (wb) wb += (size_t(tok) * H + h) * D;
-  __nv_bfloat16* cache = is_q ? nullptr : (is_k ? p.cache_k : p.cache_v) + (size_t(h) * p.cap + pos) * D;
+  // ring caches keep position pos in slot pos & ring_mask; positions at or past write_end (the
+  // zero-padded tail of a prefill chunk) must not reach the cache, where they would wrap onto live slots
+  __nv_bfloat16* cache = (is_q || pos >= p.write_end)
+                             ? nullptr
+                             : (is_k ? p.cache_k : p.cache_v) + (size_t(h) * p.cap + (pos & p.ring_mask)) * D;
 
   float ss = 0.f;
   for (uint32_t d = lane; d < D; d += 32) {
@@ -173,7 +177,8 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) dg_attn_general_kernel(const A
       if (p.attend) {
         if (!p.attend[size_t(row) * T + t]) continue;
       }
-      const uint4* kr = reinterpret_cast<const uint4*>(kbase + size_t(t) * D);
+      const uint32_t ts = t & p.ring_mask;   // cache slot of key position t
+      const uint4* kr = reinterpret_cast<const uint4*>(kbase + size_t(ts) * D);
       float dot = 0.f;
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
@@ -195,7 +200,7 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) dg_attn_general_kernel(const A
       const float pe = exp2f(s2 - mn);
       l = l * corr + pe;
       m = mn;
-      const uint4* vr = reinterpret_cast<const uint4*>(vbase + size_t(t) * D);
+      const uint4* vr = reinterpret_cast<const uint4*>(vbase + size_t(ts) * D);
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const uint32_t c = lane + 32u * j;

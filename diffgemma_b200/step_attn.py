@@ -132,13 +132,22 @@ class Context:
 class KvCache:
     """dg_kv: one layer's head-major bf16 cache for one canvas stream."""
 
-    def __init__(self, ctx: Context, layer: AttnLayer, capacity_tokens: int):
+    def __init__(self, ctx: Context, layer: AttnLayer, capacity_tokens: int = 0, ring_slots: int | None = None):
+        """Linear cache of `capacity_tokens` positions, or (sliding layers) a ring of `ring_slots` slots
+        that keeps position pos in slot pos & (ring_slots - 1)."""
         self.ctx = ctx
         self.layer = layer
         h = C.c_void_p()
         d = layer.c_desc()
-        check(ctx.lib.dg_kv_create(ctx.h, C.byref(d), capacity_tokens, C.byref(h)), "dg_kv_create")
+        if ring_slots is None:
+            check(ctx.lib.dg_kv_create(ctx.h, C.byref(d), capacity_tokens, C.byref(h)), "dg_kv_create")
+        else:
+            check(ctx.lib.dg_kv_create_ring(ctx.h, C.byref(d), ring_slots, C.byref(h)), "dg_kv_create_ring")
         self.h = h
+
+    @property
+    def ring_mask(self) -> int:
+        return int(self.ctx.lib.dg_kv_ring_mask(self.h))
 
     @property
     def capacity(self) -> int:
@@ -151,16 +160,19 @@ class KvCache:
         if not k.is_cuda:
             self.ctx.synchronize()   # pageable host source must outlive the copy
 
-    def append(self, k: torch.Tensor, v: torch.Tensor, pos0: int, kw: torch.Tensor | None = None) -> None:
-        """Norm + RoPE raw keys and write them (and V) at [pos0, pos0+n).  Device tensors."""
+    def append(self, k: torch.Tensor, v: torch.Tensor, pos0: int, kw: torch.Tensor | None = None,
+               write_end: int | None = None) -> None:
+        """Norm + RoPE raw keys and write them (and V) at [pos0, pos0+n).  Device tensors.  Positions at
+        or past `write_end` (a padded chunk tail) are left out of the cache."""
         d = self.layer.c_desc()
         n = k.shape[0]
         done = 0
+        we = 0xFFFFFFFF if write_end is None else int(write_end)
         while done < n:
             step = min(32768, n - done)
-            check(self.ctx.lib.dg_kv_append(self.ctx.h, C.byref(d), self.h, pos0 + done, step,
-                                            _ptr(k[done:done + step]), _ptr(v[done:done + step]), _ptr(kw)),
-                  "dg_kv_append")
+            check(self.ctx.lib.dg_kv_append_guarded(self.ctx.h, C.byref(d), self.h, pos0 + done, step,
+                                                    _ptr(k[done:done + step]), _ptr(v[done:done + step]), _ptr(kw), we),
+                  "dg_kv_append_guarded")
             done += step
 
     def read(self, pos0: int, n: int):

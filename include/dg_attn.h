@@ -124,10 +124,21 @@ int32_t dg_ctx_set_splits(dg_ctx* ctx, uint32_t n_splits);
  * monolithic buffer (src/metal/step_kv/mod.rs:1-25, src/metal/step_kernel/mod.rs:506-527).
  * `capacity_tokens` must cover prefix + canvas; it is rounded up to a multiple of 128.          */
 int32_t dg_kv_create(dg_ctx* ctx, const dg_layer_desc* desc, uint64_t capacity_tokens, dg_kv** out);
+/* Ring cache for sliding-window layers: `ring_slots` (a power of two, at least 256) slots per KV head,
+ * position pos lives in slot pos & (ring_slots - 1), so only the last ring_slots positions are kept and
+ * kv_len may grow without bound (up to 2^31).  The reference's LayerOffsets::kv_ring_mask
+ * (src/metal/step_kernel/mod.rs:161-166; 2048 slots for a 1024 window + 256 canvas).  Every attention
+ * call checks that what it can load - whole 128-key tiles from the first visible key of canvas row 0 to the
+ * end of the canvas - still fits the ring and returns DG_ERR_CAPACITY otherwise (an unwindowed layer on a
+ * ring works only while kv_len + canvas <= ring_slots).                                            */
+int32_t dg_kv_create_ring(dg_ctx* ctx, const dg_layer_desc* desc, uint32_t ring_slots, dg_kv** out);
+/* ring_slots - 1 of a ring cache, 0 for a linear one.                                            */
+uint32_t dg_kv_ring_mask(const dg_kv* kv);
 int32_t dg_kv_destroy(dg_kv* kv);
 uint64_t dg_kv_capacity(const dg_kv* kv);
 /* Copy `n` tokens of ready-to-use keys/values (K already normed + roped) into positions
- * [pos0, pos0+n).  k, v: token-major [n][Hkv][D] bf16, host or device pointers.                */
+ * [pos0, pos0+n).  k, v: token-major [n][Hkv][D] bf16, host or device pointers.  On a ring cache
+ * only the last ring_slots positions of the run are stored (the older ones would be overwritten).  */
 int32_t dg_kv_load_prefix(dg_kv* kv, const void* k, const void* v, uint64_t pos0, uint64_t n);
 /* Read positions [pos0, pos0+n) back as token-major [n][Hkv][D] (snapshot/export; the
  * reference's compact gather: src/metal/step_kv/mod.rs:102-151).  Synchronises.                */
@@ -137,6 +148,11 @@ int32_t dg_kv_read(dg_kv* kv, void* k_out, void* v_out, uint64_t pos0, uint64_t 
  * synthetic prefill).  k, v: device pointers [n][Hkv][D]; kw: [D] or NULL.                      */
 int32_t dg_kv_append(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* kv, uint64_t pos0, uint32_t n,
                      const void* k, const void* v, const void* kw);
+/* dg_kv_append that leaves the cache untouched for positions >= write_end: the zero-padded tail of a
+ * prefill chunk must not be stored, on a ring it would wrap onto live slots of the window.  The
+ * reference's StepParams::kv_write_end (src/metal/step_kernel/mod.rs:203-212); 0xffffffff = no guard. */
+int32_t dg_kv_append_guarded(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* kv, uint64_t pos0, uint32_t n,
+                             const void* k, const void* v, const void* kw, uint32_t write_end);
 
 /* ---- the hot path ----------------------------------------------------------------------- */
 /* Stage 1 alone (reference stage LayerQkRopeKv): per-head RMSNorm(+weight) + RoPE on canvas
