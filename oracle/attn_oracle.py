@@ -16,12 +16,16 @@ the reference project):
 * (m, l, O) block state      src/shaders/include/attention_device.metal:154-165
 
 Parity pin: the reference stores no golden output vectors for attention; this
-oracle is pinned against every known-answer value the reference's tests hold for
-the path (RMSNorm, RoPE, softmax, masks - see tests/test_oracle_pins.py) and
-against structural properties the reference tests (blocked online softmax ==
-single pass).  The windowed *denoise* mask has no unit-level pin in the
-reference (only end-to-end goldens that need the model weights): parity
-unpinned for that rule beyond the cited shader text.
+oracle is pinned (1) against every known-answer value the reference's tests hold
+for the path (RMSNorm, RoPE, softmax, masks - tests/test_oracle_pins.py) and the
+structural properties they test (blocked online softmax == single pass), and
+(2) against the reference's OWN shaders run on the CPU: attention.metal and
+qk_rope_kv.metal compile as C++ through a <metal_stdlib> stand-in
+(oracle/Makefile target `ref`, oracle/ref_attention.cpp, oracle/ref_qk_rope_kv.cpp),
+and tests/test_ref_shader_pins.py holds this module to their outputs - the
+visibility rule with a sliding window and the ring slot mapping bit for bit, both
+RoPE pairings, the V-aliases-K form, and the softmax values - live where that
+library is built and through the vectors stored in tests/golden/ elsewhere.
 """
 from __future__ import annotations
 

@@ -414,3 +414,42 @@ def test_wait_timeout_is_reported_and_context_survives(ctx):
     layer = AttnLayer(n_kv_heads=8)
     case = util.make_case(layer, 300, seed=21)
     util.assert_close(util.run_gpu(ctx, case), util.run_oracle(case), "after a reported timeout")
+
+
+# ------------------------------------------------------------------------------------------
+# the CUDA path against the reference's OWN shaders (vectors stored by tests/golden/make_ref_shader_golden.py
+# from attention.metal / qk_rope_kv.metal compiled for the CPU)
+# ------------------------------------------------------------------------------------------
+def _ref_golden():
+    import os
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.join(root, "tests", "golden"))
+    import make_ref_shader_golden as G
+    return G, np.load(os.path.join(root, "tests", "golden", "ref_shader_golden.npz"))
+
+
+@pytest.mark.parametrize("name", ["sliding_short", "sliding_window_cuts", "sliding_ring", "full_hd512_valias",
+                                  "full_hd256_vproj"])
+def test_gpu_matches_reference_shader_vectors(ctx, name):
+    G, gold = _ref_golden()
+    hd, n_q, n_kv, canvas, kv_len, is_full, window, ring, valias, seed = G.VALUE_CASES[name]
+    q, k, v, kp, vp, qw, kw = G.value_inputs(*G.VALUE_CASES[name])
+    layer = AttnLayer(n_q_heads=n_q, n_kv_heads=n_kv, head_dim=hd, canvas=canvas,
+                      rotary_dim=hd // 4 if is_full else hd, rope_theta=1e6 if is_full else 1e4, rms_eps=1e-6,
+                      softmax_scale=1.0, window=window, mask_mode=capi.MASK_WINDOW_UNIFORM if window else capi.MASK_NONE,
+                      v_norm=1, rope_pairing=capi.ROPE_PROPORTIONAL if is_full else capi.ROPE_SPLIT_HALF)
+    kv = KvCache(ctx, layer, ring_slots=ring + 1) if ring else KvCache(ctx, layer, kv_len + canvas)
+    t = lambda a: util.f2t(a).to(DEV)
+    kv.load_prefix(t(kp), t(vp), 0)
+    att = CanvasAttention(ctx, layer)
+    kc = t(k)
+    out = att.denoise([kv], [kv_len], t(q)[None], kc[None], (kc if valias else t(v))[None], t(qw), t(kw))
+    ctx.synchronize()
+    got = util.t2f(out[0])
+    ref = gold[f"{name}_out"]
+    # the shader truncates its output to bf16: one bf16 ulp of the difference is its own quantisation
+    err = np.maximum(np.abs(got - ref) - np.maximum(np.abs(ref), 2.0 ** -20) * 2.0 ** -7, 0.0)
+    assert err.max() <= 2e-2 and err.mean() <= 2e-3, (name, float(err.max()), float(err.mean()))
+    assert ctx.device_status()[0] == 0
+    kv.close()
