@@ -117,11 +117,12 @@ static PFN_encodeTiled get_encode_fn() {
   return fn;
 }
 
-static int32_t make_kv_tmap(CUtensorMap* tm, void* base, uint64_t cap, uint32_t Hkv, uint32_t box_keys = 128) {
+static int32_t make_kv_tmap(CUtensorMap* tm, void* base, uint64_t cap, uint32_t Hkv, uint32_t box_keys = 128,
+                            uint32_t D = 256) {
   PFN_encodeTiled enc = get_encode_fn();
   if (!enc) return fail(DG_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
-  const cuuint64_t dims[3] = {256, cap, Hkv};
-  const cuuint64_t strides[2] = {256 * 2, cap * 256 * 2};   // bytes, dims 1 and 2
+  const cuuint64_t dims[3] = {D, cap, Hkv};
+  const cuuint64_t strides[2] = {cuuint64_t(D) * 2, cap * D * 2};   // bytes, dims 1 and 2
   const cuuint32_t box[3] = {64, box_keys, 1};               // 128 B x box_keys keys
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, estr,
@@ -170,10 +171,13 @@ static RopeParams make_rope(const dg_layer_desc& d) {
   return rp;
 }
 
-static bool tensor_path_ok(const dg_layer_desc& d) { return d.head_dim == 256 && d.canvas <= kMaxCanvas; }
+// tensor-core kernels exist for head_dim 256 (all benchmark layers) and 512 (the reference's full layers)
+static bool tensor_path_ok(const dg_layer_desc& d) {
+  return (d.head_dim == 256 || d.head_dim == 512) && d.canvas <= kMaxCanvas;
+}
 // the in-kernel Q prologue covers full split-half rotary only
 static bool fused_q_prologue_ok(const dg_layer_desc& d) {
-  return d.rotary_dim == 256 && d.rope_pairing == DG_ROPE_SPLIT_HALF;
+  return d.head_dim == 256 && d.rotary_dim == 256 && d.rope_pairing == DG_ROPE_SPLIT_HALF;
 }
 
 static uint32_t choose_splits(const dg_ctx* ctx, uint32_t q_tiles, uint32_t k_tiles) {
@@ -283,6 +287,7 @@ extern "C" int32_t dg_ctx_create(int32_t device, dg_ctx** out) {
   if (e == cudaSuccess) e = cudaMemset(c->counters, 0, kCounterSlots * sizeof(uint32_t));
   if (e == cudaSuccess) e = sm100_attn_configure();
   if (e == cudaSuccess) e = sm100_pair_configure();
+  if (e == cudaSuccess) e = sm100_hd512_configure();
   if (e != cudaSuccess) {
     dg_ctx_destroy(c);
     return fail_cuda(e, "dg_ctx_create");
@@ -455,6 +460,15 @@ static int32_t kv_create(dg_ctx* c, const dg_layer_desc* d, uint64_t capacity_to
     r = make_kv_tmap(&kv->tm_k, kv->k, kv->cap, kv->Hkv);
     if (r == DG_OK) r = make_kv_tmap(&kv->tm_v, kv->v, kv->cap, kv->Hkv);
     if (r == DG_OK) r = make_kv_tmap(&kv->tm_k64, kv->k, kv->cap, kv->Hkv, 64);
+    if (r != DG_OK) {
+      dg_kv_destroy(kv);
+      return r;
+    }
+    kv->has_tmap = true;
+  } else if (kv->D == 512) {
+    // head_dim-512 kernel: key tiles of 64 keys for both K and V
+    r = make_kv_tmap(&kv->tm_k, kv->k, kv->cap, kv->Hkv, 64, 512);
+    if (r == DG_OK) r = make_kv_tmap(&kv->tm_v, kv->v, kv->cap, kv->Hkv, 64, 512);
     if (r != DG_OK) {
       dg_kv_destroy(kv);
       return r;
@@ -688,6 +702,25 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
   if (!tensor) {
     launch_attn_general(p, c->stream);
     DG_CUDA(cudaGetLastError());
+    c->last_launches += 1;
+    return DG_OK;
+  }
+  if (d.head_dim == 512) {
+    // value columns split over two CTAs per (query tile, key split); splits meet in the workspace
+    if (!a.q_prenormed) return fail(DG_ERR_UNSUPPORTED, "head_dim 512 tensor path needs a prenormed Q");
+    const uint32_t q_tiles5 = sm100_query_tiles(p.C, p.G, p.Hkv);
+    if (q_tiles5 * 2 > kMaxQueryTiles) return fail(DG_ERR_UNSUPPORTED, "too many query tiles");
+    p.n_splits = choose_splits(c, q_tiles5 * 2, sm100_hd512_key_tiles(p.mask));
+    p.cluster_splits = 1;
+    if (p.n_splits > 1) {
+      const int32_t r5 = ensure_split_ws(c, 2 * p.n_splits, p.C * p.Hq);
+      if (r5 != DG_OK) return r5;
+      p.ws_o = c->ws_o;
+      p.ws_ml = c->ws_ml;
+      p.ws_counters = c->counters;
+    }
+    const cudaError_t e5 = launch_attn_sm100_hd512(p, kv->tm_k, kv->tm_v, c->stream);
+    if (e5 != cudaSuccess) return fail_cuda(e5, "launch_attn_sm100_hd512");
     c->last_launches += 1;
     return DG_OK;
   }
@@ -1109,7 +1142,7 @@ extern "C" int32_t dg_attention_static_scratch(dg_ctx* c, const dg_layer_desc* d
   p.scale_log2 = d->softmax_scale * 1.4426950408889634f;
   p.eps = d->rms_eps;
 
-  if (!(tensor_path_ok(*d) && kv->has_tmap)) {
+  if (!(d->head_dim == 256 && tensor_path_ok(*d) && kv->has_tmap)) {
     // the general kernel keeps all of its state in registers and shared memory: nothing to provide
     launch_attn_general(p, c->stream);
     DG_CUDA(cudaGetLastError());

@@ -33,6 +33,11 @@ cudaError_t launch_attn_sm100_pair(const AttnParams& p, const CUtensorMap& tm_k6
 uint32_t sm100_pair_query_tiles(uint32_t C, uint32_t G, uint32_t Hkv);
 int sm100_max_active_clusters(uint32_t cluster_y);        // single-CTA kernel, clusters (1, y, 1)
 int sm100_pair_max_active_clusters(uint32_t cluster_y);   // pair kernel, clusters (2, y, 1)
+// head_dim 512 (csrc/dg_attn_sm100_hd512.cu): tm_k / tm_v are {512, cap, Hkv} maps with boxes {64, 64, 1}
+cudaError_t sm100_hd512_configure();
+cudaError_t launch_attn_sm100_hd512(const AttnParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
+                                    cudaStream_t st);
+uint32_t sm100_hd512_key_tiles(const MaskParams& mk);             // key tiles of 64 keys per CTA
 uint32_t sm100_key_tiles(const MaskParams& mk);                     // upper bound of key tiles per CTA
 
 }  // namespace dg

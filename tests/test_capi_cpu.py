@@ -66,6 +66,7 @@ def test_desc_validation_needs_no_gpu():
     assert lib.dg_attn_flops(C.byref(bad), 10) == 0.0
     assert lib.dg_uses_tensor_path(C.byref(bad)) == 0
     assert lib.dg_uses_tensor_path(C.byref(AttnLayer().c_desc())) == 1
-    assert lib.dg_uses_tensor_path(C.byref(AttnLayer(head_dim=512, rotary_dim=128).c_desc())) == 0
+    assert lib.dg_uses_tensor_path(C.byref(AttnLayer(head_dim=512, rotary_dim=128).c_desc())) == 1   # full layers
+    assert lib.dg_uses_tensor_path(C.byref(AttnLayer(head_dim=128, rotary_dim=128).c_desc())) == 0
     assert lib.dg_ctx_synchronize(None) == capi.DG_ERR_INVALID_ARG
     assert lib.dg_kv_destroy(None) == capi.DG_OK

@@ -453,3 +453,32 @@ def test_gpu_matches_reference_shader_vectors(ctx, name):
     assert err.max() <= 2e-2 and err.mean() <= 2e-3, (name, float(err.max()), float(err.mean()))
     assert ctx.device_status()[0] == 0
     kv.close()
+
+
+# ------------------------------------------------------------------------------------------
+# head_dim 512 (the reference's full-attention layers) on the tensor path
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("P,Hq,Hkv,canvas,W,mode,scale,vnorm", [
+    (60, 4, 2, 4, 0, 0, 1.0, 1),            # tiny: one partial tile
+    (700, 16, 2, 256, 0, 0, 1 / 16, 0),     # 16 query tiles per KV head, ragged last key tile
+    (4096, 16, 2, 256, 0, 0, 1 / 16, 1),    # aligned prefix
+    (3000, 8, 8, 100, 0, 0, 1 / 16, 1),     # no GQA stacking, ragged canvas
+    (5000, 16, 4, 256, 1024, 1, 1 / 16, 1), # sliding window on a 512-wide head (not a reference layer; mask logic)
+])
+def test_hd512_tensor_path_parity(ctx, P, Hq, Hkv, canvas, W, mode, scale, vnorm):
+    layer = AttnLayer(n_q_heads=Hq, n_kv_heads=Hkv, head_dim=512, canvas=canvas, rotary_dim=128, rope_theta=1e6,
+                      softmax_scale=scale, window=W, mask_mode=mode, v_norm=vnorm, rope_pairing=capi.ROPE_PROPORTIONAL)
+    case = util.make_case(layer, P, seed=P + Hq, weights=True)
+    ref = util.run_oracle(case)
+    assert CanvasAttention(ctx, layer).uses_tensor_path
+    try:
+        for splits in (0, 1, 2, 5):
+            ctx.set_splits(splits)
+            util.assert_close(util.run_gpu(ctx, case), ref, f"hd512 tensor path splits={splits}")
+    finally:
+        ctx.set_splits(0)
+    ctx.force_general(True)
+    got = util.run_gpu(ctx, case)
+    ctx.force_general(False)
+    util.assert_close(got, ref, "hd512 general path")
+    assert ctx.device_status()[0] == 0
