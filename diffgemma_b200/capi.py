@@ -72,6 +72,11 @@ SIGNATURES = {
     "dg_attention_static_scratch": (_i32, [_vp, _pd, _vp, _u32, _vp, _vp]),
     "dg_attn_denoise": (_i32, [_vp, _pd, C.POINTER(_vp), C.POINTER(_u32), _u32, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dg_attn_denoise_host": (_i32, [_vp, _pd, C.POINTER(_vp), C.POINTER(_u32), _u32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "dg_host_pipe_create": (_i32, [_vp, _pd, _u32, _u32, C.POINTER(_vp)]),
+    "dg_host_pipe_submit": (_i32, [_vp, _pd, C.POINTER(_vp), C.POINTER(_u32), _u32, _vp, _vp, _vp, _vp, _vp, _vp,
+                                   C.POINTER(_u64)]),
+    "dg_host_pipe_wait": (_i32, [_vp, _u64]),
+    "dg_host_pipe_destroy": (_i32, [_vp]),
     "dg_attn_denoise_bitmap": (_i32, [_vp, _pd, _vp, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dg_attn_partial": (_i32, [_vp, _pd, _vp, _u32, _u32, _u32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dg_attn_merge_local": (_i32, [_vp, _u32, _u32, _u32, _vp, _vp, _vp, _vp]),

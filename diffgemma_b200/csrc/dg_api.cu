@@ -887,6 +887,129 @@ extern "C" int32_t dg_attn_denoise_host(dg_ctx* c, const dg_layer_desc* d, dg_kv
   return s;
 }
 
+// ------------------------------------------------------------------------------------------
+// Host-buffer pipeline: the copies of step i+1 and i-1 overlap the kernels of step i
+// ------------------------------------------------------------------------------------------
+struct dg_host_pipe {
+  dg_ctx* ctx = nullptr;
+  uint32_t depth = 0;
+  size_t q_elems = 0, kv_elems = 0;
+  cudaStream_t h2d = nullptr, d2h = nullptr;
+  struct Slot {
+    __nv_bfloat16 *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr;
+    cudaEvent_t in = nullptr, cmp = nullptr, out = nullptr;
+    bool used = false;      // the events have been recorded at least once
+    bool pending = false;   // submitted and not yet waited for
+  } slot[8];
+  uint64_t next = 0;        // ticket of the next submit
+};
+
+extern "C" int32_t dg_host_pipe_destroy(dg_host_pipe* hp) {
+  if (!hp) return DG_OK;
+  cudaSetDevice(hp->ctx->device);
+  cudaStreamSynchronize(hp->ctx->stream);
+  if (hp->h2d) cudaStreamSynchronize(hp->h2d);
+  if (hp->d2h) cudaStreamSynchronize(hp->d2h);
+  for (uint32_t i = 0; i < hp->depth; ++i) {
+    dg_host_pipe::Slot& sl = hp->slot[i];
+    cudaFree(sl.q);
+    cudaFree(sl.k);
+    cudaFree(sl.v);
+    cudaFree(sl.o);
+    if (sl.in) cudaEventDestroy(sl.in);
+    if (sl.cmp) cudaEventDestroy(sl.cmp);
+    if (sl.out) cudaEventDestroy(sl.out);
+  }
+  if (hp->h2d) cudaStreamDestroy(hp->h2d);
+  if (hp->d2h) cudaStreamDestroy(hp->d2h);
+  delete hp;
+  return DG_OK;
+}
+
+extern "C" int32_t dg_host_pipe_create(dg_ctx* c, const dg_layer_desc* d, uint32_t max_batch, uint32_t depth,
+                                       dg_host_pipe** out) {
+  if (!c || !out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  *out = nullptr;
+  int32_t r = check_desc(d);
+  if (r != DG_OK) return r;
+  if (depth < 1 || depth > 8 || max_batch < 1) return fail(DG_ERR_INVALID_ARG, "depth must be 1..8, max_batch >= 1");
+  DG_CUDA(cudaSetDevice(c->device));
+  dg_host_pipe* hp = new (std::nothrow) dg_host_pipe();
+  if (!hp) return fail(DG_ERR_INVALID_ARG, "out of host memory");
+  hp->ctx = c;
+  hp->depth = depth;
+  hp->q_elems = size_t(max_batch) * d->canvas * d->n_q_heads * d->head_dim;
+  hp->kv_elems = size_t(max_batch) * d->canvas * d->n_kv_heads * d->head_dim;
+  cudaError_t e = cudaStreamCreateWithFlags(&hp->h2d, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&hp->d2h, cudaStreamNonBlocking);
+  for (uint32_t i = 0; i < depth && e == cudaSuccess; ++i) {
+    dg_host_pipe::Slot& sl = hp->slot[i];
+    e = cudaMalloc(&sl.q, hp->q_elems * 2);
+    if (e == cudaSuccess) e = cudaMalloc(&sl.k, hp->kv_elems * 2);
+    if (e == cudaSuccess) e = cudaMalloc(&sl.v, hp->kv_elems * 2);
+    if (e == cudaSuccess) e = cudaMalloc(&sl.o, hp->q_elems * 2);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&sl.in, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&sl.cmp, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&sl.out, cudaEventDisableTiming);
+  }
+  if (e != cudaSuccess) {
+    dg_host_pipe_destroy(hp);
+    return fail_cuda(e, "dg_host_pipe_create");
+  }
+  *out = hp;
+  return DG_OK;
+}
+
+extern "C" int32_t dg_host_pipe_wait(dg_host_pipe* hp, uint64_t ticket) {
+  if (!hp) return fail(DG_ERR_INVALID_ARG, "pipe is NULL");
+  if (ticket >= hp->next) return fail(DG_ERR_INVALID_ARG, "ticket was never issued");
+  if (ticket + hp->depth < hp->next) return DG_OK;   // its slot has been reused: that submit waited for it
+  dg_host_pipe::Slot& sl = hp->slot[ticket % hp->depth];
+  if (!sl.pending) return DG_OK;
+  DG_CUDA(cudaSetDevice(hp->ctx->device));
+  DG_CUDA(cudaEventSynchronize(sl.out));
+  sl.pending = false;
+  return DG_OK;
+}
+
+extern "C" int32_t dg_host_pipe_submit(dg_host_pipe* hp, const dg_layer_desc* d, dg_kv* const* kv, const uint32_t* kv_len,
+                                       uint32_t batch, const void* q, const void* k, const void* v, const void* qw,
+                                       const void* kw, void* out, uint64_t* ticket) {
+  if (!hp || !kv || !kv_len || !q || !k || !v || !out || !ticket) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  int32_t r = check_desc(d);
+  if (r != DG_OK) return r;
+  dg_ctx* c = hp->ctx;
+  const size_t qe = size_t(batch) * d->canvas * d->n_q_heads * d->head_dim;
+  const size_t ke = size_t(batch) * d->canvas * d->n_kv_heads * d->head_dim;
+  if (qe > hp->q_elems || ke > hp->kv_elems) return fail(DG_ERR_CAPACITY, "batch / geometry larger than the pipe was created for");
+  DG_CUDA(cudaSetDevice(c->device));
+  dg_host_pipe::Slot& sl = hp->slot[hp->next % hp->depth];
+  if (sl.pending) {   // the caller has not collected this slot's previous result: finish it first
+    DG_CUDA(cudaEventSynchronize(sl.out));
+    sl.pending = false;
+  }
+  // copies in: after the previous kernels that read this slot's staging buffers
+  if (sl.used) DG_CUDA(cudaStreamWaitEvent(hp->h2d, sl.cmp, 0));
+  DG_CUDA(cudaMemcpyAsync(sl.q, q, qe * 2, cudaMemcpyHostToDevice, hp->h2d));
+  DG_CUDA(cudaMemcpyAsync(sl.k, k, ke * 2, cudaMemcpyHostToDevice, hp->h2d));
+  DG_CUDA(cudaMemcpyAsync(sl.v, v, ke * 2, cudaMemcpyHostToDevice, hp->h2d));
+  DG_CUDA(cudaEventRecord(sl.in, hp->h2d));
+  // kernels: after this slot's inputs have landed and its previous output has left
+  DG_CUDA(cudaStreamWaitEvent(c->stream, sl.in, 0));
+  if (sl.used) DG_CUDA(cudaStreamWaitEvent(c->stream, sl.out, 0));
+  r = dg_attn_denoise(c, d, kv, kv_len, batch, sl.q, sl.k, sl.v, qw, kw, sl.o);
+  if (r != DG_OK) return r;
+  DG_CUDA(cudaEventRecord(sl.cmp, c->stream));
+  // copy out
+  DG_CUDA(cudaStreamWaitEvent(hp->d2h, sl.cmp, 0));
+  DG_CUDA(cudaMemcpyAsync(out, sl.o, qe * 2, cudaMemcpyDeviceToHost, hp->d2h));
+  DG_CUDA(cudaEventRecord(sl.out, hp->d2h));
+  sl.used = true;
+  sl.pending = true;
+  *ticket = hp->next++;
+  return DG_OK;
+}
+
 extern "C" int32_t dg_attn_denoise_bitmap(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint32_t kv_len, const void* q,
                                           const void* k, const void* v, const void* qw, const void* kw,
                                           const uint8_t* attend, void* out) {

@@ -1,4 +1,5 @@
-"""Multi-GPU partitioning of the canvas attention: split-KV and KV-head sharding.
+"""Multi-GPU partitioning of the canvas attention: split-KV (SplitKvGroup) and KV-head sharding
+(HeadShardGroup).
 
 One process per GPU.  torch.distributed is used only for rendezvous (to carry the NCCL unique id
 to the other ranks); the data path is the CUDA library's own NCCL communicator.
@@ -81,20 +82,7 @@ class SplitKvGroup:
             check(lib.dg_p2p_connect(h, C.cast(flat, C.c_void_p)), "dg_p2p_connect")
             dist.barrier(group=group)
             return
-        ident = torch.zeros(128, dtype=torch.uint8)
-        if self.rank == 0:
-            buf = (C.c_uint8 * 128)()
-            check(lib.dg_nccl_unique_id(C.cast(buf, C.c_void_p)), "dg_nccl_unique_id")
-            ident = torch.tensor(list(buf), dtype=torch.uint8)
-        # rendezvous only: carry the id over whatever backend the group has
-        dev = torch.device("cuda", ctx.device) if dist.get_backend(group) == "nccl" else torch.device("cpu")
-        ident = ident.to(dev)
-        dist.broadcast(ident, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
-        idb = (C.c_uint8 * 128)(*ident.cpu().tolist())
-        comm = C.c_void_p()
-        check(lib.dg_nccl_comm_create(ctx.h, C.cast(idb, C.c_void_p), self.world, self.rank, C.byref(comm)),
-              "dg_nccl_comm_create")
-        self.comm = comm
+        self.comm = _nccl_comm(ctx, group)
 
     def shard_bounds(self, kv_len: int):
         b = plan_shards(kv_len, self.world)
@@ -124,6 +112,69 @@ class SplitKvGroup:
                 dist.barrier(group=self.group)   # nobody unmaps a buffer a peer's kernel may still read
             self.ctx.lib.dg_p2p_destroy(self.p2p)
             self.p2p = None
+        if self.comm:
+            self.ctx.synchronize()
+            self.ctx.lib.dg_nccl_comm_destroy(self.comm)
+            self.comm = None
+
+
+def _nccl_comm(ctx: Context, group):
+    """The library's own NCCL communicator over the ranks of `group` (torch.distributed carries the id)."""
+    lib = ctx.lib
+    rank = dist.get_rank(group)
+    ident = torch.zeros(128, dtype=torch.uint8)
+    if rank == 0:
+        buf = (C.c_uint8 * 128)()
+        check(lib.dg_nccl_unique_id(C.cast(buf, C.c_void_p)), "dg_nccl_unique_id")
+        ident = torch.tensor(list(buf), dtype=torch.uint8)
+    dev = torch.device("cuda", ctx.device) if dist.get_backend(group) == "nccl" else torch.device("cpu")
+    ident = ident.to(dev)
+    dist.broadcast(ident, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+    idb = (C.c_uint8 * 128)(*ident.cpu().tolist())
+    comm = C.c_void_p()
+    check(lib.dg_nccl_comm_create(ctx.h, C.cast(idb, C.c_void_p), dist.get_world_size(group), rank, C.byref(comm)),
+          "dg_nccl_comm_create")
+    return comm
+
+
+class HeadShardGroup:
+    """KV-head sharding over the ranks of a process group: rank r owns KV heads [r*Hkv/N, (r+1)*Hkv/N) and their
+    query heads, with its own cache of those heads.  No softmax merge is needed; one all-gather of the output
+    head slices gives every rank the full result.  n_kv_heads must be a multiple of the world size."""
+
+    def __init__(self, ctx: Context, layer: AttnLayer, group=None):
+        self.ctx, self.group = ctx, group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        assert layer.n_kv_heads % self.world == 0, "n_kv_heads must be a multiple of the number of ranks"
+        self.full = layer
+        self.G = layer.n_q_heads // layer.n_kv_heads
+        self.kv_per = layer.n_kv_heads // self.world
+        self.q_per = self.kv_per * self.G
+        from dataclasses import replace
+        self.local = replace(layer, n_q_heads=self.q_per, n_kv_heads=self.kv_per)   # what this rank computes
+        self.att = CanvasAttention(ctx, self.local)
+        self.comm = _nccl_comm(ctx, group)
+
+    def kv_heads(self):
+        h0 = self.rank * self.kv_per
+        return h0, h0 + self.kv_per
+
+    def denoise(self, kv: KvCache, kv_len: int, q, k, v, qw=None, kw=None):
+        """q: [C,Hq,D], k, v: [C,Hkv,D] (full, replicated).  kv: this rank's cache (its KV heads only).
+        Returns the full [C,Hq,D] output on every rank."""
+        h0, h1 = self.kv_heads()
+        ql = q[:, h0 * self.G:h1 * self.G].contiguous()
+        kl = k[:, h0:h1].contiguous()
+        vl = v[:, h0:h1].contiguous()
+        ol = self.att.denoise([kv], [kv_len], ql[None], kl[None], vl[None], qw, kw)[0]     # [C, q_per, D]
+        gathered = torch.empty((self.world,) + tuple(ol.shape), dtype=ol.dtype, device=ol.device)
+        check(self.ctx.lib.dg_nccl_all_gather(self.ctx.h, self.comm, _ptr(ol), _ptr(gathered), ol.numel() * 2),
+              "dg_nccl_all_gather")
+        # [N, C, q_per, D] -> [C, N * q_per, D]
+        return gathered.permute(1, 0, 2, 3).reshape(ol.shape[0], self.world * self.q_per, ol.shape[2])
+
+    def close(self):
         if self.comm:
             self.ctx.synchronize()
             self.ctx.lib.dg_nccl_comm_destroy(self.comm)

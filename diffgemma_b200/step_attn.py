@@ -270,3 +270,33 @@ class CanvasAttention:
         check(self.lib.dg_attn_visibility(self.ctx.h, C.byref(self.desc), kv_len, t0, t1, int(include_canvas),
                                           _ptr(out)), "dg_attn_visibility")
         return out
+
+
+class HostPipe:
+    """dg_host_pipe: pipelined host-buffer steps (copies of neighbouring steps overlap the kernels)."""
+
+    def __init__(self, ctx: Context, layer: AttnLayer, max_batch: int = 1, depth: int = 3):
+        self.ctx, self.layer = ctx, layer
+        self.desc = layer.c_desc()
+        h = C.c_void_p()
+        check(ctx.lib.dg_host_pipe_create(ctx.h, C.byref(self.desc), max_batch, depth, C.byref(h)), "dg_host_pipe_create")
+        self.h = h
+        self.depth = depth
+
+    def submit(self, kvs, kv_lens, q, k, v, out, qw=None, kw=None) -> int:
+        """Host tensors q, k, v (read) and out (written) stay in use until wait(ticket) returns."""
+        B = len(kvs)
+        kv_arr = (C.c_void_p * B)(*[kv.h for kv in kvs])
+        len_arr = (C.c_uint32 * B)(*kv_lens)
+        t = C.c_uint64()
+        check(self.ctx.lib.dg_host_pipe_submit(self.h, C.byref(self.desc), kv_arr, len_arr, B, _ptr(q), _ptr(k), _ptr(v),
+                                               _ptr(qw), _ptr(kw), _ptr(out), C.byref(t)), "dg_host_pipe_submit")
+        return int(t.value)
+
+    def wait(self, ticket: int) -> None:
+        check(self.ctx.lib.dg_host_pipe_wait(self.h, ticket), "dg_host_pipe_wait")
+
+    def close(self) -> None:
+        if self.h:
+            self.ctx.lib.dg_host_pipe_destroy(self.h)
+            self.h = None

@@ -192,6 +192,23 @@ int32_t dg_attn_denoise(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* const* kv
 int32_t dg_attn_denoise_host(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* const* kv, const uint32_t* kv_len,
                              uint32_t batch, const void* q, const void* k, const void* v, const void* qw,
                              const void* kw, void* out);
+/* Pipelined form of the host-buffer call for hosts that issue many steps: `depth` staging slots, a copy-in
+ * and a copy-out stream beside the context's stream, so that the host-to-device copies of the next step and
+ * the device-to-host copy of the previous one overlap the kernels of the current one.  submit() returns at
+ * once with a ticket; the host buffers of a submit (q, k, v read, out written) belong to the library until
+ * wait(ticket) returns (or until a later submit reuses the slot, which waits for it first).  Results are in
+ * submission order.  q, k, v, out should be pinned host memory (pageable memory makes the copies synchronous).
+ * Device-side conditions are reported by dg_ctx_synchronize / dg_ctx_last_device_status as for every other
+ * call.  One pipe per context; other calls on the context may be interleaved, they are ordered on its stream.
+ * No counterpart in the reference, whose activations never leave the device.                       */
+typedef struct dg_host_pipe dg_host_pipe;
+int32_t dg_host_pipe_create(dg_ctx* ctx, const dg_layer_desc* desc, uint32_t max_batch, uint32_t depth,
+                            dg_host_pipe** out);
+int32_t dg_host_pipe_submit(dg_host_pipe* pipe, const dg_layer_desc* desc, dg_kv* const* kv, const uint32_t* kv_len,
+                            uint32_t batch, const void* q, const void* k, const void* v, const void* qw,
+                            const void* kw, void* out, uint64_t* ticket);
+int32_t dg_host_pipe_wait(dg_host_pipe* pipe, uint64_t ticket);
+int32_t dg_host_pipe_destroy(dg_host_pipe* pipe);
 /* General decoder bitmap (reference DecoderAttnMask, src/model/mask.rs:4-27): attend is a
  * device pointer to uint8 [C][kv_len+C], 1 = visible.  Served by the general kernel.            */
 int32_t dg_attn_denoise_bitmap(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* kv, uint32_t kv_len,

@@ -482,3 +482,30 @@ def test_hd512_tensor_path_parity(ctx, P, Hq, Hkv, canvas, W, mode, scale, vnorm
     ctx.force_general(False)
     util.assert_close(got, ref, "hd512 general path")
     assert ctx.device_status()[0] == 0
+
+
+# ------------------------------------------------------------------------------------------
+# host-buffer pipeline
+# ------------------------------------------------------------------------------------------
+def test_host_pipe_matches_the_synchronous_host_call(ctx):
+    from diffgemma_b200.step_attn import HostPipe
+    layer = AttnLayer(n_kv_heads=2)
+    cases = [util.make_case(layer, 3000, seed=400 + i) for i in range(7)]
+    kv, att = util.gpu_setup(ctx, cases[0])
+    pin = lambda t: t[None].contiguous().pin_memory()
+    ins = [(pin(c["q"]), pin(c["kc"]), pin(c["vc"])) for c in cases]
+    want = []
+    for q, k, v in ins:                                   # synchronous reference, one step at a time
+        o = torch.empty_like(q).pin_memory()
+        att.denoise_host([kv], [3000], q, k, v, o)
+        want.append(o.clone())
+    pipe = HostPipe(ctx, layer, 1, depth=3)
+    outs = [torch.empty_like(ins[0][0]).pin_memory() for _ in cases]
+    tickets = [pipe.submit([kv], [3000], q, k, v, o) for (q, k, v), o in zip(ins, outs)]   # more submits than slots
+    for t in reversed(tickets):                           # collected out of order
+        pipe.wait(t)
+    for o, w in zip(outs, want):
+        assert torch.equal(o.view(torch.int16), w.view(torch.int16))
+    pipe.close()
+    kv.close()
+    assert ctx.device_status()[0] == 0
