@@ -52,6 +52,11 @@ struct dg_ctx {
   cudaStream_t own_stream = nullptr;
   cudaStream_t stream = nullptr;
   DevStatus* d_status = nullptr;
+  // canvases of one batched call run concurrently on side streams (forked from / joined to `stream`)
+  cudaStream_t side[8] = {};
+  cudaEvent_t side_fork = nullptr, side_join[8] = {};
+  cudaStream_t side_active = nullptr;  // non-null while a canvas of a concurrent batch is being enqueued
+  uint32_t concurrent = 1;             // canvases in flight together: the split heuristic counts their CTAs
   float2* rope_table = nullptr;        // [kRopeSlots][kMaxCanvas][kMaxRotHalf]
   // what each table slot currently holds: denoise steps repeat at the same positions, so the table
   // of a slot is rewritten only when this key changes
@@ -303,6 +308,11 @@ extern "C" int32_t dg_ctx_destroy(dg_ctx* c) {
   if (c->stream) cudaStreamSynchronize(c->stream);
   cudaFree(c->d_status);
   cudaFree(c->rope_table);
+  for (int i = 0; i < 8; ++i) {
+    if (c->side[i]) cudaStreamDestroy(c->side[i]);
+    if (c->side_join[i]) cudaEventDestroy(c->side_join[i]);
+  }
+  if (c->side_fork) cudaEventDestroy(c->side_fork);
   cudaFree(c->counters);
   cudaFree(c->ws_o);
   cudaFree(c->ws_ml);
@@ -593,6 +603,10 @@ static int32_t check_ring_span(const dg_kv* kv, const MaskParams& mk, uint32_t c
 }
 
 // append n tokens (norm + RoPE + cache write); optionally also Q (stage 1) and the RoPE table
+// stream the kernels of the current call go to: the context's, or a side stream while the canvases of
+// a batch run concurrently
+static cudaStream_t launch_stream(const dg_ctx* c) { return c->side_active ? c->side_active : c->stream; }
+
 static int32_t do_append(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint64_t pos0, uint32_t n, const void* q_in,
                          void* q_out, const void* k_in, void* k_out, const void* v_in, void* v_out, const void* qw,
                          const void* kw, float2* table, uint32_t write_end = 0xffffffffu) {
@@ -619,7 +633,7 @@ static int32_t do_append(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint64_t 
   ap.ring_mask = kv->ring_mask ? kv->ring_mask : 0xffffffffu;
   ap.write_end = write_end;
   const RopeParams rp = make_rope(d);
-  launch_append(ap, rp, c->stream);
+  launch_append(ap, rp, launch_stream(c));
   DG_CUDA(cudaGetLastError());
   c->last_launches += 1;
   return DG_OK;
@@ -700,7 +714,7 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
   const bool tensor = tensor_path_ok(d) && kv->has_tmap && !c->force_general && a.attend == nullptr &&
                       (a.q_prenormed || fused_q_prologue_ok(d));
   if (!tensor) {
-    launch_attn_general(p, c->stream);
+    launch_attn_general(p, launch_stream(c));
     DG_CUDA(cudaGetLastError());
     c->last_launches += 1;
     return DG_OK;
@@ -719,7 +733,7 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
       p.ws_ml = c->ws_ml;
       p.ws_counters = c->counters;
     }
-    const cudaError_t e5 = launch_attn_sm100_hd512(p, kv->tm_k, kv->tm_v, c->stream);
+    const cudaError_t e5 = launch_attn_sm100_hd512(p, kv->tm_k, kv->tm_v, launch_stream(c));
     if (e5 != cudaSuccess) return fail_cuda(e5, "launch_attn_sm100_hd512");
     c->last_launches += 1;
     return DG_OK;
@@ -733,7 +747,7 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
   const bool pair = c->pair_mode == 1 || (c->pair_mode == 2 && tiles_per_head >= 2 && k_tiles >= 96);
   const uint32_t q_tiles = pair ? sm100_pair_query_tiles(p.C, p.G, p.Hkv) : sm100_query_tiles(p.C, p.G, p.Hkv);
   if (q_tiles > kMaxQueryTiles) return fail(DG_ERR_UNSUPPORTED, "too many query tiles");
-  p.n_splits = choose_splits(c, q_tiles, k_tiles);
+  p.n_splits = choose_splits(c, q_tiles * c->concurrent, k_tiles);
   // Split merge: consecutive splits of a query tile form a thread-block cluster and merge through
   // shared memory; what is left meets in the workspace.  Clusters stay at 4 CTAs in the pair form
   // (2 x 2): too few clusters of 8 are co-resident on the device.
@@ -749,10 +763,10 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
     p.ws_ml = c->ws_ml;
     p.ws_counters = c->counters;
   }
-  const bool timed = c->timing && c->ev_used + 2 <= c->ev.size();
+  const bool timed = c->timing && c->side_active == nullptr && c->ev_used + 2 <= c->ev.size();
   if (timed) DG_CUDA(cudaEventRecord(c->ev[c->ev_used], c->stream));
-  const cudaError_t e = pair ? launch_attn_sm100_pair(p, kv->tm_k64, kv->tm_v, c->stream)
-                             : launch_attn_sm100(p, kv->tm_k, kv->tm_v, c->stream);
+  const cudaError_t e = pair ? launch_attn_sm100_pair(p, kv->tm_k64, kv->tm_v, launch_stream(c))
+                             : launch_attn_sm100(p, kv->tm_k, kv->tm_v, launch_stream(c));
   if (e != cudaSuccess) return fail_cuda(e, "launch_attn_sm100");
   if (timed) {
     DG_CUDA(cudaEventRecord(c->ev[c->ev_used + 1], c->stream));
@@ -851,15 +865,70 @@ extern "C" int32_t dg_attn_denoise(dg_ctx* c, const dg_layer_desc* d, dg_kv* con
   DG_CUDA(cudaSetDevice(c->device));
   c->last_launches = 0;
   const size_t qe = size_t(d->canvas) * d->n_q_heads * d->head_dim, ke = size_t(d->canvas) * d->n_kv_heads * d->head_dim;
-  for (uint32_t b = 0; b < batch; ++b) {
+  // Independent canvases run CONCURRENTLY when nothing they use is shared: one side stream per canvas,
+  // forked from and joined to the context's stream, and a split count chosen for all their CTAs
+  // together (short key ranges then need no key split at all and so no merge).  That holds on the fused
+  // tensor path with splits merged inside clusters; anything that needs the shared staging buffer or
+  // the split workspace runs one canvas after the other.
+  bool concurrent = batch > 1 && batch <= 8 && d->head_dim == 256 && tensor_path_ok(*d) && fused_q_prologue_ok(*d) &&
+                    !c->force_general && !c->timing && c->stamps == nullptr;
+  for (uint32_t b = 0; concurrent && b < batch; ++b) concurrent = kv[b] != nullptr && kv[b]->has_tmap;
+  uint32_t conc_splits = 0;
+  bool conc_pair = false;
+  if (concurrent) {
+    // one kernel form and one split count for every canvas, and only if that needs no workspace
+    const uint32_t G = d->n_q_heads / d->n_kv_heads;
+    const uint32_t tph = sm100_query_tiles(d->canvas, G, 1);
+    uint32_t k_min = 0xffffffffu, k_max = 0;
+    for (uint32_t b = 0; b < batch; ++b) {
+      const uint32_t kt = sm100_key_tiles(make_mask(*d, kv_len[b], 0, 0xffffffffu, 1));
+      k_min = kt < k_min ? kt : k_min;
+      k_max = kt > k_max ? kt : k_max;
+    }
+    const bool pair_lo = c->pair_mode == 1 || (c->pair_mode == 2 && tph >= 2 && k_min >= 96);
+    const bool pair_hi = c->pair_mode == 1 || (c->pair_mode == 2 && tph >= 2 && k_max >= 96);
+    conc_pair = pair_lo;
+    const uint32_t q_tiles = conc_pair ? sm100_pair_query_tiles(d->canvas, G, d->n_kv_heads)
+                                       : sm100_query_tiles(d->canvas, G, d->n_kv_heads);
+    conc_splits = choose_splits(c, q_tiles * batch, k_max);
+    const bool no_ws = conc_splits == 1 || (conc_pair ? conc_splits == 2 : (conc_splits == 2 || conc_splits == 4 || conc_splits == 8));
+    concurrent = pair_lo == pair_hi && no_ws && conc_splits <= k_min;
+  }
+  const uint32_t saved_splits = c->forced_splits;
+  const int saved_pair = c->pair_mode;
+  if (concurrent) {
+    if (!c->side_fork) DG_CUDA(cudaEventCreateWithFlags(&c->side_fork, cudaEventDisableTiming));
+    for (uint32_t b = 0; b < batch; ++b) {
+      if (!c->side[b]) DG_CUDA(cudaStreamCreateWithFlags(&c->side[b], cudaStreamNonBlocking));
+      if (!c->side_join[b]) DG_CUDA(cudaEventCreateWithFlags(&c->side_join[b], cudaEventDisableTiming));
+    }
+    DG_CUDA(cudaEventRecord(c->side_fork, c->stream));
+    c->concurrent = batch;
+    c->forced_splits = conc_splits;
+    c->pair_mode = conc_pair ? 1 : 0;
+  }
+  int32_t rc = DG_OK;
+  for (uint32_t b = 0; b < batch && rc == DG_OK; ++b) {
     AttnCall a;
     a.out = static_cast<__nv_bfloat16*>(out) + b * qe;
-    r = denoise_one(c, *d, kv[b], kv_len[b], b, static_cast<const __nv_bfloat16*>(q) + b * qe,
-                    static_cast<const __nv_bfloat16*>(k) + b * ke, static_cast<const __nv_bfloat16*>(v) + b * ke, qw, kw,
-                    nullptr, a);
-    if (r != DG_OK) return r;
+    if (concurrent) {
+      c->side_active = c->side[b];
+      if (cudaStreamWaitEvent(c->side[b], c->side_fork, 0) != cudaSuccess) rc = fail(DG_ERR_CUDA, "cudaStreamWaitEvent");
+    }
+    if (rc == DG_OK)
+      rc = denoise_one(c, *d, kv[b], kv_len[b], b, static_cast<const __nv_bfloat16*>(q) + b * qe,
+                       static_cast<const __nv_bfloat16*>(k) + b * ke, static_cast<const __nv_bfloat16*>(v) + b * ke, qw, kw,
+                       nullptr, a);
+    if (concurrent) {
+      // join whatever was enqueued, also after an error, so that the context's stream stays ordered
+      if (cudaEventRecord(c->side_join[b], c->side[b]) == cudaSuccess) cudaStreamWaitEvent(c->stream, c->side_join[b], 0);
+    }
   }
-  return DG_OK;
+  c->side_active = nullptr;
+  c->concurrent = 1;
+  c->forced_splits = saved_splits;
+  c->pair_mode = saved_pair;
+  return rc;
 }
 
 extern "C" int32_t dg_attn_denoise_host(dg_ctx* c, const dg_layer_desc* d, dg_kv* const* kv, const uint32_t* kv_len,
