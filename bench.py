@@ -438,7 +438,7 @@ def run_ours(args):
                          "peak_sustained": peaks["bf16_tflops_sustained"],
                          "frac_of_sustained": (achieved / peaks["bf16_tflops_sustained"])
                          if (achieved and peaks["bf16_tflops_sustained"]) else None,
-                         "kernel": "dg_attn_sm100_kernel", "kernel_ms": k_avg_ms, "kernel_launches_timed": k_n},
+                         "kernel": "dg_attn_sm100_hd512_kernel" if lay.head_dim == 512 else "dg_attn_sm100_kernel", "kernel_ms": k_avg_ms, "kernel_launches_timed": k_n},
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e_ev,
                     "how": (f"dg_host_pipe, {PIPE_DEPTH} steps in flight: every step copies its inputs from pinned host "
                             "memory and its result back; copies of neighbouring steps overlap the kernels"
@@ -470,7 +470,7 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--cfg", type=int, default=2, choices=[0, 1, 2, 3, 4])
+    ap.add_argument("--cfg", type=int, default=2, choices=[0, 1, 2, 3, 4, 5])
     ap.add_argument("--ref-rows", type=int, default=256, help="canvas rows in the bounded CPU sample")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="multi-GPU partial exchange")

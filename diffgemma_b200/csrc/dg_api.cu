@@ -733,8 +733,14 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
       p.ws_ml = c->ws_ml;
       p.ws_counters = c->counters;
     }
+    const bool timed5 = c->timing && c->side_active == nullptr && c->ev_used + 2 <= c->ev.size();
+    if (timed5) DG_CUDA(cudaEventRecord(c->ev[c->ev_used], c->stream));
     const cudaError_t e5 = launch_attn_sm100_hd512(p, kv->tm_k, kv->tm_v, launch_stream(c));
     if (e5 != cudaSuccess) return fail_cuda(e5, "launch_attn_sm100_hd512");
+    if (timed5) {
+      DG_CUDA(cudaEventRecord(c->ev[c->ev_used + 1], c->stream));
+      c->ev_used += 2;
+    }
     c->last_launches += 1;
     return DG_OK;
   }

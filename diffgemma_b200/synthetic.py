@@ -32,6 +32,11 @@ def configs() -> dict[int, BenchConfig]:
                        AttnLayer(n_kv_heads=8, rope_theta=1e4, window=1024, mask_mode=capi.MASK_WINDOW_PER_ROW)),
         2: BenchConfig("cfg2_global_p32768", 32768, AttnLayer(n_kv_heads=2, rope_theta=1e6)),
         4: BenchConfig("cfg4_global_p131072", 131072, AttnLayer(n_kv_heads=2, rope_theta=1e6)),
+        # not one of the benchmark's configurations: the reference's real full-attention layer geometry
+        # (head_dim 512, rotary on 128 dims with proportional pairing, V normed without weight)
+        5: BenchConfig("ref_full_layer_hd512_p32768", 32768,
+                       AttnLayer(n_kv_heads=2, head_dim=512, rotary_dim=128, rope_theta=1e6, v_norm=1,
+                                 rope_pairing=capi.ROPE_PROPORTIONAL)),
     }
 
 
