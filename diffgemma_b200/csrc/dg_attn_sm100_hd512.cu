@@ -9,13 +9,16 @@
 //
 // Per CTA: 128 GQA-stacked query rows x one key split x one half of the value columns.
 //   * Q arrives already normed + roped (the stand-alone stage-1 kernel writes it to a staging
-//     buffer: full layers use partial proportional RoPE) and is copied into the UMMA K-major
-//     128B-swizzled layout: 8 atoms of 128 rows x 128 B = 128 KB.
-//   * key tiles of 64 keys: K 64 x 512 (8 atoms of 64 rows x 128 B = 64 KB), V 64 x 256 (4 atoms,
-//     32 KB), TMA 3-D boxes {64 d, 64 keys}, single-buffered: 224 KB of the 227 KB.
-//   * S = 32 x tcgen05.mma M128 N64 K16 (both operands from shared memory), two S buffers of 64
-//     TMEM columns; P (bf16) overwrites the first 32 columns of its S buffer; O += P V = 4 x
-//     tcgen05.mma M128 N256 K16 (A = P from TMEM, B = V MN-major); O in TMEM columns [256, 512).
+//     buffer: full layers use partial proportional RoPE).  Its first 256 elements per row go to
+//     TENSOR memory (columns [128, 256): the A operand of the first half of the contraction is read
+//     from there, which costs no shared-memory bandwidth), the other 256 into the UMMA K-major
+//     128B-swizzled layout in shared memory (4 atoms of 128 rows x 128 B = 64 KB).
+//   * key tiles of 64 keys: K 64 x 512 (8 atoms of 64 rows x 128 B = 64 KB) in TWO stages, V 64 x 256
+//     (4 atoms, 32 KB) in one; TMA 3-D boxes {64 d, 64 keys}: 224 KB of the 227 KB.
+//   * S = 32 x tcgen05.mma M128 N64 K16 (16 with A from tensor memory, 16 with A from shared memory),
+//     two S buffers of 64 TMEM columns; P (bf16) overwrites the first 32 columns of its S buffer;
+//     O += P V = 4 x tcgen05.mma M128 N256 K16 (A = P from TMEM, B = V MN-major); O in TMEM columns
+//     [256, 512).
 //   * 8 softmax warps, two threads per query row (32 score columns each), lazy rescale, packed
 //     fp32x2 arithmetic; warps 8 / 9 load K / V, one thread of warp 10 issues the MMAs.
 //   * key splits meet in the global workspace; the last CTA to arrive at the (query tile, half)
@@ -41,17 +44,18 @@ constexpr uint32_t CPT = TN / NTR;            // 32 score columns per thread
 constexpr uint32_t OPT = HDV / NTR;           // 128 output columns per thread
 constexpr uint32_t Q_ATOM = 128 * 128;        // 128 rows x 128 B
 constexpr uint32_t KV_ATOM = 64 * 128;        // 64 rows x 128 B
-constexpr uint32_t O_Q = 0;
-constexpr uint32_t O_K = 8 * Q_ATOM;                  // 128 KB
-constexpr uint32_t O_V = O_K + 8 * KV_ATOM;           // + 64 KB
-constexpr uint32_t O_BAR = O_V + 4 * KV_ATOM;         // + 32 KB = 224 KB
+constexpr uint32_t K_STAGE = 8 * KV_ATOM;             // 64 KB
+constexpr uint32_t O_Q = 0;                           // Q[:, 256:512]: 4 atoms = 64 KB
+constexpr uint32_t O_K = 4 * Q_ATOM;                  // two K stages = 128 KB
+constexpr uint32_t O_V = O_K + 2 * K_STAGE;           // + 32 KB
+constexpr uint32_t O_BAR = O_V + 4 * KV_ATOM;         // = 224 KB
 constexpr uint32_t O_XCH = O_BAR + 256;               // [2 tile parities][BM][NTR] floats = 2 KB
 constexpr uint32_t O_END = O_XCH + 2 * BM * NTR * 4;
 constexpr uint32_t SMEM_REQ = 232448;                 // all of the 227 KB a CTA may have
 static_assert(O_END <= SMEM_REQ, "shared-memory map does not fit");
-constexpr uint32_t T_S = 0, T_O = 256;                // TMEM columns: S buffers at 0 and 64, O at 256
-enum : uint32_t { B_Q = 0, B_K_FULL = 1, B_V_FULL = 2, B_V_EMPTY = 3 /* +tile&1 */, B_S_FULL = 5 /* +buffer */,
-                  B_P_FULL = 7 /* +buffer */, B_O_FINAL = 9, B_COUNT = 10 };
+constexpr uint32_t T_S = 0, T_Q = 128, T_O = 256;     // TMEM columns: S buffers at 0 and 64, Q[:, 0:256] at 128, O at 256
+enum : uint32_t { B_Q = 0, B_K_FULL = 1 /* +stage */, B_V_FULL = 3, B_V_EMPTY = 4 /* +tile&1 */, B_S_FULL = 6 /* +buffer */,
+                  B_P_FULL = 8 /* +buffer */, B_O_FINAL = 10, B_COUNT = 11 };
 
 __host__ __device__ inline TileSched tile_sched64(const MaskParams& mk, uint32_t row_first) {
   TileSched t{0, 0, 0, 0};
@@ -115,9 +119,9 @@ dg_attn_sm100_hd512_kernel(const AttnParams p, const __grid_constant__ CUtensorM
   // ------------------------------------------------------------------ set-up
   if (tid == 0) {
     mbar_init(bar_addr(bar_base, B_Q), SM_WARPS);
-    mbar_init(bar_addr(bar_base, B_K_FULL), 1);
     mbar_init(bar_addr(bar_base, B_V_FULL), 1);
     for (uint32_t s = 0; s < 2; ++s) {
+      mbar_init(bar_addr(bar_base, B_K_FULL + s), 1);
       mbar_init(bar_addr(bar_base, B_V_EMPTY + s), 1);
       mbar_init(bar_addr(bar_base, B_S_FULL + s), 1);
       mbar_init(bar_addr(bar_base, B_P_FULL + s), SM_WARPS);
@@ -152,15 +156,33 @@ dg_attn_sm100_hd512_kernel(const AttnParams p, const __grid_constant__ CUtensorM
       const uint32_t i = valid ? R / p.G : 0u;
       const uint32_t h = kvh * p.G + (valid ? R % p.G : 0u);
       const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t(i) * p.Hq + h) * HDQ);
+      if (half == 0) {
+        // elements [0, 256) of the row -> tensor memory: 16-byte chunk c = columns [4c, 4c + 4) of lane r,
+        // so that the 16 elements of contraction step kk sit in columns [8 kk, 8 kk + 8) (the layout P uses)
+        const uint32_t t_row = tmem + ((smw * 32u) << 16) + T_Q;
+#pragma unroll 1
+        for (uint32_t g8 = 0; g8 < 4; ++g8) {
+          uint32_t w[32];
+#pragma unroll
+          for (uint32_t j = 0; j < 8; ++j) {
+            const uint4 v4 = valid ? src[g8 * 8 + j] : make_uint4(0u, 0u, 0u, 0u);
+            w[4 * j] = v4.x; w[4 * j + 1] = v4.y; w[4 * j + 2] = v4.z; w[4 * j + 3] = v4.w;
+          }
+          tmem_st32(t_row + g8 * 32u, w);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+      } else {
+        // elements [256, 512) -> shared memory, K-major 128-byte-swizzled: atom = 64-element column block,
+        // 16-byte chunk index XOR (row & 7)
 #pragma unroll 4
-      for (uint32_t j = 0; j < 32; ++j) {
-        const uint32_t c = half * 32 + j;           // 16-byte chunk of the row, 64 per row
-        const uint4 v4 = valid ? src[c] : make_uint4(0u, 0u, 0u, 0u);
-        // K-major 128-byte-swizzled layout: atom = 64-element column block, chunk index XOR (row & 7)
-        *reinterpret_cast<uint4*>(smem + O_Q + (c >> 3) * Q_ATOM + r * 128u + (((c & 7u) ^ (r & 7u)) << 4)) = v4;
+        for (uint32_t j = 0; j < 32; ++j) {
+          const uint4 v4 = valid ? src[32 + j] : make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(smem + O_Q + (j >> 3) * Q_ATOM + r * 128u + (((j & 7u) ^ (r & 7u)) << 4)) = v4;
+        }
+        fence_proxy_async_smem();
       }
     }
-    fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) mbar_arrive(bar_addr(bar_base, B_Q));
 
@@ -251,13 +273,15 @@ dg_attn_sm100_hd512_kernel(const AttnParams p, const __grid_constant__ CUtensorM
       for (uint32_t n = 0; n < n_local; ++n) {
         const uint32_t v = v_begin + n;
         const uint32_t jt = v < ts.nA ? ts.a0 + v : ts.b0 + (v - ts.nA);
-        // the K tile is free once QK(n - 1) has completed
-        if (n > 0 && !mbar_wait(bar_addr(bar_base, B_S_FULL + ((n - 1) & 1u)), ((n - 1) >> 1) & 1u, abort_flag)) break;
-        const uint32_t full = bar_addr(bar_base, B_K_FULL);
-        mbar_expect_tx(full, 8 * KV_ATOM);
+        // K stage n & 1 is free once QK(n - 2) has completed
+        const uint32_t st = n & 1u;
+        if (n > 1 && !mbar_wait(bar_addr(bar_base, B_S_FULL + st), ((n - 2) >> 1) & 1u, abort_flag)) break;
+        const uint32_t full = bar_addr(bar_base, B_K_FULL + st);
+        mbar_expect_tx(full, K_STAGE);
 #pragma unroll
         for (uint32_t a = 0; a < 8; ++a)
-          tma_load_3d(sK + a * KV_ATOM, &tm_k, full, int32_t(a * 64), int32_t((jt * TN) & p.ring_mask), int32_t(kvh));
+          tma_load_3d(sK + st * K_STAGE + a * KV_ATOM, &tm_k, full, int32_t(a * 64), int32_t((jt * TN) & p.ring_mask),
+                      int32_t(kvh));
       }
     }
   } else if (warp == W_V) {
@@ -287,19 +311,32 @@ dg_attn_sm100_hd512_kernel(const AttnParams p, const __grid_constant__ CUtensorM
       auto mkdesc = [](uint32_t lo, uint32_t hi) { return (uint64_t(hi) << 32) | uint64_t(lo); };
       bool ok = mbar_wait(bar_addr(bar_base, B_Q), 0u, abort_flag);
       auto issue_qk = [&](uint32_t n) -> bool {
-        if (!mbar_wait(bar_addr(bar_base, B_K_FULL), n & 1u, abort_flag)) return false;
+        const uint32_t st = n & 1u;
+        if (!mbar_wait(bar_addr(bar_base, B_K_FULL + st), (n >> 1) & 1u, abort_flag)) return false;
         tc_fence_after();
         const uint32_t d_tmem = tmem + T_S + (n & 1u) * TN;
-        uint32_t qa = q_lo, kb = k_lo;
+        uint32_t kb = k_lo + st * (K_STAGE >> 4);
+        // contraction steps 0-15: Q[:, 0:256] from tensor memory
+        uint32_t qt = tmem + T_Q;
 #pragma unroll 1
-        for (uint32_t a = 0; a < 8; ++a) {
+        for (uint32_t a = 0; a < 4; ++a) {
 #pragma unroll
           for (uint32_t kk = 0; kk < 4; ++kk)
-            umma_ss(d_tmem, mkdesc(qa + kk * 2u, HI), mkdesc(kb + kk * 2u, HI), IDESC_QK, (a | kk) != 0u);
+            umma_ts(d_tmem, qt + kk * 8u, mkdesc(kb + kk * 2u, HI), IDESC_QK, (a | kk) != 0u);
+          qt += 32u;
+          kb += KV_ATOM >> 4;
+        }
+        // contraction steps 16-31: Q[:, 256:512] from shared memory
+        uint32_t qa = q_lo;
+#pragma unroll 1
+        for (uint32_t a = 0; a < 4; ++a) {
+#pragma unroll
+          for (uint32_t kk = 0; kk < 4; ++kk)
+            umma_ss(d_tmem, mkdesc(qa + kk * 2u, HI), mkdesc(kb + kk * 2u, HI), IDESC_QK, 1u);
           qa += Q_ATOM >> 4;
           kb += KV_ATOM >> 4;
         }
-        umma_commit(bar_addr(bar_base, B_S_FULL + (n & 1u)));   // S ready; the K tile is free
+        umma_commit(bar_addr(bar_base, B_S_FULL + (n & 1u)));   // S ready; this K stage is free
         return true;
       };
       ok = ok && issue_qk(0);
