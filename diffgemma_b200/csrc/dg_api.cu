@@ -1388,6 +1388,7 @@ struct dg_p2p {
   bool opened[8] = {};
   bool connected = false;
   uint32_t step = 0;
+  int32_t mode = 0;          // 0 automatic (all rows with two ranks, slices otherwise), 1 slices, 2 all rows
   P2pParams layout;
 };
 
@@ -1402,7 +1403,7 @@ static void p2p_layout(dg_p2p* x) {
     L.off_l[p] = take(size_t(x->rows) * 4);
     L.off_res[p] = take(size_t(x->rows) * x->D * 2);
   }
-  L.off_pflag = take(2 * 4);
+  L.off_pflag = take(2 * 8 * 4);
   L.off_rflag = take(2 * 8 * 4);
   L.off_done = take(2 * 4);
   x->bytes = off;
@@ -1436,6 +1437,13 @@ extern "C" int32_t dg_p2p_create(dg_ctx* c, uint32_t rows, uint32_t head_dim, in
   }
   x->peer[rank] = x->local;
   *out = x;
+  return DG_OK;
+}
+
+extern "C" int32_t dg_p2p_set_mode(dg_p2p* x, int32_t mode) {
+  if (!x) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  if (mode < 0 || mode > 2) return fail(DG_ERR_INVALID_ARG, "mode must be 0 (automatic), 1 (row slices) or 2 (all rows)");
+  x->mode = mode;
   return DG_OK;
 }
 
@@ -1505,6 +1513,7 @@ extern "C" int32_t dg_attn_denoise_split_p2p(dg_ctx* c, const dg_layer_desc* d, 
   P2pParams pp = x->layout;
   pp.step = x->step;
   pp.parity = par;
+  pp.all_rows = (x->mode == 2 || (x->mode == 0 && x->world == 2)) ? 1u : 0u;
   launch_p2p_merge(pp, out, c->num_sms, c->stream);
   DG_CUDA(cudaGetLastError());
   c->last_launches += 1;

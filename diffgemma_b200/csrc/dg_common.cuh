@@ -141,10 +141,11 @@ struct AttnParams {
 struct P2pParams {
   uint8_t* peer[8];        // exchange buffer of every rank, as mapped into this process
   size_t off_o[2], off_m[2], off_l[2], off_res[2];   // per parity
-  size_t off_pflag, off_rflag, off_done;             // u32 pflag[2], rflag[2][8], done[2]
+  size_t off_pflag, off_rflag, off_done;             // u32 pflag[2][8], rflag[2][8], done[2]
   DevStatus* status;
   long long wait_limit;    // cycles
   uint32_t world, rank, rows, D, step, parity;
+  uint32_t all_rows;       // 1: every rank merges every row itself (no result scatter, no second flag round)
 };
 
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(uint32_t(b) << 16); }

@@ -8,6 +8,10 @@
 // slices have landed locally - copies the result to the caller's output.  Two parities
 // of every buffer and flag alternate between steps; flags carry a monotonically increasing step id.
 //
+// With two ranks the slices are not worth their second exchange: each rank reads the peer's whole
+// partial (4.2 MB, a few microseconds of NVLink) and merges every row itself, so there is one flag
+// round trip instead of two and no result scatter.
+//
 // All waits are bounded: a flag that does not arrive within the limit records DG_DEV_WAIT_TIMEOUT
 // and the kernel carries on without it.
 #include "dg_common.cuh"
@@ -53,26 +57,40 @@ __global__ void __launch_bounds__(256) dg_p2p_merge_kernel(const P2pParams q, ui
   uint8_t* mine = q.peer[q.rank];
   if (tid == 0) s_ok = 1u;
   // 1. publish this rank's partial (written by the preceding kernel on the stream)
-  if (blockIdx.x == 0 && tid == 0) {
+  //    by WRITING the step id into every rank's flag array, so that waiting is a poll of local memory
+  if (blockIdx.x == 0 && tid < q.world) {
     __threadfence_system();
-    st_release_sys(reinterpret_cast<uint32_t*>(mine + q.off_pflag) + par, q.step);
+    st_release_sys(reinterpret_cast<uint32_t*>(q.peer[tid] + q.off_pflag) + par * 8 + q.rank, q.step);
   }
   __syncthreads();
   // 2. every CTA waits for every peer's partial
   if (tid < q.world) {
-    const uint32_t* f = reinterpret_cast<const uint32_t*>(q.peer[tid] + q.off_pflag) + par;
+    const uint32_t* f = reinterpret_cast<const uint32_t*>(mine + q.off_pflag) + par * 8 + tid;
     if (!wait_flag(f, q.step, q.wait_limit)) {
       s_ok = 0u;
       dev_status_set(q.status, DG_DEV_WAIT_TIMEOUT, KID_MERGE, blockIdx.x, tid);
     }
   }
   __syncthreads();
-  // 3. merge this rank's slice of the rows
-  const uint32_t r0 = uint32_t((uint64_t(q.rank) * q.rows) / q.world);
-  const uint32_t r1 = uint32_t((uint64_t(q.rank + 1) * q.rows) / q.world);
+  // 3. merge this rank's slice of the rows (two ranks: every row, written straight to the output)
+  const bool all_rows = q.all_rows != 0u;
+  const uint32_t r0 = all_rows ? 0u : uint32_t((uint64_t(q.rank) * q.rows) / q.world);
+  const uint32_t r1 = all_rows ? q.rows : uint32_t((uint64_t(q.rank + 1) * q.rows) / q.world);
   const uint32_t D = q.D, W = q.world;
   if (s_ok) {
     for (uint32_t row = r0 + blockIdx.x * 8 + warp; row < r1; row += gridDim.x * 8) {
+      // the row's first 256 columns of every partial are requested together with its (m, l) pairs, so
+      // that one NVLink round trip covers both
+      float4 a0[8], b0[8];
+#pragma unroll
+      for (uint32_t w = 0; w < 8; ++w) {
+        a0[w] = b0[w] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (w < W) {
+          const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(q.peer[w] + q.off_o[par]) + size_t(row) * D + lane * 8);
+          a0[w] = ld_sys_f4(src);
+          b0[w] = ld_sys_f4(src + 1);
+        }
+      }
       float mw = -INFINITY, lw = 0.f;
       if (lane < W) {
         mw = ld_sys_f(reinterpret_cast<const float*>(q.peer[lane] + q.off_m[par]) + row);
@@ -93,11 +111,15 @@ __global__ void __launch_bounds__(256) dg_p2p_merge_kernel(const P2pParams q, ui
         float4 a[8], b[8];
 #pragma unroll
         for (uint32_t w = 0; w < 8; ++w) {
-          a[w] = b[w] = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (w < W) {   // uniform: only the W real partials cross the link, all issued before first use
-            const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(q.peer[w] + q.off_o[par]) + size_t(row) * D + c0);
-            a[w] = ld_sys_f4(src);
-            b[w] = ld_sys_f4(src + 1);
+          a[w] = a0[w];
+          b[w] = b0[w];
+          if (c0 >= 256u) {
+            a[w] = b[w] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (w < W) {   // uniform: only the W real partials cross the link, all issued before first use
+              const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(q.peer[w] + q.off_o[par]) + size_t(row) * D + c0);
+              a[w] = ld_sys_f4(src);
+              b[w] = ld_sys_f4(src + 1);
+            }
           }
         }
 #pragma unroll
@@ -114,11 +136,16 @@ __global__ void __launch_bounds__(256) dg_p2p_merge_kernel(const P2pParams q, ui
         o4.y = *reinterpret_cast<uint32_t*>(&h1);
         o4.z = *reinterpret_cast<uint32_t*>(&h2);
         o4.w = *reinterpret_cast<uint32_t*>(&h3);
-        for (uint32_t w = 0; w < W; ++w)
-          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(q.peer[w] + q.off_res[par]) + size_t(row) * D + c0) = o4;
+        if (all_rows) {
+          out[(size_t(row) * D + c0) / 8] = o4;
+        } else {
+          for (uint32_t w = 0; w < W; ++w)
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(q.peer[w] + q.off_res[par]) + size_t(row) * D + c0) = o4;
+        }
       }
     }
   }
+  if (all_rows) return;   // nothing was sent: no second exchange
   // 4. the last CTA to finish tells every rank that this rank's slice has landed.  One
   //    system-scope fence per CTA, issued after the CTA barrier, covers the stores of all its threads.
   __syncthreads();
@@ -151,7 +178,7 @@ __global__ void __launch_bounds__(256) dg_p2p_merge_kernel(const P2pParams q, ui
 }
 
 void launch_p2p_merge(const P2pParams& q, void* out, int num_sms, cudaStream_t st) {
-  const uint32_t slice = (q.rows + q.world - 1) / q.world;
+  const uint32_t slice = q.all_rows ? q.rows : (q.rows + q.world - 1) / q.world;
   uint32_t grid = (slice + 7) / 8;
   if (grid > uint32_t(num_sms)) grid = uint32_t(num_sms);
   if (grid == 0) grid = 1;

@@ -54,7 +54,7 @@ class SplitKvGroup:
     over NVLink (CUDA IPC mappings); exchange="nccl": two NCCL all-reduces (max of m, sum of [O | l]).
     """
 
-    def __init__(self, ctx: Context, layer: AttnLayer, group=None, exchange: str = "p2p"):
+    def __init__(self, ctx: Context, layer: AttnLayer, group=None, exchange: str = "p2p", p2p_mode: int = 0):
         assert exchange in ("p2p", "nccl")
         self.ctx = ctx
         self.layer = layer
@@ -73,6 +73,7 @@ class SplitKvGroup:
             rows = layer.canvas * layer.n_q_heads
             check(lib.dg_p2p_create(ctx.h, rows, layer.head_dim, self.world, self.rank, C.byref(h)), "dg_p2p_create")
             self.p2p = h
+            check(lib.dg_p2p_set_mode(h, p2p_mode), "dg_p2p_set_mode")   # 0 automatic, 1 row slices, 2 all rows
             buf = (C.c_uint8 * 64)()
             check(lib.dg_p2p_handle(h, C.cast(buf, C.c_void_p)), "dg_p2p_handle")
             mine = torch.tensor(list(buf), dtype=torch.uint8, device=xdev)

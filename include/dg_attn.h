@@ -254,6 +254,10 @@ int32_t dg_nccl_all_gather(dg_ctx* ctx, void* comm, const void* send, void* recv
 typedef struct dg_p2p dg_p2p;
 int32_t dg_p2p_create(dg_ctx* ctx, uint32_t rows, uint32_t head_dim, int32_t world, int32_t rank, dg_p2p** out);
 int32_t dg_p2p_handle(dg_p2p* x, uint8_t handle_out[64]);
+/* How the merge is shared out: 1 = every rank merges its slice of the rows and sends the finished rows to the
+ * others (two flag rounds), 2 = every rank reads all partials and merges every row itself (one flag round; pays
+ * off with two ranks), 0 = automatic (default: 2 with two ranks, 1 otherwise).  Every rank must use the same.  */
+int32_t dg_p2p_set_mode(dg_p2p* x, int32_t mode);
 int32_t dg_p2p_connect(dg_p2p* x, const uint8_t* handles);
 int32_t dg_p2p_destroy(dg_p2p* x);
 int32_t dg_attn_denoise_split_p2p(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* kv, uint32_t kv_len, uint32_t t0,

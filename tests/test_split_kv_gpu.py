@@ -34,7 +34,8 @@ def _rank_main(rank, world, port, P, W, mode, exchange, ret):
         t0, t1 = b[rank], b[rank + 1]
         if t1 > t0:                                        # only this rank's shard is resident
             kv.load_prefix(case["kp"][t0:t1].contiguous().to(dev), case["vp"][t0:t1].contiguous().to(dev), t0)
-        grp = SplitKvGroup(ctx, layer, exchange=exchange)
+        mode = {"p2p": 0, "p2p-slices": 1, "p2p-allrows": 2}.get(exchange, 0)
+        grp = SplitKvGroup(ctx, layer, exchange="nccl" if exchange == "nccl" else "p2p", p2p_mode=mode)
         out = None
         for _ in range(3):                                 # several steps: buffer parities and flags are reused
             out = grp.denoise(kv, P, case["q"].to(dev), case["kc"].to(dev), case["vc"].to(dev))
@@ -48,7 +49,7 @@ def _rank_main(rank, world, port, P, W, mode, exchange, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["p2p", "nccl"])
+@pytest.mark.parametrize("exchange", ["p2p", "p2p-slices", "p2p-allrows", "nccl"])
 @pytest.mark.parametrize("P,W,mode,port", [(6000, 0, 0, 29721), (3000, 1024, 1, 29722)])
 def test_split_kv_matches_oracle(P, W, mode, port, exchange):
     world = min(torch.cuda.device_count(), 4)
@@ -56,7 +57,7 @@ def test_split_kv_matches_oracle(P, W, mode, port, exchange):
         pytest.skip("needs at least 2 GPUs")
     mgr = mp.Manager()
     ret = mgr.dict()
-    port += 10 if exchange == "nccl" else 0
+    port += {"p2p": 0, "nccl": 10, "p2p-slices": 20, "p2p-allrows": 30}[exchange]
     mp.spawn(_rank_main, args=(world, port, P, W, mode, exchange, ret), nprocs=world, join=True)
     assert len(ret) == world
     for rank, (mx, mean, tol) in ret.items():
