@@ -21,6 +21,7 @@ DG_ERR_NO_DEVICE = -5
 DG_ERR_NCCL = -6
 DG_ERR_ALIGNMENT = -7
 DG_DEV_WAIT_TIMEOUT = 1
+DG_DEV_SMEM_LAYOUT = 3
 DG_DEV_BAD_SHAPE = 2
 
 MASK_NONE, MASK_WINDOW_UNIFORM, MASK_WINDOW_PER_ROW = 0, 1, 2

@@ -262,6 +262,7 @@ extern "C" const char* dg_status_str(int32_t s) {
     case DG_ERR_NCCL: return "NCCL error";
     case DG_ERR_ALIGNMENT: return "pointer not 16-byte aligned";
     case DG_DEV_WAIT_TIMEOUT: return "device-side wait timed out";
+    case DG_DEV_SMEM_LAYOUT: return "shared-memory map did not fit the block's window";
     case DG_DEV_BAD_SHAPE: return "device-side shape check failed";
     default: return "unknown status";
   }

@@ -92,7 +92,7 @@ dg_attn_sm100_hd512_kernel(const AttnParams p, const __grid_constant__ CUtensorM
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // the map above needs a 1024-byte aligned base and leaves 768 bytes of slack for it
   if (smem_base - smem_u32(smem_raw) + O_END > SMEM_REQ) {
-    if (tid == 0) dev_status_set(p.status, DG_DEV_WAIT_TIMEOUT, KID_SM100, 0xA11Cu, smem_base - smem_u32(smem_raw));
+    if (tid == 0) dev_status_set(p.status, DG_DEV_SMEM_LAYOUT, KID_SM100, blockIdx.x, smem_base - smem_u32(smem_raw));
     return;
   }
   const uint32_t sQ = smem_base + O_Q, sK = smem_base + O_K, sV = smem_base + O_V;

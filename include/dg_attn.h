@@ -40,7 +40,9 @@ enum {
   DG_ERR_NCCL = -6,          /* NCCL not loadable or an NCCL call failed                        */
   DG_ERR_ALIGNMENT = -7,     /* a device pointer is not 16-byte aligned                         */
   DG_DEV_WAIT_TIMEOUT = 1,   /* a bounded device-side wait gave up (kernel unwound cleanly)     */
-  DG_DEV_BAD_SHAPE = 2       /* device-side shape assertion                                     */
+  DG_DEV_BAD_SHAPE = 2,      /* device-side shape assertion                                     */
+  DG_DEV_SMEM_LAYOUT = 3     /* a kernel's shared-memory map did not fit its (unaligned) window; it
+                              * returned without doing anything                                  */
 };
 
 /* mask modes: which PREFIX keys a canvas row sees (canvas keys are always visible to every

@@ -509,3 +509,33 @@ def test_host_pipe_matches_the_synchronous_host_call(ctx):
     pipe.close()
     kv.close()
     assert ctx.device_status()[0] == 0
+
+
+# ------------------------------------------------------------------------------------------
+# a warmed-up step can be captured into a CUDA graph and replayed (what a 48-step denoise loop does)
+# ------------------------------------------------------------------------------------------
+def test_step_is_capturable_into_a_cuda_graph(ctx):
+    layer = AttnLayer(n_kv_heads=8, window=1024, mask_mode=capi.MASK_WINDOW_UNIFORM, rope_theta=1e4)
+    cases = [util.make_case(layer, 3000 - 64 * b, seed=500 + b) for b in range(3)]
+    kvs = [util.gpu_setup(ctx, c)[0] for c in cases]
+    att = CanvasAttention(ctx, layer)
+    lens = [c["prefix"] for c in cases]
+    q = torch.stack([c["q"] for c in cases]).to(DEV)
+    k = torch.stack([c["kc"] for c in cases]).to(DEV)
+    v = torch.stack([c["vc"] for c in cases]).to(DEV)
+    out = torch.empty_like(q)
+    for _ in range(2):                                     # warm-up: workspaces, side streams, RoPE tables
+        att.denoise(kvs, lens, q, k, v, out=out)
+    ctx.synchronize()
+    want = out.clone()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=ctx.torch_stream):
+        att.denoise(kvs, lens, q, k, v, out=out)
+    out.zero_()
+    g.replay()
+    ctx.synchronize()
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+    for b, c in enumerate(cases):
+        util.assert_close(util.t2f(out[b]), util.run_oracle(c), f"graph replay, canvas {b}")
+    for kv in kvs:
+        kv.close()
