@@ -313,7 +313,7 @@ def run_ours(args):
     q, kc, vc = q_h.to(dev), kc_h.to(dev), vc_h.to(dev)
     out = torch.empty_like(q)
     att = CanvasAttention(ctx, lay)
-    group = SplitKvGroup(ctx, lay, exchange=args.exchange) if world > 1 else None
+    group = SplitKvGroup(ctx, lay, exchange=args.exchange, p2p_mode=args.p2p_mode) if world > 1 else None
     stream = ctx.torch_stream
 
     def step_dev(i):
@@ -474,6 +474,8 @@ def main():
     ap.add_argument("--ref-rows", type=int, default=256, help="canvas rows in the bounded CPU sample")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="multi-GPU partial exchange")
+    ap.add_argument("--p2p-mode", type=int, default=0, choices=[0, 1, 2],
+                    help="peer-memory merge: 0 automatic, 1 row slices per rank, 2 every rank merges all rows")
     ap.add_argument("--kernel-form", default="auto", choices=["auto", "pair", "single"],
                     help="tensor-kernel form: CTA pairs, one CTA per query tile, or the library's choice")
     args = ap.parse_args()
