@@ -182,94 +182,106 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   float m_used = -INFINITY, l_run = 0.f;
 
   if (warp < SM_WARPS) {
-    // ---------------------------------------------------------------- Q prologue (four threads per row)
-    // Thread (row, qd) owns the RoPE pairs (d, d+128) with d in [32 qd, 32 qd + 32): four 16-byte
-    // chunks from each half of the row.  No shuffles; the partial sums of squares meet through
-    // shared memory.
+    // ---------------------------------------------------------------- Q prologue (one warp per row)
+    // A warp takes eight rows of the tile; lane c owns the 16-byte chunk c of a row, so every global
+    // access is one contiguous 512-byte row.  The raw rows are copied asynchronously straight into
+    // their final (swizzled) place; each lane then reads back its own chunk and its RoPE partner,
+    // chunk c ^ 16, and overwrites its own chunk with
+    //     rsqrt(mean(x^2) + eps) * (x * (w cos) -/+ partner * (w_partner sin)),
+    // in packed fp32 pairs.  The prologue is bound by instruction issue (sixteen warps on four
+    // schedulers), so the per-row work is kept to the reads, one butterfly and four packed products.
+    // Consecutive stacked rows share their canvas row, hence their table entries, G at a time.
     {
-      constexpr int NJ = 16 / NTR;
-      const uint32_t R = mt * BM + r;
-      const bool valid = R < rows_per_head;
-      const uint32_t i = valid ? R / p.G : 0u;
-      const uint32_t h = kvh * p.G + (valid ? R % p.G : 0u);
-      const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t(i) * p.Hq + h) * HD);
+      constexpr uint32_t RPW = BM / SM_WARPS;
       const bool do_norm = !p.q_prenormed;
-      uint4 lo[NJ], hi[NJ];
+      const uint32_t c = lane, c16 = lane & 15u;
+      const uint32_t R0 = mt * BM + warp * RPW;
+      const uint32_t i0 = R0 / p.G, g0 = R0 % p.G;
+      // byte offset of (row it of this warp, chunk c): (c ^ 16) has the same low three bits, so the
+      // partner sits at the same place two swizzle atoms away
+      uint8_t* q_own = smem + OFF_Q + (c >> 3) * ATOM_BYTES + warp * RPW * 128u;
+      uint8_t* q_par = smem + OFF_Q + ((c ^ 16u) >> 3) * ATOM_BYTES + warp * RPW * 128u;
+      {
+        uint32_t i = i0, g = g0;
 #pragma unroll
-      for (int j = 0; j < NJ; ++j) {
-        lo[j] = src[qd * NJ + j];
-        hi[j] = src[16 + qd * NJ + j];
+        for (uint32_t it = 0; it < RPW; ++it) {
+          const bool valid = R0 + it < rows_per_head;   // warp-uniform; rows past the end are zero-filled
+          const __nv_bfloat16* src = valid ? p.q + (size_t(i) * p.Hq + kvh * p.G + g) * HD + c * 8u : p.q;
+          cp_async_16(smem_u32(q_own + it * 128u + (((c & 7u) ^ it) << 4)), src, valid ? 16u : 0u);
+          if (++g == p.G) { g = 0; ++i; }
+        }
       }
-      if (!valid) {
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) lo[j] = hi[j] = make_uint4(0u, 0u, 0u, 0u);
-      }
-      // RoPE-table entries of this thread's pairs: issued now so that they arrive while the sums of
-      // squares are reduced
-      float4 tabv[NJ * 4];
       if (do_norm) {
-        const float4* tab = reinterpret_cast<const float4*>(p.rope_table + size_t(i) * 128 + qd * (8 * NJ));
+        uint4 w4 = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u), wp4 = w4;   // bf16 1.0
+        if (p.qw) {
+          w4 = reinterpret_cast<const uint4*>(p.qw)[c];
+          wp4 = reinterpret_cast<const uint4*>(p.qw)[c ^ 16u];
+        }
+        // low half of a row: x cos - partner sin; high half: x cos + partner sin
+        const float sgn = lane < 16u ? -1.0f : 1.0f;
+        const uint64_t sgn2 = pack_f32x2(sgn, sgn);
+        const uint32_t wm[4] = {w4.x, w4.y, w4.z, w4.w};
+        const uint32_t wq[4] = {wp4.x, wp4.y, wp4.z, wp4.w};
+        uint64_t wm2[4], wq2[4];
 #pragma unroll
-        for (int t = 0; t < NJ * 4; ++t) tabv[t] = tab[t];
-      }
-      float inv = 1.0f;
-      if (do_norm) {
-        float ss0 = 0.f, ss1 = 0.f;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) {
-          const uint32_t a[4] = {lo[j].x, lo[j].y, lo[j].z, lo[j].w};
-          const uint32_t b[4] = {hi[j].x, hi[j].y, hi[j].z, hi[j].w};
+        for (int e = 0; e < 4; ++e) {
+          wm2[e] = bf16x2_to_f32x2(wm[e]);
+          wq2[e] = mul_f32x2(bf16x2_to_f32x2(wq[e]), sgn2);
+        }
+        uint64_t A[4], B[4];   // w cos and -/+ w_partner sin of this lane's eight pairs
+        auto load_table = [&](uint32_t i) {
+          // (cos, sin) of the pairs 8 c16 .. 8 c16 + 7 of canvas row i
+          const float4* tab = reinterpret_cast<const float4*>(p.rope_table + size_t(i) * 128 + c16 * 8u);
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float a0 = __uint_as_float(a[e] << 16), a1 = __uint_as_float(a[e] & 0xffff0000u);
-            const float b0 = __uint_as_float(b[e] << 16), b1 = __uint_as_float(b[e] & 0xffff0000u);
-            ss0 += a0 * a0 + a1 * a1;
-            ss1 += b0 * b0 + b1 * b1;
+            const float4 cs = tab[e];
+            A[e] = mul_f32x2(wm2[e], pack_f32x2(cs.x, cs.z));
+            B[e] = mul_f32x2(wq2[e], pack_f32x2(cs.y, cs.w));
           }
-        }
-        xch_misc[r * NTR + qd] = ss0 + ss1;
-        row_group_sync(smw);
-        float ss = 0.f;
+        };
+        if (R0 < rows_per_head) load_table(i0);
+        cp_async_wait_all();
+        __syncwarp();
+        uint32_t i = i0, g = g0;
 #pragma unroll
-        for (uint32_t k = 0; k < NTR; ++k) ss += xch_misc[r * NTR + k];   // same order in every thread
-        inv = 1.0f / sqrtf(ss / float(HD) + p.eps);
-      }
-#pragma unroll
-      for (int j = 0; j < NJ; ++j) {
-        const uint32_t c_lo = qd * NJ + j, c_hi = c_lo + 16;
-        uint4 out_lo = lo[j], out_hi = hi[j];
-        if (do_norm) {
-          uint4 wl4 = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u), wh4 = wl4;   // bf16 1.0
-          if (p.qw) {
-            wl4 = reinterpret_cast<const uint4*>(p.qw)[c_lo];
-            wh4 = reinterpret_cast<const uint4*>(p.qw)[c_hi];
-          }
-          const uint32_t a[4] = {lo[j].x, lo[j].y, lo[j].z, lo[j].w};
-          const uint32_t b[4] = {hi[j].x, hi[j].y, hi[j].z, hi[j].w};
-          const uint32_t wa[4] = {wl4.x, wl4.y, wl4.z, wl4.w};
-          const uint32_t wb[4] = {wh4.x, wh4.y, wh4.z, wh4.w};
-          uint32_t ya[4], yb[4];
+        for (uint32_t it = 0; it < RPW; ++it) {
+          if (R0 + it >= rows_per_head) break;   // warp-uniform
+          if (it != 0 && g == 0) load_table(i);
+          const uint32_t off = it * 128u + (((c & 7u) ^ it) << 4);
+          const uint4 xm = *reinterpret_cast<const uint4*>(q_own + off);
+          const uint4 xq = *reinterpret_cast<const uint4*>(q_par + off);
+          const uint32_t m[4] = {xm.x, xm.y, xm.z, xm.w};
+          const uint32_t q[4] = {xq.x, xq.y, xq.z, xq.w};
+          uint64_t m2[4];
+          uint64_t acc = 0ull;
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float4 cs = tabv[j * 4 + e];   // (cos, sin) of pairs 8*c_lo + 2e and + 2e + 1
-            const float a0 = __uint_as_float(a[e] << 16) * (inv * __uint_as_float(wa[e] << 16));
-            const float a1 = __uint_as_float(a[e] & 0xffff0000u) * (inv * __uint_as_float(wa[e] & 0xffff0000u));
-            const float b0 = __uint_as_float(b[e] << 16) * (inv * __uint_as_float(wb[e] << 16));
-            const float b1 = __uint_as_float(b[e] & 0xffff0000u) * (inv * __uint_as_float(wb[e] & 0xffff0000u));
-            ya[e] = pack_bf16x2(a0 * cs.x - b0 * cs.y, a1 * cs.z - b1 * cs.w);
-            yb[e] = pack_bf16x2(a0 * cs.y + b0 * cs.x, a1 * cs.w + b1 * cs.z);
+            m2[e] = bf16x2_to_f32x2(m[e]);
+            acc = fma_f32x2(m2[e], m2[e], acc);
           }
-          out_lo = make_uint4(ya[0], ya[1], ya[2], ya[3]);
-          out_hi = make_uint4(yb[0], yb[1], yb[2], yb[3]);
+          float s0, s1;
+          unpack_f32x2(acc, s0, s1);
+          float ss = s0 + s1;
+#pragma unroll
+          for (uint32_t o = 16; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // identical in every lane
+          const float inv = rsqrtf(ss * (1.0f / float(HD)) + p.eps);
+          const uint64_t inv2 = pack_f32x2(inv, inv);
+          uint32_t y[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint64_t t = fma_f32x2(m2[e], A[e], mul_f32x2(bf16x2_to_f32x2(q[e]), B[e]));
+            float y0, y1;
+            unpack_f32x2(mul_f32x2(t, inv2), y0, y1);
+            y[e] = pack_bf16x2(y0, y1);
+          }
+          __syncwarp();   // the partner has read this chunk
+          *reinterpret_cast<uint4*>(q_own + off) = make_uint4(y[0], y[1], y[2], y[3]);
+          if (++g == p.G) { g = 0; ++i; }
         }
-        // K-major 128-byte-swizzled layout: atom = 64-element column block, 16-byte chunk index
-        // XORed with (row & 7)
-        *reinterpret_cast<uint4*>(smem + OFF_Q + (c_lo >> 3) * ATOM_BYTES + r * 128u + (((c_lo & 7u) ^ (r & 7u)) << 4)) = out_lo;
-        *reinterpret_cast<uint4*>(smem + OFF_Q + (c_hi >> 3) * ATOM_BYTES + r * 128u + (((c_hi & 7u) ^ (r & 7u)) << 4)) = out_hi;
+      } else {
+        cp_async_wait_all();
       }
     }
-    // every lane publishes its own stores (in the pair form the leader's MMA thread reads this
-    // tile through the async proxy from the other SM), then one lane arrives for the warp
     if (PAIR) fence_proxy_async_all(); else fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {
