@@ -92,7 +92,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + B_COUNT * 8);
   // ctl[0] = TMEM base address, ctl[1] = abort flag, ctl[2] = "this CTA merges" flag
   float* xch_max = reinterpret_cast<float*>(smem + OFF_XCH);   // [2 tile parities][BM][NTR]
-  float* xch_misc = xch_max + 2 * BM * NTR;                     // [BM][NTR]: prologue sums of squares
+  float* xch_misc = xch_max + 2 * BM * NTR;                     // [BM][NTR]: spare
   float* xch_l = xch_misc + BM * NTR;                           // [BM][NTR]: final softmax denominators
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;

@@ -9,6 +9,7 @@ call the CUDA library; torch is used only to own device memory and streams.
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from dataclasses import dataclass
 
 import torch
@@ -71,6 +72,8 @@ class Context:
         self.h = h
         self.device = device
         self._made_current = make_current
+        # caches and pipes made from this context refer to it natively: they are closed first
+        self._dependents = weakref.WeakSet()
         if make_current:
             # torch owns the stream (so that nothing torch remembers about it can outlive it); the
             # context is told to launch on it
@@ -115,6 +118,8 @@ class Context:
 
     def close(self) -> None:
         if self.h:
+            for dep in list(self._dependents):
+                dep.close()
             if self._made_current:
                 # hand torch its default stream back before the context's stream is destroyed
                 torch.cuda.synchronize(self.device)
@@ -144,6 +149,7 @@ class KvCache:
         else:
             check(ctx.lib.dg_kv_create_ring(ctx.h, C.byref(d), ring_slots, C.byref(h)), "dg_kv_create_ring")
         self.h = h
+        ctx._dependents.add(self)
 
     @property
     def ring_mask(self) -> int:
@@ -282,6 +288,7 @@ class HostPipe:
         check(ctx.lib.dg_host_pipe_create(ctx.h, C.byref(self.desc), max_batch, depth, C.byref(h)), "dg_host_pipe_create")
         self.h = h
         self.depth = depth
+        ctx._dependents.add(self)
 
     def submit(self, kvs, kv_lens, q, k, v, out, qw=None, kw=None) -> int:
         """Host tensors q, k, v (read) and out (written) stay in use until wait(ticket) returns."""

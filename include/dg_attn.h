@@ -82,7 +82,9 @@ typedef struct dg_kv dg_kv;
 
 /* ---- context ---------------------------------------------------------------------------- */
 /* Replaces the reference's Metal device/queue/pipeline objects (src/metal/device.rs,
- * src/metal/step_kernel/build.rs:303-).  Creates a stream and a workspace on `device`.         */
+ * src/metal/step_kernel/build.rs:303-).  Creates a stream and a workspace on `device`.
+ * Caches, host pipes and p2p groups made from a context keep a pointer to it: destroy them
+ * before the context.                                                                          */
 int32_t dg_ctx_create(int32_t device, dg_ctx** out);
 int32_t dg_ctx_destroy(dg_ctx* ctx);
 /* Use a caller-owned CUDA stream (cudaStream_t passed as void*) instead of the internal one.   */
