@@ -688,51 +688,60 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
     n_rows = rpc;
     const float* recv = reinterpret_cast<const float*>(smem + OFF_Q);        // [cs][rpc][OBUF_LD]
     const float2* recv_ml = reinterpret_cast<const float2*>(smem + OFF_ML);  // [cs][rpc]
-    for (uint32_t rl = warp; rl < rpc; rl += THREADS / 32) {
-      const uint32_t rr = rank * rpc + rl;
-      const uint32_t R = mt * BM + rr;
-      if (R >= rows_per_head) continue;
-      const size_t orow = size_t(R / p.G) * p.Hq + kvh * p.G + R % p.G;
-      float2 ml = make_float2(-INFINITY, 0.f);
-      if (lane < cs) ml = recv_ml[lane * rpc + rl];
-      float mg = ml.x;
+    // A warp merges four rows at a time (lane = eight columns), every lane reading the cs (m, l)
+    // pairs itself: no shuffles and four independent chains, because this pass is bound by latency
+    constexpr uint32_t RK1 = 4;
+    for (uint32_t rl0 = warp * RK1; rl0 < rpc; rl0 += (THREADS / 32) * RK1) {
+      float mg[RK1], lg[RK1], acc[RK1][8];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, o));
-      const float w_mine = (ml.x == -INFINITY) ? 0.f : fast_exp2(ml.x - mg);
-      float lg = w_mine * ml.y;
+      for (uint32_t k = 0; k < RK1; ++k) {
+        const uint32_t rl = rl0 + k < rpc ? rl0 + k : rpc - 1;
+        mg[k] = -INFINITY;
+        for (uint32_t s2 = 0; s2 < cs; ++s2) mg[k] = fmaxf(mg[k], recv_ml[s2 * rpc + rl].x);
+        lg[k] = 0.f;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) lg += __shfl_xor_sync(0xffffffffu, lg, o);
-      float acc[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-      for (uint32_t s2 = 0; s2 < cs; ++s2) {
-        const float w = __shfl_sync(0xffffffffu, w_mine, int(s2));
-        const float4* src = reinterpret_cast<const float4*>(recv + (s2 * rpc + rl) * OBUF_LD + lane * 8);
-        const float4 a = src[0], bq = src[1];
-        acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * a.z; acc[3] += w * a.w;
-        acc[4] += w * bq.x; acc[5] += w * bq.y; acc[6] += w * bq.z; acc[7] += w * bq.w;
+        for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
       }
-      if (n_groups > 1) {
-        // the group's merged partial (still un-normalised, relative to mg) goes to the workspace
-        float4* dst = reinterpret_cast<float4*>(p.ws_o + (size_t(grp) * rows_total + orow) * HD + lane * 8);
-        dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-        dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-        if (lane == 0) reinterpret_cast<float2*>(p.ws_ml)[size_t(grp) * rows_total + orow] = make_float2(mg, lg);
-      } else if (p.out) {
-        const float inv = lg > 0.f ? 1.0f / lg : 0.f;
-        uint4 w4;
-        w4.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
-        w4.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
-        w4.z = pack_bf16x2(acc[4] * inv, acc[5] * inv);
-        w4.w = pack_bf16x2(acc[6] * inv, acc[7] * inv);
-        *reinterpret_cast<uint4*>(p.out + orow * HD + lane * 8) = w4;
-      } else {
-        float4* dst = reinterpret_cast<float4*>(p.out_o + orow * HD + lane * 8);
-        dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-        dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-        if (lane == 0) {
-          p.out_m[orow] = mg * 0.6931471805599453f;
-          p.out_l[orow] = lg;
+      for (uint32_t s2 = 0; s2 < cs; ++s2) {
+#pragma unroll
+        for (uint32_t k = 0; k < RK1; ++k) {
+          const uint32_t rl = rl0 + k < rpc ? rl0 + k : rpc - 1;
+          const float2 ml = recv_ml[s2 * rpc + rl];
+          const float w = (ml.x == -INFINITY) ? 0.f : fast_exp2(ml.x - mg[k]);
+          lg[k] += w * ml.y;
+          const float4* src = reinterpret_cast<const float4*>(recv + (s2 * rpc + rl) * OBUF_LD + lane * 8);
+          const float4 a = src[0], bq = src[1];
+          acc[k][0] += w * a.x; acc[k][1] += w * a.y; acc[k][2] += w * a.z; acc[k][3] += w * a.w;
+          acc[k][4] += w * bq.x; acc[k][5] += w * bq.y; acc[k][6] += w * bq.z; acc[k][7] += w * bq.w;
+        }
+      }
+#pragma unroll
+      for (uint32_t k = 0; k < RK1; ++k) {
+        const uint32_t R = mt * BM + rank * rpc + rl0 + k;
+        if (rl0 + k >= rpc || R >= rows_per_head) continue;
+        const size_t orow = size_t(R / p.G) * p.Hq + kvh * p.G + R % p.G;
+        if (n_groups > 1) {
+          // the group's merged partial (still un-normalised, relative to mg) goes to the workspace
+          float4* dst = reinterpret_cast<float4*>(p.ws_o + (size_t(grp) * rows_total + orow) * HD + lane * 8);
+          dst[0] = make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
+          dst[1] = make_float4(acc[k][4], acc[k][5], acc[k][6], acc[k][7]);
+          if (lane == 0) reinterpret_cast<float2*>(p.ws_ml)[size_t(grp) * rows_total + orow] = make_float2(mg[k], lg[k]);
+        } else if (p.out) {
+          const float inv = lg[k] > 0.f ? 1.0f / lg[k] : 0.f;
+          uint4 w4;
+          w4.x = pack_bf16x2(acc[k][0] * inv, acc[k][1] * inv);
+          w4.y = pack_bf16x2(acc[k][2] * inv, acc[k][3] * inv);
+          w4.z = pack_bf16x2(acc[k][4] * inv, acc[k][5] * inv);
+          w4.w = pack_bf16x2(acc[k][6] * inv, acc[k][7] * inv);
+          *reinterpret_cast<uint4*>(p.out + orow * HD + lane * 8) = w4;
+        } else {
+          float4* dst = reinterpret_cast<float4*>(p.out_o + orow * HD + lane * 8);
+          dst[0] = make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
+          dst[1] = make_float4(acc[k][4], acc[k][5], acc[k][6], acc[k][7]);
+          if (lane == 0) {
+            p.out_m[orow] = mg[k] * 0.6931471805599453f;
+            p.out_l[orow] = lg[k];
+          }
         }
       }
     }
@@ -754,6 +763,61 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
     if (ctl[2]) {
       __threadfence();
       const float2* ml_all = reinterpret_cast<const float2*>(p.ws_ml);
+      if (S == 2) {
+        // Two groups (the 32k pair form): one round trip.  A warp takes four rows, every lane loads
+        // both (m, l) pairs and its eight columns of both partials at once.
+        constexpr uint32_t RK2 = 4;
+        for (uint32_t r0 = warp * RK2; r0 < n_rows; r0 += (THREADS / 32) * RK2) {
+          size_t orow[RK2];
+          bool live[RK2];
+          float2 ml[RK2][2];
+          float4 a[RK2][2], bq[RK2][2];
+#pragma unroll
+          for (uint32_t k = 0; k < RK2; ++k) {
+            const uint32_t R = mt * BM + row0 + r0 + k;
+            live[k] = (r0 + k < n_rows) && (R < rows_per_head);
+            const uint32_t Rc = live[k] ? R : mt * BM;
+            orow[k] = size_t(Rc / p.G) * p.Hq + kvh * p.G + Rc % p.G;
+#pragma unroll
+            for (uint32_t j = 0; j < 2; ++j) {
+              ml[k][j] = ml_all[size_t(j) * rows_total + orow[k]];
+              const float4* src = reinterpret_cast<const float4*>(p.ws_o + (size_t(j) * rows_total + orow[k]) * HD + lane * 8);
+              a[k][j] = src[0];
+              bq[k][j] = src[1];
+            }
+          }
+#pragma unroll
+          for (uint32_t k = 0; k < RK2; ++k) {
+            if (!live[k]) continue;
+            const float mg = fmaxf(ml[k][0].x, ml[k][1].x);
+            const float w0 = (ml[k][0].x == -INFINITY) ? 0.f : fast_exp2(ml[k][0].x - mg);
+            const float w1 = (ml[k][1].x == -INFINITY) ? 0.f : fast_exp2(ml[k][1].x - mg);
+            const float lg = w0 * ml[k][0].y + w1 * ml[k][1].y;
+            float acc[8];
+            acc[0] = w0 * a[k][0].x + w1 * a[k][1].x; acc[1] = w0 * a[k][0].y + w1 * a[k][1].y;
+            acc[2] = w0 * a[k][0].z + w1 * a[k][1].z; acc[3] = w0 * a[k][0].w + w1 * a[k][1].w;
+            acc[4] = w0 * bq[k][0].x + w1 * bq[k][1].x; acc[5] = w0 * bq[k][0].y + w1 * bq[k][1].y;
+            acc[6] = w0 * bq[k][0].z + w1 * bq[k][1].z; acc[7] = w0 * bq[k][0].w + w1 * bq[k][1].w;
+            if (p.out) {
+              const float inv = lg > 0.f ? 1.0f / lg : 0.f;
+              uint4 w4;
+              w4.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
+              w4.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
+              w4.z = pack_bf16x2(acc[4] * inv, acc[5] * inv);
+              w4.w = pack_bf16x2(acc[6] * inv, acc[7] * inv);
+              *reinterpret_cast<uint4*>(p.out + orow[k] * HD + lane * 8) = w4;
+            } else {
+              float4* dst = reinterpret_cast<float4*>(p.out_o + orow[k] * HD + lane * 8);
+              dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+              dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+              if (lane == 0) {
+                p.out_m[orow[k]] = mg * 0.6931471805599453f;
+                p.out_l[orow[k]] = lg;
+              }
+            }
+          }
+        }
+      } else {
       // Phase A: one thread per row turns the S (m, l) pairs into merge weights, kept in shared
       // memory (the Q tile is dead): wsm[row][s] = 2^(m_s - m_g), plus m_g and l_g per row.
       float* wsm = reinterpret_cast<float*>(smem + OFF_Q);            // [BM][32]
@@ -853,6 +917,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
           }
         }
       }
+      }   // S > 2
       if (tid == 0) *counter = 0u;   // ready for the next launch
     }
   }
