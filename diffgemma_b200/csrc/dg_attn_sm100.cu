@@ -562,31 +562,58 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
     if (via_dsmem) {
       // The partial stays on chip.  Row r of the query tile is merged by CTA r / (BM / S) of the
       // cluster, so each thread pushes its columns of the un-normalised O row (and one thread the
-      // (m, l) pair) straight into that CTA's receive buffer with remote shared-memory stores:
-      // recv[source CTA][row within the owner's share][OBUF_LD floats] in the dead Q/K/V region.
+      // row's (m, l, 1 / scale)) straight into that CTA's receive buffer with remote shared-memory
+      // stores: recv[source CTA][row within the owner's share][HBUF_LD halves] in the dead Q/K/V
+      // region.  An SM moves only about 16 B/clk into another SM's shared memory, so the rows travel
+      // as fp16 with one power-of-two scale per row that puts the row's largest magnitude into
+      // [2^14, 2^15): 11 significant bits relative to the row maximum whatever the range of V, against
+      // the 8 bits of the bf16 output, and half the bytes.
       const uint32_t rpc = BM / cs;
       // split index of this CTA inside the cluster and cluster rank of the CTA that owns row r
       // (pair form: the CTA with the same position in its pair)
       const uint32_t src_rank = PAIR ? (crank >> 1) : crank;
       const uint32_t owner_split = r / rpc, rl = r % rpc;
       const uint32_t owner = PAIR ? ((owner_split << 1) | xi) : owner_split;
-      const uint32_t dst_row = dsmem_addr(smem_base + OFF_Q + ((src_rank * rpc + rl) * OBUF_LD) * 4u, owner);
-#pragma unroll 1
-      for (uint32_t c = 0; c < OPT / 32; ++c) {
-        const uint32_t col0 = qd * OPT + c * 32u;
-        uint32_t o[32];
-        if (have_o) {
-          tmem_ld32(t_lane + TM_O + col0, o);
-          tmem_wait_ld();
-        } else {
+      const uint32_t dst_row = dsmem_addr(smem_base + OFF_Q + ((src_rank * rpc + rl) * HBUF_LD) * 2u, owner);
+      uint32_t oa[32], ob[32];
+      if (have_o) {
+        tmem_ld32(t_lane + TM_O + qd * OPT, oa);
+        tmem_ld32(t_lane + TM_O + qd * OPT + 32u, ob);
+        tmem_wait_ld();
+      } else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) o[e] = 0u;
-        }
-#pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4)
-          dsmem_st_u4(dst_row + (col0 + q4 * 4) * 4u, make_uint4(o[q4 * 4], o[q4 * 4 + 1], o[q4 * 4 + 2], o[q4 * 4 + 3]));
+        for (uint32_t e = 0; e < 32; ++e) oa[e] = ob[e] = 0u;
       }
-      if (qd == 0) dsmem_st_f2(dsmem_addr(smem_base + OFF_ML + (src_rank * rpc + rl) * 8u, owner), make_float2(m_used, l_tot));
+      float amax = 0.f;
+#pragma unroll
+      for (uint32_t e = 0; e < 32; e += 2) {
+        amax = max3_f32(amax, fabsf(__uint_as_float(oa[e])), fabsf(__uint_as_float(oa[e + 1])));
+        amax = max3_f32(amax, fabsf(__uint_as_float(ob[e])), fabsf(__uint_as_float(ob[e + 1])));
+      }
+      xch_misc[r * NTR + qd] = amax;
+      row_group_sync(smw);
+      float rmax = 0.f;
+#pragma unroll
+      for (uint32_t k = 0; k < NTR; ++k) rmax = fmaxf(rmax, xch_misc[r * NTR + k]);
+      // biased exponent of the row maximum; tiny, zero, infinite or NaN maxima travel unscaled
+      const uint32_t eb = (__float_as_uint(rmax) >> 23) & 0xffu;
+      const bool scaled = eb >= 15u && eb < 255u;
+      const float sc = scaled ? __uint_as_float((268u - eb) << 23) : 1.0f;       // 2^(14 - exponent)
+      const float inv_sc = scaled ? __uint_as_float((eb - 14u) << 23) : 1.0f;
+#pragma unroll
+      for (uint32_t q4 = 0; q4 < 4; ++q4) {
+        uint32_t ha[4], hb[4];
+#pragma unroll
+        for (uint32_t e = 0; e < 4; ++e) {
+          ha[e] = pack_f16x2(__uint_as_float(oa[q4 * 8 + 2 * e]) * sc, __uint_as_float(oa[q4 * 8 + 2 * e + 1]) * sc);
+          hb[e] = pack_f16x2(__uint_as_float(ob[q4 * 8 + 2 * e]) * sc, __uint_as_float(ob[q4 * 8 + 2 * e + 1]) * sc);
+        }
+        dsmem_st_u4(dst_row + (qd * OPT + q4 * 8u) * 2u, make_uint4(ha[0], ha[1], ha[2], ha[3]));
+        dsmem_st_u4(dst_row + (qd * OPT + 32u + q4 * 8u) * 2u, make_uint4(hb[0], hb[1], hb[2], hb[3]));
+      }
+      if (qd == 0)
+        dsmem_st_u4(dsmem_addr(smem_base + OFF_ML + (src_rank * rpc + rl) * 16u, owner),
+                    make_uint4(__float_as_uint(m_used), __float_as_uint(l_tot), __float_as_uint(inv_sc), 0u));
     } else {
     const bool to_bf16 = direct && p.out != nullptr;
     const float inv_l = l_tot > 0.f ? 1.0f / l_tot : 0.f;
@@ -686,8 +713,8 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
     const uint32_t rpc = BM / cs;
     row0 = rank * rpc;
     n_rows = rpc;
-    const float* recv = reinterpret_cast<const float*>(smem + OFF_Q);        // [cs][rpc][OBUF_LD]
-    const float2* recv_ml = reinterpret_cast<const float2*>(smem + OFF_ML);  // [cs][rpc]
+    const __half* recv = reinterpret_cast<const __half*>(smem + OFF_Q);      // [cs][rpc][HBUF_LD], scaled
+    const float4* recv_ml = reinterpret_cast<const float4*>(smem + OFF_ML);  // [cs][rpc]: m, l, 1 / scale
     // A warp merges four rows at a time (lane = eight columns), every lane reading the cs (m, l)
     // pairs itself: no shuffles and four independent chains, because this pass is bound by latency
     constexpr uint32_t RK1 = 4;
@@ -706,13 +733,14 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
 #pragma unroll
         for (uint32_t k = 0; k < RK1; ++k) {
           const uint32_t rl = rl0 + k < rpc ? rl0 + k : rpc - 1;
-          const float2 ml = recv_ml[s2 * rpc + rl];
+          const float4 ml = recv_ml[s2 * rpc + rl];
           const float w = (ml.x == -INFINITY) ? 0.f : fast_exp2(ml.x - mg[k]);
           lg[k] += w * ml.y;
-          const float4* src = reinterpret_cast<const float4*>(recv + (s2 * rpc + rl) * OBUF_LD + lane * 8);
-          const float4 a = src[0], bq = src[1];
-          acc[k][0] += w * a.x; acc[k][1] += w * a.y; acc[k][2] += w * a.z; acc[k][3] += w * a.w;
-          acc[k][4] += w * bq.x; acc[k][5] += w * bq.y; acc[k][6] += w * bq.z; acc[k][7] += w * bq.w;
+          const float ws = w * ml.z;   // the row's scale folded into its weight
+          const uint4 x = *reinterpret_cast<const uint4*>(recv + (s2 * rpc + rl) * HBUF_LD + lane * 8);
+          const float2 x0 = unpack_f16x2(x.x), x1 = unpack_f16x2(x.y), x2 = unpack_f16x2(x.z), x3 = unpack_f16x2(x.w);
+          acc[k][0] += ws * x0.x; acc[k][1] += ws * x0.y; acc[k][2] += ws * x1.x; acc[k][3] += ws * x1.y;
+          acc[k][4] += ws * x2.x; acc[k][5] += ws * x2.y; acc[k][6] += ws * x3.x; acc[k][7] += ws * x3.y;
         }
       }
 #pragma unroll

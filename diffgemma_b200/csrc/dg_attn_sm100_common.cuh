@@ -20,9 +20,9 @@ constexpr uint32_t OFF_K = TILE_BYTES;
 constexpr uint32_t OFF_V = 2 * TILE_BYTES;
 constexpr uint32_t OFF_BAR = 3 * TILE_BYTES;
 constexpr uint32_t OFF_XCH = OFF_BAR + 256;             // row-group exchange scratch (8 KB)
-constexpr uint32_t OFF_ML = OFF_XCH + 8192;             // (m, l) of the on-chip partial, [BM] float2
-constexpr uint32_t OBUF_LD = 260;                       // floats per row of the on-chip partial (padded 256)
-constexpr uint32_t SMEM_BYTES = OFF_ML + 1024 + 1024;   // + alignment slack
+constexpr uint32_t OFF_ML = OFF_XCH + 8192;             // (m, l, 1 / scale, -) of the on-chip partial rows, [BM] float4
+constexpr uint32_t HBUF_LD = 264;                       // halves per row of the on-chip partial (padded 256)
+constexpr uint32_t SMEM_BYTES = OFF_ML + 2048 + 1024;   // + alignment slack
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TM_S = 0;            // two S buffers of 128 columns
 constexpr uint32_t TM_O = 256;          // O accumulator, 256 columns

@@ -399,6 +399,24 @@ __device__ __forceinline__ float max3_f32(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
+// two fp32 -> packed f16x2 (round to nearest even), `lo` in the low half, and back
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ float2 unpack_f16x2(uint32_t v) {
+  float2 r;
+  asm("{\n\t"
+      ".reg .b16 L, H;\n\t"
+      "mov.b32 {L, H}, %2;\n\t"
+      "cvt.f32.f16 %0, L;\n\t"
+      "cvt.f32.f16 %1, H;\n\t"
+      "}\n"
+      : "=f"(r.x), "=f"(r.y)
+      : "r"(v));
+  return r;
+}
 // two fp32 -> packed bf16x2 (round to nearest even); `lo` lands in the low half
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t r;
