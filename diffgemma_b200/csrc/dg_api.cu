@@ -102,7 +102,7 @@ struct dg_kv {
 
 constexpr uint32_t kRopeSlots = 8;
 constexpr uint32_t kMaxQueryTiles = 4096;
-constexpr uint32_t kCounterSlots = kMaxQueryTiles * 8 + 1;   // (query tile, row slice) arrival counters + the self-test flag
+constexpr uint32_t kCounterSlots = kMaxQueryTiles * 32 + 1;   // (query tile, four-row slice) arrival counters + the self-test flag
 
 // ------------------------------------------------------------------------------------------
 // driver entry point for tensor-map encoding (no link-time dependency on libcuda)

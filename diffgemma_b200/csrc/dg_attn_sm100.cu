@@ -700,8 +700,6 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   }
 
   // ------------------------------------------------------------------ split merge, level 1: inside the cluster
-  // rows of the query tile this CTA is responsible for in level 2 (all of them without clusters)
-  uint32_t row0 = 0, n_rows = BM;
   if (cs > 1) {
     // The cs CTAs that hold consecutive splits of this query tile are one thread-block cluster
     // (cluster dims (1, cs, 1), pair form (2, cs, 1)).  Every CTA has pushed each partial row to the
@@ -711,8 +709,6 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
     if (!PAIR) cluster_sync_all();
     const uint32_t rank = PAIR ? (crank >> 1) : crank;
     const uint32_t rpc = BM / cs;
-    row0 = rank * rpc;
-    n_rows = rpc;
     const __half* recv = reinterpret_cast<const __half*>(smem + OFF_Q);      // [cs][rpc][HBUF_LD], scaled
     const float4* recv_ml = reinterpret_cast<const float4*>(smem + OFF_ML);  // [cs][rpc]: m, l, 1 / scale
     // A warp merges four rows at a time (lane = eight columns), every lane reading the cs (m, l)
@@ -743,44 +739,93 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
           acc[k][4] += ws * x2.x; acc[k][5] += ws * x2.y; acc[k][6] += ws * x3.x; acc[k][7] += ws * x3.y;
         }
       }
+      size_t orow[RK1];
+      bool live[RK1];
 #pragma unroll
       for (uint32_t k = 0; k < RK1; ++k) {
         const uint32_t R = mt * BM + rank * rpc + rl0 + k;
-        if (rl0 + k >= rpc || R >= rows_per_head) continue;
-        const size_t orow = size_t(R / p.G) * p.Hq + kvh * p.G + R % p.G;
-        if (n_groups > 1) {
-          // the group's merged partial (still un-normalised, relative to mg) goes to the workspace
-          float4* dst = reinterpret_cast<float4*>(p.ws_o + (size_t(grp) * rows_total + orow) * HD + lane * 8);
+        live[k] = rl0 + k < rpc && R < rows_per_head;
+        const uint32_t Rc = live[k] ? R : mt * BM;
+        orow[k] = size_t(Rc / p.G) * p.Hq + kvh * p.G + Rc % p.G;
+      }
+      if (n_groups > 1) {
+        // Level 2, per warp: the group's merged rows (un-normalised, relative to mg) go to the
+        // workspace, the warp counts itself in on the arrival counter of these four rows, and the
+        // warp of the LAST group to arrive folds the other groups' rows into the ones it still holds
+        // in registers.  No CTA-wide barrier, and nobody reads its own partial back.
+#pragma unroll
+        for (uint32_t k = 0; k < RK1; ++k) {
+          if (!live[k]) continue;
+          float4* dst = reinterpret_cast<float4*>(p.ws_o + (size_t(grp) * rows_total + orow[k]) * HD + lane * 8);
           dst[0] = make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
           dst[1] = make_float4(acc[k][4], acc[k][5], acc[k][6], acc[k][7]);
-          if (lane == 0) reinterpret_cast<float2*>(p.ws_ml)[size_t(grp) * rows_total + orow] = make_float2(mg[k], lg[k]);
-        } else if (p.out) {
+          if (lane == 0) reinterpret_cast<float2*>(p.ws_ml)[size_t(grp) * rows_total + orow[k]] = make_float2(mg[k], lg[k]);
+        }
+        __threadfence();
+        __syncwarp();
+        uint32_t* cnt = p.ws_counters + blockIdx.x * (BM / RK1) + (rank * rpc + rl0) / RK1;
+        uint32_t old = 0;
+        if (lane == 0) old = atomicAdd(cnt, 1u);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old != n_groups - 1u) continue;   // warp-uniform
+        __threadfence();
+        if (lane == 0) *cnt = 0u;             // ready for the next launch
+        for (uint32_t g2 = 0; g2 < n_groups; ++g2) {
+          if (g2 == grp) continue;
+          float2 ml2[RK1];
+          float4 a2[RK1], b2[RK1];
+#pragma unroll
+          for (uint32_t k = 0; k < RK1; ++k) {
+            const size_t slot = size_t(g2) * rows_total + orow[k];
+            ml2[k] = __ldcg(reinterpret_cast<const float2*>(p.ws_ml) + slot);
+            const float4* src = reinterpret_cast<const float4*>(p.ws_o + slot * HD + lane * 8);
+            a2[k] = __ldcg(src);
+            b2[k] = __ldcg(src + 1);
+          }
+#pragma unroll
+          for (uint32_t k = 0; k < RK1; ++k) {
+            const float mn = fmaxf(mg[k], ml2[k].x);
+            const float wa = (mg[k] == -INFINITY) ? 0.f : fast_exp2(mg[k] - mn);
+            const float wb = (ml2[k].x == -INFINITY) ? 0.f : fast_exp2(ml2[k].x - mn);
+            lg[k] = wa * lg[k] + wb * ml2[k].y;
+            mg[k] = mn;
+            acc[k][0] = wa * acc[k][0] + wb * a2[k].x; acc[k][1] = wa * acc[k][1] + wb * a2[k].y;
+            acc[k][2] = wa * acc[k][2] + wb * a2[k].z; acc[k][3] = wa * acc[k][3] + wb * a2[k].w;
+            acc[k][4] = wa * acc[k][4] + wb * b2[k].x; acc[k][5] = wa * acc[k][5] + wb * b2[k].y;
+            acc[k][6] = wa * acc[k][6] + wb * b2[k].z; acc[k][7] = wa * acc[k][7] + wb * b2[k].w;
+          }
+        }
+      }
+#pragma unroll
+      for (uint32_t k = 0; k < RK1; ++k) {
+        if (!live[k]) continue;
+        if (p.out) {
           const float inv = lg[k] > 0.f ? 1.0f / lg[k] : 0.f;
           uint4 w4;
           w4.x = pack_bf16x2(acc[k][0] * inv, acc[k][1] * inv);
           w4.y = pack_bf16x2(acc[k][2] * inv, acc[k][3] * inv);
           w4.z = pack_bf16x2(acc[k][4] * inv, acc[k][5] * inv);
           w4.w = pack_bf16x2(acc[k][6] * inv, acc[k][7] * inv);
-          *reinterpret_cast<uint4*>(p.out + orow * HD + lane * 8) = w4;
+          *reinterpret_cast<uint4*>(p.out + orow[k] * HD + lane * 8) = w4;
         } else {
-          float4* dst = reinterpret_cast<float4*>(p.out_o + orow * HD + lane * 8);
+          float4* dst = reinterpret_cast<float4*>(p.out_o + orow[k] * HD + lane * 8);
           dst[0] = make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
           dst[1] = make_float4(acc[k][4], acc[k][5], acc[k][6], acc[k][7]);
           if (lane == 0) {
-            p.out_m[orow] = mg[k] * 0.6931471805599453f;
-            p.out_l[orow] = lg[k];
+            p.out_m[orow[k]] = mg[k] * 0.6931471805599453f;
+            p.out_l[orow[k]] = lg[k];
           }
         }
       }
     }
-    if (n_groups > 1) __threadfence();
   }
-  if (n_groups > 1) {
-    // ---------------------------------------------------------------- level 2: the last group to arrive merges
-    // one arrival counter per (query tile, row slice); the partials of the n_groups groups are in
-    // the workspace
+  if (n_groups > 1 && cs == 1) {
+    // ---------------------------------------------------------------- splits without clusters
+    // (odd split counts, the fixed-scratch entry point): every CTA wrote its whole partial to the
+    // workspace in the epilogue; one arrival counter per query tile, the last CTA to arrive merges
+    const uint32_t row0 = 0, n_rows = BM;
     const uint32_t S = n_groups;
-    uint32_t* counter = p.ws_counters + blockIdx.x * cs + (cs > 1 ? (PAIR ? (crank >> 1) : crank) : 0u);
+    uint32_t* counter = p.ws_counters + blockIdx.x;
     __syncthreads();
     if (tid == 0) {
       __threadfence();
@@ -792,7 +837,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       __threadfence();
       const float2* ml_all = reinterpret_cast<const float2*>(p.ws_ml);
       if (S == 2) {
-        // Two groups (the 32k pair form): one round trip.  A warp takes four rows, every lane loads
+        // Two splits: one round trip.  A warp takes four rows, every lane loads
         // both (m, l) pairs and its eight columns of both partials at once.
         constexpr uint32_t RK2 = 4;
         for (uint32_t r0 = warp * RK2; r0 < n_rows; r0 += (THREADS / 32) * RK2) {
