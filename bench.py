@@ -32,7 +32,7 @@ L2_BYTES = 126e6
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention-kernel launch of the benchmark
 # workload (70.08 MB + 7.52 MB), from the ncu capture summarised in
 # profiles/dg_attn_sm100_kernel__cfg2_global_p32768.md
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {2: 77.60e6}
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {2: 75.70e6}
 
 
 def _peaks():
