@@ -770,8 +770,13 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
         if (old != n_groups - 1u) continue;   // warp-uniform
         __threadfence();
         if (lane == 0) *cnt = 0u;             // ready for the next launch
+        // The result must not depend on which group happened to arrive last.  With two groups the
+        // fold is written symmetrically (separately rounded products, one addition), so folding the
+        // other group into the rows held in registers gives the same bits either way round; with
+        // more groups the rows are re-read and folded in group order.
+        const bool two = n_groups == 2;
         for (uint32_t g2 = 0; g2 < n_groups; ++g2) {
-          if (g2 == grp) continue;
+          if (two && g2 == grp) continue;
           float2 ml2[RK1];
           float4 a2[RK1], b2[RK1];
 #pragma unroll
@@ -784,15 +789,21 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
           }
 #pragma unroll
           for (uint32_t k = 0; k < RK1; ++k) {
+            if (!two && g2 == 0) {   // group order: start from group 0 as it is in the workspace
+              mg[k] = ml2[k].x;
+              lg[k] = ml2[k].y;
+              acc[k][0] = a2[k].x; acc[k][1] = a2[k].y; acc[k][2] = a2[k].z; acc[k][3] = a2[k].w;
+              acc[k][4] = b2[k].x; acc[k][5] = b2[k].y; acc[k][6] = b2[k].z; acc[k][7] = b2[k].w;
+              continue;
+            }
             const float mn = fmaxf(mg[k], ml2[k].x);
             const float wa = (mg[k] == -INFINITY) ? 0.f : fast_exp2(mg[k] - mn);
             const float wb = (ml2[k].x == -INFINITY) ? 0.f : fast_exp2(ml2[k].x - mn);
-            lg[k] = wa * lg[k] + wb * ml2[k].y;
+            lg[k] = __fadd_rn(__fmul_rn(wa, lg[k]), __fmul_rn(wb, ml2[k].y));
             mg[k] = mn;
-            acc[k][0] = wa * acc[k][0] + wb * a2[k].x; acc[k][1] = wa * acc[k][1] + wb * a2[k].y;
-            acc[k][2] = wa * acc[k][2] + wb * a2[k].z; acc[k][3] = wa * acc[k][3] + wb * a2[k].w;
-            acc[k][4] = wa * acc[k][4] + wb * b2[k].x; acc[k][5] = wa * acc[k][5] + wb * b2[k].y;
-            acc[k][6] = wa * acc[k][6] + wb * b2[k].z; acc[k][7] = wa * acc[k][7] + wb * b2[k].w;
+            const float x2[8] = {a2[k].x, a2[k].y, a2[k].z, a2[k].w, b2[k].x, b2[k].y, b2[k].z, b2[k].w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[k][e] = __fadd_rn(__fmul_rn(wa, acc[k][e]), __fmul_rn(wb, x2[e]));
           }
         }
       }

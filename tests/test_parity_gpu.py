@@ -377,6 +377,33 @@ def test_output_guard_rows_untouched(ctx):
     kv.close()
 
 
+@pytest.mark.parametrize("v_scale", [2.0 ** 14, 2.0 ** -10, 2.0 ** -100])
+def test_split_exchange_is_range_independent(ctx, v_scale):
+    """Inside a cluster the partial rows cross between CTAs as fp16 with one power-of-two scale per
+    row.  V scaled by a power of two (exact in bf16) must give the same output scaled by it, bit for
+    bit after rescaling, with and without key splits, and stay within tolerance of the oracle."""
+    layer = AttnLayer(n_kv_heads=2, rope_theta=1e6)
+    case = util.make_case(layer, 3000, seed=4242)
+    ref = util.run_oracle(case)
+    scaled = dict(case)
+    scaled["vp"] = (case["vp"].float() * v_scale).to(torch.bfloat16)
+    scaled["vc"] = (case["vc"].float() * v_scale).to(torch.bfloat16)
+    assert torch.equal(scaled["vp"].float() / v_scale, case["vp"].float())     # the scaling was exact
+    try:
+        for pair in (False, True):
+            ctx.set_pair_mode(pair)
+            for splits in (1, 2, 4):
+                ctx.set_splits(splits)
+                base = util.run_gpu(ctx, case)
+                got = util.run_gpu(ctx, scaled).astype(np.float64) / v_scale
+                assert np.array_equal(got.astype(np.float32), base), f"pair={pair} splits={splits} scale={v_scale}"
+                util.assert_close(got.astype(np.float32), ref, f"pair={pair} splits={splits} scale={v_scale}")
+    finally:
+        ctx.set_splits(0)
+        ctx.set_pair_mode(None)
+    assert ctx.device_status()[0] == 0
+
+
 # ------------------------------------------------------------------------------------------
 # CTA-pair kernel variant (tcgen05 cta_group::2)
 # ------------------------------------------------------------------------------------------
