@@ -130,7 +130,7 @@ def test_denoise_parity(ctx, P, Hkv, W, mode, scale, canvas, weights, vnorm):
     try:
         for pair in (None, False):   # automatic choice (CTA pairs where they apply), then the single-CTA form
             ctx.set_pair_mode(pair)
-            for splits in (0, 1, 3):
+            for splits in (0, 1, 3, 8):     # 8: one cluster of eight CTAs in the single-CTA form (clamped to the key tiles)
                 ctx.set_splits(splits)
                 got = util.run_gpu(ctx, case)
                 util.assert_close(got, ref, f"tensor path pair={pair} splits={splits}")
