@@ -613,7 +613,8 @@ static cudaStream_t launch_stream(const dg_ctx* c) { return c->side_active ? c->
 
 static int32_t do_append(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint64_t pos0, uint32_t n, const void* q_in,
                          void* q_out, const void* k_in, void* k_out, const void* v_in, void* v_out, const void* qw,
-                         const void* kw, float2* table, uint32_t write_end = 0xffffffffu) {
+                         const void* kw, float2* table, uint32_t write_end = 0xffffffffu,
+                         const float2* table_in = nullptr) {
   AppendParams ap;
   ap.q_in = static_cast<const __nv_bfloat16*>(q_in);
   ap.q_out = static_cast<__nv_bfloat16*>(q_out);
@@ -626,6 +627,7 @@ static int32_t do_append(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint64_t 
   ap.cache_k = kv->k;
   ap.cache_v = kv->v;
   ap.rope_table = table;
+  ap.rope_table_in = table_in;
   ap.cap = kv->cap;
   ap.pos0 = uint32_t(pos0);
   ap.n = n;
@@ -812,7 +814,8 @@ static int32_t denoise_one(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint32_
     dg_ctx::RopeKey& key = c->rope_key[slot % kRopeSlots];
     const bool cached = key.valid && key.kv_len == kv_len && key.canvas == d.canvas && key.rotary_dim == d.rotary_dim &&
                         key.pairing == d.rope_pairing && key.head_dim == d.head_dim && key.theta == d.rope_theta;
-    r = do_append(c, d, kv, kv_len, d.canvas, nullptr, nullptr, k, nullptr, v, nullptr, nullptr, kw, cached ? nullptr : table);
+    r = do_append(c, d, kv, kv_len, d.canvas, nullptr, nullptr, k, nullptr, v, nullptr, nullptr, kw, cached ? nullptr : table,
+                  0xffffffffu, cached ? table : nullptr);
     if (r != DG_OK) return r;
     if (!cached) {
       key.valid = true;

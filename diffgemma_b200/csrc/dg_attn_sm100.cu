@@ -131,6 +131,24 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   const uint32_t v_end = uint32_t((uint64_t(split + 1) * n_tiles) / p.n_splits);
   const uint32_t n_local = v_end - v_begin;
 
+  // Q prologue, first half: a warp copies its eight raw query rows asynchronously into their final
+  // (swizzled) place, lane c the 16-byte chunk c of each row.  When Q does not come from the kernel
+  // that precedes this one on the stream, the copies are issued before the set-up barrier and fly
+  // during it.
+  auto issue_q_rows = [&]() {
+    constexpr uint32_t RPW = BM / SM_WARPS;
+    const uint32_t c = lane, R0 = mt * BM + warp * RPW;
+    uint8_t* q_own = smem + OFF_Q + (c >> 3) * ATOM_BYTES + warp * RPW * 128u;
+    uint32_t i = R0 / p.G, g = R0 % p.G;
+#pragma unroll
+    for (uint32_t it = 0; it < RPW; ++it) {
+      const bool valid = R0 + it < rows_per_head;   // warp-uniform; rows past the end are zero-filled
+      const __nv_bfloat16* src = valid ? p.q + (size_t(i) * p.Hq + kvh * p.G + g) * HD + c * 8u : p.q;
+      cp_async_16(smem_u32(q_own + it * 128u + (((c & 7u) ^ it) << 4)), src, valid ? 16u : 0u);
+      if (++g == p.G) { g = 0; ++i; }
+    }
+  };
+  if (p.early_q && warp < SM_WARPS) issue_q_rows();
   stamp(p, 0);
   // ------------------------------------------------------------------ set-up
   if (tid == 0) {
@@ -201,16 +219,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       // partner sits at the same place two swizzle atoms away
       uint8_t* q_own = smem + OFF_Q + (c >> 3) * ATOM_BYTES + warp * RPW * 128u;
       uint8_t* q_par = smem + OFF_Q + ((c ^ 16u) >> 3) * ATOM_BYTES + warp * RPW * 128u;
-      {
-        uint32_t i = i0, g = g0;
-#pragma unroll
-        for (uint32_t it = 0; it < RPW; ++it) {
-          const bool valid = R0 + it < rows_per_head;   // warp-uniform; rows past the end are zero-filled
-          const __nv_bfloat16* src = valid ? p.q + (size_t(i) * p.Hq + kvh * p.G + g) * HD + c * 8u : p.q;
-          cp_async_16(smem_u32(q_own + it * 128u + (((c & 7u) ^ it) << 4)), src, valid ? 16u : 0u);
-          if (++g == p.G) { g = 0; ++i; }
-        }
-      }
+      if (!p.early_q) issue_q_rows();
       if (do_norm) {
         uint4 w4 = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u), wp4 = w4;   // bf16 1.0
         if (p.qw) {

@@ -98,6 +98,7 @@ struct AppendParams {
   __nv_bfloat16* cache_k;      // K[Hkv][cap][D]
   __nv_bfloat16* cache_v;
   float2* rope_table;          // [n][rot_half] (cos, sin) of positions pos0 + i, or null
+  const float2* rope_table_in; // the same table, already written by an earlier launch for these positions, or null
   uint64_t cap;
   uint32_t pos0, n;
   uint32_t Hq, Hkv, D;

@@ -15,6 +15,14 @@ __device__ __forceinline__ float warp_sum(float v) {
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
+// RoPE of the pair (x0, x1) = (element i, element i + pair offset), with the rounding spelled out so
+// that every kernel that rotates K produces the same bits
+__device__ __forceinline__ float rope_rotate_lo(float x0, float x1, float c, float s) {
+  return __fmaf_rn(x0, c, -__fmul_rn(x1, s));
+}
+__device__ __forceinline__ float rope_rotate_hi(float x0, float x1, float c, float s) {
+  return __fmaf_rn(x0, s, __fmul_rn(x1, c));
+}
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
@@ -57,11 +65,16 @@ __global__ void __launch_bounds__(32) dg_append_kernel(const AppendParams p, con
                              ? nullptr
                              : (is_k ? p.cache_k : p.cache_v) + (size_t(h) * p.cap + (pos & p.ring_mask)) * D;
 
+  // sum of squares in the order of dg_append_table_kernel (a lane takes 8 consecutive elements, then a
+  // butterfly), and the rotation through rope_rotate in both, so that the two kernels write the same bits
   float ss = 0.f;
-  for (uint32_t d = lane; d < D; d += 32) {
-    const float x = __bfloat162float(src[d]);
-    xs[d] = x;
-    ss += x * x;
+  for (uint32_t c = lane; c < D / 8; c += 32) {
+#pragma unroll
+    for (uint32_t e = 0; e < 8; ++e) {
+      const float x = __bfloat162float(src[c * 8 + e]);
+      xs[c * 8 + e] = x;
+      ss = __fmaf_rn(x, x, ss);
+    }
   }
   ss = warp_sum(ss);
   const bool norm = is_q || is_k || p.v_norm;
@@ -79,8 +92,8 @@ __global__ void __launch_bounds__(32) dg_append_kernel(const AppendParams p, con
       const float a = fpos * rp.inv_freq[i];
       const float c = cosf(a), s = sinf(a);
       const float x0 = xs[i], x1 = xs[rp.pair_off + i];
-      xs[i] = x0 * c - x1 * s;
-      xs[rp.pair_off + i] = x0 * s + x1 * c;
+      xs[i] = rope_rotate_lo(x0, x1, c, s);
+      xs[rp.pair_off + i] = rope_rotate_hi(x0, x1, c, s);
     }
     __syncwarp();
   }
@@ -91,8 +104,82 @@ __global__ void __launch_bounds__(32) dg_append_kernel(const AppendParams p, con
   }
 }
 
+// Canvas append when the RoPE table of these positions is already in memory (the denoise steps of a
+// canvas revisit the same positions): head_dim 256, full split-half rotary, cache writes only.
+// One warp per (token, K or V head vector), lane c owns the 16-byte chunk c, the RoPE partner of a
+// chunk is chunk c ^ 16 (one shuffle away); eight warps per CTA.  No sincos, no shared memory, 512-byte
+// coalesced loads and stores: the kernel is short enough to hide behind the attention kernel's Q
+// prologue, which overlaps it through programmatic dependent launch.
+__global__ void __launch_bounds__(256) dg_append_table_kernel(const AppendParams p) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const uint32_t lane = threadIdx.x & 31u, w = blockIdx.x * 8u + (threadIdx.x >> 5);
+  const uint32_t per_tok = 2u * p.Hkv;
+  if (w >= p.n * per_tok) return;
+  const uint32_t tok = w / per_tok, slot = w % per_tok;
+  const bool is_k = slot < p.Hkv;
+  const uint32_t h = is_k ? slot : slot - p.Hkv;
+  const uint32_t pos = p.pos0 + tok;
+  if (pos >= p.write_end) return;   // zero-padded tail of a chunk: must not wrap onto live ring slots
+  const uint4 x = reinterpret_cast<const uint4*>((is_k ? p.k_in : p.v_in) + (size_t(tok) * p.Hkv + h) * 256u)[lane];
+  uint4 y = x;
+  if (is_k || p.v_norm) {
+    const uint32_t m[4] = {x.x, x.y, x.z, x.w};
+    float f[8];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      f[2 * e] = __uint_as_float(m[e] << 16);
+      f[2 * e + 1] = __uint_as_float(m[e] & 0xffff0000u);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss = __fmaf_rn(f[e], f[e], ss);
+    ss = warp_sum(ss);   // butterfly: identical in every lane
+    const float inv = 1.0f / sqrtf(ss / 256.0f + p.eps);
+    float r[8];
+    if (is_k) {
+      uint4 w4 = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u), wp4 = w4;   // bf16 1.0
+      if (p.kw) {
+        w4 = reinterpret_cast<const uint4*>(p.kw)[lane];
+        wp4 = reinterpret_cast<const uint4*>(p.kw)[lane ^ 16u];
+      }
+      const float4* tab = reinterpret_cast<const float4*>(p.rope_table_in + size_t(tok) * 128u + (lane & 15u) * 8u);
+      const uint32_t q[4] = {__shfl_xor_sync(0xffffffffu, m[0], 16), __shfl_xor_sync(0xffffffffu, m[1], 16),
+                             __shfl_xor_sync(0xffffffffu, m[2], 16), __shfl_xor_sync(0xffffffffu, m[3], 16)};
+      const uint32_t wm[4] = {w4.x, w4.y, w4.z, w4.w};
+      const uint32_t wq[4] = {wp4.x, wp4.y, wp4.z, wp4.w};
+      const bool low = lane < 16u;   // this lane holds element i (low) or its partner i + 128 (high) of each pair
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float4 cs = tab[e];   // (cos, sin) of pairs 8 (lane & 15) + 2e and + 2e + 1
+        const float m0 = f[2 * e] * (inv * __uint_as_float(wm[e] << 16));
+        const float m1 = f[2 * e + 1] * (inv * __uint_as_float(wm[e] & 0xffff0000u));
+        const float q0 = __uint_as_float(q[e] << 16) * (inv * __uint_as_float(wq[e] << 16));
+        const float q1 = __uint_as_float(q[e] & 0xffff0000u) * (inv * __uint_as_float(wq[e] & 0xffff0000u));
+        r[2 * e] = low ? rope_rotate_lo(m0, q0, cs.x, cs.y) : rope_rotate_hi(q0, m0, cs.x, cs.y);
+        r[2 * e + 1] = low ? rope_rotate_lo(m1, q1, cs.z, cs.w) : rope_rotate_hi(q1, m1, cs.z, cs.w);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) r[e] = f[e] * inv;
+    }
+    __nv_bfloat162 b[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) b[e] = __floats2bfloat162_rn(r[2 * e], r[2 * e + 1]);
+    y = make_uint4(*reinterpret_cast<uint32_t*>(&b[0]), *reinterpret_cast<uint32_t*>(&b[1]),
+                   *reinterpret_cast<uint32_t*>(&b[2]), *reinterpret_cast<uint32_t*>(&b[3]));
+  }
+  __nv_bfloat16* cache = (is_k ? p.cache_k : p.cache_v) + (size_t(h) * p.cap + (pos & p.ring_mask)) * 256u;
+  reinterpret_cast<uint4*>(cache)[lane] = y;
+}
+
 void launch_append(const AppendParams& p, const RopeParams& rp, cudaStream_t st) {
   if (p.n == 0) return;
+  if (p.rope_table_in && !p.rope_table && !p.q_in && !p.k_out && !p.v_out && p.D == 256 && rp.rot_half == 128 &&
+      rp.pair_off == 128) {
+    const uint32_t warps = p.n * 2u * p.Hkv;
+    dg_append_table_kernel<<<(warps + 7u) / 8u, 256, 0, st>>>(p);
+    return;
+  }
   const uint32_t slots = (p.q_in ? p.Hq : 0u) + 2u * p.Hkv + (p.rope_table ? 1u : 0u);
   dg_append_kernel<<<dim3(p.n, slots), 32, 0, st>>>(p, rp);
 }

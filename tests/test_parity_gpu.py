@@ -206,6 +206,35 @@ def test_batch_of_independent_canvases(ctx):
         kv.close()
 
 
+@pytest.mark.parametrize("Hkv,W,weights", [(8, 0, True), (2, 0, False), (8, 1024, True)])
+def test_append_with_cached_rope_table_writes_the_same_bits(ctx, Hkv, W, weights):
+    """The first step at a position computes the RoPE table and runs the general append kernel; later
+    steps at the same positions read the table in a shorter kernel.  Cache contents and output must
+    be the same, bit for bit."""
+    layer = AttnLayer(n_kv_heads=Hkv, window=W, mask_mode=capi.MASK_WINDOW_UNIFORM if W else 0,
+                      rope_theta=1e4 if W else 1e6)
+    P = 1300
+    case = util.make_case(layer, P, seed=71 + Hkv, weights=weights)
+    kv, att = util.gpu_setup(ctx, case)
+    args = ([kv], [P], util.dev(case, "q")[None], util.dev(case, "kc")[None], util.dev(case, "vc")[None],
+            util.dev(case, "qw"), util.dev(case, "kw"))
+    # another position first (on a scratch cache), so that the table of position P is certainly not cached
+    scratch = KvCache(ctx, layer, 100 + layer.canvas)
+    scratch.load_prefix(util.dev(case, "kp")[:100].contiguous(), util.dev(case, "vp")[:100].contiguous(), 0)
+    att.denoise([scratch], [100], *args[2:])
+    scratch.close()
+    first = att.denoise(*args).clone()
+    k1, v1 = kv.read(P, layer.canvas)
+    second = att.denoise(*args).clone()
+    k2, v2 = kv.read(P, layer.canvas)
+    ctx.synchronize()
+    assert torch.equal(k1.view(torch.int16), k2.view(torch.int16))
+    assert torch.equal(v1.view(torch.int16), v2.view(torch.int16))
+    assert torch.equal(first.view(torch.int16), second.view(torch.int16))
+    util.assert_close(util.t2f(second[0]), util.run_oracle(case), "cached-table step")
+    kv.close()
+
+
 def test_host_buffer_call_matches_device_call(ctx):
     layer = AttnLayer(n_kv_heads=8)
     case = util.make_case(layer, 777, seed=5)
