@@ -195,11 +195,11 @@ static uint32_t choose_splits(const dg_ctx* ctx, uint32_t q_tiles, uint32_t k_ti
   // automatic choice: powers of two up to 8, the split counts that merge inside a cluster
   for (uint32_t s = 1; s <= smax && s <= 8u; s *= 2) {
     const uint64_t waves = (uint64_t(q_tiles) * s + sms - 1) / sms;
-    // in tenths of a key tile's time (about 1.7 us): the fixed cost of a CTA (set-up, Q prologue,
-    // epilogue) and the measured cost of exchanging and merging the partial rows of s splits
-    // (about 7 us for two, 10 us for four), so that a short key range is not split at all
-    const uint64_t merge = s == 1 ? 0 : s == 2 ? 40 : s == 4 ? 55 : 65;
-    const uint64_t per = 10 * ((k_tiles + s - 1) / s) + 60 + merge;
+    // in tenths of a key tile's time (about 1.75 us): the fixed cost of a step (launches, set-up, Q
+    // prologue, epilogue: about 12 us) and the measured cost of exchanging and merging the partial rows
+    // of s splits (about 6.3 us for two, 7.7 us for four), so that a short key range is not split at all
+    const uint64_t merge = s == 1 ? 0 : s == 2 ? 36 : s == 4 ? 44 : 55;
+    const uint64_t per = 10 * ((k_tiles + s - 1) / s) + 70 + merge;
     const uint64_t cost = waves * per;
     if (cost < best_cost) {
       best_cost = cost;
