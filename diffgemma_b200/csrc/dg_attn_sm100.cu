@@ -1,7 +1,8 @@
 // Denoise-step canvas attention for head_dim 256 on sm_100a: one fused flash-style kernel.
 //
 //   * Q prologue in the kernel: per-head RMSNorm(+weight) + split-half RoPE on the CTA's 128
-//     query rows, rounded to bf16 and written straight into the UMMA shared-memory layout.
+//     query rows, rounded to bf16 and written straight into the UMMA shared-memory layout (one warp
+//     per row, the raw rows copied asynchronously into place before the set-up barrier).
 //   * K/V tiles of 128 keys are TMA-staged (3-D tiled loads, 128-byte swizzle, no multicast) from
 //     the head-major bf16 cache K[Hkv][cap][256], V[Hkv][cap][256]; a ring cache (sliding layers) keeps
 //     key position t in slot t & ring_mask, and because the ring is a multiple of 128 slots a key
@@ -16,10 +17,14 @@
 //     stages.  The single-CTA form is bound by shared-memory bandwidth (per 128-key tile it reads
 //     Q 64 KB + K 64 KB + V 64 KB as MMA operands and takes 128 KB of TMA writes = 320 KB against
 //     128 B/clk = 2,560 cycles, the MMAs alone need 2,048); the pair form moves 192 KB per tile.
-//   * intra-GPU split-KV: grid.y CTAs share one query tile and merge their (O, m, l) partials either
-//     through distributed shared memory (single-CTA form, 2 / 4 / 8 splits: one thread-block cluster
-//     per query tile) or through a global workspace with the last CTA to finish doing the merge.
-//     Either way there is no second launch.
+//   * intra-GPU split-KV: grid.y CTAs share one query tile.  Consecutive splits form a thread-block
+//     cluster (2 / 4 / 8 in the single-CTA form, 2 pairs in the pair form): every CTA pushes its partial
+//     rows into the shared memory of the CTA that owns them - as fp16 with a power-of-two scale per
+//     row, because an SM moves only about 16 B/clk into another SM - and merges the rows it owns.
+//     Groups that are left meet in a global workspace, per warp: the warp of the last group to
+//     arrive at a four-row counter folds the others into the rows it still holds.  Split counts
+//     that form no cluster write whole partials to the workspace and the last CTA to arrive merges.
+//     Either way there is no second launch, and the result does not depend on arrival order.
 //   * the MMA-issuing thread is the critical resource: it shares a scheduler with four softmax
 //     warps, so its instruction stream is kept short (rolled loops, descriptor adds, one commit per
 //     MMA group - S_FULL doubles as "K stage free", V_EMPTY as "PV done") and nothing is polled.
@@ -92,7 +97,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + B_COUNT * 8);
   // ctl[0] = TMEM base address, ctl[1] = abort flag, ctl[2] = "this CTA merges" flag
   float* xch_max = reinterpret_cast<float*>(smem + OFF_XCH);   // [2 tile parities][BM][NTR]
-  float* xch_misc = xch_max + 2 * BM * NTR;                     // [BM][NTR]: spare
+  float* xch_misc = xch_max + 2 * BM * NTR;                     // [BM][NTR]: row maxima of |O| for the fp16 exchange
   float* xch_l = xch_misc + BM * NTR;                           // [BM][NTR]: final softmax denominators
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
