@@ -24,7 +24,7 @@ DG_DEV_WAIT_TIMEOUT = 1
 DG_DEV_SMEM_LAYOUT = 3
 DG_DEV_BAD_SHAPE = 2
 
-MASK_NONE, MASK_WINDOW_UNIFORM, MASK_WINDOW_PER_ROW = 0, 1, 2
+MASK_NONE, MASK_WINDOW_UNIFORM, MASK_WINDOW_PER_ROW, MASK_CAUSAL = 0, 1, 2, 3
 ROPE_SPLIT_HALF, ROPE_PROPORTIONAL = 0, 1
 
 

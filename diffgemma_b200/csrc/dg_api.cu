@@ -152,7 +152,7 @@ static int32_t check_desc(const dg_layer_desc* d) {
   if (d->canvas == 0 || d->canvas > kMaxCanvas) return fail(DG_ERR_UNSUPPORTED, "canvas must be in 1..256");
   if (d->rotary_dim > d->head_dim || d->rotary_dim % 2 != 0)
     return fail(DG_ERR_INVALID_ARG, "rotary_dim must be even and <= head_dim");
-  if (d->mask_mode > DG_MASK_WINDOW_PER_ROW) return fail(DG_ERR_INVALID_ARG, "unknown mask_mode");
+  if (d->mask_mode > DG_MASK_CAUSAL) return fail(DG_ERR_INVALID_ARG, "unknown mask_mode");
   if (d->rope_pairing > DG_ROPE_PROPORTIONAL) return fail(DG_ERR_INVALID_ARG, "unknown rope_pairing");
   if (d->rope_pairing == DG_ROPE_SPLIT_HALF && d->rotary_dim / 2 + d->rotary_dim / 2 > d->head_dim)
     return fail(DG_ERR_INVALID_ARG, "rotary_dim too large");
@@ -1152,8 +1152,8 @@ extern "C" double dg_attn_flops(const dg_layer_desc* d, uint32_t kv_len) {
   const MaskParams mk = make_mask(*d, kv_len, 0, 0xffffffffu, 1);
   double vis = 0.0;
   for (uint32_t r = 0; r < d->canvas; ++r) {
-    const uint32_t lo = mask_row_lo(mk, r);
-    vis += double(mk.pre_hi > lo ? mk.pre_hi - lo : 0u) + double(mk.can_hi - mk.kv_len);
+    const RowVis rv = mask_row(mk, r);
+    vis += double(mk.pre_hi > rv.lo ? mk.pre_hi - rv.lo : 0u) + double(rv.can_hi - rv.can_lo);
   }
   return 4.0 * d->head_dim * d->n_q_heads * vis;
 }

@@ -130,7 +130,8 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
 
   // both CTAs of a pair walk the same key tiles: schedule from the pair's first canvas row
   const uint32_t row_first = ((PAIR ? (mt & ~1u) : mt) * BM) / p.G;
-  const TileSched ts = tile_sched(mk, row_first < p.C ? row_first : p.C - 1);
+  const uint32_t row_last = (((PAIR ? (mt | 1u) : mt) + 1u) * BM - 1u) / p.G;
+  const TileSched ts = tile_sched(mk, row_first < p.C ? row_first : p.C - 1, row_last < p.C ? row_last : p.C - 1);
   const uint32_t n_tiles = ts.nA + ts.nB;
   const uint32_t v_begin = uint32_t((uint64_t(split) * n_tiles) / p.n_splits);
   const uint32_t v_end = uint32_t((uint64_t(split + 1) * n_tiles) / p.n_splits);
@@ -306,9 +307,8 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
     // ---------------------------------------------------------------- softmax main loop
     const uint32_t R = mt * BM + r;
     const uint32_t i_row = (R < rows_per_head) ? R / p.G : p.C - 1;
-    const uint32_t row_lo = mask_row_lo(mk, i_row);
+    const RowVis rv = mask_row(mk, i_row);
     const uint32_t t_lane = tmem + ((smw * 32u) << 16);
-    const bool contiguous = (mk.pre_hi == mk.kv_len) && (mk.can_hi > mk.kv_len);
     const float sc = p.scale_log2;
     const uint32_t p_full0 = PAIR ? lead_bar(B_P_FULL) : bar_addr(bar_base, B_P_FULL);
     const uint32_t p_full1 = PAIR ? lead_bar(B_P_FULL + 1) : bar_addr(bar_base, B_P_FULL + 1);
@@ -325,12 +325,10 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       tmem_ld32(t_lane + TM_S + b * 128u + qd * CPT, sraw);
       tmem_wait_ld();
 
-      const bool full = (k0 >= row_lo && k0 + BN <= mk.pre_hi) || (k0 >= mk.kv_len && k0 + BN <= mk.can_hi) ||
-                        (contiguous && k0 >= row_lo && k0 + BN <= mk.can_hi);
-      if (!full) {
+      if (!mask_range_full(mk, rv, k0, BN)) {
 #pragma unroll
         for (int e = 0; e < 32; ++e)
-          if (!mask_visible_lo(mk, row_lo, k0 + qd * CPT + e)) sraw[e] = 0xff800000u;  // -inf
+          if (!mask_visible_row(mk, rv, k0 + qd * CPT + e)) sraw[e] = 0xff800000u;  // -inf
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -1060,7 +1058,7 @@ uint32_t sm100_pair_query_tiles(uint32_t C, uint32_t G, uint32_t Hkv) {
 }
 
 uint32_t sm100_key_tiles(const MaskParams& mk) {
-  const TileSched t = tile_sched(mk, 0);
+  const TileSched t = tile_sched(mk, 0, kMaxCanvas - 1);
   return t.nA + t.nB;
 }
 

@@ -31,17 +31,20 @@ constexpr float RESCALE_THRESHOLD = 8.0f;   // log2 units
 struct TileSched {
   uint32_t a0, nA, b0, nB;
 };
-// Key tiles (absolute index = key / 128) a CTA whose first canvas row is `row_first` must visit:
-// the prefix interval [lo, pre_hi) and the canvas interval [kv_len, can_hi), merged when they touch.
-__host__ __device__ inline TileSched tile_sched(const MaskParams& mk, uint32_t row_first) {
+// Key tiles (absolute index = key / 128) a CTA whose canvas rows are [row_first, row_last] must visit:
+// the prefix interval [lo(row_first), pre_hi) and the canvas interval [kv_len, can_hi) - in the causal
+// mode only up to row_last's own position -, merged when they touch.  (The lower bounds grow with the
+// row, the causal upper bound too, so the first row gives the lowest key and the last row the highest.)
+__host__ __device__ inline TileSched tile_sched(const MaskParams& mk, uint32_t row_first, uint32_t row_last) {
   TileSched t{0, 0, 0, 0};
   const uint32_t lo = mask_row_lo(mk, row_first);
   if (mk.pre_hi > lo) {
     t.a0 = lo / BN;
     t.nA = (mk.pre_hi + BN - 1) / BN - t.a0;
   }
-  if (mk.can_hi > mk.kv_len) {
-    const uint32_t b0 = mk.kv_len / BN, b1 = (mk.can_hi + BN - 1) / BN;
+  const uint32_t can_hi = mask_can_hi_rows(mk, row_last);
+  if (can_hi > mk.kv_len) {
+    const uint32_t b0 = mk.kv_len / BN, b1 = (can_hi + BN - 1) / BN;
     if (t.nA > 0 && b0 < t.a0 + t.nA) {
       const uint32_t a1 = (t.a0 + t.nA) > b1 ? (t.a0 + t.nA) : b1;
       t.nA = a1 - t.a0;

@@ -57,15 +57,16 @@ constexpr uint32_t T_S = 0, T_Q = 128, T_O = 256;     // TMEM columns: S buffers
 enum : uint32_t { B_Q = 0, B_K_FULL = 1 /* +stage */, B_V_FULL = 3, B_V_EMPTY = 4 /* +tile&1 */, B_S_FULL = 6 /* +buffer */,
                   B_P_FULL = 8 /* +buffer */, B_O_FINAL = 10, B_COUNT = 11 };
 
-__host__ __device__ inline TileSched tile_sched64(const MaskParams& mk, uint32_t row_first) {
+__host__ __device__ inline TileSched tile_sched64(const MaskParams& mk, uint32_t row_first, uint32_t row_last) {
   TileSched t{0, 0, 0, 0};
   const uint32_t lo = mask_row_lo(mk, row_first);
   if (mk.pre_hi > lo) {
     t.a0 = lo / TN;
     t.nA = (mk.pre_hi + TN - 1) / TN - t.a0;
   }
-  if (mk.can_hi > mk.kv_len) {
-    const uint32_t b0 = mk.kv_len / TN, b1 = (mk.can_hi + TN - 1) / TN;
+  const uint32_t can_hi = mask_can_hi_rows(mk, row_last);
+  if (can_hi > mk.kv_len) {
+    const uint32_t b0 = mk.kv_len / TN, b1 = (can_hi + TN - 1) / TN;
     if (t.nA > 0 && b0 < t.a0 + t.nA) {
       const uint32_t a1 = (t.a0 + t.nA) > b1 ? (t.a0 + t.nA) : b1;
       t.nA = a1 - t.a0;
@@ -110,7 +111,8 @@ dg_attn_sm100_hd512_kernel(const AttnParams p, const __grid_constant__ CUtensorM
   const MaskParams mk = p.mask;
 
   const uint32_t row_first = (mt * BM) / p.G;
-  const TileSched ts = tile_sched64(mk, row_first < p.C ? row_first : p.C - 1);
+  const uint32_t row_last = ((mt + 1u) * BM - 1u) / p.G;
+  const TileSched ts = tile_sched64(mk, row_first < p.C ? row_first : p.C - 1, row_last < p.C ? row_last : p.C - 1);
   const uint32_t n_tiles = ts.nA + ts.nB;
   const uint32_t v_begin = uint32_t((uint64_t(split) * n_tiles) / p.n_splits);
   const uint32_t v_end = uint32_t((uint64_t(split + 1) * n_tiles) / p.n_splits);
@@ -189,9 +191,8 @@ dg_attn_sm100_hd512_kernel(const AttnParams p, const __grid_constant__ CUtensorM
     // ---------------------------------------------------------------- softmax main loop
     const uint32_t R = mt * BM + r;
     const uint32_t i_row = (R < rows_per_head) ? R / p.G : p.C - 1;
-    const uint32_t row_lo = mask_row_lo(mk, i_row);
+    const RowVis rv = mask_row(mk, i_row);
     const uint32_t t_lane = tmem + ((smw * 32u) << 16);
-    const bool contiguous = (mk.pre_hi == mk.kv_len) && (mk.can_hi > mk.kv_len);
     const float sc = p.scale_log2;
 
     for (uint32_t n = 0; n < n_local; ++n) {
@@ -204,12 +205,10 @@ dg_attn_sm100_hd512_kernel(const AttnParams p, const __grid_constant__ CUtensorM
       uint32_t sraw[32];
       tmem_ld32(t_lane + T_S + b * TN + half * CPT, sraw);
       tmem_wait_ld();
-      const bool full = (k0 >= row_lo && k0 + TN <= mk.pre_hi) || (k0 >= mk.kv_len && k0 + TN <= mk.can_hi) ||
-                        (contiguous && k0 >= row_lo && k0 + TN <= mk.can_hi);
-      if (!full) {
+      if (!mask_range_full(mk, rv, k0, TN)) {
 #pragma unroll
         for (int e = 0; e < 32; ++e)
-          if (!mask_visible_lo(mk, row_lo, k0 + half * CPT + e)) sraw[e] = 0xff800000u;  // -inf
+          if (!mask_visible_row(mk, rv, k0 + half * CPT + e)) sraw[e] = 0xff800000u;  // -inf
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -518,7 +517,7 @@ cudaError_t sm100_hd512_configure() {
 }
 
 uint32_t sm100_hd512_key_tiles(const MaskParams& mk) {
-  const TileSched t = h5::tile_sched64(mk, 0);
+  const TileSched t = h5::tile_sched64(mk, 0, kMaxCanvas - 1);
   return t.nA + t.nB;
 }
 

@@ -14,10 +14,11 @@ constexpr uint32_t kMaxHeadDim = 512;
 constexpr uint32_t kMaxCanvas = 256;
 constexpr uint32_t kMaxRotHalf = 256;   // rotary_dim / 2 <= 256
 
-// Which keys a canvas row may attend (src/shaders/attn/attention/attention.metal:52-63 for the
-// window rule; split-KV shards intersect the prefix interval with [t0, t1)).
+// Which keys a canvas row may attend (src/shaders/attn/attention/attention.metal:51-63 for the
+// window and causal rules; split-KV shards intersect the prefix interval with [t0, t1)).
 //   prefix key t (t < kv_len) visible  iff  max(lo(row), t0) <= t < pre_hi
-//   canvas key t (kv_len <= t < can_hi) visible iff include_canvas
+//   canvas key t (kv_len <= t < can_hi) visible iff include_canvas, and in the causal mode only
+//   for lo(row) <= t <= kv_len + row (the query's own position)
 struct MaskParams {
   uint32_t kv_len;    // first canvas position = number of prefix keys
   uint32_t t0;        // shard lower bound (0 when unsharded)
@@ -43,21 +44,55 @@ __host__ __device__ inline MaskParams make_mask(const dg_layer_desc& d, uint32_t
   return m;
 }
 
+// lower end of the window of canvas row `row` (0 without a window), before any shard bound
+__host__ __device__ inline uint32_t mask_window_lo(const MaskParams& m, uint32_t row) {
+  if (!m.windowed) return 0u;
+  const uint32_t qpos = (m.mode == DG_MASK_WINDOW_UNIFORM) ? m.kv_len : m.kv_len + row;
+  return qpos > m.wm1 ? qpos - m.wm1 : 0u;
+}
+
 // lowest visible prefix key of canvas row `row`
 __host__ __device__ inline uint32_t mask_row_lo(const MaskParams& m, uint32_t row) {
-  uint32_t lo = 0;
-  if (m.windowed) {
-    const uint32_t qpos = (m.mode == DG_MASK_WINDOW_PER_ROW) ? m.kv_len + row : m.kv_len;
-    lo = qpos > m.wm1 ? qpos - m.wm1 : 0u;
-  }
+  const uint32_t lo = mask_window_lo(m, row);
   return lo > m.t0 ? lo : m.t0;
 }
 
-__host__ __device__ inline bool mask_visible_lo(const MaskParams& m, uint32_t row_lo, uint32_t t) {
-  return (t >= row_lo && t < m.pre_hi) || (t >= m.kv_len && t < m.can_hi);
+// What one canvas row sees: prefix keys [lo, pre_hi) and canvas keys [can_lo, can_hi).
+struct RowVis {
+  uint32_t lo, can_lo, can_hi;
+};
+__host__ __device__ inline RowVis mask_row(const MaskParams& m, uint32_t row) {
+  RowVis v;
+  v.lo = mask_row_lo(m, row);
+  v.can_lo = m.kv_len;
+  v.can_hi = m.can_hi;
+  if (m.mode == DG_MASK_CAUSAL) {
+    const uint32_t wlo = mask_window_lo(m, row);
+    const uint32_t own = m.kv_len + row + 1u;             // one past the query's own position
+    if (wlo > v.can_lo) v.can_lo = wlo;
+    if (own < v.can_hi) v.can_hi = own;
+    if (v.can_hi < v.can_lo) v.can_hi = v.can_lo;         // nothing of the canvas
+  }
+  return v;
+}
+
+__host__ __device__ inline bool mask_visible_row(const MaskParams& m, const RowVis& v, uint32_t t) {
+  return (t >= v.lo && t < m.pre_hi) || (t >= v.can_lo && t < v.can_hi);
 }
 __host__ __device__ inline bool mask_visible(const MaskParams& m, uint32_t row, uint32_t t) {
-  return mask_visible_lo(m, mask_row_lo(m, row), t);
+  return mask_visible_row(m, mask_row(m, row), t);
+}
+// whole key range [k0, k0 + n) visible to the row
+__host__ __device__ inline bool mask_range_full(const MaskParams& m, const RowVis& v, uint32_t k0, uint32_t n) {
+  const bool joined = m.pre_hi == m.kv_len && v.can_lo == m.kv_len && v.can_hi > m.kv_len;
+  return (k0 >= v.lo && k0 + n <= m.pre_hi) || (k0 >= v.can_lo && k0 + n <= v.can_hi) ||
+         (joined && k0 >= v.lo && k0 + n <= v.can_hi);
+}
+// one past the last canvas key any of the canvas rows [row_first, row_last] sees
+__host__ __device__ inline uint32_t mask_can_hi_rows(const MaskParams& m, uint32_t row_last) {
+  if (m.mode != DG_MASK_CAUSAL) return m.can_hi;
+  const uint32_t own = m.kv_len + row_last + 1u;
+  return own < m.can_hi ? own : m.can_hi;
 }
 
 // Device status word {code, kernel_id, cta, value}: first writer wins.

@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) dg_attn_general_kernel(const A
   float m = -INFINITY, l = 0.f;
 
   const MaskParams mk = p.mask;
-  const uint32_t row_lo = mask_row_lo(mk, row);
+  const RowVis rv = mask_row(mk, row);
   const uint32_t T = mk.kv_len + p.C;
   const __nv_bfloat16* kbase = p.cache_k + size_t(kvh) * p.cap * D;
   const __nv_bfloat16* vbase = p.cache_v + size_t(kvh) * p.cap * D;
@@ -254,11 +254,11 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) dg_attn_general_kernel(const A
       lo = 0;
       hi = T;
     } else if (range == 0) {
-      lo = row_lo;
+      lo = rv.lo;
       hi = mk.pre_hi;
     } else {
-      lo = mk.kv_len;
-      hi = mk.can_hi;
+      lo = rv.can_lo;
+      hi = rv.can_hi;
     }
     for (uint32_t t = lo + warp; t < hi; t += GEN_WARPS) {
       if (p.attend) {
@@ -417,9 +417,9 @@ void launch_merge_finalize(uint32_t rows, uint32_t D, const float* pay, __nv_bfl
 __global__ void dg_visibility_kernel(MaskParams mk, uint32_t C, uint8_t* __restrict__ out) {
   const uint32_t T = mk.kv_len + C;
   const uint32_t row = blockIdx.y;
-  const uint32_t row_lo = mask_row_lo(mk, row);
+  const RowVis rv = mask_row(mk, row);
   for (uint32_t t = blockIdx.x * blockDim.x + threadIdx.x; t < T; t += gridDim.x * blockDim.x)
-    out[size_t(row) * T + t] = mask_visible_lo(mk, row_lo, t) ? 1 : 0;
+    out[size_t(row) * T + t] = mask_visible_row(mk, rv, t) ? 1 : 0;
 }
 void launch_visibility(const MaskParams& mk, uint32_t C, uint8_t* out, cudaStream_t st) {
   const uint32_t T = mk.kv_len + C;

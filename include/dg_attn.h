@@ -45,12 +45,19 @@ enum {
                               * returned without doing anything                                  */
 };
 
-/* mask modes: which PREFIX keys a canvas row sees (canvas keys are always visible to every
- * row, bidirectionally).  src/shaders/attn/attention/attention.metal:52-63                     */
+/* mask modes: which keys a canvas row sees.  In the three denoise modes the canvas keys are visible
+ * to every row, bidirectionally, and the mode only restricts the PREFIX keys
+ * (src/shaders/attn/attention/attention.metal:52-63 with dims.causal == 0).  DG_MASK_CAUSAL is the
+ * shader's dims.causal != 0 branch (attention.metal:51,57-62), which the reference uses when it
+ * re-prefills a committed block (src/metal/step_generate/turn.rs:1235-1295): the query at position
+ * kv_len+i sees keys [max(0, kv_len+i-(window-1)), kv_len+i], canvas keys included in that rule.
+ * DG_MASK_WINDOW_PER_ROW is an extension for the benchmark's sliding-layer configuration (a window
+ * that slides per row while the canvas stays bidirectional); the reference has no such mode.     */
 enum {
   DG_MASK_NONE = 0,           /* all prefix keys (global layers)                                */
   DG_MASK_WINDOW_UNIFORM = 1, /* reference denoise rule: t >= max(0, kv_len-(window-1)), all rows */
-  DG_MASK_WINDOW_PER_ROW = 2  /* row i (position kv_len+i): t >= max(0, kv_len+i-(window-1))    */
+  DG_MASK_WINDOW_PER_ROW = 2, /* row i (position kv_len+i): t >= max(0, kv_len+i-(window-1))    */
+  DG_MASK_CAUSAL = 3          /* row i: max(0, kv_len+i-(window-1)) <= t <= kv_len+i (window 0: no lower bound) */
 };
 
 /* RoPE pairings.  src/shaders/attn/cpu.rs:31-65                                                */

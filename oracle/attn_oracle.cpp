@@ -12,6 +12,7 @@
 //   attention (online softmax, GQA kvh = qh / (Hq/Hkv))
 //                            src/shaders/attn/cpu.rs:148-197
 //   denoise window rule      src/shaders/attn/attention/attention.metal:52-63
+//   causal (re-prefill) rule src/shaders/attn/attention/attention.metal:51,57-62
 //   decoder bitmap mask      src/model/mask.rs:4-27, src/model/attention.rs:889-907
 // The key loop is blocked (64-key tiles, online softmax carried as (m, l, O)) the way
 // src/shaders/attn/attention_flash/mod.rs:20-95 blocks its CPU reference; the result is
@@ -38,7 +39,7 @@ typedef struct {
   uint32_t window, mask_mode, v_norm, rope_pairing;
 } dgo_desc;
 
-enum { DGO_MASK_NONE = 0, DGO_MASK_WINDOW_UNIFORM = 1, DGO_MASK_WINDOW_PER_ROW = 2 };
+enum { DGO_MASK_NONE = 0, DGO_MASK_WINDOW_UNIFORM = 1, DGO_MASK_WINDOW_PER_ROW = 2, DGO_MASK_CAUSAL = 3 };
 
 }  // extern "C"
 
@@ -172,12 +173,16 @@ void dgo_qk_rope_kv(const dgo_desc* dp, uint32_t kv_len, const uint16_t* q, cons
 // Visibility of key t for canvas row `row` (bit-exact mask rule).
 int dgo_visible(const dgo_desc* d, uint32_t kv_len, uint32_t t0, uint32_t t1, int include_canvas,
                 uint32_t row, uint32_t t) {
-  if (t >= kv_len) return include_canvas && t < kv_len + d->canvas;
   uint32_t lo = 0;
   if (d->mask_mode != DGO_MASK_NONE && d->window != 0) {
     const uint32_t wm1 = d->window - 1;
-    const uint32_t qpos = d->mask_mode == DGO_MASK_WINDOW_PER_ROW ? kv_len + row : kv_len;
+    const uint32_t qpos = d->mask_mode == DGO_MASK_WINDOW_UNIFORM ? kv_len : kv_len + row;
     lo = qpos > wm1 ? qpos - wm1 : 0;
+  }
+  if (t >= kv_len) {
+    if (!include_canvas || t >= kv_len + d->canvas) return 0;
+    if (d->mask_mode == DGO_MASK_CAUSAL) return t <= kv_len + row && t >= lo;
+    return 1;
   }
   return t >= lo && t >= t0 && t < t1;
 }
@@ -213,7 +218,7 @@ int dgo_attention(const dgo_desc* dp, uint32_t kv_len, const uint16_t* qn, const
   uint32_t lo_any = t0;
   if (!attend && d.mask_mode != DGO_MASK_NONE && d.window != 0) {
     const uint32_t wm1 = d.window - 1;
-    const uint32_t qpos = d.mask_mode == DGO_MASK_WINDOW_PER_ROW ? kv_len + row_begin : kv_len;
+    const uint32_t qpos = d.mask_mode == DGO_MASK_WINDOW_UNIFORM ? kv_len : kv_len + row_begin;
     lo_any = std::max(lo_any, qpos > wm1 ? qpos - wm1 : 0u);
   }
   if (attend) lo_any = 0;

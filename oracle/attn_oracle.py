@@ -12,6 +12,7 @@ the reference project):
 * GQA attention + softmax    src/shaders/attn/cpu.rs:148-197, src/model/attention.rs:861-934,
                              src/shaders/cpu/mod.rs:175-190
 * denoise window rule        src/shaders/attn/attention/attention.metal:52-63
+* causal (re-prefill) rule   src/shaders/attn/attention/attention.metal:51,57-62
 * general decoder bitmap     src/model/mask.rs:4-27, src/model/attention.rs:889-907
 * (m, l, O) block state      src/shaders/include/attention_device.metal:154-165
 
@@ -37,6 +38,7 @@ import numpy as np
 MASK_NONE = 0          # every prefix key visible (global layers)
 MASK_WINDOW_UNIFORM = 1  # reference denoise rule: one t_lo for every canvas row
 MASK_WINDOW_PER_ROW = 2  # query at position p sees prefix keys [p-(W-1), p]
+MASK_CAUSAL = 3        # prefill rule: query at position p sees keys [p-(W-1), p], canvas keys included
 
 ROPE_SPLIT_HALF = 0    # pairs (d, d + rot/2)          (sliding layers)
 ROPE_PROPORTIONAL = 1  # pairs (d, head_dim/2 + d)     (global layers, partial rotary)
@@ -186,12 +188,17 @@ def visibility(desc: LayerDesc, kv_len: int, t0: int = 0, t1: int | None = None,
         t_lo = np.zeros((C, 1), dtype=np.int64)
     elif desc.mask_mode == MASK_WINDOW_UNIFORM:
         t_lo = np.full((C, 1), max(0, kv_len - (desc.window - 1)), dtype=np.int64)
-    elif desc.mask_mode == MASK_WINDOW_PER_ROW:
+    elif desc.mask_mode in (MASK_WINDOW_PER_ROW, MASK_CAUSAL):
         t_lo = np.maximum(0, kv_len + rows - (desc.window - 1)).astype(np.int64)
     else:
         raise ValueError("mask_mode")
+    if desc.mask_mode not in (MASK_NONE, MASK_WINDOW_UNIFORM, MASK_WINDOW_PER_ROW, MASK_CAUSAL):
+        raise ValueError("mask_mode")
     prefix = (t >= t_lo) & (t >= t0) & (t < t1) & (t < kv_len)
     canvas = (t >= kv_len) & bool(include_canvas)
+    if desc.mask_mode == MASK_CAUSAL:
+        # T = min(T_all, kv_len + tok + 1) and the window's lower bound also cuts canvas keys
+        canvas = canvas & (t <= kv_len + rows) & (t >= t_lo)
     return prefix | canvas
 
 

@@ -24,6 +24,10 @@ OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ref_shader_golde
 # visibility cases: (kv_len, window, ring_mask), canvas 16, one key per output dimension
 MASK_CASES = [(200, 0, 0), (200, 64, 0), (30, 64, 0), (63, 64, 0), (64, 64, 0), (65, 64, 0), (200, 64, 255),
               (1000, 64, 255), (5000, 100, 255), (100000, 128, 255), (240, 1, 0), (240, 2, 0)]
+# the same probe with dims.causal = 1 (the re-prefill of a committed block): plain causal, causal with a
+# window, a window shorter than the canvas (its lower bound then cuts canvas keys too), an empty prefix, a ring
+CAUSAL_MASK_CASES = [(200, 0, 0), (200, 64, 0), (30, 64, 0), (5, 8, 0), (0, 0, 0), (0, 4, 0), (1000, 64, 255),
+                     (240, 1, 0), (240, 2, 0)]
 # value cases: name -> (hd, n_q, n_kv, canvas, kv_len, is_full, window, ring_mask, v_aliases_k, seed)
 VALUE_CASES = {
     "sliding_short": (256, 8, 2, 8, 40, 0, 1024, 0, 0, 1),
@@ -31,6 +35,11 @@ VALUE_CASES = {
     "sliding_ring": (256, 8, 2, 8, 2500, 0, 128, 511, 0, 3),
     "full_hd512_valias": (512, 4, 2, 4, 60, 1, 0, 0, 1, 4),
     "full_hd256_vproj": (256, 4, 1, 4, 33, 1, 0, 0, 0, 5),
+}
+# value cases run with dims.causal = 1, same tuple layout
+CAUSAL_VALUE_CASES = {
+    "causal_sliding": (256, 8, 2, 8, 300, 0, 128, 0, 0, 6),
+    "causal_full_hd256": (256, 4, 1, 8, 33, 1, 0, 0, 0, 7),
 }
 
 
@@ -64,7 +73,7 @@ def value_inputs(hd, n_q, n_kv, canvas, kv_len, is_full, window, ring, valias, s
     return q, k, v, kp, vp, qw, kw
 
 
-def run_value_case(hd, n_q, n_kv, canvas, kv_len, is_full, window, ring, valias, seed):
+def run_value_case(hd, n_q, n_kv, canvas, kv_len, is_full, window, ring, valias, seed, causal=0):
     q, k, v, kp, vp, qw, kw = value_inputs(hd, n_q, n_kv, canvas, kv_len, is_full, window, ring, valias, seed)
     T = kv_len + canvas
     cache = rs.make_cache(ring + 1 if ring else T, n_kv, hd)
@@ -73,7 +82,7 @@ def run_value_case(hd, n_q, n_kv, canvas, kv_len, is_full, window, ring, valias,
     bits = rs.bf16_bits_trunc
     qb, kb, vb = rs.qk_rope_kv(bits(q), bits(k), bits(v), cache, bits(qw), bits(kw), kv_len, is_full, valias,
                                ring_mask=ring)
-    out = rs.attention(qb, cache, kv_len, window, 0, ring)
+    out = rs.attention(qb, cache, kv_len, window, causal, ring)
     # the canvas K / V the stage left in the cache (f16), in position order
     slots = [((kv_len + i) & ring) if ring else kv_len + i for i in range(canvas)]
     kc = cache[slots, 0].view(np.float16).astype(np.float32)
@@ -89,10 +98,16 @@ def main():
         out = rs.attention(q, cache, kv_len, window, 0, ring)
         store[f"mask{i}_visible"] = out[:, 0, :] > 0
         print("mask", kv_len, window, ring, "visible per row", int((out[0, 0] > 0).sum()))
-    for name, cfg in VALUE_CASES.items():
-        for key, val in run_value_case(*cfg).items():
-            store[f"{name}_{key}"] = val.astype(np.float32)
-        print("value", name, "max |out|", float(np.abs(store[f"{name}_out"]).max()))
+    for i, (kv_len, window, ring) in enumerate(CAUSAL_MASK_CASES):
+        q, cache = mask_inputs(kv_len, window, ring)
+        out = rs.attention(q, cache, kv_len, window, 1, ring)
+        store[f"cmask{i}_visible"] = out[:, 0, :] > 0
+        print("causal mask", kv_len, window, ring, "visible per row", (out[:, 0] > 0).sum(axis=1).tolist())
+    for cases, causal in ((VALUE_CASES, 0), (CAUSAL_VALUE_CASES, 1)):
+        for name, cfg in cases.items():
+            for key, val in run_value_case(*cfg, causal=causal).items():
+                store[f"{name}_{key}"] = val.astype(np.float32)
+            print("value", name, "max |out|", float(np.abs(store[f"{name}_out"]).max()))
     np.savez_compressed(OUT, **store)
     print("wrote", OUT, os.path.getsize(OUT), "bytes")
 

@@ -113,6 +113,21 @@ def test_window_two_blocks_distant_past():
     assert list(m[0]) == [False, True, True]
 
 
+# --- the same Rust test as a whole 3 x 3 causal sliding mask (kv_len = 0, three tokens, window 2):
+# the future and the distant past are both hidden
+def test_causal_sliding_mask_blocks_future_and_distant_past():
+    d = ao.LayerDesc(canvas=3, window=2, mask_mode=ao.MASK_CAUSAL)
+    m = ao.visibility(d, 0)
+    assert m.tolist() == [[True, False, False], [True, True, False], [False, True, True]]
+    np.testing.assert_array_equal(m, co.visibility(d, 0))
+    # without a window the causal mode is the plain lower triangle over [prefix | canvas]
+    d = ao.LayerDesc(canvas=4, window=0, mask_mode=ao.MASK_CAUSAL)
+    m = ao.visibility(d, 3)
+    for r in range(4):
+        assert m[r].tolist() == [t <= 3 + r for t in range(7)]
+    np.testing.assert_array_equal(m, co.visibility(d, 3))
+
+
 # --- src/shaders/attn/attention_flash/mod_tests.rs:21-36: blocked online softmax == single pass
 @pytest.mark.parametrize("block", [1, 3, 8, 16, 64, 4096])
 def test_blocked_equals_single_pass(block):

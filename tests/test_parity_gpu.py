@@ -116,6 +116,11 @@ PARITY_CASES = [
     (500, 8, 0, 0, 1 / 16, 128, False, 0),      # narrower active canvases
     (500, 2, 0, 0, 1 / 16, 64, True, 0),
     (333, 8, 64, 2, 1 / 16, 100, False, 0),     # ragged canvas, tiny window
+    (0, 8, 0, 3, 1 / 16, 256, False, 0),        # causal re-prefill of a block on an empty cache
+    (700, 8, 0, 3, 1.0, 256, True, 1),          # causal, no window, reference semantics
+    (3000, 8, 1024, 3, 1.0, 256, False, 1),     # causal sliding: query p sees [p - 1023, p]
+    (3000, 2, 1024, 3, 1 / 16, 256, False, 0),  # the same with 16 query tiles per KV head (tile-range trimming)
+    (333, 8, 64, 3, 1 / 16, 100, False, 0),     # causal window shorter than the canvas: it cuts canvas keys too
 ]
 
 
@@ -253,7 +258,9 @@ def test_host_buffer_call_matches_device_call(ctx):
 # ------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("P,W,mode,canvas", [(0, 0, 0, 256), (300, 0, 0, 256), (700, 1024, 1, 256), (1023, 1024, 2, 256),
                                              (1024, 1024, 2, 256), (1025, 1024, 1, 256), (3000, 1024, 2, 256),
-                                             (8192, 1024, 2, 256), (8192, 1024, 1, 256), (333, 64, 2, 100)])
+                                             (8192, 1024, 2, 256), (8192, 1024, 1, 256), (333, 64, 2, 100),
+                                             (0, 0, 3, 256), (300, 0, 3, 256), (1025, 1024, 3, 256), (333, 64, 3, 100),
+                                             (5, 8, 3, 16)])
 def test_visibility_bitmap_bit_exact(ctx, P, W, mode, canvas):
     layer = AttnLayer(window=W, mask_mode=mode, canvas=canvas)
     att = CanvasAttention(ctx, layer)
@@ -268,6 +275,7 @@ def test_visibility_bitmap_bit_exact(ctx, P, W, mode, canvas):
 @pytest.mark.parametrize("P,W,mode,t0,t1,inc", [
     (100, 0, 0, 0, 100, True), (100, 64, 1, 0, 100, True), (100, 64, 2, 0, 100, True),
     (100, 64, 2, 30, 80, False), (100, 0, 0, 50, 50, True), (90, 32, 2, 0, 90, True),
+    (100, 0, 3, 0, 100, True), (100, 64, 3, 0, 100, True), (100, 16, 3, 20, 100, True), (0, 8, 3, 0, 0, True),
 ])
 def test_kernel_mask_bit_exact_through_indicator_values(ctx, force_general, P, W, mode, t0, t1, inc):
     """With Q = 0 every visible key has weight exactly 1, so l counts the visible keys of a row and,
@@ -486,14 +494,16 @@ def _ref_golden():
 
 
 @pytest.mark.parametrize("name", ["sliding_short", "sliding_window_cuts", "sliding_ring", "full_hd512_valias",
-                                  "full_hd256_vproj"])
+                                  "full_hd256_vproj", "causal_sliding", "causal_full_hd256"])
 def test_gpu_matches_reference_shader_vectors(ctx, name):
     G, gold = _ref_golden()
-    hd, n_q, n_kv, canvas, kv_len, is_full, window, ring, valias, seed = G.VALUE_CASES[name]
-    q, k, v, kp, vp, qw, kw = G.value_inputs(*G.VALUE_CASES[name])
+    cases = {**G.VALUE_CASES, **G.CAUSAL_VALUE_CASES}
+    hd, n_q, n_kv, canvas, kv_len, is_full, window, ring, valias, seed = cases[name]
+    q, k, v, kp, vp, qw, kw = G.value_inputs(*cases[name])
+    mode = capi.MASK_CAUSAL if name in G.CAUSAL_VALUE_CASES else (capi.MASK_WINDOW_UNIFORM if window else capi.MASK_NONE)
     layer = AttnLayer(n_q_heads=n_q, n_kv_heads=n_kv, head_dim=hd, canvas=canvas,
                       rotary_dim=hd // 4 if is_full else hd, rope_theta=1e6 if is_full else 1e4, rms_eps=1e-6,
-                      softmax_scale=1.0, window=window, mask_mode=capi.MASK_WINDOW_UNIFORM if window else capi.MASK_NONE,
+                      softmax_scale=1.0, window=window, mask_mode=mode,
                       v_norm=1, rope_pairing=capi.ROPE_PROPORTIONAL if is_full else capi.ROPE_SPLIT_HALF)
     kv = KvCache(ctx, layer, ring_slots=ring + 1) if ring else KvCache(ctx, layer, kv_len + canvas)
     t = lambda a: util.f2t(a).to(DEV)
@@ -520,6 +530,7 @@ def test_gpu_matches_reference_shader_vectors(ctx, name):
     (4096, 16, 2, 256, 0, 0, 1 / 16, 1),    # aligned prefix
     (3000, 8, 8, 100, 0, 0, 1 / 16, 1),     # no GQA stacking, ragged canvas
     (5000, 16, 4, 256, 1024, 1, 1 / 16, 1), # sliding window on a 512-wide head (not a reference layer; mask logic)
+    (700, 16, 2, 256, 0, 3, 1.0, 1),        # causal re-prefill of a block on a full layer
 ])
 def test_hd512_tensor_path_parity(ctx, P, Hq, Hkv, canvas, W, mode, scale, vnorm):
     layer = AttnLayer(n_q_heads=Hq, n_kv_heads=Hkv, head_dim=512, canvas=canvas, rotary_dim=128, rope_theta=1e6,

@@ -7,7 +7,8 @@ tree is absent; where the compiled library is present the stored vectors are add
 against a live run.
 
 What is pinned: the denoise visibility rule with and without a sliding window, bit for bit
-(attention.metal:52-63: t_lo = kv_len - (window - 1), uniform over canvas rows), the ring slot mapping
+(attention.metal:52-63: t_lo = kv_len - (window - 1), uniform over canvas rows), the causal rule of the
+same shader (attention.metal:51,57-62: the committed-block re-prefill), the ring slot mapping
 (attention_device.metal:27-33), both RoPE pairings with their rotary extents and thetas and the
 V-aliases-raw-K form of full layers (qk_rope_kv.metal:58-101), and the streaming softmax values."""
 import os
@@ -26,11 +27,12 @@ from oracle import ref_shader as rs  # noqa: E402
 GOLD = np.load(os.path.join(ROOT, "tests", "golden", "ref_shader_golden.npz"))
 
 
-def oracle_desc(hd, n_q, n_kv, canvas, is_full, window):
+def oracle_desc(hd, n_q, n_kv, canvas, is_full, window, causal=0):
     # what qk_rope_kv.metal:58-60 and attention.metal hard-wire per layer kind
+    mode = ao.MASK_CAUSAL if causal else (ao.MASK_WINDOW_UNIFORM if window else ao.MASK_NONE)
     return ao.LayerDesc(n_q_heads=n_q, n_kv_heads=n_kv, head_dim=hd, canvas=canvas,
                         rotary_dim=hd // 4 if is_full else hd, rope_theta=1e6 if is_full else 1e4, rms_eps=1e-6,
-                        softmax_scale=1.0, window=window, mask_mode=1 if window else 0, v_norm=1,
+                        softmax_scale=1.0, window=window, mask_mode=mode, v_norm=1,
                         rope_pairing=1 if is_full else 0)
 
 
@@ -47,15 +49,34 @@ def test_visibility_rule_matches_the_reference_shader_bit_for_bit(idx):
     assert np.array_equal(GOLD[f"mask{idx}_visible"], expect), (kv_len, window, ring)
 
 
+@pytest.mark.parametrize("idx", range(len(G.CAUSAL_MASK_CASES)))
+def test_causal_rule_matches_the_reference_shader_bit_for_bit(idx):
+    """dims.causal = 1 (attention.metal:51,57-62): query kv_len+i sees [kv_len+i-(window-1), kv_len+i]."""
+    kv_len, window, ring = G.CAUSAL_MASK_CASES[idx]
+    canvas, hd = 16, 256
+    d = oracle_desc(hd, 4, 2, canvas, 0, window, causal=1)
+    mine = ao.visibility(d, kv_len)
+    expect = np.zeros((canvas, hd), bool)
+    for t in range(kv_len + canvas):
+        expect[:, t % hd] |= mine[:, t]
+    assert np.array_equal(GOLD[f"cmask{idx}_visible"], expect), (kv_len, window, ring)
+    # the C++ twin evaluates the same rule
+    from oracle import c_oracle as co
+    assert np.array_equal(co.visibility(d, kv_len), mine)
+
+
 def ulp_bf16(x):
     return np.maximum(np.abs(x), 2.0 ** -20) * 2.0 ** -7
 
 
-@pytest.mark.parametrize("name", list(G.VALUE_CASES))
+ALL_VALUE_CASES = {**G.VALUE_CASES, **G.CAUSAL_VALUE_CASES}
+
+
+@pytest.mark.parametrize("name", list(ALL_VALUE_CASES))
 def test_stage1_and_attention_values_match_the_reference_shaders(name):
-    hd, n_q, n_kv, canvas, kv_len, is_full, window, ring, valias, seed = G.VALUE_CASES[name]
-    q, k, v, kp, vp, qw, kw = G.value_inputs(*G.VALUE_CASES[name])
-    d = oracle_desc(hd, n_q, n_kv, canvas, is_full, window)
+    hd, n_q, n_kv, canvas, kv_len, is_full, window, ring, valias, seed = ALL_VALUE_CASES[name]
+    q, k, v, kp, vp, qw, kw = G.value_inputs(*ALL_VALUE_CASES[name])
+    d = oracle_desc(hd, n_q, n_kv, canvas, is_full, window, causal=int(name in G.CAUSAL_VALUE_CASES))
     qn, kn, vn = ao.qk_rope_kv(q, k, k if valias else v, qw, kw, d, kv_len)
     # stage 1: the shader truncates Q to bf16 and keeps K / V in f16; the oracle rounds all three to bf16
     assert (np.abs(qn - GOLD[f"{name}_q_out"]) <= 2.0 * ulp_bf16(qn) + 1e-6).all()
@@ -94,6 +115,13 @@ def test_stored_vectors_equal_a_live_run_of_the_compiled_shaders():
         q, cache = G.mask_inputs(kv_len, window, ring)
         out = rs.attention(q, cache, kv_len, window, 0, ring)
         assert np.array_equal(out[:, 0, :] > 0, GOLD[f"mask{i}_visible"])
+    for i, (kv_len, window, ring) in enumerate(G.CAUSAL_MASK_CASES[:4]):
+        q, cache = G.mask_inputs(kv_len, window, ring)
+        out = rs.attention(q, cache, kv_len, window, 1, ring)
+        assert np.array_equal(out[:, 0, :] > 0, GOLD[f"cmask{i}_visible"])
+    live = G.run_value_case(*G.CAUSAL_VALUE_CASES["causal_sliding"], causal=1)
+    for key, val in live.items():
+        assert np.array_equal(val.astype(np.float32), GOLD[f"causal_sliding_{key}"]), key
     for name in ("sliding_short", "full_hd512_valias"):
         live = G.run_value_case(*G.VALUE_CASES[name])
         for key, val in live.items():
