@@ -61,6 +61,8 @@ SIGNATURES = {
     "dg_ctx_max_active_clusters": (_i32, [_vp, _i32, _u32]),
     "dg_kv_create": (_i32, [_vp, _pd, _u64, C.POINTER(_vp)]),
     "dg_kv_create_ring": (_i32, [_vp, _pd, _u32, C.POINTER(_vp)]),
+    "dg_kv_create_shard": (_i32, [_vp, _pd, _u64, _u64, C.POINTER(_vp)]),
+    "dg_kv_pos_base": (_u64, [_vp]),
     "dg_kv_ring_mask": (_u32, [_vp]),
     "dg_kv_destroy": (_i32, [_vp]),
     "dg_kv_capacity": (_u64, [_vp]),
@@ -88,10 +90,15 @@ SIGNATURES = {
     "dg_nccl_all_gather": (_i32, [_vp, _vp, _vp, _vp, _u64]),
     "dg_p2p_create": (_i32, [_vp, _u32, _u32, _i32, _i32, C.POINTER(_vp)]),
     "dg_p2p_set_mode": (_i32, [_vp, _i32]),
+    "dg_p2p_slice": (_i32, [_vp, C.POINTER(_u32), C.POINTER(_u32)]),
+    "dg_p2p_set_wait_limit": (_i32, [_vp, _u64]),
+    "dg_p2p_reset": (_i32, [_vp]),
     "dg_p2p_handle": (_i32, [_vp, _vp]),
     "dg_p2p_connect": (_i32, [_vp, _vp]),
     "dg_p2p_destroy": (_i32, [_vp]),
     "dg_attn_denoise_split_p2p": (_i32, [_vp, _pd, _vp, _u32, _u32, _u32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "dg_host_pipe_submit_split": (_i32, [_vp, _pd, _vp, _u32, _u32, _u32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                         C.POINTER(_u64)]),
     "dg_attn_visibility": (_i32, [_vp, _pd, _u32, _u32, _u32, _i32, _vp]),
     "dg_attn_flops": (C.c_double, [_pd, _u32]),
     "dg_ctx_last_launch_count": (_u32, [_vp]),

@@ -57,14 +57,6 @@ struct dg_ctx {
   cudaEvent_t side_fork = nullptr, side_join[8] = {};
   cudaStream_t side_active = nullptr;  // non-null while a canvas of a concurrent batch is being enqueued
   uint32_t concurrent = 1;             // canvases in flight together: the split heuristic counts their CTAs
-  float2* rope_table = nullptr;        // [kRopeSlots][kMaxCanvas][kMaxRotHalf]
-  // what each table slot currently holds: denoise steps repeat at the same positions, so the table
-  // of a slot is rewritten only when this key changes
-  struct RopeKey {
-    bool valid = false;
-    uint32_t kv_len = 0, canvas = 0, rotary_dim = 0, pairing = 0, head_dim = 0;
-    float theta = 0.f;
-  } rope_key[8];
   uint32_t* counters = nullptr;        // [kCounterSlots], zero between launches
   float* ws_o = nullptr;               // split partials
   float* ws_ml = nullptr;
@@ -88,19 +80,36 @@ struct dg_ctx {
   size_t ev_used = 0;
 };
 
+// What a cache's RoPE table currently holds.  Denoise steps repeat at the same positions, so the
+// table is rewritten only when this key changes.
+struct RopeKey {
+  bool valid = false;
+  uint32_t kv_len = 0, canvas = 0, rotary_dim = 0, pairing = 0, head_dim = 0;
+  float theta = 0.f;
+};
+
 struct dg_kv {
   dg_ctx* ctx = nullptr;
+  // (cos, sin) of the canvas positions [kv_len, kv_len + canvas) of the fused path, two regions of
+  // [kMaxCanvas][head_dim / 2] entries.  The table belongs to the CACHE, so that a step replayed from a CUDA
+  // graph reads the table of its own cache and positions whatever other caches were used since.
+  // Region 0 is maintained by eager calls and described by rope_key.  Launches recorded under stream
+  // capture may read region 0 (when it already holds their positions) but never write it: a replay is
+  // invisible to the host, so a table a graph writes lives in region 1, which only that graph reads.
+  float2* rope_table = nullptr;
+  RopeKey rope_key;
   __nv_bfloat16* k = nullptr;   // [Hkv][cap][D]
   __nv_bfloat16* v = nullptr;
   uint64_t cap = 0;
   uint32_t ring_mask = 0;       // 0: linear cache; else slots - 1 of a ring (slot = pos & ring_mask)
+  uint32_t pos_base = 0;        // shard caches: the first position held, multiple of 128
+  bool shard = false;           // holds [pos_base, pos_base + cap) of a longer prefix (dg_kv_create_shard)
   uint32_t Hkv = 0, D = 0;
   bool has_tmap = false;
   CUtensorMap tm_k, tm_v;
   CUtensorMap tm_k64;   // K with 64-key boxes (CTA-pair kernel: each CTA stages half of a key tile)
 };
 
-constexpr uint32_t kRopeSlots = 8;
 constexpr uint32_t kMaxQueryTiles = 4096;
 constexpr uint32_t kCounterSlots = kMaxQueryTiles * 32 + 1;   // (query tile, four-row slice) arrival counters + the self-test flag
 
@@ -291,7 +300,6 @@ extern "C" int32_t dg_ctx_create(int32_t device, dg_ctx** out) {
   cudaError_t e = cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaMalloc(&c->d_status, sizeof(DevStatus));
   if (e == cudaSuccess) e = cudaMemset(c->d_status, 0, sizeof(DevStatus));
-  if (e == cudaSuccess) e = cudaMalloc(&c->rope_table, size_t(kRopeSlots) * kMaxCanvas * kMaxRotHalf * sizeof(float2));
   if (e == cudaSuccess) e = cudaMalloc(&c->counters, kCounterSlots * sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaMemset(c->counters, 0, kCounterSlots * sizeof(uint32_t));
   if (e == cudaSuccess) e = sm100_attn_configure();
@@ -311,7 +319,6 @@ extern "C" int32_t dg_ctx_destroy(dg_ctx* c) {
   cudaSetDevice(c->device);
   if (c->stream) cudaStreamSynchronize(c->stream);
   cudaFree(c->d_status);
-  cudaFree(c->rope_table);
   for (int i = 0; i < 8; ++i) {
     if (c->side[i]) cudaStreamDestroy(c->side[i]);
     if (c->side_join[i]) cudaEventDestroy(c->side_join[i]);
@@ -446,7 +453,8 @@ extern "C" int32_t dg_ctx_kernel_time(dg_ctx* c, double* total_ms, uint32_t* lau
 // ------------------------------------------------------------------------------------------
 // KV cache
 // ------------------------------------------------------------------------------------------
-static int32_t kv_create(dg_ctx* c, const dg_layer_desc* d, uint64_t capacity_tokens, uint32_t ring_mask, dg_kv** out) {
+static int32_t kv_create(dg_ctx* c, const dg_layer_desc* d, uint64_t capacity_tokens, uint32_t ring_mask, dg_kv** out,
+                         uint32_t pos_base = 0, bool shard = false) {
   if (!c || !out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
   *out = nullptr;
   int32_t r = check_desc(d);
@@ -458,6 +466,8 @@ static int32_t kv_create(dg_ctx* c, const dg_layer_desc* d, uint64_t capacity_to
   kv->ctx = c;
   kv->cap = (capacity_tokens + 127) / 128 * 128;
   kv->ring_mask = ring_mask;
+  kv->pos_base = pos_base;
+  kv->shard = shard;
   kv->Hkv = d->n_kv_heads;
   kv->D = d->head_dim;
   const size_t bytes = size_t(kv->Hkv) * kv->cap * kv->D * 2;
@@ -466,6 +476,7 @@ static int32_t kv_create(dg_ctx* c, const dg_layer_desc* d, uint64_t capacity_to
   // rows in [T, cap) are read by whole-tile loads and masked afterwards: they must be finite
   if (e == cudaSuccess) e = cudaMemsetAsync(kv->k, 0, bytes, c->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(kv->v, 0, bytes, c->stream);
+  if (e == cudaSuccess) e = cudaMalloc(&kv->rope_table, 2 * size_t(kMaxCanvas) * (kv->D / 2) * sizeof(float2));
   if (e != cudaSuccess) {
     dg_kv_destroy(kv);
     return fail_cuda(e, "dg_kv_create");
@@ -500,7 +511,14 @@ extern "C" int32_t dg_kv_create_ring(dg_ctx* c, const dg_layer_desc* d, uint32_t
     return fail(DG_ERR_INVALID_ARG, "ring_slots must be a power of two, at least 256");
   return kv_create(c, d, ring_slots, ring_slots - 1u, out);
 }
+extern "C" int32_t dg_kv_create_shard(dg_ctx* c, const dg_layer_desc* d, uint64_t pos_base, uint64_t capacity_tokens,
+                                      dg_kv** out) {
+  if (pos_base % 128 != 0 || pos_base >= (1ull << 31))
+    return fail(DG_ERR_INVALID_ARG, "pos_base must be a multiple of 128 below 2^31");
+  return kv_create(c, d, capacity_tokens, 0u, out, uint32_t(pos_base), true);
+}
 extern "C" uint32_t dg_kv_ring_mask(const dg_kv* kv) { return kv ? kv->ring_mask : 0u; }
+extern "C" uint64_t dg_kv_pos_base(const dg_kv* kv) { return kv ? kv->pos_base : 0u; }
 
 extern "C" int32_t dg_kv_destroy(dg_kv* kv) {
   if (!kv) return DG_OK;
@@ -510,6 +528,7 @@ extern "C" int32_t dg_kv_destroy(dg_kv* kv) {
   }
   cudaFree(kv->k);
   cudaFree(kv->v);
+  cudaFree(kv->rope_table);
   delete kv;
   return DG_OK;
 }
@@ -524,7 +543,7 @@ struct SlotRuns {
 static SlotRuns slot_runs(const dg_kv* kv, uint64_t pos0, uint64_t n) {
   SlotRuns r;
   if (kv->ring_mask == 0) {
-    r.slot[0] = pos0;
+    r.slot[0] = pos0 - kv->pos_base;
     r.len[0] = n;
     return r;
   }
@@ -543,7 +562,8 @@ static SlotRuns slot_runs(const dg_kv* kv, uint64_t pos0, uint64_t n) {
 
 extern "C" int32_t dg_kv_load_prefix(dg_kv* kv, const void* k, const void* v, uint64_t pos0, uint64_t n) {
   if (!kv || !k || !v) return fail(DG_ERR_INVALID_ARG, "NULL argument");
-  if (kv->ring_mask == 0 && pos0 + n > kv->cap) return fail(DG_ERR_CAPACITY, "prefix does not fit the cache");
+  if (kv->ring_mask == 0 && (pos0 < kv->pos_base || pos0 + n > kv->pos_base + kv->cap))
+    return fail(DG_ERR_CAPACITY, "prefix does not fit the cache");
   if (n == 0) return DG_OK;
   DG_CUDA(cudaSetDevice(kv->ctx->device));
   const size_t row = size_t(kv->D) * 2, spitch = size_t(kv->Hkv) * row;
@@ -566,7 +586,7 @@ extern "C" int32_t dg_kv_load_prefix(dg_kv* kv, const void* k, const void* v, ui
 
 extern "C" int32_t dg_kv_read(dg_kv* kv, void* k_out, void* v_out, uint64_t pos0, uint64_t n) {
   if (!kv || !k_out || !v_out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
-  if (kv->ring_mask == 0 ? (pos0 + n > kv->cap) : (n > kv->cap))
+  if (kv->ring_mask == 0 ? (pos0 < kv->pos_base || pos0 + n > kv->pos_base + kv->cap) : (n > kv->cap))
     return fail(DG_ERR_CAPACITY, "range outside the cache");
   DG_CUDA(cudaSetDevice(kv->ctx->device));
   const size_t row = size_t(kv->D) * 2, dpitch = size_t(kv->Hkv) * row;
@@ -591,18 +611,32 @@ extern "C" int32_t dg_kv_read(dg_kv* kv, void* k_out, void* v_out, uint64_t pos0
 static int32_t check_kv(const dg_layer_desc& d, const dg_kv* kv, uint64_t end_pos) {
   if (!kv) return fail(DG_ERR_INVALID_ARG, "kv is NULL");
   if (kv->Hkv != d.n_kv_heads || kv->D != d.head_dim) return fail(DG_ERR_INVALID_ARG, "kv geometry differs from desc");
-  if (kv->ring_mask == 0 && end_pos > kv->cap) return fail(DG_ERR_CAPACITY, "kv_len + canvas exceeds the cache capacity");
+  // a shard holds part of the positions only: what a call may touch is checked against
+  // its visible key range (check_ring_span), and appends outside the shard are dropped
+  if (kv->ring_mask == 0 && !kv->shard && end_pos > kv->cap)
+    return fail(DG_ERR_CAPACITY, "kv_len + canvas exceeds the cache capacity");
   if (end_pos > (1ull << 31)) return fail(DG_ERR_CAPACITY, "position beyond 2^31");
   return DG_OK;
 }
-// A ring holds the last `cap` positions: every key an attention call can load (whole 128-key tiles
-// from the first visible position of canvas row 0 to the end of the canvas) must still be in it.
+// A ring holds the last `cap` positions, a shard the positions [pos_base, pos_base + cap): every key an
+// attention call can load (whole 128-key tiles from the first visible position of canvas row 0 to the
+// end of what it sees) must be in the cache.
 static int32_t check_ring_span(const dg_kv* kv, const MaskParams& mk, uint32_t canvas) {
-  if (kv->ring_mask == 0) return DG_OK;
-  const uint32_t lo = mask_row_lo(mk, 0) / 128u * 128u;
-  const uint64_t end = uint64_t(mk.kv_len) + canvas;
-  if (end - lo > kv->cap)
-    return fail(DG_ERR_CAPACITY, "the visible key range (window + canvas, tile aligned) exceeds the ring");
+  if (kv->ring_mask == 0 && !kv->shard) return DG_OK;
+  const uint32_t lo0 = mask_row_lo(mk, 0);
+  const uint32_t lo = lo0 / 128u * 128u;
+  if (kv->ring_mask != 0) {
+    const uint64_t end = uint64_t(mk.kv_len) + canvas;
+    if (end - lo > kv->cap)
+      return fail(DG_ERR_CAPACITY, "the visible key range (window + canvas, tile aligned) exceeds the ring");
+    return DG_OK;
+  }
+  const bool sees_prefix = mk.pre_hi > lo0, sees_canvas = mk.can_hi > mk.kv_len;
+  if (!sees_prefix && !sees_canvas) return DG_OK;
+  const uint64_t first = sees_prefix ? lo : mk.kv_len / 128u * 128u;
+  const uint64_t last = sees_canvas ? mk.can_hi : mk.pre_hi;   // one past the last visible key
+  if (first < kv->pos_base || (last + 127u) / 128u * 128u > uint64_t(kv->pos_base) + kv->cap)
+    return fail(DG_ERR_CAPACITY, "the visible key range (tile aligned) lies outside this shard of the cache");
   return DG_OK;
 }
 
@@ -638,6 +672,13 @@ static int32_t do_append(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint64_t 
   ap.eps = d.rms_eps;
   ap.ring_mask = kv->ring_mask ? kv->ring_mask : 0xffffffffu;
   ap.write_end = write_end;
+  ap.pos_base = kv->pos_base;
+  if (kv->shard) {
+    // positions outside the shard are not stored (a rank that does not own the canvas keys still
+    // runs the step with the replicated canvas K/V)
+    const uint64_t end = uint64_t(kv->pos_base) + kv->cap;
+    if (end < ap.write_end) ap.write_end = uint32_t(end);
+  }
   const RopeParams rp = make_rope(d);
   launch_append(ap, rp, launch_stream(c));
   DG_CUDA(cudaGetLastError());
@@ -682,7 +723,18 @@ struct AttnCall {
   int include_canvas = 1;
 };
 
-static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const AttnCall& a) {
+// A split workspace that the caller provides instead of the context's grown cudaMalloc buffers
+// (dg_attention_static_scratch): partial O, partial (m, l), arrival counters, with their capacities.
+struct FixedWs {
+  float* o = nullptr;
+  float* ml = nullptr;
+  uint32_t* counters = nullptr;
+  size_t o_floats = 0, ml_floats = 0;
+  uint32_t n_counters = 0;
+};
+
+static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const AttnCall& a,
+                            const FixedWs* fixed = nullptr) {
   AttnParams p;
   std::memset(&p, 0, sizeof(p));
   p.q = static_cast<const __nv_bfloat16*>(a.q);
@@ -701,6 +753,7 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
   p.cap = kv->cap;
   p.mask = make_mask(d, a.kv_len, a.t0, a.t1, a.include_canvas);
   p.ring_mask = kv->ring_mask ? kv->ring_mask : 0xffffffffu;
+  p.pos_base = kv->pos_base;
   {
     const int32_t rr = check_ring_span(kv, p.mask, d.canvas);
     if (rr != DG_OK) return rr;
@@ -729,10 +782,20 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
     // value columns split over two CTAs per (query tile, key split); splits meet in the workspace
     if (!a.q_prenormed) return fail(DG_ERR_UNSUPPORTED, "head_dim 512 tensor path needs a prenormed Q");
     const uint32_t q_tiles5 = sm100_query_tiles(p.C, p.G, p.Hkv);
-    if (q_tiles5 * 2 > kMaxQueryTiles) return fail(DG_ERR_UNSUPPORTED, "too many query tiles");
+    if (q_tiles5 * 2 > (fixed ? fixed->n_counters : kMaxQueryTiles)) return fail(DG_ERR_UNSUPPORTED, "too many query tiles");
     p.n_splits = choose_splits(c, q_tiles5 * 2, sm100_hd512_key_tiles(p.mask));
     p.cluster_splits = 1;
-    if (p.n_splits > 1) {
+    if (fixed) {
+      // as many splits as the fixed arrays hold: [splits][rows][512] partial O, [2 splits][rows] (m, l) pairs
+      const size_t rows5 = size_t(p.C) * p.Hq;
+      const size_t cap_o = fixed->o_floats / (rows5 * 512), cap_ml = fixed->ml_floats / (rows5 * 4);
+      const size_t cap = cap_o < cap_ml ? cap_o : cap_ml;
+      if (cap == 0) return fail(DG_ERR_UNSUPPORTED, "rows exceed the fixed workspace");
+      if (p.n_splits > cap) p.n_splits = uint32_t(cap);
+      p.ws_o = fixed->o;
+      p.ws_ml = fixed->ml;
+      p.ws_counters = fixed->counters;
+    } else if (p.n_splits > 1) {
       const int32_t r5 = ensure_split_ws(c, 2 * p.n_splits, p.C * p.Hq);
       if (r5 != DG_OK) return r5;
       p.ws_o = c->ws_o;
@@ -756,19 +819,30 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
   // more than the per-tile saving returns below about a hundred key tiles.
   const uint32_t tiles_per_head = sm100_query_tiles(p.C, p.G, 1);
   const uint32_t k_tiles = sm100_key_tiles(p.mask);
-  const bool pair = c->pair_mode == 1 || (c->pair_mode == 2 && tiles_per_head >= 2 && k_tiles >= 96);
+  const bool pair = !fixed && (c->pair_mode == 1 || (c->pair_mode == 2 && tiles_per_head >= 2 && k_tiles >= 96));
   const uint32_t q_tiles = pair ? sm100_pair_query_tiles(p.C, p.G, p.Hkv) : sm100_query_tiles(p.C, p.G, p.Hkv);
-  if (q_tiles > kMaxQueryTiles) return fail(DG_ERR_UNSUPPORTED, "too many query tiles");
+  if (q_tiles > (fixed ? fixed->n_counters : kMaxQueryTiles)) return fail(DG_ERR_UNSUPPORTED, "too many query tiles");
   p.n_splits = choose_splits(c, q_tiles * c->concurrent, k_tiles);
   // Split merge: consecutive splits of a query tile form a thread-block cluster and merge through
   // shared memory; what is left meets in the workspace.  Clusters stay at 4 CTAs in the pair form
   // (2 x 2): too few clusters of 8 are co-resident on the device.
   p.cluster_splits = 1;
-  if (p.n_splits % 2 == 0) {
+  if (fixed) {
+    // every split meets in the caller's arrays (single-CTA form, no cluster merge): as many splits
+    // as they hold, [splits][rows][256] partial O and [splits][rows] (m, l) pairs
+    const size_t rows = size_t(p.C) * p.Hq;
+    const size_t cap_o = fixed->o_floats / (rows * 256), cap_ml = fixed->ml_floats / (rows * 2);
+    const size_t cap = cap_o < cap_ml ? cap_o : cap_ml;
+    if (cap == 0) return fail(DG_ERR_UNSUPPORTED, "rows exceed the fixed workspace");
+    if (p.n_splits > cap) p.n_splits = uint32_t(cap);
+    p.ws_o = fixed->o;
+    p.ws_ml = fixed->ml;
+    p.ws_counters = fixed->counters;
+  } else if (p.n_splits % 2 == 0) {
     if (pair) p.cluster_splits = 2;
     else if (p.n_splits == 2 || p.n_splits == 4 || p.n_splits == 8) p.cluster_splits = p.n_splits;
   }
-  if (p.n_splits / p.cluster_splits > 1) {
+  if (!fixed && p.n_splits / p.cluster_splits > 1) {
     const int32_t r = ensure_split_ws(c, p.n_splits, p.C * p.Hq);
     if (r != DG_OK) return r;
     p.ws_o = c->ws_o;
@@ -800,7 +874,10 @@ static int32_t denoise_one(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint32_
                            AttnCall a) {
   int32_t r = check_kv(d, kv, uint64_t(kv_len) + d.canvas);
   if (r != DG_OK) return r;
-  float2* table = c->rope_table + size_t(slot % kRopeSlots) * kMaxCanvas * kMaxRotHalf;
+  // everything that can refuse the call is checked before the first launch, so that a refused call
+  // leaves nothing queued (a split-KV group then stays in step with its peers)
+  r = check_ring_span(kv, make_mask(d, kv_len, a.t0, a.t1, a.include_canvas), d.canvas);
+  if (r != DG_OK) return r;
   const bool tensor = tensor_path_ok(d) && kv->has_tmap && !c->force_general && attend == nullptr;
   if (tensor && !fused_q_prologue_ok(d)) {
     // partial / proportional rotary: run the stand-alone Q prologue into the staging buffer
@@ -811,13 +888,19 @@ static int32_t denoise_one(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint32_
     a.q = c->stage_q;
     a.q_prenormed = true;
   } else {
-    dg_ctx::RopeKey& key = c->rope_key[slot % kRopeSlots];
+    RopeKey& key = kv->rope_key;
     const bool cached = key.valid && key.kv_len == kv_len && key.canvas == d.canvas && key.rotary_dim == d.rotary_dim &&
                         key.pairing == d.rope_pairing && key.head_dim == d.head_dim && key.theta == d.rope_theta;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    DG_CUDA(cudaStreamIsCapturing(launch_stream(c), &cap));
+    const bool capturing = cap != cudaStreamCaptureStatusNone;
+    // eager: region 0, rewritten when the key changes.  captured: region 0 read-only when it already
+    // holds these positions, else region 1, written and read by the recorded launches themselves.
+    float2* table = kv->rope_table + ((capturing && !cached) ? size_t(kMaxCanvas) * (kv->D / 2) : 0);
     r = do_append(c, d, kv, kv_len, d.canvas, nullptr, nullptr, k, nullptr, v, nullptr, nullptr, kw, cached ? nullptr : table,
                   0xffffffffu, cached ? table : nullptr);
     if (r != DG_OK) return r;
-    if (!cached) {
+    if (!cached && !capturing) {
       key.valid = true;
       key.kv_len = kv_len;
       key.canvas = d.canvas;
@@ -1092,6 +1175,58 @@ extern "C" int32_t dg_host_pipe_submit(dg_host_pipe* hp, const dg_layer_desc* d,
   return DG_OK;
 }
 
+// One split-KV step through the pipe: like dg_host_pipe_submit for one canvas, with the kernels of
+// dg_attn_denoise_split_p2p.  A rank that does not count the canvas keys and whose cache is a shard
+// never stores the canvas K/V, so their host-to-device copies are left out; in the push form of the
+// exchange only this rank's row slice of the output is copied back.
+struct dg_p2p;
+static bool p2p_is_push(const dg_p2p* x);
+static void p2p_slice_bytes(const dg_p2p* x, size_t* off, size_t* bytes);
+extern "C" int32_t dg_attn_denoise_split_p2p(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint32_t kv_len, uint32_t t0,
+                                             uint32_t t1, int32_t include_canvas, dg_p2p* x, const void* q, const void* k,
+                                             const void* v, const void* qw, const void* kw, void* out);
+extern "C" int32_t dg_host_pipe_submit_split(dg_host_pipe* hp, const dg_layer_desc* d, dg_kv* kv, uint32_t kv_len,
+                                             uint32_t t0, uint32_t t1, int32_t include_canvas, dg_p2p* x, const void* q,
+                                             const void* k, const void* v, const void* qw, const void* kw, void* out,
+                                             uint64_t* ticket) {
+  if (!hp || !kv || !x || !q || !k || !v || !out || !ticket) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  int32_t r = check_desc(d);
+  if (r != DG_OK) return r;
+  dg_ctx* c = hp->ctx;
+  const size_t qe = size_t(d->canvas) * d->n_q_heads * d->head_dim;
+  const size_t ke = size_t(d->canvas) * d->n_kv_heads * d->head_dim;
+  if (qe > hp->q_elems || ke > hp->kv_elems) return fail(DG_ERR_CAPACITY, "geometry larger than the pipe was created for");
+  DG_CUDA(cudaSetDevice(c->device));
+  dg_host_pipe::Slot& sl = hp->slot[hp->next % hp->depth];
+  if (sl.pending) {
+    DG_CUDA(cudaEventSynchronize(sl.out));
+    sl.pending = false;
+  }
+  if (sl.used) DG_CUDA(cudaStreamWaitEvent(hp->h2d, sl.cmp, 0));
+  DG_CUDA(cudaMemcpyAsync(sl.q, q, qe * 2, cudaMemcpyHostToDevice, hp->h2d));
+  const bool stores_canvas = include_canvas != 0 || !kv->shard;
+  if (stores_canvas) {
+    DG_CUDA(cudaMemcpyAsync(sl.k, k, ke * 2, cudaMemcpyHostToDevice, hp->h2d));
+    DG_CUDA(cudaMemcpyAsync(sl.v, v, ke * 2, cudaMemcpyHostToDevice, hp->h2d));
+  }
+  DG_CUDA(cudaEventRecord(sl.in, hp->h2d));
+  DG_CUDA(cudaStreamWaitEvent(c->stream, sl.in, 0));
+  if (sl.used) DG_CUDA(cudaStreamWaitEvent(c->stream, sl.out, 0));
+  r = dg_attn_denoise_split_p2p(c, d, kv, kv_len, t0, t1, include_canvas, x, sl.q, sl.k, sl.v, qw, kw, sl.o);
+  if (r != DG_OK) return r;
+  DG_CUDA(cudaEventRecord(sl.cmp, c->stream));
+  DG_CUDA(cudaStreamWaitEvent(hp->d2h, sl.cmp, 0));
+  size_t off = 0, bytes = qe * 2;
+  if (p2p_is_push(x)) p2p_slice_bytes(x, &off, &bytes);
+  DG_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(out) + off, reinterpret_cast<uint8_t*>(sl.o) + off, bytes,
+                          cudaMemcpyDeviceToHost, hp->d2h));
+  DG_CUDA(cudaEventRecord(sl.out, hp->d2h));
+  sl.used = true;
+  sl.pending = true;
+  *ticket = hp->next++;
+  return DG_OK;
+}
+
 extern "C" int32_t dg_attn_denoise_bitmap(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint32_t kv_len, const void* q,
                                           const void* k, const void* v, const void* qw, const void* kw,
                                           const uint8_t* attend, void* out) {
@@ -1324,63 +1459,40 @@ extern "C" int32_t dg_attention_static_scratch(dg_ctx* c, const dg_layer_desc* d
   if (r != DG_OK) return r;
   DG_CUDA(cudaSetDevice(c->device));
   c->last_launches = 0;
-
-  AttnParams p;
-  std::memset(&p, 0, sizeof(p));
-  p.q = static_cast<const __nv_bfloat16*>(q);
-  p.cache_k = kv->k;
-  p.cache_v = kv->v;
-  p.out = static_cast<__nv_bfloat16*>(out);
-  p.status = c->d_status;
-  p.cap = kv->cap;
-  p.mask = make_mask(*d, kv_len, 0, 0xffffffffu, 1);
-  p.C = d->canvas;
-  p.Hq = d->n_q_heads;
-  p.Hkv = d->n_kv_heads;
-  p.G = d->n_q_heads / d->n_kv_heads;
-  p.D = d->head_dim;
-  p.q_prenormed = 1u;
-  p.ring_mask = kv->ring_mask ? kv->ring_mask : 0xffffffffu;
-  p.n_splits = 1;
-  p.rot_half = d->rotary_dim / 2;
-  p.pair_off = d->rope_pairing == DG_ROPE_SPLIT_HALF ? d->rotary_dim / 2 : d->head_dim / 2;
-  p.scale_log2 = d->softmax_scale * 1.4426950408889634f;
-  p.eps = d->rms_eps;
-
-  if (!(d->head_dim == 256 && tensor_path_ok(*d) && kv->has_tmap)) {
-    // the general kernel keeps all of its state in registers and shared memory: nothing to provide
-    launch_attn_general(p, c->stream);
-    DG_CUDA(cudaGetLastError());
-    c->last_launches = 1;
-    return DG_OK;
-  }
-  const uint32_t rows = p.C * p.Hq;
-  const uint32_t q_tiles = sm100_query_tiles(p.C, p.G, p.Hkv);
-  if (rows > kStaticRows || q_tiles > kStaticTiles) {
+  AttnCall a;
+  a.q = q;
+  a.q_prenormed = true;
+  a.out = out;
+  a.kv_len = kv_len;
+  const bool tensor = tensor_path_ok(*d) && kv->has_tmap && !c->force_general;
+  // the general kernel keeps all of its state in registers and shared memory: nothing to provide
+  if (!tensor) return do_attention(c, *d, kv, a);
+  const uint32_t rows = d->canvas * d->n_q_heads;
+  const uint32_t q_tiles = sm100_query_tiles(d->canvas, d->n_q_heads / d->n_kv_heads, d->n_kv_heads) *
+                           (d->head_dim == 512 ? 2u : 1u);
+  const uint32_t row_limit = kStaticRows;
+  if (rows > row_limit || q_tiles > kStaticTiles) {
     g_last_error = "dg_attention_static_scratch: canvas * n_q_heads = " + std::to_string(rows) + " rows (" +
                    std::to_string(q_tiles) + " query tiles) exceeds the built-in scratch of " +
-                   std::to_string(kStaticRows) + " rows / " + std::to_string(kStaticTiles) +
+                   std::to_string(row_limit) + " rows / " + std::to_string(kStaticTiles) +
                    " tiles; use dg_attention, which allocates its workspace";
     return DG_ERR_UNSUPPORTED;
   }
   float* scratch = nullptr;
   r = static_scratch_for_device(c->device, &scratch);
   if (r != DG_OK) return r;
-  uint32_t splits = choose_splits(c, q_tiles, sm100_key_tiles(p.mask));
-  if (splits > kStaticSplits) splits = kStaticSplits;
-  p.n_splits = splits;
-  p.cluster_splits = 1;   // every split meets in the scratch array
-  p.ws_o = scratch;
-  p.ws_ml = scratch + kStaticOFloats;
-  p.ws_counters = reinterpret_cast<uint32_t*>(scratch + kStaticOFloats + kStaticMlFloats);
+  FixedWs ws;
+  ws.o = scratch;
+  ws.o_floats = kStaticOFloats;
+  ws.ml = scratch + kStaticOFloats;
+  ws.ml_floats = kStaticMlFloats;
+  ws.counters = reinterpret_cast<uint32_t*>(scratch + kStaticOFloats + kStaticMlFloats);
+  ws.n_counters = kStaticTiles;
   // The array keeps whatever the previous call left.  Partials are fully rewritten before they are
   // read, but the per-tile arrival counters must start at zero (a call that was cut short could have
   // left them half-counted), so they are cleared on the stream ahead of the launch.
-  DG_CUDA(cudaMemsetAsync(p.ws_counters, 0, kStaticTiles * sizeof(uint32_t), c->stream));
-  const cudaError_t e = launch_attn_sm100(p, kv->tm_k, kv->tm_v, c->stream);
-  if (e != cudaSuccess) return fail_cuda(e, "launch_attn_sm100");
-  c->last_launches = 1;
-  return DG_OK;
+  DG_CUDA(cudaMemsetAsync(ws.counters, 0, kStaticTiles * sizeof(uint32_t), launch_stream(c)));
+  return do_attention(c, *d, kv, a, &ws);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1395,9 +1507,18 @@ struct dg_p2p {
   bool opened[8] = {};
   bool connected = false;
   uint32_t step = 0;
-  int32_t mode = 0;          // 0 automatic (all rows with two ranks, slices otherwise), 1 slices, 2 all rows
+  uint32_t push_uses[2] = {0, 0};   // push form: steps that have used each parity since the last reset
+  int32_t mode = 0;          // 0 automatic (all rows with two ranks, slices otherwise), 1 slices, 2 all rows, 3 push
+  bool poisoned = false;     // a launch failed half-way through a step: the ranks may disagree until dg_p2p_reset
   P2pParams layout;
 };
+
+static bool p2p_is_push(const dg_p2p* x) { return x->mode == 3; }
+static void p2p_slice_bytes(const dg_p2p* x, size_t* off, size_t* bytes) {
+  const size_t r0 = (size_t(x->rank) * x->rows) / x->world, r1 = (size_t(x->rank + 1) * x->rows) / x->world;
+  *off = r0 * x->D * 2;
+  *bytes = (r1 - r0) * x->D * 2;
+}
 
 static void p2p_layout(dg_p2p* x) {
   P2pParams& L = x->layout;
@@ -1410,9 +1531,15 @@ static void p2p_layout(dg_p2p* x) {
     L.off_l[p] = take(size_t(x->rows) * 4);
     L.off_res[p] = take(size_t(x->rows) * x->D * 2);
   }
+  L.slice_cap = (x->rows + x->world - 1) / x->world;
+  for (int p = 0; p < 2; ++p) {
+    L.off_recv[p] = take(size_t(x->world) * L.slice_cap * x->D * 2);
+    L.off_rml[p] = take(size_t(x->world) * L.slice_cap * 16);
+  }
   L.off_pflag = take(2 * 8 * 4);
   L.off_rflag = take(2 * 8 * 4);
   L.off_done = take(2 * 4);
+  L.off_cnt = take(2 * 4);
   x->bytes = off;
   L.world = x->world;
   L.rank = x->rank;
@@ -1449,8 +1576,39 @@ extern "C" int32_t dg_p2p_create(dg_ctx* c, uint32_t rows, uint32_t head_dim, in
 
 extern "C" int32_t dg_p2p_set_mode(dg_p2p* x, int32_t mode) {
   if (!x) return fail(DG_ERR_INVALID_ARG, "NULL argument");
-  if (mode < 0 || mode > 2) return fail(DG_ERR_INVALID_ARG, "mode must be 0 (automatic), 1 (row slices) or 2 (all rows)");
+  if (mode < 0 || mode > 3)
+    return fail(DG_ERR_INVALID_ARG, "mode must be 0 (automatic), 1 (row slices), 2 (all rows) or 3 (push, row slice only)");
   x->mode = mode;
+  return DG_OK;
+}
+
+extern "C" int32_t dg_p2p_set_wait_limit(dg_p2p* x, uint64_t limit_cycles) {
+  if (!x) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  if (limit_cycles == 0 || limit_cycles > 20000000000ull) return fail(DG_ERR_INVALID_ARG, "limit must be in 1..2e10 cycles");
+  x->layout.wait_limit = (long long)limit_cycles;
+  return DG_OK;
+}
+
+extern "C" int32_t dg_p2p_slice(const dg_p2p* x, uint32_t* row0, uint32_t* n_rows) {
+  if (!x || !row0 || !n_rows) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  const uint32_t r0 = uint32_t((uint64_t(x->rank) * x->rows) / x->world);
+  const uint32_t r1 = uint32_t((uint64_t(x->rank + 1) * x->rows) / x->world);
+  *row0 = r0;
+  *n_rows = r1 - r0;
+  return DG_OK;
+}
+
+extern "C" int32_t dg_p2p_reset(dg_p2p* x) {
+  if (!x) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  DG_CUDA(cudaSetDevice(x->ctx->device));
+  DG_CUDA(cudaStreamSynchronize(x->ctx->stream));
+  // flags, counters and the step number start again; the caller holds every rank at a host barrier
+  // before this call (no peer kernel may still be writing here) and after it
+  const P2pParams& L = x->layout;
+  DG_CUDA(cudaMemset(x->local + L.off_pflag, 0, x->bytes - L.off_pflag));
+  x->step = 0;
+  x->push_uses[0] = x->push_uses[1] = 0;
+  x->poisoned = false;
   return DG_OK;
 }
 
@@ -1496,7 +1654,9 @@ extern "C" int32_t dg_attn_denoise_split_p2p(dg_ctx* c, const dg_layer_desc* d, 
                                              uint32_t t1, int32_t include_canvas, dg_p2p* x, const void* q, const void* k,
                                              const void* v, const void* qw, const void* kw, void* out) {
   if (!c || !x || !q || !k || !v || !out) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  if (x->ctx != c) return fail(DG_ERR_INVALID_ARG, "the exchange buffer belongs to another context");
   if (!x->connected && x->world > 1) return fail(DG_ERR_INVALID_ARG, "dg_p2p_connect has not been called");
+  if (x->poisoned) return fail(DG_ERR_INVALID_ARG, "an earlier step failed after its first launch: call dg_p2p_reset on every rank");
   int32_t r = check_desc(d);
   if (r != DG_OK) return r;
   if (x->rows != d->canvas * d->n_q_heads || x->D != d->head_dim) return fail(DG_ERR_INVALID_ARG, "exchange buffer geometry differs from desc");
@@ -1504,8 +1664,11 @@ extern "C" int32_t dg_attn_denoise_split_p2p(dg_ctx* c, const dg_layer_desc* d, 
   if (r != DG_OK) return r;
   DG_CUDA(cudaSetDevice(c->device));
   c->last_launches = 0;
-  x->step += 1;
-  const uint32_t par = x->step & 1u;
+  // The step number and the buffer parity advance only once every launch of the step has been
+  // queued: a call that fails its checks (capacity, ring span, ...) leaves this rank in step with
+  // its peers, and the caller may simply repeat it.
+  const uint32_t step = x->step + 1u;
+  const uint32_t par = step & 1u;
   if (x->world == 1) x->layout.peer[0] = x->local;
   AttnCall a;
   a.out = nullptr;
@@ -1516,13 +1679,31 @@ extern "C" int32_t dg_attn_denoise_split_p2p(dg_ctx* c, const dg_layer_desc* d, 
   a.t1 = t1;
   a.include_canvas = include_canvas ? 1 : 0;
   r = denoise_one(c, *d, kv, kv_len, 0, q, k, v, qw, kw, nullptr, a);
-  if (r != DG_OK) return r;
+  if (r != DG_OK) {
+    if (c->last_launches != 0) x->poisoned = true;   // part of the step is already queued
+    return r;
+  }
   P2pParams pp = x->layout;
-  pp.step = x->step;
+  pp.step = step;
   pp.parity = par;
-  pp.all_rows = (x->mode == 2 || (x->mode == 0 && x->world == 2)) ? 1u : 0u;
-  launch_p2p_merge(pp, out, c->num_sms, c->stream);
-  DG_CUDA(cudaGetLastError());
+  if (x->mode == 3) {
+    pp.uses = x->push_uses[par] + 1u;
+    const cudaError_t e = launch_p2p_push_merge(pp, out, c->num_sms, c->stream);
+    if (e != cudaSuccess) {
+      x->poisoned = true;
+      return fail_cuda(e, "launch_p2p_push_merge");
+    }
+    x->push_uses[par] += 1u;
+  } else {
+    pp.all_rows = (x->mode == 2 || (x->mode == 0 && x->world == 2)) ? 1u : 0u;
+    launch_p2p_merge(pp, out, c->num_sms, c->stream);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+      x->poisoned = true;
+      return fail_cuda(e, "launch_p2p_merge");
+    }
+  }
+  x->step = step;
   c->last_launches += 1;
   return DG_OK;
 }

@@ -410,7 +410,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
           const uint32_t full = lead_bar(B_K_FULL + st);
 #pragma unroll
           for (uint32_t a = 0; a < 4; ++a)
-            tma_load_3d_pair(sK + st * K_STAGE + a * K_ATOM, &tm_k, full, int32_t(a * 64), int32_t((jt * BN + xi * 64) & p.ring_mask),
+            tma_load_3d_pair(sK + st * K_STAGE + a * K_ATOM, &tm_k, full, int32_t(a * 64), int32_t((jt * BN + xi * 64 - p.pos_base) & p.ring_mask),
                              int32_t(kvh));
         } else {
           if (n > 0 && !wait_bar(B_S_FULL + ((n - 1) & 1u), ((n - 1) >> 1) & 1u, abort_flag)) break;   // QK(n - 1) complete
@@ -418,7 +418,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
           mbar_expect_tx(full, TILE_BYTES);
 #pragma unroll
           for (uint32_t a = 0; a < 4; ++a)
-            tma_load_3d(sK + a * ATOM_BYTES, &tm_k, full, int32_t(a * 64), int32_t((jt * BN) & p.ring_mask), int32_t(kvh));
+            tma_load_3d(sK + a * ATOM_BYTES, &tm_k, full, int32_t(a * 64), int32_t((jt * BN - p.pos_base) & p.ring_mask), int32_t(kvh));
         }
       }
     }
@@ -437,14 +437,14 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
 #pragma unroll
           for (uint32_t a = 0; a < 2; ++a)
             tma_load_3d_pair(sV + st * V_STAGE + a * ATOM_BYTES, &tm_v, full, int32_t(xi * 128 + a * 64),
-                             int32_t((jt * BN) & p.ring_mask), int32_t(kvh));
+                             int32_t((jt * BN - p.pos_base) & p.ring_mask), int32_t(kvh));
         } else {
           if (n > 0 && !wait_bar(B_V_EMPTY + ((n - 1) & 1u), ((n - 1) >> 1) & 1u, abort_flag)) break;   // PV(n - 1) complete
           const uint32_t full = bar_addr(bar_base, B_V_FULL);
           mbar_expect_tx(full, TILE_BYTES);
 #pragma unroll
           for (uint32_t a = 0; a < 4; ++a)
-            tma_load_3d(sV + a * ATOM_BYTES, &tm_v, full, int32_t(a * 64), int32_t((jt * BN) & p.ring_mask), int32_t(kvh));
+            tma_load_3d(sV + a * ATOM_BYTES, &tm_v, full, int32_t(a * 64), int32_t((jt * BN - p.pos_base) & p.ring_mask), int32_t(kvh));
         }
       }
     }

@@ -279,7 +279,7 @@ dg_attn_sm100_hd512_kernel(const AttnParams p, const __grid_constant__ CUtensorM
         mbar_expect_tx(full, K_STAGE);
 #pragma unroll
         for (uint32_t a = 0; a < 8; ++a)
-          tma_load_3d(sK + st * K_STAGE + a * KV_ATOM, &tm_k, full, int32_t(a * 64), int32_t((jt * TN) & p.ring_mask),
+          tma_load_3d(sK + st * K_STAGE + a * KV_ATOM, &tm_k, full, int32_t(a * 64), int32_t((jt * TN - p.pos_base) & p.ring_mask),
                       int32_t(kvh));
       }
     }
@@ -294,7 +294,7 @@ dg_attn_sm100_hd512_kernel(const AttnParams p, const __grid_constant__ CUtensorM
         mbar_expect_tx(full, 4 * KV_ATOM);
 #pragma unroll
         for (uint32_t a = 0; a < 4; ++a)
-          tma_load_3d(sV + a * KV_ATOM, &tm_v, full, int32_t(dh * HDV + a * 64), int32_t((jt * TN) & p.ring_mask),
+          tma_load_3d(sV + a * KV_ATOM, &tm_v, full, int32_t(dh * HDV + a * 64), int32_t((jt * TN - p.pos_base) & p.ring_mask),
                       int32_t(kvh));
       }
     }

@@ -139,8 +139,9 @@ struct AppendParams {
   uint32_t Hq, Hkv, D;
   uint32_t v_norm;
   float eps;
-  uint32_t ring_mask;          // cache slot of position pos = pos & ring_mask (0xffffffff: linear cache)
+  uint32_t ring_mask;          // cache slot of position pos = (pos - pos_base) & ring_mask (0xffffffff: linear cache)
   uint32_t write_end;          // positions >= write_end are not written to the cache (0xffffffff: none)
+  uint32_t pos_base;           // first position the cache holds (a shard of a long prefix; 0 otherwise)
 };
 
 // attention kernels (general and sm100)
@@ -164,7 +165,8 @@ struct AttnParams {
   MaskParams mask;
   uint32_t C, Hq, Hkv, G, D;
   uint32_t q_prenormed;
-  uint32_t ring_mask;            // cache slot of key position t = t & ring_mask (0xffffffff: linear cache)
+  uint32_t ring_mask;            // cache slot of key position t = (t - pos_base) & ring_mask (0xffffffff: linear cache)
+  uint32_t pos_base;             // first position the cache holds (multiple of 128; 0 unless the cache is a shard)
   uint32_t early_q;              // 1: nothing the Q prologue reads is written by the preceding kernel on the stream
   uint32_t n_splits;
   uint32_t cluster_splits;       // consecutive splits per thread-block cluster (divides n_splits; 1 = no cluster merge)
@@ -178,10 +180,15 @@ struct P2pParams {
   uint8_t* peer[8];        // exchange buffer of every rank, as mapped into this process
   size_t off_o[2], off_m[2], off_l[2], off_res[2];   // per parity
   size_t off_pflag, off_rflag, off_done;             // u32 pflag[2][8], rflag[2][8], done[2]
+  // push form: per parity a receive area [world][slice_cap][D] fp16 rows, their [world][slice_cap]
+  // (m, l, 1 / scale, -) records, and one arrival counter (rows received since the last reset)
+  size_t off_recv[2], off_rml[2], off_cnt;
   DevStatus* status;
   long long wait_limit;    // cycles
   uint32_t world, rank, rows, D, step, parity;
   uint32_t all_rows;       // 1: every rank merges every row itself (no result scatter, no second flag round)
+  uint32_t slice_cap;      // rows of the largest row slice: ceil(rows / world)
+  uint32_t uses;           // push form: how many steps have used this parity, this one included
 };
 
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(uint32_t(b) << 16); }

@@ -17,6 +17,9 @@ void launch_merge_finalize(uint32_t rows, uint32_t D, const float* pay, __nv_bfl
 void launch_visibility(const MaskParams& mk, uint32_t C, uint8_t* out, cudaStream_t st);
 void launch_fill_f32(float* p, float v, size_t n, cudaStream_t st);
 void launch_p2p_merge(const P2pParams& q, void* out, int num_sms, cudaStream_t st);
+// push form: every rank sends each row of its partial to the rank that owns the row, the owner merges;
+// `out` receives this rank's row slice only (rows [rank * rows / world, (rank + 1) * rows / world))
+cudaError_t launch_p2p_push_merge(const P2pParams& q, void* out, int num_sms, cudaStream_t st);
 void launch_selftest_wait(uint32_t* flag, long long limit_cycles, DevStatus* status, cudaStream_t st);
 
 // Tensor-core kernel (head_dim 256).  tm_k / tm_v: 3-D tensor maps {D, cap, Hkv}, box {64, 128, 1},

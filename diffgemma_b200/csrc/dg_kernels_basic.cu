@@ -61,9 +61,9 @@ __global__ void __launch_bounds__(32) dg_append_kernel(const AppendParams p, con
   if (wb) wb += (size_t(tok) * H + h) * D;
   // ring caches keep position pos in slot pos & ring_mask; positions at or past write_end (the
   // zero-padded tail of a prefill chunk) must not reach the cache, where they would wrap onto live slots
-  __nv_bfloat16* cache = (is_q || pos >= p.write_end)
+  __nv_bfloat16* cache = (is_q || pos >= p.write_end || pos < p.pos_base)
                              ? nullptr
-                             : (is_k ? p.cache_k : p.cache_v) + (size_t(h) * p.cap + (pos & p.ring_mask)) * D;
+                             : (is_k ? p.cache_k : p.cache_v) + (size_t(h) * p.cap + ((pos - p.pos_base) & p.ring_mask)) * D;
 
   // sum of squares in the order of dg_append_table_kernel (a lane takes 8 consecutive elements, then a
   // butterfly), and the rotation through rope_rotate in both, so that the two kernels write the same bits
@@ -119,7 +119,8 @@ __global__ void __launch_bounds__(256) dg_append_table_kernel(const AppendParams
   const bool is_k = slot < p.Hkv;
   const uint32_t h = is_k ? slot : slot - p.Hkv;
   const uint32_t pos = p.pos0 + tok;
-  if (pos >= p.write_end) return;   // zero-padded tail of a chunk: must not wrap onto live ring slots
+  // zero-padded tail of a chunk: must not wrap onto live ring slots; positions below a shard's base have no slot
+  if (pos >= p.write_end || pos < p.pos_base) return;
   const uint4 x = reinterpret_cast<const uint4*>((is_k ? p.k_in : p.v_in) + (size_t(tok) * p.Hkv + h) * 256u)[lane];
   uint4 y = x;
   if (is_k || p.v_norm) {
@@ -168,7 +169,7 @@ __global__ void __launch_bounds__(256) dg_append_table_kernel(const AppendParams
     y = make_uint4(*reinterpret_cast<uint32_t*>(&b[0]), *reinterpret_cast<uint32_t*>(&b[1]),
                    *reinterpret_cast<uint32_t*>(&b[2]), *reinterpret_cast<uint32_t*>(&b[3]));
   }
-  __nv_bfloat16* cache = (is_k ? p.cache_k : p.cache_v) + (size_t(h) * p.cap + (pos & p.ring_mask)) * 256u;
+  __nv_bfloat16* cache = (is_k ? p.cache_k : p.cache_v) + (size_t(h) * p.cap + ((pos - p.pos_base) & p.ring_mask)) * 256u;
   reinterpret_cast<uint4*>(cache)[lane] = y;
 }
 
@@ -264,7 +265,7 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) dg_attn_general_kernel(const A
       if (p.attend) {
         if (!p.attend[size_t(row) * T + t]) continue;
       }
-      const uint32_t ts = t & p.ring_mask;   // cache slot of key position t
+      const uint32_t ts = (t - p.pos_base) & p.ring_mask;   // cache slot of key position t
       const uint4* kr = reinterpret_cast<const uint4*>(kbase + size_t(ts) * D);
       float dot = 0.f;
 #pragma unroll

@@ -14,6 +14,8 @@
 //
 // All waits are bounded: a flag that does not arrive within the limit records DG_DEV_WAIT_TIMEOUT
 // and the kernel carries on without it.
+#include <cuda_fp16.h>
+
 #include "dg_common.cuh"
 #include "dg_kernels.h"
 
@@ -175,6 +177,170 @@ __global__ void __launch_bounds__(256) dg_p2p_merge_kernel(const P2pParams q, ui
   const uint4* src = reinterpret_cast<const uint4*>(mine + q.off_res[par]);
   const size_t n = size_t(q.rows) * q.D / 8;   // 16-byte units
   for (size_t i = size_t(blockIdx.x) * 256 + tid; i < n; i += size_t(gridDim.x) * 256) out[i] = src[i];
+}
+
+// ------------------------------------------------------------------------------------------
+// Push form (reduce-scatter): rank r owns the row slice [r * rows / W, (r + 1) * rows / W) of the
+// output.  Phase A: every rank converts each row of its local fp32 partial to fp16 with one
+// power-of-two scale per row (the row's largest magnitude lands in [2^14, 2^15): 11 significant bits
+// relative to it, half the bytes) and STORES it, with its (m, l, 1 / scale) record, into the receive
+// area of the rank that owns the row - posted writes over NVLink, nobody waits for a load to come
+// back - then adds the number of rows it delivered to that owner's arrival counter (system-scope
+// release after a system fence).  Phase B: the owner polls its own counter in LOCAL memory until all
+// W x slice rows of this step have arrived, merges the W partial rows from local memory and writes
+// the finished bf16 rows of its slice to `out`.  Nothing is scattered back and there is no second
+// flag round: a host that needs every row on every rank gathers the slices afterwards.
+// The counters only grow (the host passes how many steps have used this parity), so no kernel ever
+// resets a word that a peer may still be adding to.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(256) dg_p2p_push_merge_kernel(const P2pParams q, __nv_bfloat16* __restrict__ out) {
+  __shared__ uint32_t s_ok, s_rows;
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t par = q.parity, W = q.world, D = q.D;
+  uint8_t* mine = q.peer[q.rank];
+  if (tid == 0) {
+    s_ok = 1u;
+    s_rows = 0u;
+  }
+  // the partial was written by the attention kernel that precedes this one on the stream
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  __syncthreads();
+
+  // ---- phase A: this CTA serves ONE owner, so that it signals exactly one counter, once
+  {
+    const uint32_t o = blockIdx.x % W, j = blockIdx.x / W;
+    const uint32_t n_o = (gridDim.x - o + W - 1u) / W;   // CTAs that serve owner o
+    const uint32_t r0 = uint32_t((uint64_t(o) * q.rows) / W), r1 = uint32_t((uint64_t(o + 1) * q.rows) / W);
+    const float* src_o = reinterpret_cast<const float*>(mine + q.off_o[par]);
+    const float* src_m = reinterpret_cast<const float*>(mine + q.off_m[par]);
+    const float* src_l = reinterpret_cast<const float*>(mine + q.off_l[par]);
+    __half* dst_rows = reinterpret_cast<__half*>(q.peer[o] + q.off_recv[par]) + size_t(q.rank) * q.slice_cap * D;
+    float4* dst_ml = reinterpret_cast<float4*>(q.peer[o] + q.off_rml[par]) + size_t(q.rank) * q.slice_cap;
+    uint32_t done = 0;
+    for (uint32_t row = r0 + j * 8u + warp; row < r1; row += n_o * 8u) {
+      float4 a[2][2];
+      float amax = 0.f;
+#pragma unroll
+      for (uint32_t c = 0; c < 2; ++c) {
+        a[c][0] = a[c][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c * 256u < D) {
+          const float4* s4 = reinterpret_cast<const float4*>(src_o + size_t(row) * D + c * 256u + lane * 8u);
+          a[c][0] = s4[0];
+          a[c][1] = s4[1];
+        }
+#pragma unroll
+        for (uint32_t h = 0; h < 2; ++h)
+          amax = fmaxf(fmaxf(amax, fmaxf(fabsf(a[c][h].x), fabsf(a[c][h].y))), fmaxf(fabsf(a[c][h].z), fabsf(a[c][h].w)));
+      }
+#pragma unroll
+      for (int sft = 16; sft > 0; sft >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sft));
+      // biased exponent of the row maximum; tiny, zero, infinite or NaN maxima travel unscaled
+      const uint32_t eb = (__float_as_uint(amax) >> 23) & 0xffu;
+      const bool scaled = eb >= 15u && eb < 255u;
+      const float sc = scaled ? __uint_as_float((268u - eb) << 23) : 1.0f;       // 2^(14 - exponent)
+      const float inv_sc = scaled ? __uint_as_float((eb - 14u) << 23) : 1.0f;
+#pragma unroll
+      for (uint32_t c = 0; c < 2; ++c) {
+        if (c * 256u >= D) break;
+        __half2 h0 = __floats2half2_rn(a[c][0].x * sc, a[c][0].y * sc), h1 = __floats2half2_rn(a[c][0].z * sc, a[c][0].w * sc);
+        __half2 h2 = __floats2half2_rn(a[c][1].x * sc, a[c][1].y * sc), h3 = __floats2half2_rn(a[c][1].z * sc, a[c][1].w * sc);
+        uint4 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&h0);
+        pk.y = *reinterpret_cast<uint32_t*>(&h1);
+        pk.z = *reinterpret_cast<uint32_t*>(&h2);
+        pk.w = *reinterpret_cast<uint32_t*>(&h3);
+        *reinterpret_cast<uint4*>(dst_rows + size_t(row - r0) * D + c * 256u + lane * 8u) = pk;
+      }
+      if (lane == 0) dst_ml[row - r0] = make_float4(src_m[row], src_l[row], inv_sc, 0.f);
+      ++done;
+    }
+    if (lane == 0 && done) atomicAdd(&s_rows, done);
+    __syncthreads();
+    if (tid == 0 && s_rows) {
+      __threadfence_system();   // after the CTA barrier: covers the stores of all threads of the CTA
+      red_release_sys_add(reinterpret_cast<uint32_t*>(q.peer[o] + q.off_cnt) + par, s_rows);
+    }
+  }
+
+  // ---- phase B: wait until every rank's rows of this rank's slice have landed here
+  const uint32_t r0 = uint32_t((uint64_t(q.rank) * q.rows) / W), r1 = uint32_t((uint64_t(q.rank + 1) * q.rows) / W);
+  if (tid == 0) {
+    const uint32_t want = q.uses * (r1 - r0) * W;
+    if (!wait_flag(reinterpret_cast<const uint32_t*>(mine + q.off_cnt) + par, want, q.wait_limit)) {
+      s_ok = 0u;
+      dev_status_set(q.status, DG_DEV_WAIT_TIMEOUT, KID_MERGE, blockIdx.x, 200u);
+    }
+  }
+  __syncthreads();
+  if (!s_ok) return;   // some rank's rows never arrived: the status word says so, the output is left alone
+  const __half* rows_in = reinterpret_cast<const __half*>(mine + q.off_recv[par]);
+  const float4* ml_in = reinterpret_cast<const float4*>(mine + q.off_rml[par]);
+  for (uint32_t row = r0 + blockIdx.x * 8u + warp; row < r1; row += gridDim.x * 8u) {
+    const uint32_t rl = row - r0;
+    float4 rec = make_float4(-INFINITY, 0.f, 1.f, 0.f);
+    if (lane < W) rec = ml_in[size_t(lane) * q.slice_cap + rl];
+    float mg = rec.x;
+#pragma unroll
+    for (int sft = 16; sft > 0; sft >>= 1) mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, sft));
+    const float w_mine = (rec.x == -INFINITY) ? 0.f : expf(rec.x - mg);
+    float lg = w_mine * rec.y;
+#pragma unroll
+    for (int sft = 16; sft > 0; sft >>= 1) lg += __shfl_xor_sync(0xffffffffu, lg, sft);
+    const float inv = lg > 0.f ? 1.0f / lg : 0.f;
+    const float ws_mine = w_mine * rec.z;   // the row's scale folded into its weight
+    for (uint32_t c0 = lane * 8u; c0 < D; c0 += 256u) {
+      uint4 x[8];
+#pragma unroll
+      for (uint32_t w = 0; w < 8; ++w) {
+        x[w] = make_uint4(0u, 0u, 0u, 0u);
+        if (w < W) x[w] = *reinterpret_cast<const uint4*>(rows_in + (size_t(w) * q.slice_cap + rl) * D + c0);
+      }
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+      for (uint32_t w = 0; w < 8; ++w) {
+        float wt = __shfl_sync(0xffffffffu, ws_mine, int(w));
+        if (w >= W) wt = 0.f;
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&x[w].x));
+        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&x[w].y));
+        const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&x[w].z));
+        const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&x[w].w));
+        acc[0] += wt * f0.x; acc[1] += wt * f0.y; acc[2] += wt * f1.x; acc[3] += wt * f1.y;
+        acc[4] += wt * f2.x; acc[5] += wt * f2.y; acc[6] += wt * f3.x; acc[7] += wt * f3.y;
+      }
+      __nv_bfloat162 h0 = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv), h1 = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
+      __nv_bfloat162 h2 = __floats2bfloat162_rn(acc[4] * inv, acc[5] * inv), h3 = __floats2bfloat162_rn(acc[6] * inv, acc[7] * inv);
+      uint4 o4;
+      o4.x = *reinterpret_cast<uint32_t*>(&h0);
+      o4.y = *reinterpret_cast<uint32_t*>(&h1);
+      o4.z = *reinterpret_cast<uint32_t*>(&h2);
+      o4.w = *reinterpret_cast<uint32_t*>(&h3);
+      *reinterpret_cast<uint4*>(out + size_t(row) * D + c0) = o4;
+    }
+  }
+}
+
+cudaError_t launch_p2p_push_merge(const P2pParams& q, void* out, int num_sms, cudaStream_t st) {
+  // every CTA must be resident while it waits (at most one per SM), and every owner needs a CTA
+  uint32_t grid = (q.rows + 7u) / 8u;
+  if (grid > uint32_t(num_sms)) grid = uint32_t(num_sms);
+  if (grid < q.world) grid = q.world;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(256);
+  cfg.stream = st;
+  // start while the attention kernel drains; the kernel waits (griddepcontrol.wait) before it reads
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, dg_p2p_push_merge_kernel, q, static_cast<__nv_bfloat16*>(out));
 }
 
 void launch_p2p_merge(const P2pParams& q, void* out, int num_sms, cudaStream_t st) {

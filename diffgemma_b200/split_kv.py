@@ -50,8 +50,10 @@ def head_shards(n_kv_heads: int, world: int) -> list[tuple[int, int]]:
 class SplitKvGroup:
     """Split-KV attention over the ranks of a torch.distributed process group.
 
-    exchange="p2p" (default): partials are merged by a kernel that reads the peers' exchange buffers
-    over NVLink (CUDA IPC mappings); exchange="nccl": two NCCL all-reduces (max of m, sum of [O | l]).
+    exchange="p2p" (default): partials are merged by a kernel over the peers' exchange buffers (CUDA IPC
+    mappings, NVLink); p2p_mode 0-2 leave the full output on every rank, p2p_mode 3 (push form) leaves
+    every rank with its own row slice (`row_slice`) only.  exchange="nccl": two NCCL all-reduces (max of
+    m, sum of [O | l]).
     """
 
     def __init__(self, ctx: Context, layer: AttnLayer, group=None, exchange: str = "p2p", p2p_mode: int = 0):
@@ -73,7 +75,8 @@ class SplitKvGroup:
             rows = layer.canvas * layer.n_q_heads
             check(lib.dg_p2p_create(ctx.h, rows, layer.head_dim, self.world, self.rank, C.byref(h)), "dg_p2p_create")
             self.p2p = h
-            check(lib.dg_p2p_set_mode(h, p2p_mode), "dg_p2p_set_mode")   # 0 automatic, 1 row slices, 2 all rows
+            check(lib.dg_p2p_set_mode(h, p2p_mode), "dg_p2p_set_mode")   # 0 automatic, 1 row slices, 2 all rows, 3 push
+            self.p2p_mode = p2p_mode
             buf = (C.c_uint8 * 64)()
             check(lib.dg_p2p_handle(h, C.cast(buf, C.c_void_p)), "dg_p2p_handle")
             mine = torch.tensor(list(buf), dtype=torch.uint8, device=xdev)
@@ -89,13 +92,62 @@ class SplitKvGroup:
         b = plan_shards(kv_len, self.world)
         return b[self.rank], b[self.rank + 1]
 
+    @property
+    def owns_canvas(self) -> bool:
+        return self.rank == canvas_owner(self.world)
+
+    def make_shard_cache(self, kv_len: int, canvas_room: bool = True) -> KvCache:
+        """A cache that holds this rank's prefix shard only (plus, on the rank that counts the canvas
+        keys, room for the canvas): shard + canvas tokens of HBM instead of the whole prefix."""
+        t0, t1 = self.shard_bounds(kv_len)
+        cap = max(128, t1 - t0 + (self.layer.canvas if self.owns_canvas and canvas_room else 0))
+        return KvCache(self.ctx, self.layer, cap, pos_base=t0)
+
+    def row_slice(self):
+        """(first row, number of rows) of the canvas * n_q_heads output rows this rank owns in p2p_mode 3."""
+        r0, n = C.c_uint32(), C.c_uint32()
+        check(self.ctx.lib.dg_p2p_slice(self.p2p, C.byref(r0), C.byref(n)), "dg_p2p_slice")
+        return int(r0.value), int(n.value)
+
+    def set_wait_limit(self, cycles: int) -> None:
+        check(self.ctx.lib.dg_p2p_set_wait_limit(self.p2p, cycles), "dg_p2p_set_wait_limit")
+
+    def reset(self) -> None:
+        """Resynchronise the group after a timed-out or failed step: drain, barrier, zero this rank's flags
+        and step number, barrier (every rank must call it)."""
+        try:
+            self.ctx.synchronize()
+        except capi.DgError:
+            pass                      # the device status that led here
+        dist.barrier(group=self.group)
+        check(self.ctx.lib.dg_p2p_reset(self.p2p), "dg_p2p_reset")
+        check(self.ctx.lib.dg_ctx_clear_device_status(self.ctx.h), "dg_ctx_clear_device_status")
+        self.ctx.synchronize()
+        dist.barrier(group=self.group)
+
+    def gather_rows(self, out):
+        """p2p_mode 3 leaves each rank with its row slice of `out` [C,Hq,D]; this collects all slices on every
+        rank with one all-gather over the process group (not part of the timed path)."""
+        flat = out.reshape(self.layer.canvas * self.layer.n_q_heads, self.layer.head_dim)
+        r0, n = self.row_slice()
+        cap = (flat.shape[0] + self.world - 1) // self.world
+        mine = torch.zeros((cap, flat.shape[1]), dtype=flat.dtype, device=flat.device)
+        mine[:n] = flat[r0:r0 + n]
+        parts = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(parts, mine, group=self.group)
+        full = torch.empty_like(flat)
+        for w, part in enumerate(parts):
+            a, b = (w * flat.shape[0]) // self.world, ((w + 1) * flat.shape[0]) // self.world
+            full[a:b] = part[:b - a]
+        return full.reshape(out.shape)
+
     def denoise(self, kv: KvCache, kv_len: int, q, k, v, qw=None, kw=None, out=None):
         """q: [C,Hq,D], k, v: [C,Hkv,D] (replicated inputs).  Every rank gets the full bf16 output."""
         t0, t1 = self.shard_bounds(kv_len)
-        out = torch.empty_like(q) if out is None else out
+        out = torch.zeros_like(q) if out is None else out
         if self.exchange == "p2p":
             check(self.ctx.lib.dg_attn_denoise_split_p2p(self.ctx.h, C.byref(self.att.desc), kv.h, kv_len, t0, t1,
-                                                         int(self.rank == canvas_owner(self.world)), self.p2p,
+                                                         int(self.owns_canvas), self.p2p,
                                                          _ptr(q), _ptr(k), _ptr(v), _ptr(qw), _ptr(kw), _ptr(out)),
                   "dg_attn_denoise_split_p2p")
             return out

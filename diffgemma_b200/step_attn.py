@@ -137,14 +137,19 @@ class Context:
 class KvCache:
     """dg_kv: one layer's head-major bf16 cache for one canvas stream."""
 
-    def __init__(self, ctx: Context, layer: AttnLayer, capacity_tokens: int = 0, ring_slots: int | None = None):
+    def __init__(self, ctx: Context, layer: AttnLayer, capacity_tokens: int = 0, ring_slots: int | None = None,
+                 pos_base: int | None = None):
         """Linear cache of `capacity_tokens` positions, or (sliding layers) a ring of `ring_slots` slots
-        that keeps position pos in slot pos & (ring_slots - 1)."""
+        that keeps position pos in slot pos & (ring_slots - 1), or (pos_base given) one rank's shard of a
+        long prefix: the positions [pos_base, pos_base + capacity_tokens) only."""
         self.ctx = ctx
         self.layer = layer
         h = C.c_void_p()
         d = layer.c_desc()
-        if ring_slots is None:
+        if pos_base is not None:
+            check(ctx.lib.dg_kv_create_shard(ctx.h, C.byref(d), pos_base, capacity_tokens, C.byref(h)),
+                  "dg_kv_create_shard")
+        elif ring_slots is None:
             check(ctx.lib.dg_kv_create(ctx.h, C.byref(d), capacity_tokens, C.byref(h)), "dg_kv_create")
         else:
             check(ctx.lib.dg_kv_create_ring(ctx.h, C.byref(d), ring_slots, C.byref(h)), "dg_kv_create_ring")
@@ -298,6 +303,15 @@ class HostPipe:
         t = C.c_uint64()
         check(self.ctx.lib.dg_host_pipe_submit(self.h, C.byref(self.desc), kv_arr, len_arr, B, _ptr(q), _ptr(k), _ptr(v),
                                                _ptr(qw), _ptr(kw), _ptr(out), C.byref(t)), "dg_host_pipe_submit")
+        return int(t.value)
+
+    def submit_split(self, kv, kv_len: int, t0: int, t1: int, include_canvas: bool, p2p, q, k, v, out,
+                     qw=None, kw=None) -> int:
+        """One split-KV step of this rank with host tensors (dg_host_pipe_submit_split)."""
+        t = C.c_uint64()
+        check(self.ctx.lib.dg_host_pipe_submit_split(self.h, C.byref(self.desc), kv.h, kv_len, t0, t1,
+                                                     int(include_canvas), p2p, _ptr(q), _ptr(k), _ptr(v), _ptr(qw),
+                                                     _ptr(kw), _ptr(out), C.byref(t)), "dg_host_pipe_submit_split")
         return int(t.value)
 
     def wait(self, ticket: int) -> None:

@@ -143,6 +143,15 @@ int32_t dg_kv_create(dg_ctx* ctx, const dg_layer_desc* desc, uint64_t capacity_t
  * end of the canvas - still fits the ring and returns DG_ERR_CAPACITY otherwise (an unwindowed layer on a
  * ring works only while kv_len + canvas <= ring_slots).                                            */
 int32_t dg_kv_create_ring(dg_ctx* ctx, const dg_layer_desc* desc, uint32_t ring_slots, dg_kv** out);
+/* A linear cache that holds only the positions [pos_base, pos_base + capacity_tokens) (pos_base a multiple
+ * of 128): one rank's shard of a long prefix under split-KV, so that a rank's cache costs shard + canvas
+ * tokens instead of the whole prefix.  Positions keep their absolute values in every call; an attention
+ * call whose visible keys (whole 128-key tiles) are not all inside the shard returns DG_ERR_CAPACITY, and
+ * appends of positions outside the shard are dropped (a rank that does not own the canvas keys still
+ * runs the step with the replicated canvas K/V).  No counterpart in the reference (single device).      */
+int32_t dg_kv_create_shard(dg_ctx* ctx, const dg_layer_desc* desc, uint64_t pos_base, uint64_t capacity_tokens,
+                           dg_kv** out);
+uint64_t dg_kv_pos_base(const dg_kv* kv);
 /* ring_slots - 1 of a ring cache, 0 for a linear one.                                            */
 uint32_t dg_kv_ring_mask(const dg_kv* kv);
 int32_t dg_kv_destroy(dg_kv* kv);
@@ -177,11 +186,15 @@ int32_t dg_attention(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* kv, uint32_t
                      void* out);
 /* Stage 2 for hosts that must not allocate device memory while they run (all HBM already given to
  * the host's own pool, a step being captured into a CUDA graph, a thread barred from the allocator).
- * Same arguments and result as dg_attention, but the key-split workspace is a 16.13 MiB array built
- * into the library (every GPU that loads the library holds it until the process exits) and the call
- * performs no cudaMalloc / cudaFree.  Limits: canvas * n_q_heads <= 4096 rows, at most 128 query
- * tiles, at most 4 key splits (more are clamped); beyond the row/tile limits the call returns
- * DG_ERR_UNSUPPORTED with an explanatory message.  The first call on each device looks up the
+ * Same arguments, checks (ring span included) and result as dg_attention, but the key-split workspace
+ * is a 16.13 MiB array built into the library (every GPU that loads the library holds it until the
+ * process exits) and the call performs no cudaMalloc / cudaFree.  It always runs the one-CTA-per-tile
+ * form of the tensor kernels (head_dim 256 and 512) with every key split meeting in that array, so it
+ * is a little slower than dg_attention on long key ranges; other geometries run the general kernel,
+ * which needs no workspace.  Limits: canvas * n_q_heads <= 4096 rows, at most 128 query tiles (64 for
+ * head_dim 512); the number of key splits is clamped to what the array holds for the call's row
+ * count (4 at 4096 rows of head_dim 256, 2 at head_dim 512); beyond the row / tile limits the call
+ * returns DG_ERR_UNSUPPORTED with an explanatory message.  The first call on each device looks up the
  * array's device address; make that first call before starting any stream capture.  All calls on a
  * device share the one array and it keeps the previous call's contents (the call clears the part
  * that must start at zero): two calls whose kernels overlap on the GPU (different streams, or
@@ -265,15 +278,41 @@ int32_t dg_nccl_all_gather(dg_ctx* ctx, void* comm, const void* send, void* recv
 typedef struct dg_p2p dg_p2p;
 int32_t dg_p2p_create(dg_ctx* ctx, uint32_t rows, uint32_t head_dim, int32_t world, int32_t rank, dg_p2p** out);
 int32_t dg_p2p_handle(dg_p2p* x, uint8_t handle_out[64]);
-/* How the merge is shared out: 1 = every rank merges its slice of the rows and sends the finished rows to the
- * others (two flag rounds), 2 = every rank reads all partials and merges every row itself (one flag round; pays
- * off with two ranks), 0 = automatic (default: 2 with two ranks, 1 otherwise).  Every rank must use the same.  */
+/* How the merge is shared out.  Every rank must use the same mode.
+ *   1 = every rank merges its slice of the rows and sends the finished rows to the others (two flag rounds);
+ *   2 = every rank reads all partials and merges every row itself (one flag round; pays off with two ranks);
+ *   0 = automatic (default: 2 with two ranks, 1 otherwise).  Modes 0-2 leave the full output on every rank.
+ *   3 = push form (reduce-scatter): every rank STORES each row of its partial, as fp16 with a power-of-two
+ *       scale per row, into the buffer of the rank that owns the row and bumps that rank's arrival counter;
+ *       the owner waits on its own memory, merges and writes ONLY its row slice of `out` (dg_p2p_slice; the
+ *       other rows of `out` are left untouched).  One exchange, no result scatter: the form for a host whose
+ *       next operator is sharded by rows, or that gathers the slices itself.                                  */
 int32_t dg_p2p_set_mode(dg_p2p* x, int32_t mode);
+/* The rows of the output this rank owns in mode 3: [*row0, *row0 + *n_rows) of the canvas * n_q_heads rows.    */
+int32_t dg_p2p_slice(const dg_p2p* x, uint32_t* row0, uint32_t* n_rows);
+/* Upper bound, in SM clock cycles, of every device-side wait of the exchange (default 1e9, about half a
+ * second; at most 2e10).  The wait covers the peers' host-side launch skew as well as their GPU progress.       */
+int32_t dg_p2p_set_wait_limit(dg_p2p* x, uint64_t limit_cycles);
+/* After DG_DEV_WAIT_TIMEOUT on a p2p group (a peer never delivered: the step's output was left unwritten) or
+ * after a call that failed half-way, the ranks no longer agree on the step number and a late peer may still
+ * write into buffers of the abandoned step: the group must not be used again until every rank has (1) drained
+ * its stream, (2) met the others at a host barrier, (3) called dg_p2p_reset, which zeroes the flags, counters
+ * and the step number of this rank's buffer, and (4) met the others at a second host barrier.  Clear the
+ * device status word (dg_ctx_clear_device_status) as well.                                                     */
+int32_t dg_p2p_reset(dg_p2p* x);
 int32_t dg_p2p_connect(dg_p2p* x, const uint8_t* handles);
 int32_t dg_p2p_destroy(dg_p2p* x);
 int32_t dg_attn_denoise_split_p2p(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* kv, uint32_t kv_len, uint32_t t0,
                                   uint32_t t1, int32_t include_canvas, dg_p2p* x, const void* q, const void* k,
                                   const void* v, const void* qw, const void* kw, void* out);
+/* The same step with HOST buffers through a dg_host_pipe of this rank's context (one canvas): copies in,
+ * kernels and the copy out of neighbouring steps overlap as in dg_host_pipe_submit.  A rank that does not
+ * count the canvas keys (include_canvas = 0) and whose cache is a shard never stores the canvas K/V, so it
+ * does not copy k and v at all; in mode 3 only this rank's row slice of `out` is copied back (to the same
+ * offset in `out` that the rows have in the full output).                                                   */
+int32_t dg_host_pipe_submit_split(dg_host_pipe* pipe, const dg_layer_desc* desc, dg_kv* kv, uint32_t kv_len, uint32_t t0,
+                                  uint32_t t1, int32_t include_canvas, dg_p2p* x, const void* q, const void* k,
+                                  const void* v, const void* qw, const void* kw, void* out, uint64_t* ticket);
 
 /* ---- mask introspection (bit-exact mask parity) ----------------------------------------- */
 /* Evaluate on the GPU the same visibility predicate the attention kernels use and write it as

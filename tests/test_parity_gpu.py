@@ -606,3 +606,124 @@ def test_step_is_capturable_into_a_cuda_graph(ctx):
         util.assert_close(util.t2f(out[b]), util.run_oracle(c), f"graph replay, canvas {b}")
     for kv in kvs:
         kv.close()
+
+
+def test_graph_replay_survives_eager_calls_at_other_positions(ctx):
+    """A captured step reads the RoPE table of its own cache.  Eager calls on OTHER caches at other
+    positions between capture and replay, and a step captured before its cache's table was ever written
+    (the recorded launches then write and read a table of their own), must both replay correctly."""
+    layer = AttnLayer(n_kv_heads=8, rope_theta=1e4)
+    a = util.make_case(layer, 700, seed=811)
+    b = util.make_case(layer, 1500, seed=812)
+    c = util.make_case(layer, 300, seed=813)
+    att = CanvasAttention(ctx, layer)
+    kv_a, _ = util.gpu_setup(ctx, a)
+    kv_b, _ = util.gpu_setup(ctx, b)
+    kv_c, _ = util.gpu_setup(ctx, c)
+    dv = lambda case, n: util.dev(case, n)[None]
+    out_a = torch.empty_like(dv(a, "q"))
+    out_c = torch.empty_like(dv(c, "q"))
+    # warm the workspaces on cache B only, so that A's table is valid (eager step) and C's is not
+    att.denoise([kv_b], [b["prefix"]], dv(b, "q"), dv(b, "kc"), dv(b, "vc"))
+    att.denoise([kv_a], [a["prefix"]], dv(a, "q"), dv(a, "kc"), dv(a, "vc"), out=out_a)
+    ctx.synchronize()
+    want_a = out_a.clone()
+    qa, ka, va = dv(a, "q"), dv(a, "kc"), dv(a, "vc")
+    qc, kc, vc = dv(c, "q"), dv(c, "kc"), dv(c, "vc")
+    g_a, g_c = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g_a, stream=ctx.torch_stream):      # table of A already holds these positions
+        att.denoise([kv_a], [a["prefix"]], qa, ka, va, out=out_a)
+    with torch.cuda.graph(g_c, stream=ctx.torch_stream):      # C has never run: the graph carries its own table
+        att.denoise([kv_c], [c["prefix"]], qc, kc, vc, out=out_c)
+    # eager calls at other positions on another cache, and an eager call on C AFTER its capture
+    got_b = att.denoise([kv_b], [b["prefix"]], dv(b, "q"), dv(b, "kc"), dv(b, "vc"))
+    got_c_eager = att.denoise([kv_c], [c["prefix"]], qc, kc, vc)
+    out_a.zero_()
+    out_c.zero_()
+    g_a.replay()
+    g_c.replay()
+    got_c_eager2 = att.denoise([kv_c], [c["prefix"]], qc, kc, vc)   # eager again after the replay
+    ctx.synchronize()
+    assert torch.equal(out_a.view(torch.int16), want_a.view(torch.int16))
+    util.assert_close(util.t2f(out_a[0]), util.run_oracle(a), "graph replay after eager calls elsewhere")
+    ref_c = util.run_oracle(c)
+    util.assert_close(util.t2f(out_c[0]), ref_c, "graph captured before the cache's table existed")
+    util.assert_close(util.t2f(got_c_eager[0]), ref_c, "eager call between capture and replay")
+    util.assert_close(util.t2f(got_c_eager2[0]), ref_c, "eager call after the replay")
+    util.assert_close(util.t2f(got_b[0]), util.run_oracle(b), "eager call on the other cache")
+    assert ctx.device_status()[0] == 0
+    for kv in (kv_a, kv_b, kv_c):
+        kv.close()
+
+
+# ------------------------------------------------------------------------------------------
+# shard caches and the peer-memory exchange on ONE rank (the multi-rank forms need >= 2 GPUs)
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("P,t0,t1,inc", [(6000, 2560, 4224, False), (6000, 4224, 6000, True), (5000, 0, 1280, False)])
+def test_shard_cache_partial_matches_full_cache(ctx, P, t0, t1, inc):
+    """A cache that holds only positions [t0, t1) (+ the canvas on the rank that counts it) gives the same
+    partial as a full-size cache, bit for bit, and refuses calls whose keys lie outside it."""
+    layer = AttnLayer(n_kv_heads=2)
+    case = util.make_case(layer, P, seed=P + t0)
+    att = CanvasAttention(ctx, layer)
+    full, _ = util.gpu_setup(ctx, case)
+    cap = t1 - t0 + (layer.canvas if inc else 0)
+    shard = KvCache(ctx, layer, cap, pos_base=t0)
+    shard.load_prefix(case["kp"][t0:t1].contiguous().to(DEV), case["vp"][t0:t1].contiguous().to(DEV), t0)
+    q, kc, vc = util.dev(case, "q"), util.dev(case, "kc"), util.dev(case, "vc")
+    want = att.partial(full, P, t0, t1, inc, q, kc, vc)
+    got = att.partial(shard, P, t0, t1, inc, q, kc, vc)
+    ctx.synchronize()
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    o, m, l = util.run_oracle(case, partial=(t0, t1, inc))
+    lg = np.where(l > 0, l, 1.0)
+    util.assert_close(got[0].cpu().numpy() / got[2].cpu().numpy().clip(min=1e-30)[..., None], o / lg[..., None], "shard partial")
+    # keys outside the shard: refused before anything is launched
+    with pytest.raises(capi.DgError) as ei:
+        att.partial(shard, P, 0 if t0 else t1, t1 + 1024, inc, q, kc, vc)
+    assert ei.value.status == capi.DG_ERR_CAPACITY
+    k_back, _ = shard.read(t0, 128)
+    assert torch.equal(k_back, case["kp"][t0:t0 + 128].to(DEV))
+    full.close()
+    shard.close()
+
+
+@pytest.mark.parametrize("mode", [0, 1, 3])
+def test_peer_exchange_forms_on_one_rank(ctx, mode):
+    """world = 1: the exchange kernels run with this rank as the only peer (the push form stores its rows
+    into its own receive area and merges them from there) and must reproduce the plain call."""
+    import ctypes as C
+    layer = AttnLayer(n_kv_heads=2)
+    P = 3000
+    case = util.make_case(layer, P, seed=515)
+    kv, att = util.gpu_setup(ctx, case)
+    lib = ctx.lib
+    x = C.c_void_p()
+    capi.check(lib.dg_p2p_create(ctx.h, layer.canvas * layer.n_q_heads, layer.head_dim, 1, 0, C.byref(x)), "dg_p2p_create")
+    capi.check(lib.dg_p2p_set_mode(x, mode), "dg_p2p_set_mode")
+    q, kc, vc = util.dev(case, "q"), util.dev(case, "kc"), util.dev(case, "vc")
+    ref = util.run_oracle(case)
+    for step in range(3):
+        out = torch.zeros_like(q)
+        capi.check(lib.dg_attn_denoise_split_p2p(ctx.h, C.byref(att.desc), kv.h, P, 0, P, 1, x, util_ptr(q), util_ptr(kc),
+                                                 util_ptr(vc), None, None, util_ptr(out)), "dg_attn_denoise_split_p2p")
+        ctx.synchronize()
+        util.assert_close(util.t2f(out), ref, f"one-rank exchange mode {mode} step {step}")
+    r0, n = C.c_uint32(), C.c_uint32()
+    capi.check(lib.dg_p2p_slice(x, C.byref(r0), C.byref(n)), "dg_p2p_slice")
+    assert (r0.value, n.value) == (0, layer.canvas * layer.n_q_heads)
+    capi.check(lib.dg_p2p_reset(x), "dg_p2p_reset")
+    out = torch.zeros_like(q)
+    capi.check(lib.dg_attn_denoise_split_p2p(ctx.h, C.byref(att.desc), kv.h, P, 0, P, 1, x, util_ptr(q), util_ptr(kc),
+                                             util_ptr(vc), None, None, util_ptr(out)), "dg_attn_denoise_split_p2p")
+    ctx.synchronize()
+    util.assert_close(util.t2f(out), ref, "after reset")
+    assert ctx.device_status()[0] == 0
+    lib.dg_p2p_destroy(x)
+    kv.close()
+
+
+def util_ptr(t):
+    import ctypes as C
+    return C.c_void_p(t.data_ptr())

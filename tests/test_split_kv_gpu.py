@@ -1,6 +1,8 @@
-"""Split-KV across GPUs over NCCL: every rank holds one prefix shard, the per-rank (O, m, l) partials
-are merged by dg_attn_merge_nccl, and the result must equal the single-GPU oracle.  Needs >= 2 GPUs
-(skipped otherwise); ranks are child processes, one per GPU."""
+"""Split-KV across GPUs: every rank holds one prefix shard, the per-rank (O, m, l) partials are merged
+over peer memory (four forms) or by dg_attn_merge_nccl, and the result must equal the single-GPU oracle.
+Also KV-head sharding, and the failure path of the peer-memory exchange (a rank that skips a step makes
+the other's bounded wait give up; the group is resynchronised and carries on).  Needs >= 2 GPUs (skipped
+otherwise); ranks are child processes, one per GPU, NVLS off, plain peer loads and stores only."""
 import os
 import sys
 
@@ -22,6 +24,7 @@ def _rank_main(rank, world, port, P, W, mode, exchange, ret):
     from diffgemma_b200.step_attn import AttnLayer, Context, KvCache
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
@@ -30,15 +33,18 @@ def _rank_main(rank, world, port, P, W, mode, exchange, ret):
         case = util.make_case(layer, P, seed=77)          # same seed on every rank: replicated inputs
         dev = f"cuda:{rank}"
         b = plan_shards(P, world)
-        kv = KvCache(ctx, layer, P + layer.canvas)
         t0, t1 = b[rank], b[rank + 1]
+        mode = {"p2p": 0, "p2p-slices": 1, "p2p-allrows": 2, "p2p-push": 3}.get(exchange, 0)
+        grp = SplitKvGroup(ctx, layer, exchange="nccl" if exchange == "nccl" else "p2p", p2p_mode=mode)
+        # the push form runs on shard caches (shard + canvas tokens per rank), the others on full-size ones
+        kv = grp.make_shard_cache(P) if exchange == "p2p-push" else KvCache(ctx, layer, P + layer.canvas)
         if t1 > t0:                                        # only this rank's shard is resident
             kv.load_prefix(case["kp"][t0:t1].contiguous().to(dev), case["vp"][t0:t1].contiguous().to(dev), t0)
-        mode = {"p2p": 0, "p2p-slices": 1, "p2p-allrows": 2}.get(exchange, 0)
-        grp = SplitKvGroup(ctx, layer, exchange="nccl" if exchange == "nccl" else "p2p", p2p_mode=mode)
         out = None
         for _ in range(3):                                 # several steps: buffer parities and flags are reused
             out = grp.denoise(kv, P, case["q"].to(dev), case["kc"].to(dev), case["vc"].to(dev))
+        if exchange == "p2p-push":
+            out = grp.gather_rows(out)                     # every rank holds its row slice only
         ctx.synchronize()
         ref = util.run_oracle(case)
         ret[rank] = util.errors(util.t2f(out), ref) + (float(util.max_abs_tol(ref)),)
@@ -49,7 +55,7 @@ def _rank_main(rank, world, port, P, W, mode, exchange, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["p2p", "p2p-slices", "p2p-allrows", "nccl"])
+@pytest.mark.parametrize("exchange", ["p2p", "p2p-slices", "p2p-allrows", "p2p-push", "nccl"])
 @pytest.mark.parametrize("P,W,mode,port", [(6000, 0, 0, 29721), (3000, 1024, 1, 29722)])
 def test_split_kv_matches_oracle(P, W, mode, port, exchange):
     world = min(torch.cuda.device_count(), 4)
@@ -57,11 +63,92 @@ def test_split_kv_matches_oracle(P, W, mode, port, exchange):
         pytest.skip("needs at least 2 GPUs")
     mgr = mp.Manager()
     ret = mgr.dict()
-    port += {"p2p": 0, "nccl": 10, "p2p-slices": 20, "p2p-allrows": 30}[exchange]
+    port += {"p2p": 0, "nccl": 10, "p2p-slices": 20, "p2p-allrows": 30, "p2p-push": 40}[exchange]
     mp.spawn(_rank_main, args=(world, port, P, W, mode, exchange, ret), nprocs=world, join=True)
     assert len(ret) == world
     for rank, (mx, mean, tol) in ret.items():
         assert mx <= tol and mean <= 2e-3, (rank, mx, mean)
+
+
+def _failure_main(rank, world, port, ret):
+    """Rank 1 skips one step: rank 0's bounded wait gives up and reports it; both ranks resynchronise;
+    a failed host-side call on one rank must not desynchronise the group; clean steps follow."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import util
+    from diffgemma_b200 import capi
+    from diffgemma_b200.split_kv import SplitKvGroup, plan_shards
+    from diffgemma_b200.step_attn import AttnLayer, Context, KvCache
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        ctx = Context(rank)
+        layer = AttnLayer(n_kv_heads=2)
+        P = 3000
+        case = util.make_case(layer, P, seed=78)
+        dev = f"cuda:{rank}"
+        grp = SplitKvGroup(ctx, layer, exchange="p2p", p2p_mode=3)
+        kv = grp.make_shard_cache(P)
+        t0, t1 = grp.shard_bounds(P)
+        kv.load_prefix(case["kp"][t0:t1].contiguous().to(dev), case["vp"][t0:t1].contiguous().to(dev), t0)
+        q, kc, vc = case["q"].to(dev), case["kc"].to(dev), case["vc"].to(dev)
+        ref = util.run_oracle(case)
+        res = {}
+        out = grp.gather_rows(grp.denoise(kv, P, q, kc, vc))
+        ctx.synchronize()
+        res["first"] = util.errors(util.t2f(out), ref)
+        # -- a host-side failure on rank 0 only (the visible keys lie outside its shard): nothing is launched,
+        #    the step number does not advance, and the repeated call merges with the peer's
+        if rank == 0:
+            with pytest.raises(capi.DgError) as ei:
+                grp.denoise(kv, P + 4096, q, kc, vc)
+            res["host_error"] = ei.value.status
+        out = grp.gather_rows(grp.denoise(kv, P, q, kc, vc))
+        ctx.synchronize()
+        res["after_host_error"] = util.errors(util.t2f(out), ref)
+        # -- rank 1 sits one step out (between steps, nothing of its own in flight)
+        dist.barrier()
+        grp.set_wait_limit(40_000_000)                     # about 20 ms
+        if rank == 0:
+            grp.denoise(kv, P, q, kc, vc)
+            st = ctx.device_status()
+            res["timeout_status"] = (st[0], st[1])
+        dist.barrier()
+        grp.set_wait_limit(1_000_000_000)
+        grp.reset()                                        # drain, barrier, zero flags, barrier
+        res["status_after_reset"] = ctx.device_status()[0]
+        for _ in range(3):
+            out = grp.gather_rows(grp.denoise(kv, P, q, kc, vc))
+        ctx.synchronize()
+        res["after_reset"] = util.errors(util.t2f(out), ref)
+        res["tol"] = float(util.max_abs_tol(ref))
+        ret[rank] = res
+        grp.close()
+        kv.close()
+        ctx.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_push_exchange_timeout_is_reported_and_group_recovers():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_failure_main, args=(2, 29761, ret), nprocs=2, join=True)
+    assert len(ret) == 2
+    from diffgemma_b200 import capi
+    assert ret[0]["host_error"] == capi.DG_ERR_CAPACITY
+    assert ret[0]["timeout_status"] == (capi.DG_DEV_WAIT_TIMEOUT, 4)      # kernel id 4: the merge kernel
+    for rank in range(2):
+        r = ret[rank]
+        assert r["status_after_reset"] == 0
+        for key in ("first", "after_host_error", "after_reset"):
+            mx, mean = r[key]
+            assert mx <= r["tol"] and mean <= 2e-3, (rank, key, mx, mean)
 
 
 def _head_shard_main(rank, world, port, P, W, mode, ret):
