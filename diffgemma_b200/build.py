@@ -51,8 +51,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
            "-I", os.path.join(ROOT, "include"), "-I", _nccl_include()]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += sources() + ["-o", LIB, "-ldl"]
+    # link under a temporary name and rename: a reader never sees a half-written library
+    tmp = LIB + ".tmp"
+    cmd += sources() + ["-o", tmp, "-ldl"]
     subprocess.check_call(cmd)
+    os.replace(tmp, LIB)
     return LIB
 
 

@@ -87,6 +87,8 @@ SIGNATURES = {
     "dg_nccl_unique_id": (_i32, [_vp]),
     "dg_nccl_comm_create": (_i32, [_vp, _vp, _i32, _i32, C.POINTER(_vp)]),
     "dg_nccl_comm_destroy": (_i32, [_vp]),
+    "dg_nccl_comm_check": (_i32, [_vp]),
+    "dg_nccl_comm_abort": (_i32, [_vp]),
     "dg_nccl_all_gather": (_i32, [_vp, _vp, _vp, _vp, _u64]),
     "dg_p2p_create": (_i32, [_vp, _u32, _u32, _i32, _i32, C.POINTER(_vp)]),
     "dg_p2p_set_mode": (_i32, [_vp, _i32]),

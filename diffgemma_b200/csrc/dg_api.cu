@@ -680,7 +680,9 @@ static int32_t do_append(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint64_t 
     if (end < ap.write_end) ap.write_end = uint32_t(end);
   }
   const RopeParams rp = make_rope(d);
-  launch_append(ap, rp, launch_stream(c));
+  // scheduled while the kernel ahead of it on the stream drains (it waits for that kernel's completion
+  // before it touches memory): 1-3 us per step of launch latency hidden
+  launch_append(ap, rp, launch_stream(c), true);
   DG_CUDA(cudaGetLastError());
   c->last_launches += 1;
   return DG_OK;
@@ -1305,6 +1307,8 @@ struct NcclApi {
   ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
   const char* (*GetErrorString)(ncclResult_t) = nullptr;
+  ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;   // optional: the host-side watchdog
+  ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
   bool ok = false;
 };
 NcclApi& nccl() {
@@ -1326,6 +1330,8 @@ NcclApi& nccl() {
   api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(api.handle, "ncclAllReduce"));
   api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(api.handle, "ncclAllGather"));
   api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(api.handle, "ncclGetErrorString"));
+  api.CommGetAsyncError = reinterpret_cast<decltype(api.CommGetAsyncError)>(dlsym(api.handle, "ncclCommGetAsyncError"));
+  api.CommAbort = reinterpret_cast<decltype(api.CommAbort)>(dlsym(api.handle, "ncclCommAbort"));
   api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce && api.AllGather && api.GetErrorString;
   return api;
 }
@@ -1364,6 +1370,24 @@ extern "C" int32_t dg_nccl_comm_destroy(void* comm) {
   if (!comm) return DG_OK;
   if (!nccl().ok) return fail(DG_ERR_NCCL, "NCCL not loaded");
   DG_NCCL(nccl().CommDestroy(static_cast<ncclComm_t>(comm)));
+  return DG_OK;
+}
+
+// Host-side watchdog of a communicator: NCCL reports failures of collectives that are already queued (a
+// peer that died, a network error) asynchronously; a host loop polls this between steps and, on an error,
+// aborts the communicator so that the kernels still waiting on it return instead of spinning.
+extern "C" int32_t dg_nccl_comm_check(void* comm) {
+  if (!comm) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  if (!nccl().ok || !nccl().CommGetAsyncError) return fail(DG_ERR_NCCL, "ncclCommGetAsyncError not available");
+  ncclResult_t async = ncclSuccess;
+  DG_NCCL(nccl().CommGetAsyncError(static_cast<ncclComm_t>(comm), &async));
+  if (async != ncclSuccess && async != ncclInProgress) return fail_nccl(async, "asynchronous NCCL error");
+  return DG_OK;
+}
+extern "C" int32_t dg_nccl_comm_abort(void* comm) {
+  if (!comm) return DG_OK;
+  if (!nccl().ok || !nccl().CommAbort) return fail(DG_ERR_NCCL, "ncclCommAbort not available");
+  DG_NCCL(nccl().CommAbort(static_cast<ncclComm_t>(comm)));
   return DG_OK;
 }
 

@@ -546,16 +546,21 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   const uint32_t rows_total = p.C * p.Hq;
   bool have_o = false;
   if (warp < SM_WARPS) {
+    // the warps that skipped the wait at the top must not write anything (output, workspace) that the
+    // kernels ahead of this one on the stream may still use; normally long satisfied by now
+    if (p.early_q) asm volatile("griddepcontrol.wait;" ::: "memory");
     have_o = __all_sync(0xffffffffu, n_local > 0 && !*abort_flag);
     if (have_o) {
       have_o = __all_sync(0xffffffffu, wait_bar(B_O_FINAL, 0u, abort_flag));
       tc_fence_after();
     }
   }
+  stamp(p, 12);
   // Cluster merge: partial rows are pushed into the owner CTA's Q/K/V region, which must be dead
   // in EVERY CTA of the cluster first - all of this CTA's MMAs are complete once its softmax
   // warps have seen O_FINAL, and this barrier collects that from all CTAs.
   if (cs > 1) cluster_sync_all();
+  stamp(p, 13);
   if (warp < SM_WARPS) {
     const uint32_t R = mt * BM + r;
     const bool valid = R < rows_per_head;
@@ -719,6 +724,7 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
     // [k*BM/cs, (k+1)*BM/cs) in its own shared memory and merges them.  Nothing touches remote
     // shared memory after the barrier, so no second barrier is needed.
     if (!PAIR) cluster_sync_all();
+    stamp(p, 14);
     const uint32_t rank = PAIR ? (crank >> 1) : crank;
     const uint32_t rpc = BM / cs;
     const __half* recv = reinterpret_cast<const __half*>(smem + OFF_Q);      // [cs][rpc][HBUF_LD], scaled

@@ -63,6 +63,8 @@ __device__ __forceinline__ uint32_t bar_addr(uint32_t bar_base, uint32_t idx) { 
 // Slots 6-11 hold SM-clock cycles that single threads spent waiting inside the key loop:
 // 6 MMA issuer on K tiles, 7 on V tiles, 8 on P (softmax output), 9 its whole loop,
 // 10 softmax thread 0 on S (scores), 11 softmax thread 0 on the rescale barrier.
+// Slots 12-14 are time stamps inside the tail: 12 the last PV has completed, 13 the cluster's CTAs have all
+// finished their MMAs (cluster merge only), 14 the partial rows of the cluster have all arrived.
 constexpr uint32_t STAMP_SLOTS = 16;
 __device__ __forceinline__ void stamp(const AttnParams& p, uint32_t slot) {
   if (p.stamps != nullptr && threadIdx.x == 0) {

@@ -7,7 +7,7 @@
 
 namespace dg {
 
-void launch_append(const AppendParams& p, const RopeParams& rp, cudaStream_t st);
+void launch_append(const AppendParams& p, const RopeParams& rp, cudaStream_t st, bool early = false);
 void launch_attn_general(const AttnParams& p, cudaStream_t st);
 void launch_merge_local(uint32_t n_parts, uint32_t rows, uint32_t D, const float* o, const float* m,
                         const float* l, __nv_bfloat16* out, cudaStream_t st);

@@ -38,6 +38,9 @@ __global__ void __launch_bounds__(32) dg_append_kernel(const AppendParams p, con
   // let a dependent kernel (the attention launch that follows on the stream) begin its set-up now;
   // it synchronises on this grid's completion before it reads the cache or the RoPE table
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // when this kernel was itself launched ahead of the end of its predecessor (programmatic dependent
+  // launch), everything it reads or writes may still be in use by that kernel: wait for it here
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const uint32_t tok = blockIdx.x, slot = blockIdx.y, lane = threadIdx.x;
   const uint32_t D = p.D;
   const uint32_t pos = p.pos0 + tok;
@@ -112,6 +115,7 @@ __global__ void __launch_bounds__(32) dg_append_kernel(const AppendParams p, con
 // prologue, which overlaps it through programmatic dependent launch.
 __global__ void __launch_bounds__(256) dg_append_table_kernel(const AppendParams p) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // see dg_append_kernel
   const uint32_t lane = threadIdx.x & 31u, w = blockIdx.x * 8u + (threadIdx.x >> 5);
   const uint32_t per_tok = 2u * p.Hkv;
   if (w >= p.n * per_tok) return;
@@ -173,16 +177,29 @@ __global__ void __launch_bounds__(256) dg_append_table_kernel(const AppendParams
   reinterpret_cast<uint4*>(cache)[lane] = y;
 }
 
-void launch_append(const AppendParams& p, const RopeParams& rp, cudaStream_t st) {
+void launch_append(const AppendParams& p, const RopeParams& rp, cudaStream_t st, bool early) {
   if (p.n == 0) return;
+  // `early`: the kernel may be scheduled while its predecessor on the stream is still draining (it
+  // waits for that kernel's completion before it touches memory), which hides its launch latency
+  cudaLaunchConfig_t cfg = {};
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = early ? 1 : 0;
   if (p.rope_table_in && !p.rope_table && !p.q_in && !p.k_out && !p.v_out && p.D == 256 && rp.rot_half == 128 &&
       rp.pair_off == 128) {
     const uint32_t warps = p.n * 2u * p.Hkv;
-    dg_append_table_kernel<<<(warps + 7u) / 8u, 256, 0, st>>>(p);
+    cfg.gridDim = dim3((warps + 7u) / 8u);
+    cfg.blockDim = dim3(256);
+    cudaLaunchKernelEx(&cfg, dg_append_table_kernel, p);
     return;
   }
   const uint32_t slots = (p.q_in ? p.Hq : 0u) + 2u * p.Hkv + (p.rope_table ? 1u : 0u);
-  dg_append_kernel<<<dim3(p.n, slots), 32, 0, st>>>(p, rp);
+  cfg.gridDim = dim3(p.n, slots);
+  cfg.blockDim = dim3(32);
+  cudaLaunchKernelEx(&cfg, dg_append_kernel, p, rp);
 }
 
 // ------------------------------------------------------------------------------------------

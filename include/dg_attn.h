@@ -263,6 +263,12 @@ int32_t dg_attn_merge_nccl(dg_ctx* ctx, void* nccl_comm, float* o_unnorm, float*
 int32_t dg_nccl_unique_id(uint8_t id_out[128]);
 int32_t dg_nccl_comm_create(dg_ctx* ctx, const uint8_t id[128], int32_t world_size, int32_t rank, void** comm_out);
 int32_t dg_nccl_comm_destroy(void* comm);
+/* Host-side watchdog between steps: DG_OK while the communicator is healthy, DG_ERR_NCCL (with NCCL's text in
+ * dg_last_error_message) once a queued collective has failed asynchronously (ncclCommGetAsyncError); the host then
+ * calls dg_nccl_comm_abort, which ends the communicator and lets its kernels that are still waiting return.  The
+ * reference is single-device and has no counterpart; its own failure channel is DebugStatus (dg_ctx_last_device_status). */
+int32_t dg_nccl_comm_check(void* comm);
+int32_t dg_nccl_comm_abort(void* comm);
 /* All-gather of per-rank output head slices (KV-head sharding): every rank contributes
  * `bytes_per_rank` bytes at send and receives world*bytes_per_rank at recv (device pointers).   */
 int32_t dg_nccl_all_gather(dg_ctx* ctx, void* comm, const void* send, void* recv, uint64_t bytes_per_rank);
@@ -333,8 +339,9 @@ int32_t dg_ctx_kernel_timing(dg_ctx* ctx, int32_t on, uint32_t max_launches);
  * tensor-path kernel stores globaltimer stamps (ns) at its phase boundaries: 0 start, 1 set-up done,
  * 2 Q prologue done, 3 key loop done, 4 epilogue done, 5 merge done; slots 6-11 hold SM-clock
  * cycles single threads spent waiting inside the key loop (6 MMA issuer on K, 7 on V, 8 on P,
- * 9 the issuer's whole loop, 10 softmax thread 0 on S, 11 on the rescale barrier).  The stamps
- * cost time; NULL switches them off.                                                             */
+ * 9 the issuer's whole loop, 10 softmax thread 0 on S, 11 on the rescale barrier); slots 12-14 are
+ * stamps inside the tail (12 last PV complete, 13 cluster's MMAs complete, 14 cluster's rows arrived).  The
+ * stamps cost time; NULL switches them off.                                                             */
 int32_t dg_ctx_phase_stamps(dg_ctx* ctx, void* device_buffer);
 int32_t dg_ctx_kernel_time(dg_ctx* ctx, double* total_ms, uint32_t* launches);
 

@@ -7,7 +7,7 @@ outputs are what tests/test_ref_shader_pins.py holds the numpy oracle to, also w
 (and so the compiled library) is absent.
 
 Run from the repository root, where the reference tree is present:
-    make -C oracle ref && python tests/golden/make_ref_shader_golden.py
+    make -C oracle ref REF=<reference tree> && python tests/golden/make_ref_shader_golden.py
 """
 import os
 import sys
@@ -91,7 +91,7 @@ def run_value_case(hd, n_q, n_kv, canvas, kv_len, is_full, window, ring, valias,
 
 
 def main():
-    assert rs.available(), "build the reference shaders first: make -C oracle ref"
+    assert rs.available(), "build the reference shaders first: make -C oracle ref REF=<reference tree>"
     store = {}
     for i, (kv_len, window, ring) in enumerate(MASK_CASES):
         q, cache = mask_inputs(kv_len, window, ring)

@@ -138,14 +138,14 @@ def test_denoise_parity(ctx, P, Hkv, W, mode, scale, canvas, weights, vnorm):
             for splits in (0, 1, 3, 8):     # 8: one cluster of eight CTAs in the single-CTA form (clamped to the key tiles)
                 ctx.set_splits(splits)
                 got = util.run_gpu(ctx, case)
-                util.assert_close(got, ref, f"tensor path pair={pair} splits={splits}")
+                util.assert_close(got, ref, f"tensor path pair={pair} splits={splits}", stress=(scale == 1.0))
     finally:
         ctx.set_splits(0)
         ctx.set_pair_mode(None)
     ctx.force_general(True)
     got = util.run_gpu(ctx, case)
     ctx.force_general(False)
-    util.assert_close(got, ref, "general path")
+    util.assert_close(got, ref, "general path", stress=(scale == 1.0))
     assert ctx.device_status()[0] == 0
 
 
@@ -290,7 +290,8 @@ def test_kernel_mask_bit_exact_through_indicator_values(ctx, force_general, P, W
     for t in range(T):
         onehot[t, :, t] = 1.0
     kv = KvCache(ctx, layer, T)
-    kv.load_prefix(torch.zeros(P, 8, 256, dtype=torch.bfloat16).to(DEV), onehot[:P].to(DEV), 0)
+    if P > 0:
+        kv.load_prefix(torch.zeros(P, 8, 256, dtype=torch.bfloat16).to(DEV), onehot[:P].to(DEV), 0)
     att = CanvasAttention(ctx, layer)
     q = torch.zeros(canvas, 16, 256, dtype=torch.bfloat16, device=DEV)
     kc = torch.zeros(canvas, 8, 256, dtype=torch.bfloat16, device=DEV)
@@ -456,7 +457,7 @@ def test_pair_kernel_parity(ctx, P, Hkv, W, mode, scale, canvas):
     try:
         for splits in (0, 1, 2, 3, 4):
             ctx.set_splits(splits)
-            util.assert_close(util.run_gpu(ctx, case), ref, f"pair kernel splits={splits}")
+            util.assert_close(util.run_gpu(ctx, case), ref, f"pair kernel splits={splits}", stress=(scale == 1.0))
     finally:
         ctx.set_splits(0)
         ctx.set_pair_mode(None)
@@ -541,13 +542,13 @@ def test_hd512_tensor_path_parity(ctx, P, Hq, Hkv, canvas, W, mode, scale, vnorm
     try:
         for splits in (0, 1, 2, 5):
             ctx.set_splits(splits)
-            util.assert_close(util.run_gpu(ctx, case), ref, f"hd512 tensor path splits={splits}")
+            util.assert_close(util.run_gpu(ctx, case), ref, f"hd512 tensor path splits={splits}", stress=(scale == 1.0))
     finally:
         ctx.set_splits(0)
     ctx.force_general(True)
     got = util.run_gpu(ctx, case)
     ctx.force_general(False)
-    util.assert_close(got, ref, "hd512 general path")
+    util.assert_close(got, ref, "hd512 general path", stress=(scale == 1.0))
     assert ctx.device_status()[0] == 0
 
 

@@ -87,16 +87,25 @@ def errors(got: np.ndarray, ref: np.ndarray):
 
 
 def max_abs_tol(ref: np.ndarray) -> float:
-    """2e-2 for outputs of magnitude <= 2 (every benchmark configuration).  bf16 has 8 significant
-    bits, so rounding the OUTPUT alone costs up to 2^-9 * 2^ceil(log2|o|): 7.8e-3 below 2, 1.6e-2 in
-    [2, 4), 3.1e-2 in [4, 8).  The unscaled-logit stress cases reach |o| > 4, so the bound grows in
+    """The bound of the STRESS cases only (unscaled logits, huge or tiny values): 2e-2 for outputs of
+    magnitude <= 2.  bf16 has 8 significant bits, so rounding the OUTPUT alone costs up to
+    2^-9 * 2^ceil(log2|o|): 7.8e-3 below 2, 1.6e-2 in [2, 4), 3.1e-2 in [4, 8); there the bound grows in
     proportion to the largest reference magnitude beyond 2."""
     return MAX_ABS_TOL * max(1.0, float(np.abs(ref).max()) / 2.0)
 
 
-def assert_close(got, ref, what=""):
+# every comparison that needed more than the flat 2e-2: (what, max-abs, bound used)
+RELAXED = []
+
+
+def assert_close(got, ref, what="", stress=False):
+    """max-abs <= 2e-2 and mean-abs <= 2e-3, flat.  Only a test that declares itself a stress case
+    (softmax_scale = 1 on N(0,1) inputs, values scaled by 2^14, ...) may use the bound that grows with the
+    output magnitude; such comparisons are recorded in RELAXED when they really exceeded 2e-2."""
     mx, mean = errors(got, ref)
     assert np.isfinite(got).all(), f"{what}: non-finite output"
-    tol = max_abs_tol(ref)
+    tol = max_abs_tol(ref) if stress else MAX_ABS_TOL
+    if mx > MAX_ABS_TOL and stress:
+        RELAXED.append((what, mx, tol))
     assert mx <= tol and mean <= MEAN_ABS_TOL, f"{what}: max-abs {mx:.3e} (tol {tol:.2e}) mean-abs {mean:.3e}"
     return mx, mean
