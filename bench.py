@@ -116,6 +116,14 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+_T0 = time.time()
+
+
+def log(msg: str) -> None:
+    """Progress on stderr (every rank; the JSON line on stdout stays alone)."""
+    print(f"[bench {time.time() - _T0:7.1f}s rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
+
+
 def _cfg(idx: int):
     from diffgemma_b200 import synthetic
     return synthetic.configs()[idx]
@@ -461,6 +469,7 @@ def _kernel_pass(ctx, timed, fn, steps):
 
 def measure_block(ctx, cfg_idx, world, rank, args, steps, timed, peaks, redraw=1, want_e2e=False):
     """A short measurement of one configuration for the `extra` object of the line."""
+    log(f"extra block: cfg {cfg_idx}")
     wl = Workload(ctx, cfg_idx, world, rank, args, redraw=redraw)
     try:
         par = wl.parity()
@@ -520,6 +529,7 @@ def run_stack(args, as_block=False):
     assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
     dev = torch.device("cuda", local)
     ctx = Context(local)
+    ctx.set_inputs_stable(True)        # resident inputs, written before the timed region
     comm = _nccl_comm(ctx, None) if world > 1 else None
     P, B = 16384, 4
     layers = synthetic.stack_layers()
@@ -579,6 +589,7 @@ def run_stack(args, as_block=False):
 
     # ---- parity: the seeded canvas 0 of layers 0 and 5, every rank's block of the gathered output against the oracle
     mx, tot, cnt = 0.0, 0.0, 0
+    log("stack: caches built; parity of layers 0 and 5")
     for li in (0, 5):
         lay = layers[li]
         step(upto=li + 1)                                   # the shared output buffers then hold layer li
@@ -606,12 +617,15 @@ def run_stack(args, as_block=False):
               "gate": {"max_abs": MAX_ABS_GATE, "mean_abs": MEAN_ABS_GATE}}
     parity["ok"] = bool(cnt > 0 and mx <= MAX_ABS_GATE and parity["mean_abs"] <= MEAN_ABS_GATE) if rank == 0 else True
 
+    log(f"stack: parity {parity['max_abs']:.3e} / {parity['mean_abs']:.3e}; warm-up")
     warm = max(3, args.warmup)
     for _ in range(warm):
         step()
     ctx.synchronize()
     graph = None
-    if not args.stack_eager:
+    # one rank per GPU: the per-layer all-gathers are issued eagerly (a NCCL collective inside a replayed graph
+    # is left out of the measured path); one GPU: the step is one CUDA graph
+    if not args.stack_eager and world == 1:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=ctx.torch_stream):
             step()
@@ -700,17 +714,24 @@ def run_ours(args):
     ctx = Context(local)
     if args.kernel_form != "auto":
         ctx.set_pair_mode(args.kernel_form == "pair")
+    # the inputs of the timed steps are resident tensors written before the timed region, never by work queued
+    # ahead of a step: the library may start a step's Q prologue while the previous step drains
+    ctx.set_inputs_stable(True)
     peaks = _peaks()
     redraw = 48 if args.cfg == 4 else 1          # configuration 4: a block of 48 steps, Q/K/V re-drawn per step
+    log(f"building workload cfg {args.cfg} on {world} GPU(s)")
     wl = Workload(ctx, args.cfg, world, rank, args, redraw=redraw)
     lay, P, flops = wl.lay, wl.P, wl.flops
     timed = _timer(world, dev, ctx.torch_stream)
+    log("parity check of one step against the oracle")
     parity = wl.parity()
+    log(f"parity {parity['max_abs']:.3e} / {parity['mean_abs']:.3e}; timing {args.steps} steps")
 
     warm = max(3, args.warmup)
     with ClockSampler(local) as clk:
         # device-resident arm
         ms_dev = timed(wl.step_dev, args.steps, warm)
+        log(f"device-resident: {ms_dev * 1e3:.1f} us per step; kernel-timed pass")
         mark = clk.mark()
         k_avg_ms, k_n = _kernel_pass(ctx, timed, wl.step_dev, args.steps)
         launches_per_step = ctx.last_launch_count
@@ -720,6 +741,7 @@ def run_ours(args):
         sustained = None
         if ms_dev * args.steps < 1000.0 and not args.no_sustained:
             n_sus = int(min(60000, math.ceil(1200.0 / ms_dev)))
+            log(f"sustained loop of {n_sus} steps")
             timed(wl.step_dev, max(1, n_sus // 3), 0)          # reach the steady clock first
             mark = clk.mark()
             ms_sus = timed(wl.step_dev, n_sus, 0)
@@ -733,8 +755,10 @@ def run_ours(args):
                          "sm_mhz_median": cs["sm_mhz"], "reasons": cs["reasons"],
                          "kernel_ms_x_sm_mhz": ks_ms * cs["sm_mhz"] if (ks_ms and cs["sm_mhz"]) else None}
         # end-to-end arm: host buffers, H2D + kernels + D2H every step
+        log("end-to-end arm (host buffers)")
         wl.host_setup()
         ms_e2e = timed(wl.step_host, args.steps, warm, wl.finish_host)
+        log(f"end to end: {ms_e2e * 1e3:.1f} us per step")
     st = ctx.device_status()
     assert st[0] == 0, f"device status {st}"
 
@@ -804,7 +828,9 @@ def run_ours(args):
     ctx.close()
     stack_blk = None
     if args.cfg == 2 and not args.no_extra and not args.no_stack:
+        log("extra block: 30-layer stack")
         stack_blk = run_stack(args, as_block=True)          # builds its own context; every rank takes part
+    log("done")
     if rank == 0:
         if stack_blk is not None:
             line.setdefault("extra", {})["cfg3_stack30_p16384_batch4"] = stack_blk

@@ -57,6 +57,8 @@ SIGNATURES = {
     "dg_uses_tensor_path": (_i32, [_pd]),
     "dg_ctx_force_general": (_i32, [_vp, _i32]),
     "dg_ctx_set_splits": (_i32, [_vp, _u32]),
+    "dg_ctx_set_fused_append": (_i32, [_vp, _i32]),
+    "dg_ctx_set_inputs_stable": (_i32, [_vp, _i32]),
     "dg_ctx_set_pair_mode": (_i32, [_vp, _i32]),
     "dg_ctx_max_active_clusters": (_i32, [_vp, _i32, _u32]),
     "dg_kv_create": (_i32, [_vp, _pd, _u64, C.POINTER(_vp)]),

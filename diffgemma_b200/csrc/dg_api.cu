@@ -52,10 +52,6 @@ struct dg_ctx {
   cudaStream_t own_stream = nullptr;
   cudaStream_t stream = nullptr;
   DevStatus* d_status = nullptr;
-  // canvases of one batched call run concurrently on side streams (forked from / joined to `stream`)
-  cudaStream_t side[8] = {};
-  cudaEvent_t side_fork = nullptr, side_join[8] = {};
-  cudaStream_t side_active = nullptr;  // non-null while a canvas of a concurrent batch is being enqueued
   uint32_t concurrent = 1;             // canvases in flight together: the split heuristic counts their CTAs
   uint32_t* counters = nullptr;        // [kCounterSlots], zero between launches
   float* ws_o = nullptr;               // split partials
@@ -70,6 +66,8 @@ struct dg_ctx {
   float* nccl_mg = nullptr;            // [rows]
   size_t nccl_rows = 0, nccl_d = 0;
   int force_general = 0;
+  int fused_append = 1;                // 1: the canvas append runs inside the attention launch where it can
+  int inputs_stable = 0;               // 1: the caller's q/k/v are not written by work queued ahead of a call
   int pair_mode = 2;                   // tensor path: 0 single-CTA kernel, 1 CTA-pair (cta_group::2) kernel, 2 automatic
   uint32_t forced_splits = 0;
   uint32_t last_launches = 0;
@@ -98,6 +96,7 @@ struct dg_kv {
   // invisible to the host, so a table a graph writes lives in region 1, which only that graph reads.
   float2* rope_table = nullptr;
   RopeKey rope_key;
+  uint32_t* ap_ctl = nullptr;   // {ticket, vectors done, CTAs finished} of the in-launch canvas append; zero between launches
   __nv_bfloat16* k = nullptr;   // [Hkv][cap][D]
   __nv_bfloat16* v = nullptr;
   uint64_t cap = 0;
@@ -319,11 +318,6 @@ extern "C" int32_t dg_ctx_destroy(dg_ctx* c) {
   cudaSetDevice(c->device);
   if (c->stream) cudaStreamSynchronize(c->stream);
   cudaFree(c->d_status);
-  for (int i = 0; i < 8; ++i) {
-    if (c->side[i]) cudaStreamDestroy(c->side[i]);
-    if (c->side_join[i]) cudaEventDestroy(c->side_join[i]);
-  }
-  if (c->side_fork) cudaEventDestroy(c->side_fork);
   cudaFree(c->counters);
   cudaFree(c->ws_o);
   cudaFree(c->ws_ml);
@@ -408,6 +402,16 @@ extern "C" int32_t dg_ctx_set_pair_mode(dg_ctx* c, int32_t mode) {
   c->pair_mode = mode;
   return DG_OK;
 }
+extern "C" int32_t dg_ctx_set_fused_append(dg_ctx* c, int32_t on) {
+  if (!c) return fail(DG_ERR_INVALID_ARG, "ctx is NULL");
+  c->fused_append = on ? 1 : 0;
+  return DG_OK;
+}
+extern "C" int32_t dg_ctx_set_inputs_stable(dg_ctx* c, int32_t on) {
+  if (!c) return fail(DG_ERR_INVALID_ARG, "ctx is NULL");
+  c->inputs_stable = on ? 1 : 0;
+  return DG_OK;
+}
 extern "C" int32_t dg_ctx_set_splits(dg_ctx* c, uint32_t n) {
   if (!c) return fail(DG_ERR_INVALID_ARG, "ctx is NULL");
   if (n > kSm100MaxSplits) return fail(DG_ERR_INVALID_ARG, "at most 32 splits");
@@ -477,6 +481,8 @@ static int32_t kv_create(dg_ctx* c, const dg_layer_desc* d, uint64_t capacity_to
   if (e == cudaSuccess) e = cudaMemsetAsync(kv->k, 0, bytes, c->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(kv->v, 0, bytes, c->stream);
   if (e == cudaSuccess) e = cudaMalloc(&kv->rope_table, 2 * size_t(kMaxCanvas) * (kv->D / 2) * sizeof(float2));
+  if (e == cudaSuccess) e = cudaMalloc(&kv->ap_ctl, 4 * sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMemsetAsync(kv->ap_ctl, 0, 4 * sizeof(uint32_t), c->stream);
   if (e != cudaSuccess) {
     dg_kv_destroy(kv);
     return fail_cuda(e, "dg_kv_create");
@@ -529,6 +535,7 @@ extern "C" int32_t dg_kv_destroy(dg_kv* kv) {
   cudaFree(kv->k);
   cudaFree(kv->v);
   cudaFree(kv->rope_table);
+  cudaFree(kv->ap_ctl);
   delete kv;
   return DG_OK;
 }
@@ -640,11 +647,10 @@ static int32_t check_ring_span(const dg_kv* kv, const MaskParams& mk, uint32_t c
   return DG_OK;
 }
 
-// append n tokens (norm + RoPE + cache write); optionally also Q (stage 1) and the RoPE table
-// stream the kernels of the current call go to: the context's, or a side stream while the canvases of
-// a batch run concurrently
-static cudaStream_t launch_stream(const dg_ctx* c) { return c->side_active ? c->side_active : c->stream; }
+// stream the kernels of the current call go to
+static cudaStream_t launch_stream(const dg_ctx* c) { return c->stream; }
 
+// append n tokens (norm + RoPE + cache write); optionally also Q (stage 1) and the RoPE table
 static int32_t do_append(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint64_t pos0, uint32_t n, const void* q_in,
                          void* q_out, const void* k_in, void* k_out, const void* v_in, void* v_out, const void* qw,
                          const void* kw, float2* table, uint32_t write_end = 0xffffffffu,
@@ -710,7 +716,18 @@ extern "C" int32_t dg_kv_append_guarded(dg_ctx* c, const dg_layer_desc* d, dg_kv
 // ------------------------------------------------------------------------------------------
 // attention launch (stage 2), shared by every entry point
 // ------------------------------------------------------------------------------------------
+// A head_dim-256 tensor-kernel launch that has been prepared but not issued: the canvases of a batch are
+// collected and go out as one launch.
+struct Prepared {
+  bool filled = false;
+  bool pair = false;
+  AttnParams p;
+  const CUtensorMap* tm_k = nullptr;
+  const CUtensorMap* tm_v = nullptr;
+};
+
 struct AttnCall {
+  Prepared* defer = nullptr;     // non-null: do not launch the head_dim-256 tensor kernel, describe it here
   const void* q = nullptr;       // [C][Hq][D]
   const void* qw = nullptr;
   const float2* table = nullptr;
@@ -723,6 +740,11 @@ struct AttnCall {
   float* out_l = nullptr;
   uint32_t kv_len = 0, t0 = 0, t1 = 0xffffffffu;
   int include_canvas = 1;
+  // canvas append inside the attention launch (raw canvas K / V, K norm weight); null: already appended
+  const void* ap_k = nullptr;
+  const void* ap_v = nullptr;
+  const void* ap_kw = nullptr;
+  uint32_t ap_write_end = 0xffffffffu;
 };
 
 // A split workspace that the caller provides instead of the context's grown cudaMalloc buffers
@@ -771,9 +793,22 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
   p.pair_off = d.rope_pairing == DG_ROPE_SPLIT_HALF ? d.rotary_dim / 2 : d.head_dim / 2;
   p.scale_log2 = d.softmax_scale * 1.4426950408889634f;
   p.eps = d.rms_eps;
+  if (a.ap_k != nullptr) {
+    p.ap_k = static_cast<const __nv_bfloat16*>(a.ap_k);
+    p.ap_v = static_cast<const __nv_bfloat16*>(a.ap_v);
+    p.ap_kw = static_cast<const __nv_bfloat16*>(a.ap_kw);
+    p.ap_cache_k = kv->k;
+    p.ap_cache_v = kv->v;
+    p.ap_ctl = kv->ap_ctl;
+    p.ap_vectors = d.canvas * 2u * d.n_kv_heads;
+    p.ap_v_norm = d.v_norm;
+    p.ap_write_end = a.ap_write_end;
+  }
 
   const bool tensor = tensor_path_ok(d) && kv->has_tmap && !c->force_general && a.attend == nullptr &&
                       (a.q_prenormed || fused_q_prologue_ok(d));
+  if (a.ap_k != nullptr && !(tensor && d.head_dim == 256))
+    return fail(DG_ERR_INVALID_ARG, "internal: in-launch append needs the head_dim-256 tensor kernel");
   if (!tensor) {
     launch_attn_general(p, launch_stream(c));
     DG_CUDA(cudaGetLastError());
@@ -804,7 +839,7 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
       p.ws_ml = c->ws_ml;
       p.ws_counters = c->counters;
     }
-    const bool timed5 = c->timing && c->side_active == nullptr && c->ev_used + 2 <= c->ev.size();
+    const bool timed5 = c->timing && c->ev_used + 2 <= c->ev.size();
     if (timed5) DG_CUDA(cudaEventRecord(c->ev[c->ev_used], c->stream));
     const cudaError_t e5 = launch_attn_sm100_hd512(p, kv->tm_k, kv->tm_v, launch_stream(c));
     if (e5 != cudaSuccess) return fail_cuda(e5, "launch_attn_sm100_hd512");
@@ -851,7 +886,15 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
     p.ws_ml = c->ws_ml;
     p.ws_counters = c->counters;
   }
-  const bool timed = c->timing && c->side_active == nullptr && c->ev_used + 2 <= c->ev.size();
+  if (a.defer != nullptr) {
+    a.defer->filled = true;
+    a.defer->pair = pair;
+    a.defer->p = p;
+    a.defer->tm_k = pair ? &kv->tm_k64 : &kv->tm_k;
+    a.defer->tm_v = &kv->tm_v;
+    return DG_OK;
+  }
+  const bool timed = c->timing && c->ev_used + 2 <= c->ev.size();
   if (timed) DG_CUDA(cudaEventRecord(c->ev[c->ev_used], c->stream));
   const cudaError_t e = pair ? launch_attn_sm100_pair(p, kv->tm_k64, kv->tm_v, launch_stream(c))
                              : launch_attn_sm100(p, kv->tm_k, kv->tm_v, launch_stream(c));
@@ -899,9 +942,28 @@ static int32_t denoise_one(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint32_
     // eager: region 0, rewritten when the key changes.  captured: region 0 read-only when it already
     // holds these positions, else region 1, written and read by the recorded launches themselves.
     float2* table = kv->rope_table + ((capturing && !cached) ? size_t(kMaxCanvas) * (kv->D / 2) : 0);
-    r = do_append(c, d, kv, kv_len, d.canvas, nullptr, nullptr, k, nullptr, v, nullptr, nullptr, kw, cached ? nullptr : table,
-                  0xffffffffu, cached ? table : nullptr);
-    if (r != DG_OK) return r;
+    // what of the canvas positions this cache stores at all (a shard may hold none of them)
+    uint32_t write_end = 0xffffffffu;
+    if (kv->shard) {
+      const uint64_t end = uint64_t(kv->pos_base) + kv->cap;
+      if (end < write_end) write_end = uint32_t(end);
+    }
+    const bool stores_canvas = write_end > kv_len;
+    // With the table in memory the append can run inside the attention launch (one kernel per step);
+    // the first step at new positions still goes through the stand-alone kernel, which writes the table.
+    const bool in_launch = cached && tensor && c->fused_append && d.head_dim == 256;
+    if (in_launch) {
+      if (stores_canvas) {
+        a.ap_k = k;
+        a.ap_v = v;
+        a.ap_kw = kw;
+        a.ap_write_end = write_end;
+      }
+    } else if (stores_canvas || !cached) {
+      r = do_append(c, d, kv, kv_len, d.canvas, nullptr, nullptr, k, nullptr, v, nullptr, nullptr, kw, cached ? nullptr : table,
+                    0xffffffffu, cached ? table : nullptr);
+      if (r != DG_OK) return r;
+    }
     if (!cached && !capturing) {
       key.valid = true;
       key.kv_len = kv_len;
@@ -915,7 +977,11 @@ static int32_t denoise_one(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint32_
     a.qw = qw;
     a.table = table;
     a.q_prenormed = false;
-    a.early_q = cached;
+    // the Q prologue may start before the kernel ahead of this launch has drained when nothing it reads
+    // (Q, its weight, the table) comes from that kernel: the stand-alone append kernel is known not to
+    // write them; with the append inside the launch the kernel ahead is the caller's, so the caller must
+    // have said that its inputs are stable
+    a.early_q = in_launch ? (c->inputs_stable != 0) : cached;
   }
   a.kv_len = kv_len;
   a.attend = attend;
@@ -963,13 +1029,12 @@ extern "C" int32_t dg_attn_denoise(dg_ctx* c, const dg_layer_desc* d, dg_kv* con
   DG_CUDA(cudaSetDevice(c->device));
   c->last_launches = 0;
   const size_t qe = size_t(d->canvas) * d->n_q_heads * d->head_dim, ke = size_t(d->canvas) * d->n_kv_heads * d->head_dim;
-  // Independent canvases run CONCURRENTLY when nothing they use is shared: one side stream per canvas,
-  // forked from and joined to the context's stream, and a split count chosen for all their CTAs
-  // together (short key ranges then need no key split at all and so no merge).  That holds on the fused
-  // tensor path with splits merged inside clusters; anything that needs the shared staging buffer or
-  // the split workspace runs one canvas after the other.
+  // Independent canvases go out as ONE launch (grid z = canvas) when nothing they use is shared, with a
+  // split count chosen for all their CTAs together (short key ranges then need no key split at all and so
+  // no merge).  That holds on the fused tensor path with splits merged inside clusters; anything that
+  // needs the shared staging buffer or the split workspace runs one canvas after the other.
   bool concurrent = batch > 1 && batch <= 8 && d->head_dim == 256 && tensor_path_ok(*d) && fused_q_prologue_ok(*d) &&
-                    !c->force_general && !c->timing && c->stamps == nullptr;
+                    !c->force_general && !c->timing;
   for (uint32_t b = 0; concurrent && b < batch; ++b) concurrent = kv[b] != nullptr && kv[b]->has_tmap;
   uint32_t conc_splits = 0;
   bool conc_pair = false;
@@ -994,38 +1059,50 @@ extern "C" int32_t dg_attn_denoise(dg_ctx* c, const dg_layer_desc* d, dg_kv* con
   }
   const uint32_t saved_splits = c->forced_splits;
   const int saved_pair = c->pair_mode;
+  int32_t rc = DG_OK;
   if (concurrent) {
-    if (!c->side_fork) DG_CUDA(cudaEventCreateWithFlags(&c->side_fork, cudaEventDisableTiming));
-    for (uint32_t b = 0; b < batch; ++b) {
-      if (!c->side[b]) DG_CUDA(cudaStreamCreateWithFlags(&c->side[b], cudaStreamNonBlocking));
-      if (!c->side_join[b]) DG_CUDA(cudaEventCreateWithFlags(&c->side_join[b], cudaEventDisableTiming));
-    }
-    DG_CUDA(cudaEventRecord(c->side_fork, c->stream));
+    // one launch per group of up to kMaxBatchLaunch canvases (blockIdx.z = canvas): the appends that are
+    // still needed (first step at new positions) are queued first, the attention launches are described
+    // by denoise_one and issued together
     c->concurrent = batch;
     c->forced_splits = conc_splits;
     c->pair_mode = conc_pair ? 1 : 0;
-  }
-  int32_t rc = DG_OK;
-  for (uint32_t b = 0; b < batch && rc == DG_OK; ++b) {
-    AttnCall a;
-    a.out = static_cast<__nv_bfloat16*>(out) + b * qe;
-    if (concurrent) {
-      c->side_active = c->side[b];
-      if (cudaStreamWaitEvent(c->side[b], c->side_fork, 0) != cudaSuccess) rc = fail(DG_ERR_CUDA, "cudaStreamWaitEvent");
-    }
-    if (rc == DG_OK)
+    Prepared prep[8];
+    for (uint32_t b = 0; b < batch && rc == DG_OK; ++b) {
+      AttnCall a;
+      a.out = static_cast<__nv_bfloat16*>(out) + b * qe;
+      a.defer = &prep[b];
       rc = denoise_one(c, *d, kv[b], kv_len[b], b, static_cast<const __nv_bfloat16*>(q) + b * qe,
                        static_cast<const __nv_bfloat16*>(k) + b * ke, static_cast<const __nv_bfloat16*>(v) + b * ke, qw, kw,
                        nullptr, a);
-    if (concurrent) {
-      // join whatever was enqueued, also after an error, so that the context's stream stays ordered
-      if (cudaEventRecord(c->side_join[b], c->side[b]) == cudaSuccess) cudaStreamWaitEvent(c->stream, c->side_join[b], 0);
+      if (rc == DG_OK && !prep[b].filled) rc = fail(DG_ERR_INVALID_ARG, "internal: batched canvas did not take the tensor path");
     }
+    c->concurrent = 1;
+    c->forced_splits = saved_splits;
+    c->pair_mode = saved_pair;
+    for (uint32_t b0 = 0; b0 < batch && rc == DG_OK; b0 += kMaxBatchLaunch) {
+      const uint32_t n = batch - b0 < kMaxBatchLaunch ? batch - b0 : kMaxBatchLaunch;
+      AttnParams ps[kMaxBatchLaunch];
+      const CUtensorMap* tk[kMaxBatchLaunch];
+      const CUtensorMap* tv[kMaxBatchLaunch];
+      for (uint32_t i = 0; i < n; ++i) {
+        ps[i] = prep[b0 + i].p;
+        tk[i] = prep[b0 + i].tm_k;
+        tv[i] = prep[b0 + i].tm_v;
+      }
+      const cudaError_t e = launch_attn_sm100_batch(ps, tk, tv, n, prep[b0].pair, c->stream);
+      if (e != cudaSuccess) rc = fail_cuda(e, "launch_attn_sm100_batch");
+      c->last_launches += 1;
+    }
+    return rc;
   }
-  c->side_active = nullptr;
-  c->concurrent = 1;
-  c->forced_splits = saved_splits;
-  c->pair_mode = saved_pair;
+  for (uint32_t b = 0; b < batch && rc == DG_OK; ++b) {
+    AttnCall a;
+    a.out = static_cast<__nv_bfloat16*>(out) + b * qe;
+    rc = denoise_one(c, *d, kv[b], kv_len[b], b, static_cast<const __nv_bfloat16*>(q) + b * qe,
+                     static_cast<const __nv_bfloat16*>(k) + b * ke, static_cast<const __nv_bfloat16*>(v) + b * ke, qw, kw,
+                     nullptr, a);
+  }
   return rc;
 }
 
@@ -1164,7 +1241,14 @@ extern "C" int32_t dg_host_pipe_submit(dg_host_pipe* hp, const dg_layer_desc* d,
   // kernels: after this slot's inputs have landed and its previous output has left
   DG_CUDA(cudaStreamWaitEvent(c->stream, sl.in, 0));
   if (sl.used) DG_CUDA(cudaStreamWaitEvent(c->stream, sl.out, 0));
-  r = dg_attn_denoise(c, d, kv, kv_len, batch, sl.q, sl.k, sl.v, qw, kw, sl.o);
+  {
+    // the slot's staging buffers are complete before the kernels may start (they wait for sl.in) and are
+    // not rewritten before sl.cmp: the Q prologue may read them as early as it likes
+    const int saved = c->inputs_stable;
+    c->inputs_stable = 1;
+    r = dg_attn_denoise(c, d, kv, kv_len, batch, sl.q, sl.k, sl.v, qw, kw, sl.o);
+    c->inputs_stable = saved;
+  }
   if (r != DG_OK) return r;
   DG_CUDA(cudaEventRecord(sl.cmp, c->stream));
   // copy out
@@ -1214,7 +1298,12 @@ extern "C" int32_t dg_host_pipe_submit_split(dg_host_pipe* hp, const dg_layer_de
   DG_CUDA(cudaEventRecord(sl.in, hp->h2d));
   DG_CUDA(cudaStreamWaitEvent(c->stream, sl.in, 0));
   if (sl.used) DG_CUDA(cudaStreamWaitEvent(c->stream, sl.out, 0));
-  r = dg_attn_denoise_split_p2p(c, d, kv, kv_len, t0, t1, include_canvas, x, sl.q, sl.k, sl.v, qw, kw, sl.o);
+  {
+    const int saved = c->inputs_stable;   // as in dg_host_pipe_submit
+    c->inputs_stable = 1;
+    r = dg_attn_denoise_split_p2p(c, d, kv, kv_len, t0, t1, include_canvas, x, sl.q, sl.k, sl.v, qw, kw, sl.o);
+    c->inputs_stable = saved;
+  }
   if (r != DG_OK) return r;
   DG_CUDA(cudaEventRecord(sl.cmp, c->stream));
   DG_CUDA(cudaStreamWaitEvent(hp->d2h, sl.cmp, 0));

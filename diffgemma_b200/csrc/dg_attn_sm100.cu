@@ -38,6 +38,7 @@
 //   fully masked row -> 0), src/shaders/include/attention_device.metal:154-165 ((m, l, O) state).
 #include <cuda.h>
 
+#include "dg_append_vec.cuh"
 #include "dg_attn_sm100_common.cuh"
 #include "dg_kernels.h"
 
@@ -84,11 +85,14 @@ __device__ __forceinline__ void row_group_sync(uint32_t smw) {
 // for S, 128 of the 256 value columns for O), so every K/V byte enters an SM's shared memory once
 // per pair and is read from it half as often.  tm_k then has boxes {64 d, 64 keys}.  No load uses
 // multicast.
+// blockIdx.z selects one of the independent canvases of the launch: its parameters and tensor maps.
 template <bool PAIR>
 __global__ void __launch_bounds__(one::THREADS, 1)
-dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_k,
-                     const __grid_constant__ CUtensorMap tm_v) {
+dg_attn_sm100_kernel(const __grid_constant__ AttnBatch bat) {
   using namespace one;
+  const AttnParams& p = bat.p[blockIdx.z];
+  const CUtensorMap& tm_k = bat.tm_k[blockIdx.z];
+  const CUtensorMap& tm_v = bat.tm_v[blockIdx.z];
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -154,6 +158,12 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       if (++g == p.G) { g = 0; ++i; }
     }
   };
+  // Let the kernel that follows this one on the stream be scheduled as soon as SMs free up, if it was
+  // launched to allow that (the library's own append, attention and merge kernels are; each of them waits
+  // for this grid's completion before it touches anything this grid reads or writes).  Every CTA of this
+  // grid has started by the time the last one executes this, so a waiting successor never keeps a CTA of
+  // this grid off the device.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (p.early_q && warp < SM_WARPS) issue_q_rows();
   stamp(p, 0);
   // ------------------------------------------------------------------ set-up
@@ -244,24 +254,35 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
           wq2[e] = mul_f32x2(bf16x2_to_f32x2(wq[e]), sgn2);
         }
         uint64_t A[4], B[4];   // w cos and -/+ w_partner sin of this lane's eight pairs
-        auto load_table = [&](uint32_t i) {
+        float4 raw[4];         // the table entries of the NEXT canvas row, requested one canvas row ahead
+        auto fetch_table = [&](uint32_t i) {
           // (cos, sin) of the pairs 8 c16 .. 8 c16 + 7 of canvas row i
-          const float4* tab = reinterpret_cast<const float4*>(p.rope_table + size_t(i) * 128 + c16 * 8u);
+          const float4* tab = reinterpret_cast<const float4*>(p.rope_table + size_t(i < p.C ? i : p.C - 1u) * 128 + c16 * 8u);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) raw[e] = tab[e];
+        };
+        auto use_table = [&]() {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float4 cs = tab[e];
-            A[e] = mul_f32x2(wm2[e], pack_f32x2(cs.x, cs.z));
-            B[e] = mul_f32x2(wq2[e], pack_f32x2(cs.y, cs.w));
+            A[e] = mul_f32x2(wm2[e], pack_f32x2(raw[e].x, raw[e].z));
+            B[e] = mul_f32x2(wq2[e], pack_f32x2(raw[e].y, raw[e].w));
           }
         };
-        if (R0 < rows_per_head) load_table(i0);
+        if (R0 < rows_per_head) fetch_table(i0);
         cp_async_wait_all();
         __syncwarp();
         uint32_t i = i0, g = g0;
+        if (R0 < rows_per_head) {
+          use_table();
+          fetch_table(i0 + 1u);   // in flight while the rows of canvas row i0 are worked on
+        }
 #pragma unroll
         for (uint32_t it = 0; it < RPW; ++it) {
           if (R0 + it >= rows_per_head) break;   // warp-uniform
-          if (it != 0 && g == 0) load_table(i);
+          if (it != 0 && g == 0) {
+            use_table();
+            fetch_table(i + 1u);
+          }
           const uint32_t off = it * 128u + (((c & 7u) ^ it) << 4);
           const uint4 xm = *reinterpret_cast<const uint4*>(q_own + off);
           const uint4 xq = *reinterpret_cast<const uint4*>(q_par + off);
@@ -303,6 +324,48 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       if (PAIR) mbar_arrive_cluster(lead_bar(B_Q)); else mbar_arrive(bar_addr(bar_base, B_Q));
     }
     stamp(p, 2);
+
+    // ---------------------------------------------------------------- canvas append inside the launch
+    // Every CTA takes a ticket when it gets here and appends the share of the canvas K / V head vectors
+    // that the ticket names, so every share belongs to a CTA that is already running: whoever waits for
+    // the append (the loaders, before a key tile that holds canvas positions) waits only for CTAs that
+    // need nothing from anybody to finish their share.  The window between "Q is ready" and the first
+    // score tile is otherwise idle for these warps.  The ticket counter wraps by itself; the last CTA
+    // to leave the kernel clears the done counter.
+    if (p.ap_vectors != 0u) {
+      if (p.early_q) asm volatile("griddepcontrol.wait;" ::: "memory");   // the cache may still be in use ahead of us
+      const uint32_t n_ctas = gridDim.x * gridDim.y;
+      if (tid == 0) ctl[3] = atomicInc(p.ap_ctl, n_ctas - 1u);
+      asm volatile("bar.sync 5, %0;" ::"n"(SM_WARPS * 32) : "memory");
+      const uint32_t ticket = ctl[3];
+      const uint32_t per = (p.ap_vectors + n_ctas - 1u) / n_ctas;
+      const uint32_t v0 = ticket * per, v1 = (v0 + per < p.ap_vectors) ? v0 + per : p.ap_vectors;
+      if (v0 + warp < v1) {
+        AppendVecArgs av;
+        av.k_in = p.ap_k;
+        av.v_in = p.ap_v;
+        av.kw = p.ap_kw;
+        av.table = p.rope_table;
+        av.cache_k = p.ap_cache_k;
+        av.cache_v = p.ap_cache_v;
+        av.cap = p.cap;
+        av.pos0 = mk.kv_len;
+        av.Hkv = p.Hkv;
+        av.v_norm = p.ap_v_norm;
+        av.ring_mask = p.ring_mask;
+        av.write_end = p.ap_write_end;
+        av.pos_base = p.pos_base;
+        av.eps = p.eps;
+        uint32_t mine = 0;
+        for (uint32_t v = v0 + warp; v < v1; v += SM_WARPS) {
+          append_table_vector(av, v, lane);
+          ++mine;
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(p.ap_ctl + 1, mine);
+      }
+    }
 
     // ---------------------------------------------------------------- softmax main loop
     const uint32_t R = mt * BM + r;
@@ -399,9 +462,14 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   } else if (warp == W_K) {
     // ---------------------------------------------------------------- K loader
     if (lane == 0) {
+      bool canvas_ready = p.ap_vectors == 0u || mk.can_hi <= mk.kv_len;
       for (uint32_t n = 0; n < n_local; ++n) {
         const uint32_t v = v_begin + n;
         const uint32_t jt = v < ts.nA ? ts.a0 + v : ts.b0 + (v - ts.nA);
+        if (!canvas_ready && jt * BN + BN > mk.kv_len) {
+          if (!wait_counter_gpu(p.ap_ctl + 1, p.ap_vectors, abort_flag)) break;
+          canvas_ready = true;
+        }
         if (PAIR) {
           // this CTA's 64 keys of the tile into stage n & 1
           const uint32_t st = n & 1u, u = n >> 1;
@@ -425,9 +493,14 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
   } else if (warp == W_V) {
     // ---------------------------------------------------------------- V loader
     if (lane == 0) {
+      bool canvas_ready = p.ap_vectors == 0u || mk.can_hi <= mk.kv_len;
       for (uint32_t n = 0; n < n_local; ++n) {
         const uint32_t v = v_begin + n;
         const uint32_t jt = v < ts.nA ? ts.a0 + v : ts.b0 + (v - ts.nA);
+        if (!canvas_ready && jt * BN + BN > mk.kv_len) {
+          if (!wait_counter_gpu(p.ap_ctl + 1, p.ap_vectors, abort_flag)) break;
+          canvas_ready = true;
+        }
         if (PAIR) {
           // this CTA's 128 value columns of the tile into stage n & 1
           const uint32_t st = n & 1u, u = n >> 1;
@@ -591,7 +664,11 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
       const uint32_t src_rank = PAIR ? (crank >> 1) : crank;
       const uint32_t owner_split = r / rpc, rl = r % rpc;
       const uint32_t owner = PAIR ? ((owner_split << 1) | xi) : owner_split;
-      const uint32_t dst_row = dsmem_addr(smem_base + OFF_Q + ((src_rank * rpc + rl) * HBUF_LD) * 2u, owner);
+      // rows this CTA owns itself stay in its own shared memory (plain stores): only the others' rows
+      // take the SM-to-SM path
+      const bool own = owner == crank;
+      const uint32_t row_local = smem_base + OFF_Q + ((src_rank * rpc + rl) * HBUF_LD) * 2u;
+      const uint32_t dst_row = own ? row_local : dsmem_addr(row_local, owner);
       uint32_t oa[32], ob[32];
       if (have_o) {
         tmem_ld32(t_lane + TM_O + qd * OPT, oa);
@@ -625,12 +702,19 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
           ha[e] = pack_f16x2(__uint_as_float(oa[q4 * 8 + 2 * e]) * sc, __uint_as_float(oa[q4 * 8 + 2 * e + 1]) * sc);
           hb[e] = pack_f16x2(__uint_as_float(ob[q4 * 8 + 2 * e]) * sc, __uint_as_float(ob[q4 * 8 + 2 * e + 1]) * sc);
         }
-        dsmem_st_u4(dst_row + (qd * OPT + q4 * 8u) * 2u, make_uint4(ha[0], ha[1], ha[2], ha[3]));
-        dsmem_st_u4(dst_row + (qd * OPT + 32u + q4 * 8u) * 2u, make_uint4(hb[0], hb[1], hb[2], hb[3]));
+        if (own) {
+          smem_st_u4(dst_row + (qd * OPT + q4 * 8u) * 2u, make_uint4(ha[0], ha[1], ha[2], ha[3]));
+          smem_st_u4(dst_row + (qd * OPT + 32u + q4 * 8u) * 2u, make_uint4(hb[0], hb[1], hb[2], hb[3]));
+        } else {
+          dsmem_st_u4(dst_row + (qd * OPT + q4 * 8u) * 2u, make_uint4(ha[0], ha[1], ha[2], ha[3]));
+          dsmem_st_u4(dst_row + (qd * OPT + 32u + q4 * 8u) * 2u, make_uint4(hb[0], hb[1], hb[2], hb[3]));
+        }
       }
-      if (qd == 0)
-        dsmem_st_u4(dsmem_addr(smem_base + OFF_ML + (src_rank * rpc + rl) * 16u, owner),
-                    make_uint4(__float_as_uint(m_used), __float_as_uint(l_tot), __float_as_uint(inv_sc), 0u));
+      if (qd == 0) {
+        const uint32_t ml_local = smem_base + OFF_ML + (src_rank * rpc + rl) * 16u;
+        const uint4 rec = make_uint4(__float_as_uint(m_used), __float_as_uint(l_tot), __float_as_uint(inv_sc), 0u);
+        if (own) smem_st_u4(ml_local, rec); else dsmem_st_u4(dsmem_addr(ml_local, owner), rec);
+      }
     } else {
     const bool to_bf16 = direct && p.out != nullptr;
     const float inv_l = l_tot > 0.f ? 1.0f / l_tot : 0.f;
@@ -1024,6 +1108,15 @@ dg_attn_sm100_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_
     }
   }
   stamp(p, 5);
+  if (p.ap_vectors != 0u && tid == 0) {
+    // every CTA is past its own waits on the append counters by now; the last one to get here puts the
+    // done counter back to zero for the next launch (the ticket counter has wrapped to zero by itself)
+    const uint32_t n_ctas = gridDim.x * gridDim.y;
+    if (atomicInc(p.ap_ctl + 2, n_ctas - 1u) == n_ctas - 1u) {
+      p.ap_ctl[1] = 0u;
+      __threadfence();
+    }
+  }
 }
 
 cudaError_t sm100_attn_configure() {
@@ -1069,8 +1162,18 @@ uint32_t sm100_key_tiles(const MaskParams& mk) {
 }
 
 template <bool PAIR>
-static cudaError_t launch(const AttnParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, cudaStream_t st) {
-  const dim3 grid(PAIR ? sm100_pair_query_tiles(p.C, p.G, p.Hkv) : sm100_query_tiles(p.C, p.G, p.Hkv), p.n_splits);
+static cudaError_t launch(const AttnParams* ps, const CUtensorMap* const* tm_k, const CUtensorMap* const* tm_v, uint32_t n,
+                          cudaStream_t st) {
+  if (n == 0 || n > kMaxBatchLaunch) return cudaErrorInvalidValue;
+  AttnBatch bat;
+  for (uint32_t b = 0; b < kMaxBatchLaunch; ++b) {
+    const uint32_t src = b < n ? b : 0;   // unused entries repeat the first canvas
+    bat.p[b] = ps[src];
+    bat.tm_k[b] = *tm_k[src];
+    bat.tm_v[b] = *tm_v[src];
+  }
+  const AttnParams& p = ps[0];          // grid shape, split counts and cluster shape are the same for every canvas
+  const dim3 grid(PAIR ? sm100_pair_query_tiles(p.C, p.G, p.Hkv) : sm100_query_tiles(p.C, p.G, p.Hkv), p.n_splits, n);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(one::THREADS);
@@ -1093,17 +1196,26 @@ static cudaError_t launch(const AttnParams& p, const CUtensorMap& tm_k, const CU
   }
   cfg.attrs = attr;
   cfg.numAttrs = n_attr;
-  return cudaLaunchKernelEx(&cfg, dg_attn_sm100_kernel<PAIR>, p, tm_k, tm_v);
+  return cudaLaunchKernelEx(&cfg, dg_attn_sm100_kernel<PAIR>, bat);
 }
 
 cudaError_t launch_attn_sm100(const AttnParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
                               cudaStream_t st) {
-  return launch<false>(p, tm_k, tm_v, st);
+  const CUtensorMap* k = &tm_k;
+  const CUtensorMap* v = &tm_v;
+  return launch<false>(&p, &k, &v, 1, st);
 }
 // tm_k64: K tensor map with boxes {64 d, 64 keys, 1}
 cudaError_t launch_attn_sm100_pair(const AttnParams& p, const CUtensorMap& tm_k64, const CUtensorMap& tm_v,
                                    cudaStream_t st) {
-  return launch<true>(p, tm_k64, tm_v, st);
+  const CUtensorMap* k = &tm_k64;
+  const CUtensorMap* v = &tm_v;
+  return launch<true>(&p, &k, &v, 1, st);
+}
+// n <= kMaxBatchLaunch independent canvases in one launch (same geometry, split count and kernel form)
+cudaError_t launch_attn_sm100_batch(const AttnParams* p, const CUtensorMap* const* tm_k, const CUtensorMap* const* tm_v,
+                                    uint32_t n, bool pair, cudaStream_t st) {
+  return pair ? launch<true>(p, tm_k, tm_v, n, st) : launch<false>(p, tm_k, tm_v, n, st);
 }
 
 }  // namespace dg

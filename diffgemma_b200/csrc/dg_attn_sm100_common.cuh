@@ -70,12 +70,12 @@ __device__ __forceinline__ void stamp(const AttnParams& p, uint32_t slot) {
   if (p.stamps != nullptr && threadIdx.x == 0) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    p.stamps[(size_t(blockIdx.y) * gridDim.x + blockIdx.x) * STAMP_SLOTS + slot] = t;
+    p.stamps[((size_t(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * STAMP_SLOTS + slot] = t;
   }
 }
 __device__ __forceinline__ void stamp_cycles(const AttnParams& p, uint32_t slot, long long cycles) {
   if (p.stamps != nullptr)
-    p.stamps[(size_t(blockIdx.y) * gridDim.x + blockIdx.x) * STAMP_SLOTS + slot] = (unsigned long long)cycles;
+    p.stamps[((size_t(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * STAMP_SLOTS + slot] = (unsigned long long)cycles;
 }
 // runs a wait and, when profiling, adds the cycles it took to acc
 template <class F>

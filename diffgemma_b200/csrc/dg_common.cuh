@@ -3,6 +3,7 @@
 // construction), launch parameter blocks and the device status word.
 #pragma once
 #include <cstdint>
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -173,6 +174,28 @@ struct AttnParams {
   uint32_t rot_half, pair_off;
   float scale_log2;              // softmax_scale * log2(e)
   float eps;
+  // Canvas append folded into the attention launch (head_dim-256 tensor kernel, RoPE table already in
+  // memory): ap_vectors = canvas * 2 * Hkv head vectors of raw canvas K / V are normed, rotated and
+  // written to the cache by the launch's own CTAs before any of them loads a key tile that holds canvas
+  // positions.  0 = the cache already holds the canvas K / V.
+  const __nv_bfloat16* ap_k;     // [C][Hkv][256]
+  const __nv_bfloat16* ap_v;
+  const __nv_bfloat16* ap_kw;    // [256] or null
+  __nv_bfloat16* ap_cache_k;     // the cache, writable
+  __nv_bfloat16* ap_cache_v;
+  uint32_t* ap_ctl;              // {ticket, vectors done, CTAs finished}: zero between launches
+  uint32_t ap_vectors;
+  uint32_t ap_v_norm;
+  uint32_t ap_write_end;         // positions >= this are not stored (0xffffffff: none)
+};
+
+// Up to kMaxBatchLaunch independent canvases served by ONE launch of the head_dim-256 tensor kernel
+// (blockIdx.z = canvas): the kernel's whole parameter block, tensor maps first (64-byte aligned).
+constexpr uint32_t kMaxBatchLaunch = 4;
+struct alignas(64) AttnBatch {
+  CUtensorMap tm_k[kMaxBatchLaunch];
+  CUtensorMap tm_v[kMaxBatchLaunch];
+  AttnParams p[kMaxBatchLaunch];
 };
 
 // peer-to-peer split-KV merge (dg_p2p_merge.cu)

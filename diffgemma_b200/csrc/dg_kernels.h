@@ -34,6 +34,9 @@ cudaError_t sm100_pair_configure();
 cudaError_t launch_attn_sm100_pair(const AttnParams& p, const CUtensorMap& tm_k64, const CUtensorMap& tm_v,
                                    cudaStream_t st);
 uint32_t sm100_pair_query_tiles(uint32_t C, uint32_t G, uint32_t Hkv);
+// up to kMaxBatchLaunch independent canvases of one geometry, split count and kernel form in ONE launch
+cudaError_t launch_attn_sm100_batch(const AttnParams* p, const CUtensorMap* const* tm_k, const CUtensorMap* const* tm_v,
+                                    uint32_t n, bool pair, cudaStream_t st);
 int sm100_max_active_clusters(uint32_t cluster_y);        // single-CTA kernel, clusters (1, y, 1)
 int sm100_pair_max_active_clusters(uint32_t cluster_y);   // pair kernel, clusters (2, y, 1)
 // head_dim 512 (csrc/dg_attn_sm100_hd512.cu): tm_k / tm_v are {512, cap, Hkv} maps with boxes {64, 64, 1}

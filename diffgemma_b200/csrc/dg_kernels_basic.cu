@@ -6,6 +6,7 @@
 //   src/shaders/attn/qk_rope_kv/qk_rope_kv.metal:29-149, src/shaders/attn/cpu.rs:67-145 (stage 1)
 //   src/shaders/attn/attention/attention.metal:22-133, src/shaders/attn/cpu.rs:148-197 (stage 2)
 #include "dg_common.cuh"
+#include "dg_append_vec.cuh"
 #include "dg_kernels.h"
 
 namespace dg {
@@ -14,14 +15,6 @@ __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
-}
-// RoPE of the pair (x0, x1) = (element i, element i + pair offset), with the rounding spelled out so
-// that every kernel that rotates K produces the same bits
-__device__ __forceinline__ float rope_rotate_lo(float x0, float x1, float c, float s) {
-  return __fmaf_rn(x0, c, -__fmul_rn(x1, s));
-}
-__device__ __forceinline__ float rope_rotate_hi(float x0, float x1, float c, float s) {
-  return __fmaf_rn(x0, s, __fmul_rn(x1, c));
 }
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -117,64 +110,23 @@ __global__ void __launch_bounds__(256) dg_append_table_kernel(const AppendParams
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");   // see dg_append_kernel
   const uint32_t lane = threadIdx.x & 31u, w = blockIdx.x * 8u + (threadIdx.x >> 5);
-  const uint32_t per_tok = 2u * p.Hkv;
-  if (w >= p.n * per_tok) return;
-  const uint32_t tok = w / per_tok, slot = w % per_tok;
-  const bool is_k = slot < p.Hkv;
-  const uint32_t h = is_k ? slot : slot - p.Hkv;
-  const uint32_t pos = p.pos0 + tok;
-  // zero-padded tail of a chunk: must not wrap onto live ring slots; positions below a shard's base have no slot
-  if (pos >= p.write_end || pos < p.pos_base) return;
-  const uint4 x = reinterpret_cast<const uint4*>((is_k ? p.k_in : p.v_in) + (size_t(tok) * p.Hkv + h) * 256u)[lane];
-  uint4 y = x;
-  if (is_k || p.v_norm) {
-    const uint32_t m[4] = {x.x, x.y, x.z, x.w};
-    float f[8];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      f[2 * e] = __uint_as_float(m[e] << 16);
-      f[2 * e + 1] = __uint_as_float(m[e] & 0xffff0000u);
-    }
-    float ss = 0.f;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) ss = __fmaf_rn(f[e], f[e], ss);
-    ss = warp_sum(ss);   // butterfly: identical in every lane
-    const float inv = 1.0f / sqrtf(ss / 256.0f + p.eps);
-    float r[8];
-    if (is_k) {
-      uint4 w4 = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u), wp4 = w4;   // bf16 1.0
-      if (p.kw) {
-        w4 = reinterpret_cast<const uint4*>(p.kw)[lane];
-        wp4 = reinterpret_cast<const uint4*>(p.kw)[lane ^ 16u];
-      }
-      const float4* tab = reinterpret_cast<const float4*>(p.rope_table_in + size_t(tok) * 128u + (lane & 15u) * 8u);
-      const uint32_t q[4] = {__shfl_xor_sync(0xffffffffu, m[0], 16), __shfl_xor_sync(0xffffffffu, m[1], 16),
-                             __shfl_xor_sync(0xffffffffu, m[2], 16), __shfl_xor_sync(0xffffffffu, m[3], 16)};
-      const uint32_t wm[4] = {w4.x, w4.y, w4.z, w4.w};
-      const uint32_t wq[4] = {wp4.x, wp4.y, wp4.z, wp4.w};
-      const bool low = lane < 16u;   // this lane holds element i (low) or its partner i + 128 (high) of each pair
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float4 cs = tab[e];   // (cos, sin) of pairs 8 (lane & 15) + 2e and + 2e + 1
-        const float m0 = f[2 * e] * (inv * __uint_as_float(wm[e] << 16));
-        const float m1 = f[2 * e + 1] * (inv * __uint_as_float(wm[e] & 0xffff0000u));
-        const float q0 = __uint_as_float(q[e] << 16) * (inv * __uint_as_float(wq[e] << 16));
-        const float q1 = __uint_as_float(q[e] & 0xffff0000u) * (inv * __uint_as_float(wq[e] & 0xffff0000u));
-        r[2 * e] = low ? rope_rotate_lo(m0, q0, cs.x, cs.y) : rope_rotate_hi(q0, m0, cs.x, cs.y);
-        r[2 * e + 1] = low ? rope_rotate_lo(m1, q1, cs.z, cs.w) : rope_rotate_hi(q1, m1, cs.z, cs.w);
-      }
-    } else {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) r[e] = f[e] * inv;
-    }
-    __nv_bfloat162 b[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) b[e] = __floats2bfloat162_rn(r[2 * e], r[2 * e + 1]);
-    y = make_uint4(*reinterpret_cast<uint32_t*>(&b[0]), *reinterpret_cast<uint32_t*>(&b[1]),
-                   *reinterpret_cast<uint32_t*>(&b[2]), *reinterpret_cast<uint32_t*>(&b[3]));
-  }
-  __nv_bfloat16* cache = (is_k ? p.cache_k : p.cache_v) + (size_t(h) * p.cap + ((pos - p.pos_base) & p.ring_mask)) * 256u;
-  reinterpret_cast<uint4*>(cache)[lane] = y;
+  if (w >= p.n * 2u * p.Hkv) return;
+  AppendVecArgs a;
+  a.k_in = p.k_in;
+  a.v_in = p.v_in;
+  a.kw = p.kw;
+  a.table = p.rope_table_in;
+  a.cache_k = p.cache_k;
+  a.cache_v = p.cache_v;
+  a.cap = p.cap;
+  a.pos0 = p.pos0;
+  a.Hkv = p.Hkv;
+  a.v_norm = p.v_norm;
+  a.ring_mask = p.ring_mask;
+  a.write_end = p.write_end;
+  a.pos_base = p.pos_base;
+  a.eps = p.eps;
+  append_table_vector(a, w, lane);
 }
 
 void launch_append(const AppendParams& p, const RopeParams& rp, cudaStream_t st, bool early) {

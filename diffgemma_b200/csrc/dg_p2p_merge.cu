@@ -207,6 +207,7 @@ __global__ void __launch_bounds__(256) dg_p2p_push_merge_kernel(const P2pParams 
     s_rows = 0u;
   }
   // the partial was written by the attention kernel that precedes this one on the stream
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   __syncthreads();
 

@@ -91,6 +91,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Bounded wait until a counter in global memory (bumped by other CTAs of this launch after a
+// __threadfence) has reached `want`; then orders the data those CTAs wrote with generic stores before
+// the asynchronous-proxy (TMA) loads this thread issues next.
+__device__ __forceinline__ bool wait_counter_gpu(const uint32_t* ctr, uint32_t want, volatile uint32_t* abort_flag) {
+  const long long t0 = clock64();
+  for (;;) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
+    if (v >= want) break;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > DG_WAIT_LIMIT_CYCLES) {
+      *abort_flag = 1u;
+      return false;
+    }
+  }
+  asm volatile("fence.proxy.async;" ::: "memory");
+  return true;
+}
+
 // ---------------------------------------------------------------- thread-block clusters / DSMEM
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -114,6 +133,10 @@ __device__ __forceinline__ float4 dsmem_ld_f4(uint32_t addr) {
                : "r"(addr)
                : "memory");
   return v;
+}
+// plain store to this CTA's own shared memory (shared::cta address)
+__device__ __forceinline__ void smem_st_u4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 __device__ __forceinline__ void dsmem_st_u4(uint32_t addr, uint4 v) {
   asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)

@@ -99,6 +99,14 @@ class Context:
         """True: CTA-pair form of the tensor kernel, False: single-CTA form, None: automatic (default)."""
         check(self.lib.dg_ctx_set_pair_mode(self.h, 2 if on is None else int(bool(on))), "dg_ctx_set_pair_mode")
 
+    def set_fused_append(self, on: bool) -> None:
+        """True (default): the canvas append runs inside the attention launch once the RoPE table is in memory."""
+        check(self.lib.dg_ctx_set_fused_append(self.h, int(on)), "dg_ctx_set_fused_append")
+
+    def set_inputs_stable(self, on: bool) -> None:
+        """Promise that q/k/v/qw/kw of the following calls are not written by work queued ahead of them."""
+        check(self.lib.dg_ctx_set_inputs_stable(self.h, int(on)), "dg_ctx_set_inputs_stable")
+
     def set_splits(self, n: int) -> None:
         check(self.lib.dg_ctx_set_splits(self.h, n), "dg_ctx_set_splits")
 

@@ -126,6 +126,18 @@ int32_t dg_ctx_set_pair_mode(dg_ctx* ctx, int32_t mode);
 /* Number of thread-block clusters of the tensor-path kernel (pair = 0: (1, cluster_y, 1) CTAs,
  * pair = 1: (2, cluster_y, 1) CTAs) that can be resident on the device at once; negative on error. */
 int32_t dg_ctx_max_active_clusters(dg_ctx* ctx, int32_t pair, uint32_t cluster_y);
+/* Where the canvas K/V append of dg_attn_denoise runs once the RoPE table of the canvas positions is in
+ * memory (every step after the first at those positions): 1 (default) = inside the attention launch - the
+ * launch's own CTAs norm, rotate and store the canvas K/V before any of them loads a key tile that holds
+ * canvas positions, one kernel per step; 0 = in the stand-alone append kernel ahead of the attention kernel
+ * (the reference's two dispatches: src/metal/step_kernel/enc.rs:1733-1806, 2102-2296).  Same bits either way. */
+int32_t dg_ctx_set_fused_append(dg_ctx* ctx, int32_t on);
+/* A promise by the caller: the q, k, v, qw, kw buffers of the following hot-path calls are not written by any
+ * work queued on the context's stream ahead of those calls (they were uploaded, or produced and waited for,
+ * earlier).  With the append inside the attention launch (above) the library then lets the Q prologue of a
+ * step start while the kernel ahead of it on the stream - normally the previous step's attention - is still
+ * draining.  Off by default: without the promise every read waits for the kernel ahead.                       */
+int32_t dg_ctx_set_inputs_stable(dg_ctx* ctx, int32_t on);
 /* Override the number of key splits per query tile on the tensor path (0 = automatic).         */
 int32_t dg_ctx_set_splits(dg_ctx* ctx, uint32_t n_splits);
 
@@ -335,7 +347,8 @@ uint32_t dg_ctx_last_launch_count(const dg_ctx* ctx);
  * bracketed by a CUDA event pair on the launching stream, up to max_launches launches;
  * dg_ctx_kernel_time synchronises and returns their summed duration and count.                  */
 int32_t dg_ctx_kernel_timing(dg_ctx* ctx, int32_t on, uint32_t max_launches);
-/* Measurement aid: with a non-NULL device buffer of CTAs x 16 uint64, thread 0 of every CTA of the
+/* Measurement aid: with a non-NULL device buffer of CTAs x 16 uint64 (CTA index = (z * grid.y + y) * grid.x + x,
+ * z = canvas of a batched call), thread 0 of every CTA of the
  * tensor-path kernel stores globaltimer stamps (ns) at its phase boundaries: 0 start, 1 set-up done,
  * 2 Q prologue done, 3 key loop done, 4 epilogue done, 5 merge done; slots 6-11 hold SM-clock
  * cycles single threads spent waiting inside the key loop (6 MMA issuer on K, 7 on V, 8 on P,
