@@ -1623,6 +1623,7 @@ struct dg_p2p {
   uint32_t push_uses[2] = {0, 0};   // push form: steps that have used each parity since the last reset
   int32_t mode = 0;          // 0 automatic (all rows with two ranks, slices otherwise), 1 slices, 2 all rows, 3 push
   bool poisoned = false;     // a launch failed half-way through a step: the ranks may disagree until dg_p2p_reset
+  unsigned long long* stamps = nullptr;   // caller-owned device buffer for the merge kernel's stamps
   P2pParams layout;
 };
 
@@ -1711,6 +1712,12 @@ extern "C" int32_t dg_p2p_slice(const dg_p2p* x, uint32_t* row0, uint32_t* n_row
   return DG_OK;
 }
 
+extern "C" int32_t dg_p2p_phase_stamps(dg_p2p* x, void* device_buffer) {
+  if (!x) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  x->stamps = static_cast<unsigned long long*>(device_buffer);
+  return DG_OK;
+}
+
 extern "C" int32_t dg_p2p_reset(dg_p2p* x) {
   if (!x) return fail(DG_ERR_INVALID_ARG, "NULL argument");
   DG_CUDA(cudaSetDevice(x->ctx->device));
@@ -1791,14 +1798,16 @@ extern "C" int32_t dg_attn_denoise_split_p2p(dg_ctx* c, const dg_layer_desc* d, 
   a.t0 = t0;
   a.t1 = t1;
   a.include_canvas = include_canvas ? 1 : 0;
+  P2pParams pp = x->layout;
+  pp.step = step;
+  pp.parity = par;
+  pp.stamps = x->stamps;
   r = denoise_one(c, *d, kv, kv_len, 0, q, k, v, qw, kw, nullptr, a);
   if (r != DG_OK) {
     if (c->last_launches != 0) x->poisoned = true;   // part of the step is already queued
     return r;
   }
-  P2pParams pp = x->layout;
-  pp.step = step;
-  pp.parity = par;
+
   if (x->mode == 3) {
     pp.uses = x->push_uses[par] + 1u;
     const cudaError_t e = launch_p2p_push_merge(pp, out, c->num_sms, c->stream);

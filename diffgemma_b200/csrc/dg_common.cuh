@@ -212,6 +212,7 @@ struct P2pParams {
   uint32_t all_rows;       // 1: every rank merges every row itself (no result scatter, no second flag round)
   uint32_t slice_cap;      // rows of the largest row slice: ceil(rows / world)
   uint32_t uses;           // push form: how many steps have used this parity, this one included
+  unsigned long long* stamps;   // optional [8] globaltimer stamps of CTA 0 (measurement aid), null = off
 };
 
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(uint32_t(b) << 16); }

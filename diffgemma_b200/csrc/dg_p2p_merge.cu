@@ -193,6 +193,13 @@ __global__ void __launch_bounds__(256) dg_p2p_merge_kernel(const P2pParams q, ui
 // The counters only grow (the host passes how many steps have used this parity), so no kernel ever
 // resets a word that a peer may still be adding to.
 // ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void p2p_stamp(const P2pParams& q, uint32_t slot) {
+  if (q.stamps != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    q.stamps[slot] = t;
+  }
+}
 __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -207,9 +214,11 @@ __global__ void __launch_bounds__(256) dg_p2p_push_merge_kernel(const P2pParams 
     s_rows = 0u;
   }
   // the partial was written by the attention kernel that precedes this one on the stream
+  p2p_stamp(q, 0);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   __syncthreads();
+  p2p_stamp(q, 1);
 
   // ---- phase A: this CTA serves ONE owner, so that it signals exactly one counter, once
   {
@@ -222,51 +231,72 @@ __global__ void __launch_bounds__(256) dg_p2p_push_merge_kernel(const P2pParams 
     __half* dst_rows = reinterpret_cast<__half*>(q.peer[o] + q.off_recv[par]) + size_t(q.rank) * q.slice_cap * D;
     float4* dst_ml = reinterpret_cast<float4*>(q.peer[o] + q.off_rml[par]) + size_t(q.rank) * q.slice_cap;
     uint32_t done = 0;
-    for (uint32_t row = r0 + j * 8u + warp; row < r1; row += n_o * 8u) {
-      float4 a[2][2];
-      float amax = 0.f;
+    // two rows per warp and iteration, all their loads issued before the first use: the pass is bound by the
+    // latency of the loads, not by their bytes
+    constexpr uint32_t RA = 2;
+    for (uint32_t row0 = r0 + (j * 8u + warp) * RA; row0 < r1; row0 += n_o * 8u * RA) {
+      float4 a[RA][2][2];
+      float rm[RA], rl[RA];
 #pragma unroll
-      for (uint32_t c = 0; c < 2; ++c) {
-        a[c][0] = a[c][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (c * 256u < D) {
-          const float4* s4 = reinterpret_cast<const float4*>(src_o + size_t(row) * D + c * 256u + lane * 8u);
-          a[c][0] = s4[0];
-          a[c][1] = s4[1];
+      for (uint32_t k = 0; k < RA; ++k) {
+        const uint32_t row = row0 + k < r1 ? row0 + k : r1 - 1u;
+#pragma unroll
+        for (uint32_t c = 0; c < 2; ++c) {
+          a[k][c][0] = a[k][c][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (c * 256u < D) {
+            const float4* s4 = reinterpret_cast<const float4*>(src_o + size_t(row) * D + c * 256u + lane * 8u);
+            a[k][c][0] = s4[0];
+            a[k][c][1] = s4[1];
+          }
         }
-#pragma unroll
-        for (uint32_t h = 0; h < 2; ++h)
-          amax = fmaxf(fmaxf(amax, fmaxf(fabsf(a[c][h].x), fabsf(a[c][h].y))), fmaxf(fabsf(a[c][h].z), fabsf(a[c][h].w)));
+        rm[k] = src_m[row];
+        rl[k] = src_l[row];
       }
 #pragma unroll
-      for (int sft = 16; sft > 0; sft >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sft));
-      // biased exponent of the row maximum; tiny, zero, infinite or NaN maxima travel unscaled
-      const uint32_t eb = (__float_as_uint(amax) >> 23) & 0xffu;
-      const bool scaled = eb >= 15u && eb < 255u;
-      const float sc = scaled ? __uint_as_float((268u - eb) << 23) : 1.0f;       // 2^(14 - exponent)
-      const float inv_sc = scaled ? __uint_as_float((eb - 14u) << 23) : 1.0f;
+      for (uint32_t k = 0; k < RA; ++k) {
+        const uint32_t row = row0 + k;
+        if (row >= r1) break;   // warp-uniform
+        float amax = 0.f;
 #pragma unroll
-      for (uint32_t c = 0; c < 2; ++c) {
-        if (c * 256u >= D) break;
-        __half2 h0 = __floats2half2_rn(a[c][0].x * sc, a[c][0].y * sc), h1 = __floats2half2_rn(a[c][0].z * sc, a[c][0].w * sc);
-        __half2 h2 = __floats2half2_rn(a[c][1].x * sc, a[c][1].y * sc), h3 = __floats2half2_rn(a[c][1].z * sc, a[c][1].w * sc);
-        uint4 pk;
-        pk.x = *reinterpret_cast<uint32_t*>(&h0);
-        pk.y = *reinterpret_cast<uint32_t*>(&h1);
-        pk.z = *reinterpret_cast<uint32_t*>(&h2);
-        pk.w = *reinterpret_cast<uint32_t*>(&h3);
-        *reinterpret_cast<uint4*>(dst_rows + size_t(row - r0) * D + c * 256u + lane * 8u) = pk;
+        for (uint32_t c = 0; c < 2; ++c)
+#pragma unroll
+          for (uint32_t h = 0; h < 2; ++h)
+            amax = fmaxf(fmaxf(amax, fmaxf(fabsf(a[k][c][h].x), fabsf(a[k][c][h].y))), fmaxf(fabsf(a[k][c][h].z), fabsf(a[k][c][h].w)));
+#pragma unroll
+        for (int sft = 16; sft > 0; sft >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sft));
+        // biased exponent of the row maximum; tiny, zero, infinite or NaN maxima travel unscaled
+        const uint32_t eb = (__float_as_uint(amax) >> 23) & 0xffu;
+        const bool scaled = eb >= 15u && eb < 255u;
+        const float sc = scaled ? __uint_as_float((268u - eb) << 23) : 1.0f;       // 2^(14 - exponent)
+        const float inv_sc = scaled ? __uint_as_float((eb - 14u) << 23) : 1.0f;
+#pragma unroll
+        for (uint32_t c = 0; c < 2; ++c) {
+          if (c * 256u >= D) break;
+          __half2 h0 = __floats2half2_rn(a[k][c][0].x * sc, a[k][c][0].y * sc), h1 = __floats2half2_rn(a[k][c][0].z * sc, a[k][c][0].w * sc);
+          __half2 h2 = __floats2half2_rn(a[k][c][1].x * sc, a[k][c][1].y * sc), h3 = __floats2half2_rn(a[k][c][1].z * sc, a[k][c][1].w * sc);
+          uint4 pk;
+          pk.x = *reinterpret_cast<uint32_t*>(&h0);
+          pk.y = *reinterpret_cast<uint32_t*>(&h1);
+          pk.z = *reinterpret_cast<uint32_t*>(&h2);
+          pk.w = *reinterpret_cast<uint32_t*>(&h3);
+          *reinterpret_cast<uint4*>(dst_rows + size_t(row - r0) * D + c * 256u + lane * 8u) = pk;
+        }
+        if (lane == 0) dst_ml[row - r0] = make_float4(rm[k], rl[k], inv_sc, 0.f);
+        ++done;
       }
-      if (lane == 0) dst_ml[row - r0] = make_float4(src_m[row], src_l[row], inv_sc, 0.f);
-      ++done;
     }
     if (lane == 0 && done) atomicAdd(&s_rows, done);
     __syncthreads();
+    p2p_stamp(q, 2);
     if (tid == 0 && s_rows) {
-      __threadfence_system();   // after the CTA barrier: covers the stores of all threads of the CTA
+      // A release at system scope by one thread, after the CTA barrier, publishes the stores of every thread
+      // of the CTA (release is cumulative over what the barrier ordered before it).  No sequentially
+      // consistent fence: those are totally ordered among all CTAs and cost 10 us here with 148 of them.
       red_release_sys_add(reinterpret_cast<uint32_t*>(q.peer[o] + q.off_cnt) + par, s_rows);
     }
   }
 
+  p2p_stamp(q, 3);
   // ---- phase B: wait until every rank's rows of this rank's slice have landed here
   const uint32_t r0 = uint32_t((uint64_t(q.rank) * q.rows) / W), r1 = uint32_t((uint64_t(q.rank + 1) * q.rows) / W);
   if (tid == 0) {
@@ -277,53 +307,74 @@ __global__ void __launch_bounds__(256) dg_p2p_push_merge_kernel(const P2pParams 
     }
   }
   __syncthreads();
+  p2p_stamp(q, 4);
   if (!s_ok) return;   // some rank's rows never arrived: the status word says so, the output is left alone
   const __half* rows_in = reinterpret_cast<const __half*>(mine + q.off_recv[par]);
   const float4* ml_in = reinterpret_cast<const float4*>(mine + q.off_rml[par]);
-  for (uint32_t row = r0 + blockIdx.x * 8u + warp; row < r1; row += gridDim.x * 8u) {
-    const uint32_t rl = row - r0;
-    float4 rec = make_float4(-INFINITY, 0.f, 1.f, 0.f);
-    if (lane < W) rec = ml_in[size_t(lane) * q.slice_cap + rl];
-    float mg = rec.x;
+  // D = 256: two rows per warp and iteration with every load in flight before the first use (the pass is bound
+  // by load latency); wider rows go one at a time
+  const uint32_t RB = (D <= 256u) ? 2u : 1u;
+  for (uint32_t row0 = r0 + (blockIdx.x * 8u + warp) * RB; row0 < r1; row0 += gridDim.x * 8u * RB) {
+    float4 rec[2];
+    uint4 x[2][8];
 #pragma unroll
-    for (int sft = 16; sft > 0; sft >>= 1) mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, sft));
-    const float w_mine = (rec.x == -INFINITY) ? 0.f : expf(rec.x - mg);
-    float lg = w_mine * rec.y;
-#pragma unroll
-    for (int sft = 16; sft > 0; sft >>= 1) lg += __shfl_xor_sync(0xffffffffu, lg, sft);
-    const float inv = lg > 0.f ? 1.0f / lg : 0.f;
-    const float ws_mine = w_mine * rec.z;   // the row's scale folded into its weight
-    for (uint32_t c0 = lane * 8u; c0 < D; c0 += 256u) {
-      uint4 x[8];
+    for (uint32_t k = 0; k < 2; ++k) {
+      const uint32_t row = (k < RB && row0 + k < r1) ? row0 + k : row0;
+      const uint32_t rl = row - r0;
+      rec[k] = make_float4(-INFINITY, 0.f, 1.f, 0.f);
+      if (lane < W) rec[k] = ml_in[size_t(lane) * q.slice_cap + rl];
 #pragma unroll
       for (uint32_t w = 0; w < 8; ++w) {
-        x[w] = make_uint4(0u, 0u, 0u, 0u);
-        if (w < W) x[w] = *reinterpret_cast<const uint4*>(rows_in + (size_t(w) * q.slice_cap + rl) * D + c0);
+        x[k][w] = make_uint4(0u, 0u, 0u, 0u);
+        if (w < W) x[k][w] = *reinterpret_cast<const uint4*>(rows_in + (size_t(w) * q.slice_cap + rl) * D + lane * 8u);
       }
-      float acc[8];
+    }
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (uint32_t k = 0; k < 2; ++k) {
+      const uint32_t row = row0 + k;
+      if (k >= RB || row >= r1) break;   // warp-uniform
+      const uint32_t rl = row - r0;
+      float mg = rec[k].x;
 #pragma unroll
-      for (uint32_t w = 0; w < 8; ++w) {
-        float wt = __shfl_sync(0xffffffffu, ws_mine, int(w));
-        if (w >= W) wt = 0.f;
-        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&x[w].x));
-        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&x[w].y));
-        const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&x[w].z));
-        const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&x[w].w));
-        acc[0] += wt * f0.x; acc[1] += wt * f0.y; acc[2] += wt * f1.x; acc[3] += wt * f1.y;
-        acc[4] += wt * f2.x; acc[5] += wt * f2.y; acc[6] += wt * f3.x; acc[7] += wt * f3.y;
+      for (int sft = 16; sft > 0; sft >>= 1) mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, sft));
+      const float w_mine = (rec[k].x == -INFINITY) ? 0.f : expf(rec[k].x - mg);
+      float lg = w_mine * rec[k].y;
+#pragma unroll
+      for (int sft = 16; sft > 0; sft >>= 1) lg += __shfl_xor_sync(0xffffffffu, lg, sft);
+      const float inv = lg > 0.f ? 1.0f / lg : 0.f;
+      const float ws_mine = w_mine * rec[k].z;   // the row's scale folded into its weight
+      for (uint32_t c0 = lane * 8u; c0 < D; c0 += 256u) {
+        if (c0 >= 256u) {
+#pragma unroll
+          for (uint32_t w = 0; w < 8; ++w)
+            if (w < W) x[k][w] = *reinterpret_cast<const uint4*>(rows_in + (size_t(w) * q.slice_cap + rl) * D + c0);
+        }
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+        for (uint32_t w = 0; w < 8; ++w) {
+          float wt = __shfl_sync(0xffffffffu, ws_mine, int(w));
+          if (w >= W) wt = 0.f;
+          const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&x[k][w].x));
+          const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&x[k][w].y));
+          const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&x[k][w].z));
+          const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&x[k][w].w));
+          acc[0] += wt * f0.x; acc[1] += wt * f0.y; acc[2] += wt * f1.x; acc[3] += wt * f1.y;
+          acc[4] += wt * f2.x; acc[5] += wt * f2.y; acc[6] += wt * f3.x; acc[7] += wt * f3.y;
+        }
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv), h1 = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(acc[4] * inv, acc[5] * inv), h3 = __floats2bfloat162_rn(acc[6] * inv, acc[7] * inv);
+        uint4 o4;
+        o4.x = *reinterpret_cast<uint32_t*>(&h0);
+        o4.y = *reinterpret_cast<uint32_t*>(&h1);
+        o4.z = *reinterpret_cast<uint32_t*>(&h2);
+        o4.w = *reinterpret_cast<uint32_t*>(&h3);
+        *reinterpret_cast<uint4*>(out + size_t(row) * D + c0) = o4;
       }
-      __nv_bfloat162 h0 = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv), h1 = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
-      __nv_bfloat162 h2 = __floats2bfloat162_rn(acc[4] * inv, acc[5] * inv), h3 = __floats2bfloat162_rn(acc[6] * inv, acc[7] * inv);
-      uint4 o4;
-      o4.x = *reinterpret_cast<uint32_t*>(&h0);
-      o4.y = *reinterpret_cast<uint32_t*>(&h1);
-      o4.z = *reinterpret_cast<uint32_t*>(&h2);
-      o4.w = *reinterpret_cast<uint32_t*>(&h3);
-      *reinterpret_cast<uint4*>(out + size_t(row) * D + c0) = o4;
     }
   }
+  p2p_stamp(q, 5);
 }
 
 cudaError_t launch_p2p_push_merge(const P2pParams& q, void* out, int num_sms, cudaStream_t st) {

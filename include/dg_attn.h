@@ -318,6 +318,11 @@ int32_t dg_p2p_set_wait_limit(dg_p2p* x, uint64_t limit_cycles);
  * and the step number of this rank's buffer, and (4) met the others at a second host barrier.  Clear the
  * device status word (dg_ctx_clear_device_status) as well.                                                     */
 int32_t dg_p2p_reset(dg_p2p* x);
+/* Measurement aid for mode 3: with a non-NULL device buffer of 8 uint64, thread 0 of the merge kernel's first CTA
+ * stores globaltimer stamps (ns, comparable with dg_ctx_phase_stamps on the same GPU): 0 kernel entered, 1 the
+ * attention kernel ahead of it has completed, 2 this CTA's rows are sent, 3 its arrival count is published,
+ * 4 every rank's rows have arrived here, 5 this CTA's share of the merge is written.  NULL switches them off.   */
+int32_t dg_p2p_phase_stamps(dg_p2p* x, void* device_buffer);
 int32_t dg_p2p_connect(dg_p2p* x, const uint8_t* handles);
 int32_t dg_p2p_destroy(dg_p2p* x);
 int32_t dg_attn_denoise_split_p2p(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* kv, uint32_t kv_len, uint32_t t0,
