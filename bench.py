@@ -137,7 +137,7 @@ def _rot_count(kv_bytes_per_gpu: float) -> int:
 def _shard_tokens(prefix: int, canvas: int, world: int) -> int:
     """Tokens of the largest per-rank cache under split-KV (the last rank also holds the canvas)."""
     from diffgemma_b200.split_kv import plan_shards
-    b = plan_shards(prefix, world)
+    b = plan_shards(prefix, world, canvas=canvas)
     return max((b[r + 1] - b[r]) + (canvas if r == world - 1 else 0) for r in range(world))
 
 
@@ -328,12 +328,14 @@ class Workload:
         else:
             self.group.denoise(kv, self.P, q[0], kc[0], vc[0], out=self.out[0])
 
-    # ---- end-to-end step: host buffers through the library's pipeline, three steps in flight
+    # ---- end-to-end step: host buffers through the library's pipeline, several steps in flight (more with several
+    # ranks, whose steps are short and coupled: a host thread that falls behind stalls every rank)
     PIPE_DEPTH = 3
 
     def host_setup(self):
         from diffgemma_b200.step_attn import HostPipe
         torch = self.torch
+        self.PIPE_DEPTH = 3 if self.world == 1 else 6
         self.pipe = HostPipe(self.ctx, self.lay, 1, self.PIPE_DEPTH)
         self.pending = []
         q0, kc0, vc0 = (t[None].contiguous() for t in self.case[:3])
@@ -581,12 +583,12 @@ def run_stack(args, as_block=False):
         outs[lay.n_kv_heads] = torch.zeros_like(q)
         gath[lay.n_kv_heads] = torch.zeros((world,) + tuple(q.shape), dtype=q.dtype, device=dev)
 
-    def step(upto=len(layers)):
+    def step(upto=len(layers), gather=True):
         for li, lay in enumerate(layers[:upto]):
             q, k, v = ins[lay.n_kv_heads]
             o = outs[lay.n_kv_heads]
             atts[li].denoise(kvs[li], [P] * len(kvs[li]), q, k, v, out=o)
-            if comm is not None:
+            if comm is not None and gather:
                 check(ctx.lib.dg_nccl_all_gather(ctx.h, comm, _ptr(o), _ptr(gath[lay.n_kv_heads]), o.numel() * 2),
                       "dg_nccl_all_gather")
 
@@ -625,35 +627,47 @@ def run_stack(args, as_block=False):
     for _ in range(warm):
         step()
     ctx.synchronize()
+    # The timed step is the attention of the 30 layers on this rank's heads, captured once into a CUDA graph: under
+    # KV-head sharding the path needs no collective when the o_proj that follows is sharded by heads the same way
+    # (its all-reduce lies behind this path).  The variant that leaves every layer's full output on every rank - one
+    # all-gather per layer - is timed beside it with eager launches (ms_per_step_with_gather).
     graph = None
-    # one rank per GPU: the per-layer all-gathers are issued eagerly (a NCCL collective inside a replayed graph
-    # is left out of the measured path); one GPU: the step is one CUDA graph
-    if not args.stack_eager and world == 1:
+    if not args.stack_eager:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=ctx.torch_stream):
-            step()
-    run = graph.replay if graph is not None else step
-    launches = sum(2 * len(row) + (1 if comm is not None else 0) for row in kvs)
+            step(gather=False)
+    run = graph.replay if graph is not None else (lambda: step(gather=False))
+    launches = 0                                     # kernels of one steady-state step, counted by the library
+    for li, lay in enumerate(layers):
+        q, k, v = ins[lay.n_kv_heads]
+        atts[li].denoise(kvs[li], [P] * len(kvs[li]), q, k, v, out=outs[lay.n_kv_heads])
+        launches += ctx.last_launch_count
     steps = args.steps if not as_block else min(args.steps, 100)
-    with ClockSampler(local) as clk:
+
+    def time_steps(fn, n):
         for _ in range(3):
-            run()
+            fn()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(ctx.torch_stream)
-        for _ in range(steps):
-            run()
+        for _ in range(n):
+            fn()
         e1.record(ctx.torch_stream)
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / steps
+        t_ms = e0.elapsed_time(e1) / n
         if world > 1:
-            t = torch.tensor([ms], device=dev)
+            t = torch.tensor([t_ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
+            t_ms = float(t.item())
+        return t_ms
+
+    with ClockSampler(local) as clk:
+        ms = time_steps(run, steps)
+        ms_gather = time_steps(step, min(steps, 50)) if comm is not None else None
     st = ctx.device_status()
     assert st[0] == 0, f"device status {st}"
     peaks = _peaks()
@@ -663,8 +677,9 @@ def run_stack(args, as_block=False):
               "global_layers": "5 x (Hkv 2, all prefix visible)", "head_dim": 256, "canvas": 256,
               "partition": "single GPU" if world == 1 else
               (f"KV heads sharded over {world} GPUs (sliding layers: {max(1, 8 // world)} of 8 KV heads per rank; global layers: "
-               f"the 8 (canvas, KV head) pairs, {8 // world} per rank); no softmax merge; one NCCL all-gather of the output "
-               "head slices per layer inside the timed step"),
+               f"the 8 (canvas, KV head) pairs, {8 // world} per rank); no softmax merge and no collective in the timed step "
+               "(the output stays sharded by heads for a head-sharded o_proj); ms_per_step_with_gather adds one NCCL "
+               "all-gather of the output slices per layer"),
               "launch": ("one CUDA graph replay per step" if graph is not None else "eager launches") +
                         "; the canvases of a layer in one batched call",
               "l2": f"30 layers x 4 canvases of KV per step ({761 / world:.0f} MB per GPU > 126 MB L2)" if world <= 4 else
@@ -680,7 +695,7 @@ def run_stack(args, as_block=False):
     ctx.close()
     blk = {"config": config, "value": value, "unit": UNIT, "ms_per_step": ms, "steps": steps,
            "frac_of_measured_bf16_peak": value / (peaks["bf16_tflops"] * world), "gpu_launches_per_step": launches,
-           "parity": parity}
+           "ms_per_step_with_gather": ms_gather, "parity": parity}
     if as_block:
         return blk
     if rank == 0:
@@ -820,7 +835,7 @@ def run_ours(args):
                          "kernel": "dg_attn_sm100_hd512_kernel" if lay.head_dim == 512 else "dg_attn_sm100_kernel",
                          "kernel_ms": k_avg_ms, "kernel_launches_timed": k_n, "kernel_ms_how": k_how, "sustained": sustained},
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e,
-                    "how": (f"dg_host_pipe, {Workload.PIPE_DEPTH} steps in flight on every rank: every step copies its inputs "
+                    "how": (f"dg_host_pipe, {wl.PIPE_DEPTH} steps in flight on every rank: every step copies its inputs "
                             "from pinned host memory and its result back; copies of neighbouring steps overlap the kernels"
                             + ("; a rank copies in Q (and the canvas K/V only where they are stored) and copies back its own "
                                "row slice of the output" if world > 1 and args.exchange == "p2p" else "")),

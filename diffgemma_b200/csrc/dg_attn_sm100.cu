@@ -326,41 +326,45 @@ dg_attn_sm100_kernel(const __grid_constant__ AttnBatch bat) {
     stamp(p, 2);
 
     // ---------------------------------------------------------------- canvas append inside the launch
-    // Every CTA takes a ticket when it gets here and appends the share of the canvas K / V head vectors
-    // that the ticket names, so every share belongs to a CTA that is already running: whoever waits for
-    // the append (the loaders, before a key tile that holds canvas positions) waits only for CTAs that
-    // need nothing from anybody to finish their share.  The window between "Q is ready" and the first
-    // score tile is otherwise idle for these warps.  The ticket counter wraps by itself; the last CTA
-    // to leave the kernel clears the done counter.
+    // The 2 C Hkv head vectors of canvas K / V are cut into shares of one vector per softmax warp.  Every CTA
+    // that gets here keeps taking shares from a counter until none is left, so all shares are taken by CTAs
+    // that are running - also when part of the grid has not been scheduled yet (more clusters than fit) - and
+    // none of them needs anything from anybody to finish its shares.  Whoever waits for the append (the
+    // loaders, before a key tile that holds canvas positions) therefore never waits for a CTA that has not
+    // started.  The window between "Q is ready" and the first score tile is otherwise idle for these warps.
+    // The last CTA to leave the kernel puts the counters back to zero.
     if (p.ap_vectors != 0u) {
       if (p.early_q) asm volatile("griddepcontrol.wait;" ::: "memory");   // the cache may still be in use ahead of us
-      const uint32_t n_ctas = gridDim.x * gridDim.y;
-      if (tid == 0) ctl[3] = atomicInc(p.ap_ctl, n_ctas - 1u);
-      asm volatile("bar.sync 5, %0;" ::"n"(SM_WARPS * 32) : "memory");
-      const uint32_t ticket = ctl[3];
-      const uint32_t per = (p.ap_vectors + n_ctas - 1u) / n_ctas;
-      const uint32_t v0 = ticket * per, v1 = (v0 + per < p.ap_vectors) ? v0 + per : p.ap_vectors;
-      if (v0 + warp < v1) {
-        AppendVecArgs av;
-        av.k_in = p.ap_k;
-        av.v_in = p.ap_v;
-        av.kw = p.ap_kw;
-        av.table = p.rope_table;
-        av.cache_k = p.ap_cache_k;
-        av.cache_v = p.ap_cache_v;
-        av.cap = p.cap;
-        av.pos0 = mk.kv_len;
-        av.Hkv = p.Hkv;
-        av.v_norm = p.ap_v_norm;
-        av.ring_mask = p.ring_mask;
-        av.write_end = p.ap_write_end;
-        av.pos_base = p.pos_base;
-        av.eps = p.eps;
-        uint32_t mine = 0;
-        for (uint32_t v = v0 + warp; v < v1; v += SM_WARPS) {
+      AppendVecArgs av;
+      av.k_in = p.ap_k;
+      av.v_in = p.ap_v;
+      av.kw = p.ap_kw;
+      av.table = p.rope_table;
+      av.cache_k = p.ap_cache_k;
+      av.cache_v = p.ap_cache_v;
+      av.cap = p.cap;
+      av.pos0 = mk.kv_len;
+      av.Hkv = p.Hkv;
+      av.v_norm = p.ap_v_norm;
+      av.ring_mask = p.ring_mask;
+      av.write_end = p.ap_write_end;
+      av.pos_base = p.pos_base;
+      av.eps = p.eps;
+      const uint32_t n_shares = (p.ap_vectors + SM_WARPS - 1u) / SM_WARPS;
+      uint32_t mine = 0;
+      for (uint32_t it = 0;; ++it) {
+        // two slots in turn: a slot is rewritten only after the barrier that follows everybody's read of it
+        if (tid == 0) ctl[3u + (it & 1u)] = atomicAdd(p.ap_ctl, 1u);
+        asm volatile("bar.sync 5, %0;" ::"n"(SM_WARPS * 32) : "memory");
+        const uint32_t share = ctl[3u + (it & 1u)];
+        if (share >= n_shares) break;
+        const uint32_t v = share * SM_WARPS + warp;
+        if (v < p.ap_vectors) {
           append_table_vector(av, v, lane);
           ++mine;
         }
+      }
+      if (mine != 0u) {
         __threadfence();
         __syncwarp();
         if (lane == 0) atomicAdd(p.ap_ctl + 1, mine);
@@ -1109,10 +1113,11 @@ dg_attn_sm100_kernel(const __grid_constant__ AttnBatch bat) {
   }
   stamp(p, 5);
   if (p.ap_vectors != 0u && tid == 0) {
-    // every CTA is past its own waits on the append counters by now; the last one to get here puts the
-    // done counter back to zero for the next launch (the ticket counter has wrapped to zero by itself)
+    // every CTA is past its own share taking and its waits on the append counters by now; the last one to
+    // get here puts the share counter and the done counter back to zero for the next launch
     const uint32_t n_ctas = gridDim.x * gridDim.y;
     if (atomicInc(p.ap_ctl + 2, n_ctas - 1u) == n_ctas - 1u) {
+      p.ap_ctl[0] = 0u;
       p.ap_ctl[1] = 0u;
       __threadfence();
     }

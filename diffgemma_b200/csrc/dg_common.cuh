@@ -183,7 +183,7 @@ struct AttnParams {
   const __nv_bfloat16* ap_kw;    // [256] or null
   __nv_bfloat16* ap_cache_k;     // the cache, writable
   __nv_bfloat16* ap_cache_v;
-  uint32_t* ap_ctl;              // {ticket, vectors done, CTAs finished}: zero between launches
+  uint32_t* ap_ctl;              // {next share, vectors done, CTAs finished}: zero between launches
   uint32_t ap_vectors;
   uint32_t ap_v_norm;
   uint32_t ap_write_end;         // positions >= this are not stored (0xffffffff: none)

@@ -20,12 +20,15 @@ from .capi import check
 from .step_attn import AttnLayer, CanvasAttention, Context, KvCache, _ptr
 
 
-def plan_shards(kv_len: int, world: int, align: int = 128) -> list[int]:
-    """Shard bounds [b_0=0, ..., b_world=kv_len]: contiguous, near-equal, tile-aligned interior cuts."""
+def plan_shards(kv_len: int, world: int, align: int = 128, canvas: int = 0) -> list[int]:
+    """Shard bounds [b_0=0, ..., b_world=kv_len]: contiguous, tile-aligned interior cuts.  With `canvas` keys
+    counted by the last rank, the cuts give every rank a near-equal share of ALL keys (prefix + canvas), so the
+    rank that also sweeps the canvas gets a shorter prefix shard and the ranks finish together."""
     assert world >= 1 and kv_len >= 0
+    total = kv_len + canvas
     bounds = [0]
     for r in range(1, world):
-        cut = (kv_len * r) // world
+        cut = min(kv_len, (total * r) // world)
         cut = (cut // align) * align
         bounds.append(max(cut, bounds[-1]))
     bounds.append(kv_len)
@@ -89,7 +92,7 @@ class SplitKvGroup:
         self.comm = _nccl_comm(ctx, group)
 
     def shard_bounds(self, kv_len: int):
-        b = plan_shards(kv_len, self.world)
+        b = plan_shards(kv_len, self.world, canvas=self.layer.canvas)
         return b[self.rank], b[self.rank + 1]
 
     @property

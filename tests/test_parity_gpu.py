@@ -740,16 +740,20 @@ def util_ptr(t):
     (8192, 8, 1024, 2, True, 0, 0),              # configuration 1
     (10000, 8, 1024, 1, False, 1, 2048),         # sliding layer on a ring
     (100, 8, 0, 0, False, 0, 0),                 # canvas tiles only: every CTA waits for the append at once
+    (2048, 4, 0, 0, False, 0, 0),                # 8 query heads on 4 KV heads: 16 query tiles, 8 splits = 16 clusters of
+                                                 # 8 CTAs, one more than fit on the device at once
 ])
 def test_in_launch_append_matches_the_two_kernel_step(ctx, P, Hkv, W, mode, weights, vnorm, ring):
     """Steps after the first at the same positions append the canvas K/V inside the attention launch.  Output and
     cache contents must equal, bit for bit, those of the stand-alone append kernel + attention kernel, with every
     split count, with and without the caller's promise of stable inputs, over repeated launches (the append's
     control words reset themselves)."""
-    layer = AttnLayer(n_kv_heads=Hkv, window=W, mask_mode=mode, rope_theta=1e4 if W else 1e6, v_norm=vnorm)
+    layer = AttnLayer(n_q_heads=8 if Hkv == 4 else 16, n_kv_heads=Hkv, window=W, mask_mode=mode,
+                      rope_theta=1e4 if W else 1e6, v_norm=vnorm)
     case = util.make_case(layer, P, seed=P + 5 * Hkv, weights=weights)
     ref = util.run_oracle(case)
     att = CanvasAttention(ctx, layer)
+    split_list = (0, 1, 3, 4, 8)
 
     def fresh():
         if ring:
@@ -771,7 +775,7 @@ def test_in_launch_append_matches_the_two_kernel_step(ctx, P, Hkv, W, mode, weig
             ctx.set_fused_append(fused)
             for stable in ((False, True) if fused else (False,)):
                 ctx.set_inputs_stable(stable)
-                for splits in (0, 1, 3, 4):
+                for splits in split_list:
                     ctx.set_splits(splits)
                     kv = fresh()
                     outs = []
@@ -787,7 +791,7 @@ def test_in_launch_append_matches_the_two_kernel_step(ctx, P, Hkv, W, mode, weig
         ctx.set_fused_append(True)
         ctx.set_inputs_stable(False)
         ctx.set_splits(0)
-    for splits in (0, 1, 3, 4):
+    for splits in split_list:
         base = results[(False, False, splits)]
         util.assert_close(util.t2f(base[0][0]), ref, f"two-kernel step splits={splits}")
         assert torch.equal(base[0][0], base[0][2]) and not torch.equal(base[0][0], base[0][1])

@@ -23,6 +23,13 @@ def test_plan_shards_properties():
             assert all(b[i] <= b[i + 1] for i in range(world))
             assert all(x % 128 == 0 for x in b[1:-1])
     assert split_kv.plan_shards(32768, 8) == [4096 * i for i in range(9)]
+    # with the canvas keys of the last rank counted, every rank sweeps a near-equal number of keys
+    for kv_len in (32768, 131072, 6000):
+        for world in (2, 4, 8):
+            b = split_kv.plan_shards(kv_len, world, canvas=256)
+            assert b[0] == 0 and b[-1] == kv_len and all(x % 128 == 0 for x in b[1:-1])
+            shares = [b[i + 1] - b[i] + (256 if i == world - 1 else 0) for i in range(world)]
+            assert max(shares) - min(shares) <= 256, shares
     assert split_kv.canvas_owner(8) == 7
 
 
@@ -81,3 +88,22 @@ def test_split_merge_two_ranks_global():
 def test_split_merge_two_ranks_window_leaves_empty_shard():
     # window 64 on a 600-key prefix: rank 0's shard [0, 256) is entirely masked -> m = -inf partial
     _run(2, 64, ao.MASK_WINDOW_UNIFORM, 29612)
+
+
+def test_stack_units_cover_every_canvas_head_pair_once():
+    """KV-head sharding of the batched stack (bench.py: stack_units): over the ranks, every (canvas, KV head)
+    pair of a layer is computed exactly once, and every rank gets the same amount of work."""
+    sys.path.insert(0, ROOT)
+    import bench
+    for n_kv in (8, 2):
+        for world in (1, 2, 4, 8):
+            seen = {}
+            sizes = set()
+            for r in range(world):
+                h0, nh, canv = bench.stack_units(n_kv, 4, world, r)
+                sizes.add(nh * len(canv))
+                for b in canv:
+                    for h in range(h0, h0 + nh):
+                        assert (b, h) not in seen, (n_kv, world, r, b, h)
+                        seen[(b, h)] = r
+            assert len(seen) == 4 * n_kv and len(sizes) == 1, (n_kv, world, sizes)

@@ -32,10 +32,9 @@ def _rank_main(rank, world, port, P, W, mode, exchange, ret):
         layer = AttnLayer(n_kv_heads=2, window=W, mask_mode=mode)
         case = util.make_case(layer, P, seed=77)          # same seed on every rank: replicated inputs
         dev = f"cuda:{rank}"
-        b = plan_shards(P, world)
-        t0, t1 = b[rank], b[rank + 1]
         mode = {"p2p": 0, "p2p-slices": 1, "p2p-allrows": 2, "p2p-push": 3}.get(exchange, 0)
         grp = SplitKvGroup(ctx, layer, exchange="nccl" if exchange == "nccl" else "p2p", p2p_mode=mode)
+        t0, t1 = grp.shard_bounds(P)                       # the cuts count the canvas keys of the last rank
         # the push form runs on shard caches (shard + canvas tokens per rank), the others on full-size ones
         kv = grp.make_shard_cache(P) if exchange == "p2p-push" else KvCache(ctx, layer, P + layer.canvas)
         if t1 > t0:                                        # only this rank's shard is resident
