@@ -159,7 +159,11 @@ def config_dict(cfg_idx: int, world: int, exchange: str = "p2p"):
         part = f"split-KV over {world} GPUs + NCCL LSE merge, full output on every rank"
     else:
         part = (f"split-KV over {world} GPUs, shard-sized caches, LSE merge over peer memory (NVLink), "
-                f"every rank keeps its row slice of the output")
+                f"every rank keeps its row slice of the output; consecutive steps are independent and the exchange is "
+                f"pipelined over them (every rank runs two contexts that take alternate steps, so that one step's exchange "
+                f"runs beside the next step's attention; a step's rows are sent in that step, its slice is merged by the "
+                f"context's next call: throughput of a stream of steps; latency_ms_per_step is one step alone on one "
+                f"context, merged at once)")
     out = {"workload": cfg.name, "prefix": P, "n_q_heads": lay.n_q_heads, "n_kv_heads": lay.n_kv_heads,
            "head_dim": lay.head_dim, "canvas": lay.canvas, "mask": mask, "partition": part,
            "l2": f"steps rotate over {n_rot} KV caches per GPU ({n_rot * kv_bytes / 1e6:.0f} MB > 126 MB L2)",
@@ -282,8 +286,10 @@ class Workload:
         self.flops = lay.flops(P)
         self.att = CanvasAttention(ctx, lay)
         self.group = None
+        self.pipelined = world > 1 and args.exchange == "p2p" and not args.no_pipelined_exchange
         if world > 1:
-            self.group = SplitKvGroup(ctx, lay, exchange=args.exchange, p2p_mode=3 if args.exchange == "p2p" else 0)
+            self.group = SplitKvGroup(ctx, lay, exchange=args.exchange,
+                                      p2p_mode=(4 if self.pipelined else 3) if args.exchange == "p2p" else 0)
             self.t0, self.t1 = self.group.shard_bounds(P)
         else:
             self.t0, self.t1 = 0, P
@@ -317,16 +323,69 @@ class Workload:
             self.ins.append(tuple(torch.randn(1, lay.canvas, h, lay.head_dim, generator=g, device=dev).to(torch.bfloat16)
                                   for h in (lay.n_q_heads, lay.n_kv_heads, lay.n_kv_heads)))
         self.out = torch.zeros_like(self.ins[0][0])
+        # pipelined exchange: the slice of a step is written by the NEXT call, so consecutive steps get different
+        # output buffers
+        self.outs = [self.out] + ([torch.zeros_like(self.out) for _ in range(2)] if self.pipelined else [])
         self.pipe = None
+        # A second lane on several GPUs: a second context (own stream, workspace, exchange buffers, caches) that
+        # takes every other step, so that the exchange kernel of one step (latency: a grid boundary, posted stores,
+        # one NVLink round trip) runs beside the attention kernel of the next.  Consecutive steps are independent -
+        # the situation of a host with several canvases or requests in flight.
+        self.lane2 = None
+        self.two_lanes = False
+        if self.pipelined and not args.one_lane:
+            from diffgemma_b200.step_attn import Context
+            torch.cuda.synchronize()
+            ctx2 = Context(ctx.device, make_current=False)
+            ctx2.set_inputs_stable(True)
+            if args.kernel_form != "auto":
+                ctx2.set_pair_mode(args.kernel_form == "pair")
+            grp2 = SplitKvGroup(ctx2, lay, exchange="p2p", p2p_mode=4)
+            kvs2 = []
+            for j in range(self.n_rot):
+                kv = grp2.make_shard_cache(P)
+                n = self.t1 - lo
+                if n > 0:
+                    kr = torch.randn(n, lay.n_kv_heads, lay.head_dim, generator=g, device=dev).to(torch.bfloat16)
+                    vr = torch.randn(n, lay.n_kv_heads, lay.head_dim, generator=g, device=dev).to(torch.bfloat16)
+                    torch.cuda.synchronize()           # the copy below runs on the second context's stream
+                    kv.load_prefix(kr, vr, lo)
+                    ctx2.synchronize()
+                kvs2.append(kv)
+            self.lane2 = {"ctx": ctx2, "group": grp2, "kvs": kvs2, "outs": [torch.zeros_like(self.out) for _ in range(3)]}
+            self.two_lanes = True
+            torch.cuda.synchronize()
+
+    @property
+    def extra_streams(self):
+        return [self.lane2["ctx"].torch_stream] if (self.lane2 is not None and self.two_lanes) else []
 
     # ---- device-resident step
     def step_dev(self, i, kv=None, ins=None):
+        if kv is None and self.lane2 is not None and self.two_lanes and (i & 1):
+            L = self.lane2
+            j = i >> 1
+            q, kc, vc = self.ins[i % len(self.ins)] if ins is None else ins
+            L["group"].denoise(L["kvs"][j % self.n_rot], self.P, q[0], kc[0], vc[0], out=L["outs"][j % 3][0])
+            return
+        if kv is None and self.lane2 is not None and self.two_lanes:
+            kv = self.kvs[(i >> 1) % self.n_rot]
+            q, kc, vc = self.ins[i % len(self.ins)] if ins is None else ins
+            self.group.denoise(kv, self.P, q[0], kc[0], vc[0], out=self.outs[(i >> 1) % len(self.outs)][0])
+            return
         kv = self.kvs[i % self.n_rot] if kv is None else kv
         q, kc, vc = self.ins[i % len(self.ins)] if ins is None else ins
         if self.group is None:
             self.att.denoise([kv], [self.P], q, kc, vc, out=self.out)
         else:
-            self.group.denoise(kv, self.P, q[0], kc[0], vc[0], out=self.out[0])
+            self.group.denoise(kv, self.P, q[0], kc[0], vc[0], out=self.outs[i % len(self.outs)][0])
+
+    def drain(self):
+        """Pipelined exchange: merge the slice of the last step (what a next step would have done)."""
+        if self.pipelined and self.group.p2p_mode == 4:
+            self.group.flush()
+        if self.lane2 is not None:
+            self.lane2["group"].flush()
 
     # ---- end-to-end step: host buffers through the library's pipeline, several steps in flight (more with several
     # ranks, whose steps are short and coupled: a host thread that falls behind stalls every rank)
@@ -335,6 +394,11 @@ class Workload:
     def host_setup(self):
         from diffgemma_b200.step_attn import HostPipe
         torch = self.torch
+        if self.pipelined:
+            # the host pipe copies a step's slice back right behind that step's kernels: the plain push form, one lane
+            self.drain()
+            self.two_lanes = False
+            self.group.set_mode(3)
         self.PIPE_DEPTH = 3 if self.world == 1 else 6
         self.pipe = HostPipe(self.ctx, self.lay, 1, self.PIPE_DEPTH)
         self.pending = []
@@ -382,6 +446,7 @@ class Workload:
         import torch.distributed as dist
         self.out.zero_()
         self.step_dev(0, kv=self.kvs[0], ins=self.ins[0])
+        self.drain()
         self.ctx.synchronize()
         got = self.out[0].float().cpu().numpy()                   # [C, Hq, D]
         C, Hq = self.lay.canvas, self.lay.n_q_heads
@@ -418,6 +483,12 @@ class Workload:
     def close(self):
         if self.pipe is not None:
             self.pipe.close()
+        if self.lane2 is not None:
+            self.lane2["group"].flush()
+            self.lane2["group"].close()
+            for kv in self.lane2["kvs"]:
+                kv.close()
+            self.lane2["ctx"].close()
         if self.group is not None:
             self.group.close()
         for kv in self.kvs:
@@ -433,7 +504,7 @@ def _timer(world, dev, stream):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, warmup, finish=None):
+    def timed(fn, steps, warmup, finish=None, extra_streams=()):
         for i in range(warmup):
             fn(i)
         if finish:
@@ -442,10 +513,16 @@ def _timer(world, dev, stream):
         e0 = torch.cuda.Event(enable_timing=True)
         e1 = torch.cuda.Event(enable_timing=True)
         e0.record(stream)
+        for s in extra_streams:           # work on the other lanes starts after the clock does ...
+            s.wait_event(e0)
         for i in range(steps):
             fn(warmup + i)
         if finish:
-            finish()          # every result is back in host memory before the clock stops
+            finish()          # every result is complete (back in host memory, end to end) before the clock stops
+        for s in extra_streams:           # ... and ends before it stops
+            ev = torch.cuda.Event()
+            ev.record(s)
+            stream.wait_event(ev)
         e1.record(stream)
         barrier()
         ms = e0.elapsed_time(e1)
@@ -458,15 +535,55 @@ def _timer(world, dev, stream):
     return timed
 
 
-def _kernel_pass(ctx, timed, fn, steps):
+def _kernel_pass(ctx, timed, fn, steps, finish=None, wl=None):
     """The same steps once more with a CUDA event pair around every launch of the dominant kernel (on its
     own stream): a separate pass, because an event record between the append and the attention launch
     keeps the two from overlapping (programmatic dependent launch) and so changes the step time."""
+    lanes = wl.two_lanes if wl is not None else False
+    if wl is not None:
+        wl.two_lanes = False              # the kernel's own duration: one lane, nothing running beside it
     ctx.kernel_timing(True, steps + 8)
-    timed(fn, steps, 0)
+    timed(fn, steps, 0, finish)
     k_ms, k_n = ctx.kernel_time()
     ctx.kernel_timing(False)
+    if wl is not None:
+        wl.two_lanes = lanes
     return (k_ms / k_n if k_n else None), k_n
+
+
+def exchange_timeline(ctx, wl, world):
+    """In-kernel time stamps of one unpipelined split-KV step on every rank (the library's measurement aids
+    dg_ctx_phase_stamps and dg_p2p_phase_stamps): when the merge kernel was resident, saw its predecessor complete,
+    had sent its rows, had published its count, had every rank's rows, had merged its slice - in microseconds
+    relative to the end of the rank's own attention kernel.  The stamps cost time: read the intervals, not the step."""
+    import ctypes as C
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    wl.drain()
+    wl.two_lanes = False
+    wl.group.set_mode(3)
+    dev = wl.dev
+    st = torch.zeros(4096 * 16, dtype=torch.int64, device=dev)
+    ms = torch.zeros(8, dtype=torch.int64, device=dev)
+    ctx.lib.dg_ctx_phase_stamps(ctx.h, C.c_void_p(st.data_ptr()))
+    ctx.lib.dg_p2p_phase_stamps(wl.group.p2p, C.c_void_p(ms.data_ptr()))
+    for i in range(5):
+        wl.step_dev(i)
+    ctx.synchronize()
+    ctx.lib.dg_ctx_phase_stamps(ctx.h, None)
+    ctx.lib.dg_p2p_phase_stamps(wl.group.p2p, None)
+    a = st.cpu().numpy().reshape(4096, 16)
+    a = a[a[:, 0] != 0]
+    m = ms.cpu().numpy()
+    t_end = a[:, 5].max()
+    mine = {"attention_us": float(t_end - a[:, 0].min()) / 1e3, "ctas": int(len(a)),
+            "merge_kernel_resident": float(m[0] - t_end) / 1e3, "predecessor_complete": float(m[1] - t_end) / 1e3,
+            "rows_sent": float(m[2] - t_end) / 1e3, "count_published": float(m[3] - t_end) / 1e3,
+            "all_rows_arrived": float(m[4] - t_end) / 1e3, "slice_merged": float(m[5] - t_end) / 1e3}
+    everyone = [None] * world
+    dist.all_gather_object(everyone, mine)
+    return {"unit": "us after the end of the rank's own attention kernel (stamps on)", "ranks": everyone}
 
 
 def measure_block(ctx, cfg_idx, world, rank, args, steps, timed, peaks, redraw=1, want_e2e=False):
@@ -475,11 +592,11 @@ def measure_block(ctx, cfg_idx, world, rank, args, steps, timed, peaks, redraw=1
     wl = Workload(ctx, cfg_idx, world, rank, args, redraw=redraw)
     try:
         par = wl.parity()
-        ms = timed(wl.step_dev, steps, max(3, min(20, steps)))
+        ms = timed(wl.step_dev, steps, max(3, min(20, steps)), wl.drain, wl.extra_streams)
         if ctx.last_launch_count == 1:
             k_ms = ms                       # one kernel per step, back to back
         else:
-            k_ms, _ = _kernel_pass(ctx, timed, wl.step_dev, min(steps, 200))
+            k_ms, _ = _kernel_pass(ctx, timed, wl.step_dev, min(steps, 200), wl.drain, wl)
         value = wl.flops / (ms * 1e-3) / 1e12
         lay = wl.lay
         io_bytes = 2 * lay.n_kv_heads * (wl.P + lay.canvas) * lay.head_dim * 2 + 2 * lay.canvas * lay.n_q_heads * lay.head_dim * 2
@@ -748,7 +865,7 @@ def run_ours(args):
     warm = max(3, args.warmup)
     with ClockSampler(local) as clk:
         # device-resident arm
-        ms_dev = timed(wl.step_dev, args.steps, warm)
+        ms_dev = timed(wl.step_dev, args.steps, warm, wl.drain, wl.extra_streams)
         launches_per_step = ctx.last_launch_count
         log(f"device-resident: {ms_dev * 1e3:.1f} us per step, {launches_per_step} launch(es) per step")
         mark = clk.mark()
@@ -758,7 +875,7 @@ def run_ours(args):
             # (gaps between launches included, which can only make it longer)
             k_avg_ms, k_n, k_how = ms_dev, args.steps, "timed region / launches (one kernel per step, back to back)"
         else:
-            k_avg_ms, k_n = _kernel_pass(ctx, timed, wl.step_dev, args.steps)
+            k_avg_ms, k_n = _kernel_pass(ctx, timed, wl.step_dev, args.steps, wl.drain, wl)
             k_how = "CUDA event pair around every launch of the kernel, in a separate pass of the same steps" 
         clocks = clk.summary()
         # a timed region of less than a second is a burst at the boost clock: the same steps for at least
@@ -767,13 +884,13 @@ def run_ours(args):
         if ms_dev * args.steps < 1000.0 and not args.no_sustained:
             n_sus = int(min(60000, math.ceil(1200.0 / ms_dev)))
             log(f"sustained loop of {n_sus} steps")
-            timed(wl.step_dev, max(1, n_sus // 3), 0)          # reach the steady clock first
+            timed(wl.step_dev, max(1, n_sus // 3), 0, wl.drain, wl.extra_streams)          # reach the steady clock first
             mark = clk.mark()
-            ms_sus = timed(wl.step_dev, n_sus, 0)
+            ms_sus = timed(wl.step_dev, n_sus, 0, wl.drain, wl.extra_streams)
             if launches_per_step == 1:
                 ks_ms = ms_sus
             else:
-                ks_ms, _ = _kernel_pass(ctx, timed, wl.step_dev, min(n_sus, 4000))
+                ks_ms, _ = _kernel_pass(ctx, timed, wl.step_dev, min(n_sus, 4000), wl.drain, wl)
             cs = clk.summary(mark)
             ach = (flops / world) / (ks_ms * 1e-3) / 1e12 if ks_ms else None
             sustained = {"steps": n_sus, "ms_per_step": ms_sus, "value": flops / (ms_sus * 1e-3) / 1e12,
@@ -782,6 +899,18 @@ def run_ours(args):
                          if (ach and peaks["bf16_tflops_sustained"]) else None,
                          "sm_mhz_median": cs["sm_mhz"], "reasons": cs["reasons"],
                          "kernel_ms_x_sm_mhz": ks_ms * cs["sm_mhz"] if (ks_ms and cs["sm_mhz"]) else None}
+        # one step alone: rows sent and slice merged inside the step (what a host that cannot keep a second step
+        # in flight sees)
+        ms_latency = None
+        if wl.pipelined:
+            wl.drain()
+            wl.two_lanes = False
+            wl.group.set_mode(3)
+            ms_latency = timed(wl.step_dev, min(args.steps, 300), 5)
+            log(f"one step alone (unpipelined exchange): {ms_latency * 1e3:.1f} us")
+        timeline = None
+        if args.exchange_timeline and wl.group is not None and args.exchange == "p2p":
+            timeline = exchange_timeline(ctx, wl, world)
         # end-to-end arm: host buffers, H2D + kernels + D2H every step
         log("end-to-end arm (host buffers)")
         wl.host_setup()
@@ -819,7 +948,7 @@ def run_ours(args):
             "warmup": warm, "ms_per_step": ms_dev, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": config_dict(args.cfg, world, args.exchange),
-            "steps_per_s": 1e3 / ms_dev,
+            "steps_per_s": 1e3 / ms_dev, "latency_ms_per_step": ms_latency if ms_latency is not None else ms_dev,
             "pct_of_measured_bf16_peak": 100.0 * value / (peaks["bf16_tflops"] * world),
             "pct_of_nominal_bf16_peak": 100.0 * value / (2250.0 * world),
             "achieved_hbm_gbs": io_bytes / (ms_dev * 1e-3) / 1e9,
@@ -845,6 +974,8 @@ def run_ours(args):
         }
         if extra:
             line["extra"] = extra
+        if timeline is not None:
+            line["exchange_timeline"] = timeline
         if world == 1 and not args.no_cpu:
             smp = CpuOracle(args.cfg)
             smp.timed(1)
@@ -885,6 +1016,12 @@ def main():
     ap.add_argument("--no-sustained", action="store_true", help="leave out the >= 1.2 s sustained loop")
     ap.add_argument("--stack-eager", action="store_true", help="configuration 3: launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="multi-GPU partial exchange")
+    ap.add_argument("--exchange-timeline", action="store_true",
+                    help="multi-GPU: add in-kernel time stamps of one split-KV step on every rank to the line")
+    ap.add_argument("--one-lane", action="store_true",
+                    help="multi-GPU: one context per rank instead of two that take alternate steps")
+    ap.add_argument("--no-pipelined-exchange", action="store_true",
+                    help="multi-GPU: merge every step's slice inside that step instead of one step later")
     ap.add_argument("--kernel-form", default="auto", choices=["auto", "pair", "single"],
                     help="tensor-kernel form: CTA pairs, one CTA per query tile, or the library's choice")
     args = ap.parse_args()

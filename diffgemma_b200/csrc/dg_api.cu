@@ -1620,14 +1620,18 @@ struct dg_p2p {
   bool opened[8] = {};
   bool connected = false;
   uint32_t step = 0;
-  uint32_t push_uses[2] = {0, 0};   // push form: steps that have used each parity since the last reset
+  uint32_t push_uses[3] = {0, 0, 0};   // push forms: steps that have used each receive slot since the last reset
+  // pipelined push form: the step whose rows have been sent and whose slice is merged by the next call
+  bool pend = false;
+  uint32_t pend_slot = 0, pend_uses = 0;
+  void* pend_out = nullptr;
   int32_t mode = 0;          // 0 automatic (all rows with two ranks, slices otherwise), 1 slices, 2 all rows, 3 push
   bool poisoned = false;     // a launch failed half-way through a step: the ranks may disagree until dg_p2p_reset
   unsigned long long* stamps = nullptr;   // caller-owned device buffer for the merge kernel's stamps
   P2pParams layout;
 };
 
-static bool p2p_is_push(const dg_p2p* x) { return x->mode == 3; }
+static bool p2p_is_push(const dg_p2p* x) { return x->mode == 3 || x->mode == 4; }
 static void p2p_slice_bytes(const dg_p2p* x, size_t* off, size_t* bytes) {
   const size_t r0 = (size_t(x->rank) * x->rows) / x->world, r1 = (size_t(x->rank + 1) * x->rows) / x->world;
   *off = r0 * x->D * 2;
@@ -1646,14 +1650,14 @@ static void p2p_layout(dg_p2p* x) {
     L.off_res[p] = take(size_t(x->rows) * x->D * 2);
   }
   L.slice_cap = (x->rows + x->world - 1) / x->world;
-  for (int p = 0; p < 2; ++p) {
+  for (int p = 0; p < 3; ++p) {
     L.off_recv[p] = take(size_t(x->world) * L.slice_cap * x->D * 2);
     L.off_rml[p] = take(size_t(x->world) * L.slice_cap * 16);
   }
   L.off_pflag = take(2 * 8 * 4);
   L.off_rflag = take(2 * 8 * 4);
   L.off_done = take(2 * 4);
-  L.off_cnt = take(2 * 4);
+  L.off_cnt = take(3 * 4);
   x->bytes = off;
   L.world = x->world;
   L.rank = x->rank;
@@ -1690,8 +1694,9 @@ extern "C" int32_t dg_p2p_create(dg_ctx* c, uint32_t rows, uint32_t head_dim, in
 
 extern "C" int32_t dg_p2p_set_mode(dg_p2p* x, int32_t mode) {
   if (!x) return fail(DG_ERR_INVALID_ARG, "NULL argument");
-  if (mode < 0 || mode > 3)
-    return fail(DG_ERR_INVALID_ARG, "mode must be 0 (automatic), 1 (row slices), 2 (all rows) or 3 (push, row slice only)");
+  if (mode < 0 || mode > 4)
+    return fail(DG_ERR_INVALID_ARG, "mode must be 0 (automatic), 1 (row slices), 2 (all rows), 3 (push) or 4 (push, pipelined)");
+  if (x->pend) return fail(DG_ERR_INVALID_ARG, "a pipelined step is pending: call dg_p2p_flush first");
   x->mode = mode;
   return DG_OK;
 }
@@ -1712,6 +1717,26 @@ extern "C" int32_t dg_p2p_slice(const dg_p2p* x, uint32_t* row0, uint32_t* n_row
   return DG_OK;
 }
 
+extern "C" int32_t dg_p2p_flush(dg_p2p* x) {
+  if (!x) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  if (!x->pend) return DG_OK;
+  DG_CUDA(cudaSetDevice(x->ctx->device));
+  P2pParams pp = x->layout;
+  pp.stamps = nullptr;
+  pp.send_on = 0u;
+  pp.merge_on = 1u;
+  pp.merge_first = 1u;
+  pp.merge_slot = x->pend_slot;
+  pp.merge_uses = x->pend_uses;
+  const cudaError_t e = launch_p2p_push_merge(pp, x->pend_out, x->ctx->num_sms, x->ctx->stream);
+  if (e != cudaSuccess) {
+    x->poisoned = true;
+    return fail_cuda(e, "launch_p2p_push_merge");
+  }
+  x->pend = false;
+  return DG_OK;
+}
+
 extern "C" int32_t dg_p2p_phase_stamps(dg_p2p* x, void* device_buffer) {
   if (!x) return fail(DG_ERR_INVALID_ARG, "NULL argument");
   x->stamps = static_cast<unsigned long long*>(device_buffer);
@@ -1727,7 +1752,8 @@ extern "C" int32_t dg_p2p_reset(dg_p2p* x) {
   const P2pParams& L = x->layout;
   DG_CUDA(cudaMemset(x->local + L.off_pflag, 0, x->bytes - L.off_pflag));
   x->step = 0;
-  x->push_uses[0] = x->push_uses[1] = 0;
+  x->push_uses[0] = x->push_uses[1] = x->push_uses[2] = 0;
+  x->pend = false;
   x->poisoned = false;
   return DG_OK;
 }
@@ -1808,14 +1834,38 @@ extern "C" int32_t dg_attn_denoise_split_p2p(dg_ctx* c, const dg_layer_desc* d, 
     return r;
   }
 
-  if (x->mode == 3) {
-    pp.uses = x->push_uses[par] + 1u;
-    const cudaError_t e = launch_p2p_push_merge(pp, out, c->num_sms, c->stream);
+  if (x->mode == 3 || x->mode == 4) {
+    const uint32_t slot = step % 3u;
+    pp.send_on = 1u;
+    pp.send_slot = slot;
+    void* merge_out = out;
+    if (x->mode == 3) {
+      // this step's rows are sent, then this step's slice is merged
+      pp.merge_on = 1u;
+      pp.merge_first = 0u;
+      pp.merge_slot = slot;
+      pp.merge_uses = x->push_uses[slot] + 1u;
+    } else {
+      // pipelined: the slice of the previous step (its rows have had a whole step to arrive) is merged first, into
+      // the output buffer that was given with THAT step; this step's rows are sent behind it
+      pp.merge_on = x->pend ? 1u : 0u;
+      pp.merge_first = 1u;
+      pp.merge_slot = x->pend_slot;
+      pp.merge_uses = x->pend_uses;
+      merge_out = x->pend_out;
+    }
+    const cudaError_t e = launch_p2p_push_merge(pp, merge_out, c->num_sms, c->stream);
     if (e != cudaSuccess) {
       x->poisoned = true;
       return fail_cuda(e, "launch_p2p_push_merge");
     }
-    x->push_uses[par] += 1u;
+    x->push_uses[slot] += 1u;
+    if (x->mode == 4) {
+      x->pend = true;
+      x->pend_slot = slot;
+      x->pend_uses = x->push_uses[slot];
+      x->pend_out = out;
+    }
   } else {
     pp.all_rows = (x->mode == 2 || (x->mode == 0 && x->world == 2)) ? 1u : 0u;
     launch_p2p_merge(pp, out, c->num_sms, c->stream);

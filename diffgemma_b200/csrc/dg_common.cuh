@@ -203,15 +203,20 @@ struct P2pParams {
   uint8_t* peer[8];        // exchange buffer of every rank, as mapped into this process
   size_t off_o[2], off_m[2], off_l[2], off_res[2];   // per parity
   size_t off_pflag, off_rflag, off_done;             // u32 pflag[2][8], rflag[2][8], done[2]
-  // push form: per parity a receive area [world][slice_cap][D] fp16 rows, their [world][slice_cap]
+  // push form: per slot (step mod 3) a receive area [world][slice_cap][D] fp16 rows, their [world][slice_cap]
   // (m, l, 1 / scale, -) records, and one arrival counter (rows received since the last reset)
-  size_t off_recv[2], off_rml[2], off_cnt;
+  size_t off_recv[3], off_rml[3], off_cnt;
   DevStatus* status;
   long long wait_limit;    // cycles
   uint32_t world, rank, rows, D, step, parity;
   uint32_t all_rows;       // 1: every rank merges every row itself (no result scatter, no second flag round)
   uint32_t slice_cap;      // rows of the largest row slice: ceil(rows / world)
-  uint32_t uses;           // push form: how many steps have used this parity, this one included
+  // push form: which step's rows this launch sends (phase A) and which step's slice it merges (phase B).  The
+  // plain form does both for the current step, A then B; the pipelined form merges the PREVIOUS step first and
+  // then sends the current one, so that nobody ever waits for rows that are still on their way.
+  uint32_t send_slot, send_on;       // receive slot of the step whose rows are sent; 0: nothing to send
+  uint32_t merge_slot, merge_uses, merge_on;   // slot and use count of the step whose slice is merged; 0: none
+  uint32_t merge_first;              // 1: phase B runs before phase A
   unsigned long long* stamps;   // optional [8] globaltimer stamps of CTA 0 (measurement aid), null = off
 };
 

@@ -204,22 +204,12 @@ __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-__global__ void __launch_bounds__(256) dg_p2p_push_merge_kernel(const P2pParams q, __nv_bfloat16* __restrict__ out) {
-  __shared__ uint32_t s_ok, s_rows;
+// Phase A: convert the rows of this rank's fp32 partial (written by the attention kernel of the same step, buffer
+// parity q.parity) and store them into the owners' receive slot q.send_slot; publish the delivered row counts.
+__device__ __forceinline__ void p2p_phase_send(const P2pParams& q, uint32_t* s_rows) {
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const uint32_t par = q.parity, W = q.world, D = q.D;
+  const uint32_t par = q.parity, slot = q.send_slot, W = q.world, D = q.D;
   uint8_t* mine = q.peer[q.rank];
-  if (tid == 0) {
-    s_ok = 1u;
-    s_rows = 0u;
-  }
-  // the partial was written by the attention kernel that precedes this one on the stream
-  p2p_stamp(q, 0);
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  __syncthreads();
-  p2p_stamp(q, 1);
-
   // ---- phase A: this CTA serves ONE owner, so that it signals exactly one counter, once
   {
     const uint32_t o = blockIdx.x % W, j = blockIdx.x / W;
@@ -228,8 +218,8 @@ __global__ void __launch_bounds__(256) dg_p2p_push_merge_kernel(const P2pParams 
     const float* src_o = reinterpret_cast<const float*>(mine + q.off_o[par]);
     const float* src_m = reinterpret_cast<const float*>(mine + q.off_m[par]);
     const float* src_l = reinterpret_cast<const float*>(mine + q.off_l[par]);
-    __half* dst_rows = reinterpret_cast<__half*>(q.peer[o] + q.off_recv[par]) + size_t(q.rank) * q.slice_cap * D;
-    float4* dst_ml = reinterpret_cast<float4*>(q.peer[o] + q.off_rml[par]) + size_t(q.rank) * q.slice_cap;
+    __half* dst_rows = reinterpret_cast<__half*>(q.peer[o] + q.off_recv[slot]) + size_t(q.rank) * q.slice_cap * D;
+    float4* dst_ml = reinterpret_cast<float4*>(q.peer[o] + q.off_rml[slot]) + size_t(q.rank) * q.slice_cap;
     uint32_t done = 0;
     // two rows per warp and iteration, all their loads issued before the first use: the pass is bound by the
     // latency of the loads, not by their bytes
@@ -285,32 +275,39 @@ __global__ void __launch_bounds__(256) dg_p2p_push_merge_kernel(const P2pParams 
         ++done;
       }
     }
-    if (lane == 0 && done) atomicAdd(&s_rows, done);
+    if (lane == 0 && done) atomicAdd(s_rows, done);
     __syncthreads();
     p2p_stamp(q, 2);
-    if (tid == 0 && s_rows) {
+    if (tid == 0 && *s_rows) {
       // A release at system scope by one thread, after the CTA barrier, publishes the stores of every thread
       // of the CTA (release is cumulative over what the barrier ordered before it).  No sequentially
       // consistent fence: those are totally ordered among all CTAs and cost 10 us here with 148 of them.
-      red_release_sys_add(reinterpret_cast<uint32_t*>(q.peer[o] + q.off_cnt) + par, s_rows);
+      red_release_sys_add(reinterpret_cast<uint32_t*>(q.peer[o] + q.off_cnt) + slot, *s_rows);
     }
   }
 
-  p2p_stamp(q, 3);
+}
+
+// Phase B: wait (bounded, on this rank's own memory) until every rank's rows of this rank's slice have landed in
+// receive slot q.merge_slot, merge them and write the finished bf16 rows of the slice to `out`.
+__device__ __forceinline__ void p2p_phase_merge(const P2pParams& q, __nv_bfloat16* __restrict__ out, uint32_t* s_ok) {
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t slot = q.merge_slot, W = q.world, D = q.D;
+  uint8_t* mine = q.peer[q.rank];
   // ---- phase B: wait until every rank's rows of this rank's slice have landed here
   const uint32_t r0 = uint32_t((uint64_t(q.rank) * q.rows) / W), r1 = uint32_t((uint64_t(q.rank + 1) * q.rows) / W);
   if (tid == 0) {
-    const uint32_t want = q.uses * (r1 - r0) * W;
-    if (!wait_flag(reinterpret_cast<const uint32_t*>(mine + q.off_cnt) + par, want, q.wait_limit)) {
-      s_ok = 0u;
+    const uint32_t want = q.merge_uses * (r1 - r0) * W;
+    if (!wait_flag(reinterpret_cast<const uint32_t*>(mine + q.off_cnt) + slot, want, q.wait_limit)) {
+      *s_ok = 0u;
       dev_status_set(q.status, DG_DEV_WAIT_TIMEOUT, KID_MERGE, blockIdx.x, 200u);
     }
   }
   __syncthreads();
   p2p_stamp(q, 4);
-  if (!s_ok) return;   // some rank's rows never arrived: the status word says so, the output is left alone
-  const __half* rows_in = reinterpret_cast<const __half*>(mine + q.off_recv[par]);
-  const float4* ml_in = reinterpret_cast<const float4*>(mine + q.off_rml[par]);
+  if (!*s_ok) return;   // some rank's rows never arrived: the status word says so, the output is left alone
+  const __half* rows_in = reinterpret_cast<const __half*>(mine + q.off_recv[slot]);
+  const float4* ml_in = reinterpret_cast<const float4*>(mine + q.off_rml[slot]);
   // D = 256: two rows per warp and iteration with every load in flight before the first use (the pass is bound
   // by load latency); wider rows go one at a time
   const uint32_t RB = (D <= 256u) ? 2u : 1u;
@@ -374,6 +371,30 @@ __global__ void __launch_bounds__(256) dg_p2p_push_merge_kernel(const P2pParams 
       }
     }
   }
+}
+
+__global__ void __launch_bounds__(256) dg_p2p_push_merge_kernel(const P2pParams q, __nv_bfloat16* __restrict__ out) {
+  __shared__ uint32_t s_ok, s_rows;
+  if (threadIdx.x == 0) {
+    s_ok = 1u;
+    s_rows = 0u;
+  }
+  // the partial was written by the attention kernel that precedes this one on the stream
+  p2p_stamp(q, 0);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  __syncthreads();
+  p2p_stamp(q, 1);
+  if (q.merge_on && q.merge_first) {
+    // pipelined form: the slice of the PREVIOUS step first (its rows arrived a step ago), then this step's rows.
+    // A CTA signals this step's rows only after it has finished reading the previous step's slot, so a peer that
+    // has seen this rank's rows of step i+1 knows that this rank is done with the slot of step i.
+    p2p_phase_merge(q, out, &s_ok);
+    __syncthreads();
+  }
+  if (q.send_on) p2p_phase_send(q, &s_rows);
+  p2p_stamp(q, 3);
+  if (q.merge_on && !q.merge_first) p2p_phase_merge(q, out, &s_ok);
   p2p_stamp(q, 5);
 }
 

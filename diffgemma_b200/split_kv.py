@@ -55,7 +55,8 @@ class SplitKvGroup:
 
     exchange="p2p" (default): partials are merged by a kernel over the peers' exchange buffers (CUDA IPC
     mappings, NVLink); p2p_mode 0-2 leave the full output on every rank, p2p_mode 3 (push form) leaves
-    every rank with its own row slice (`row_slice`) only.  exchange="nccl": two NCCL all-reduces (max of
+    every rank with its own row slice (`row_slice`) only, p2p_mode 4 is the push form pipelined over
+    consecutive steps (the slice of a step is written by the next `denoise` or by `flush`).  exchange="nccl": two NCCL all-reduces (max of
     m, sum of [O | l]).
     """
 
@@ -111,6 +112,15 @@ class SplitKvGroup:
         r0, n = C.c_uint32(), C.c_uint32()
         check(self.ctx.lib.dg_p2p_slice(self.p2p, C.byref(r0), C.byref(n)), "dg_p2p_slice")
         return int(r0.value), int(n.value)
+
+    def set_mode(self, p2p_mode: int) -> None:
+        """Switch the exchange form (every rank, between steps; a pipelined step must have been flushed)."""
+        check(self.ctx.lib.dg_p2p_set_mode(self.p2p, p2p_mode), "dg_p2p_set_mode")
+        self.p2p_mode = p2p_mode
+
+    def flush(self) -> None:
+        """p2p_mode 4: merge the slice of the last step into the `out` that was given with it."""
+        check(self.ctx.lib.dg_p2p_flush(self.p2p), "dg_p2p_flush")
 
     def set_wait_limit(self, cycles: int) -> None:
         check(self.ctx.lib.dg_p2p_set_wait_limit(self.p2p, cycles), "dg_p2p_set_wait_limit")

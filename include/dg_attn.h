@@ -305,8 +305,16 @@ int32_t dg_p2p_handle(dg_p2p* x, uint8_t handle_out[64]);
  *       the owner waits on its own memory, merges and writes ONLY its row slice of `out` (dg_p2p_slice; the
  *       other rows of `out` are left untouched).  One exchange, no result scatter: the form for a host whose
  *       next operator is sharded by rows, or that gathers the slices itself.                                  */
+/*   4 = mode 3 pipelined over consecutive steps, for hosts that keep several independent steps in flight (other
+ *       canvases, other requests): a call sends the rows of ITS step, but first merges the slice of the PREVIOUS
+ *       call's step - whose rows have had a whole step to arrive, so nobody waits for data that is still on its way
+ *       or for a slower rank - into the `out` that was given with that previous call.  The slice of a step is
+ *       therefore written by the NEXT call on the group (or by dg_p2p_flush); keep each `out` valid until then, and
+ *       give consecutive calls different `out` buffers.                                                          */
 int32_t dg_p2p_set_mode(dg_p2p* x, int32_t mode);
-/* The rows of the output this rank owns in mode 3: [*row0, *row0 + *n_rows) of the canvas * n_q_heads rows.    */
+/* Mode 4: merge the slice of the last step into its `out` (the call that a next step would have made).           */
+int32_t dg_p2p_flush(dg_p2p* x);
+/* The rows of the output this rank owns in modes 3 and 4: [*row0, *row0 + *n_rows) of the canvas * n_q_heads rows.    */
 int32_t dg_p2p_slice(const dg_p2p* x, uint32_t* row0, uint32_t* n_rows);
 /* Upper bound, in SM clock cycles, of every device-side wait of the exchange (default 1e9, about half a
  * second; at most 2e10).  The wait covers the peers' host-side launch skew as well as their GPU progress.       */

@@ -690,6 +690,39 @@ def test_shard_cache_partial_matches_full_cache(ctx, P, t0, t1, inc):
     shard.close()
 
 
+def test_pipelined_push_exchange_on_one_rank(ctx):
+    """Mode 4 with this rank as the only peer: the slice of a step is written by the next call or by the flush."""
+    import ctypes as C
+    layer = AttnLayer(n_kv_heads=2)
+    P = 3000
+    cases = [util.make_case(layer, P, seed=520 + i) for i in range(4)]
+    kv, att = util.gpu_setup(ctx, cases[0])          # same prefix for all steps; canvas inputs differ per step
+    lib = ctx.lib
+    x = C.c_void_p()
+    capi.check(lib.dg_p2p_create(ctx.h, layer.canvas * layer.n_q_heads, layer.head_dim, 1, 0, C.byref(x)), "dg_p2p_create")
+    capi.check(lib.dg_p2p_set_mode(x, 4), "dg_p2p_set_mode")
+    outs = [torch.zeros_like(util.dev(cases[0], "q")) for _ in range(4)]
+    ins = [(util.dev(c, "q"), util.dev(c, "kc"), util.dev(c, "vc")) for c in cases]
+    for i in range(4):
+        q, kc, vc = ins[i]
+        capi.check(lib.dg_attn_denoise_split_p2p(ctx.h, C.byref(att.desc), kv.h, P, 0, P, 1, x, util_ptr(q), util_ptr(kc),
+                                                 util_ptr(vc), None, None, util_ptr(outs[i])), "dg_attn_denoise_split_p2p")
+        if i == 0:
+            ctx.synchronize()
+            assert not outs[0].any()                 # nothing has been merged yet
+    assert lib.dg_p2p_set_mode(x, 3) == capi.DG_ERR_INVALID_ARG      # a step is pending
+    capi.check(lib.dg_p2p_flush(x), "dg_p2p_flush")
+    ctx.synchronize()
+    for i, c in enumerate(cases):
+        cc = dict(c)
+        cc["kp"], cc["vp"] = cases[0]["kp"], cases[0]["vp"]
+        util.assert_close(util.t2f(outs[i]), util.run_oracle(cc), f"pipelined exchange, step {i}")
+    capi.check(lib.dg_p2p_set_mode(x, 3), "dg_p2p_set_mode")
+    assert ctx.device_status()[0] == 0
+    lib.dg_p2p_destroy(x)
+    kv.close()
+
+
 @pytest.mark.parametrize("mode", [0, 1, 3])
 def test_peer_exchange_forms_on_one_rank(ctx, mode):
     """world = 1: the exchange kernels run with this rank as the only peer (the push form stores its rows

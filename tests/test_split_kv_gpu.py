@@ -32,16 +32,30 @@ def _rank_main(rank, world, port, P, W, mode, exchange, ret):
         layer = AttnLayer(n_kv_heads=2, window=W, mask_mode=mode)
         case = util.make_case(layer, P, seed=77)          # same seed on every rank: replicated inputs
         dev = f"cuda:{rank}"
-        mode = {"p2p": 0, "p2p-slices": 1, "p2p-allrows": 2, "p2p-push": 3}.get(exchange, 0)
+        mode = {"p2p": 0, "p2p-slices": 1, "p2p-allrows": 2, "p2p-push": 3, "p2p-push-pipelined": 4}.get(exchange, 0)
         grp = SplitKvGroup(ctx, layer, exchange="nccl" if exchange == "nccl" else "p2p", p2p_mode=mode)
         t0, t1 = grp.shard_bounds(P)                       # the cuts count the canvas keys of the last rank
         # the push form runs on shard caches (shard + canvas tokens per rank), the others on full-size ones
-        kv = grp.make_shard_cache(P) if exchange == "p2p-push" else KvCache(ctx, layer, P + layer.canvas)
+        kv = grp.make_shard_cache(P) if exchange.startswith("p2p-push") else KvCache(ctx, layer, P + layer.canvas)
         if t1 > t0:                                        # only this rank's shard is resident
             kv.load_prefix(case["kp"][t0:t1].contiguous().to(dev), case["vp"][t0:t1].contiguous().to(dev), t0)
         out = None
-        for _ in range(3):                                 # several steps: buffer parities and flags are reused
-            out = grp.denoise(kv, P, case["q"].to(dev), case["kc"].to(dev), case["vc"].to(dev))
+        if exchange == "p2p-push-pipelined":
+            # the slice of a step is written by the NEXT call: five steps into three rotating outputs, then the flush;
+            # every output must then hold the same result (the steps have the same inputs)
+            outs = [torch.zeros_like(case["q"].to(dev)) for _ in range(3)]
+            q, kc, vc = case["q"].to(dev), case["kc"].to(dev), case["vc"].to(dev)
+            for i in range(5):
+                grp.denoise(kv, P, q, kc, vc, out=outs[i % 3])
+            grp.flush()
+            ctx.synchronize()
+            r0, n = grp.row_slice()
+            flat = [o.reshape(-1, layer.head_dim) for o in outs]
+            assert torch.equal(flat[0][r0:r0 + n], flat[1][r0:r0 + n]) and torch.equal(flat[0][r0:r0 + n], flat[2][r0:r0 + n])
+            out = grp.gather_rows(outs[1])
+        else:
+            for _ in range(3):                             # several steps: buffer parities and flags are reused
+                out = grp.denoise(kv, P, case["q"].to(dev), case["kc"].to(dev), case["vc"].to(dev))
         if exchange == "p2p-push":
             out = grp.gather_rows(out)                     # every rank holds its row slice only
         ctx.synchronize()
@@ -54,7 +68,7 @@ def _rank_main(rank, world, port, P, W, mode, exchange, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["p2p", "p2p-slices", "p2p-allrows", "p2p-push", "nccl"])
+@pytest.mark.parametrize("exchange", ["p2p", "p2p-slices", "p2p-allrows", "p2p-push", "p2p-push-pipelined", "nccl"])
 @pytest.mark.parametrize("P,W,mode,port", [(6000, 0, 0, 29721), (3000, 1024, 1, 29722)])
 def test_split_kv_matches_oracle(P, W, mode, port, exchange):
     world = min(torch.cuda.device_count(), 4)
@@ -62,7 +76,7 @@ def test_split_kv_matches_oracle(P, W, mode, port, exchange):
         pytest.skip("needs at least 2 GPUs")
     mgr = mp.Manager()
     ret = mgr.dict()
-    port += {"p2p": 0, "nccl": 10, "p2p-slices": 20, "p2p-allrows": 30, "p2p-push": 40}[exchange]
+    port += {"p2p": 0, "nccl": 10, "p2p-slices": 20, "p2p-allrows": 30, "p2p-push": 40, "p2p-push-pipelined": 50}[exchange]
     mp.spawn(_rank_main, args=(world, port, P, W, mode, exchange, ret), nprocs=world, join=True)
     assert len(ret) == world
     for rank, (mx, mean, tol) in ret.items():
