@@ -39,8 +39,8 @@ L2_BYTES = 126e6
 MAX_ABS_GATE, MEAN_ABS_GATE = 2e-2, 2e-3
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention-kernel launch of the headline
-# workload on one GPU, from an ncu capture of this kernel (read 68.2 MB + write 7.5 MB)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {2: 75.70e6}
+# workload on one GPU, from an ncu capture of this kernel (read 70.26 MB + write 4.29 MB)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {2: 74.55e6}
 
 
 def _peaks():
@@ -399,6 +399,8 @@ class Workload:
             self.drain()
             self.two_lanes = False
             self.group.set_mode(3)
+        if self.group is not None and self.args.exchange == "p2p" and not self.args.no_share_q:
+            self.group.set_share_q(True)       # every rank copies in its row slice of Q; the slices cross NVLink
         self.PIPE_DEPTH = 3 if self.world == 1 else 6
         self.pipe = HostPipe(self.ctx, self.lay, 1, self.PIPE_DEPTH)
         self.pending = []
@@ -407,7 +409,10 @@ class Workload:
                           for _ in range(self.PIPE_DEPTH)]
         owner = self.group is None or self.group.owns_canvas
         stores_canvas = owner or self.args.exchange != "p2p"
-        self.h2d_bytes = q0.numel() * 2 + (kc0.numel() * 2 + vc0.numel() * 2 if stores_canvas else 0)
+        q_bytes = q0.numel() * 2
+        if self.group is not None and self.args.exchange == "p2p" and not self.args.no_share_q:
+            q_bytes = self.group.row_slice()[1] * self.lay.head_dim * 2
+        self.h2d_bytes = q_bytes + (kc0.numel() * 2 + vc0.numel() * 2 if stores_canvas else 0)
         if self.group is not None and self.args.exchange == "p2p":
             self.d2h_bytes = self.group.row_slice()[1] * self.lay.head_dim * 2
         else:
@@ -966,8 +971,9 @@ def run_ours(args):
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e,
                     "how": (f"dg_host_pipe, {wl.PIPE_DEPTH} steps in flight on every rank: every step copies its inputs "
                             "from pinned host memory and its result back; copies of neighbouring steps overlap the kernels"
-                            + ("; a rank copies in Q (and the canvas K/V only where they are stored) and copies back its own "
-                               "row slice of the output" if world > 1 and args.exchange == "p2p" else "")),
+                            + ("; a rank copies in its row slice of Q (the ranks exchange the slices over NVLink) and the canvas "
+                               "K/V only where they are stored, and copies back its own row slice of the output"
+                               if world > 1 and args.exchange == "p2p" else "")),
                     "h2d_bytes_per_step": h2d_total, "d2h_bytes_per_step": d2h_total},
             "gpu_launches": int(launches_per_step * args.steps),
             "clocks": clocks,
@@ -1018,6 +1024,8 @@ def main():
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="multi-GPU partial exchange")
     ap.add_argument("--exchange-timeline", action="store_true",
                     help="multi-GPU: add in-kernel time stamps of one split-KV step on every rank to the line")
+    ap.add_argument("--no-share-q", action="store_true",
+                    help="multi-GPU end-to-end arm: every rank copies the whole Q from host memory")
     ap.add_argument("--one-lane", action="store_true",
                     help="multi-GPU: one context per rank instead of two that take alternate steps")
     ap.add_argument("--no-pipelined-exchange", action="store_true",

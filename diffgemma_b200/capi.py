@@ -98,6 +98,7 @@ SIGNATURES = {
     "dg_p2p_set_wait_limit": (_i32, [_vp, _u64]),
     "dg_p2p_reset": (_i32, [_vp]),
     "dg_p2p_flush": (_i32, [_vp]),
+    "dg_p2p_set_share_q": (_i32, [_vp, _i32]),
     "dg_p2p_phase_stamps": (_i32, [_vp, _vp]),
     "dg_p2p_handle": (_i32, [_vp, _vp]),
     "dg_p2p_connect": (_i32, [_vp, _vp]),

@@ -914,7 +914,7 @@ static int32_t check_ptrs16(std::initializer_list<const void*> ps) {
 }
 
 // one canvas: stage 1 on K/V (+ table), then stage 2 with the fused Q prologue
-static int32_t denoise_one(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint32_t kv_len, uint32_t slot, const void* q,
+static int32_t denoise_one(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint32_t kv_len, const void* q,
                            const void* k, const void* v, const void* qw, const void* kw, const uint8_t* attend,
                            AttnCall a) {
   int32_t r = check_kv(d, kv, uint64_t(kv_len) + d.canvas);
@@ -1072,7 +1072,7 @@ extern "C" int32_t dg_attn_denoise(dg_ctx* c, const dg_layer_desc* d, dg_kv* con
       AttnCall a;
       a.out = static_cast<__nv_bfloat16*>(out) + b * qe;
       a.defer = &prep[b];
-      rc = denoise_one(c, *d, kv[b], kv_len[b], b, static_cast<const __nv_bfloat16*>(q) + b * qe,
+      rc = denoise_one(c, *d, kv[b], kv_len[b], static_cast<const __nv_bfloat16*>(q) + b * qe,
                        static_cast<const __nv_bfloat16*>(k) + b * ke, static_cast<const __nv_bfloat16*>(v) + b * ke, qw, kw,
                        nullptr, a);
       if (rc == DG_OK && !prep[b].filled) rc = fail(DG_ERR_INVALID_ARG, "internal: batched canvas did not take the tensor path");
@@ -1099,7 +1099,7 @@ extern "C" int32_t dg_attn_denoise(dg_ctx* c, const dg_layer_desc* d, dg_kv* con
   for (uint32_t b = 0; b < batch && rc == DG_OK; ++b) {
     AttnCall a;
     a.out = static_cast<__nv_bfloat16*>(out) + b * qe;
-    rc = denoise_one(c, *d, kv[b], kv_len[b], b, static_cast<const __nv_bfloat16*>(q) + b * qe,
+    rc = denoise_one(c, *d, kv[b], kv_len[b], static_cast<const __nv_bfloat16*>(q) + b * qe,
                      static_cast<const __nv_bfloat16*>(k) + b * ke, static_cast<const __nv_bfloat16*>(v) + b * ke, qw, kw,
                      nullptr, a);
   }
@@ -1268,6 +1268,9 @@ extern "C" int32_t dg_host_pipe_submit(dg_host_pipe* hp, const dg_layer_desc* d,
 struct dg_p2p;
 static bool p2p_is_push(const dg_p2p* x);
 static void p2p_slice_bytes(const dg_p2p* x, size_t* off, size_t* bytes);
+// shared query staging: null when the group does not share Q; else the slot's device buffer, after the slice
+// exchange has been queued on `st`
+static int32_t p2p_share_q(dg_p2p* x, uint32_t slot, const void* q_host, cudaStream_t st, __nv_bfloat16** q_dev);
 extern "C" int32_t dg_attn_denoise_split_p2p(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint32_t kv_len, uint32_t t0,
                                              uint32_t t1, int32_t include_canvas, dg_p2p* x, const void* q, const void* k,
                                              const void* v, const void* qw, const void* kw, void* out);
@@ -1289,7 +1292,15 @@ extern "C" int32_t dg_host_pipe_submit_split(dg_host_pipe* hp, const dg_layer_de
     sl.pending = false;
   }
   if (sl.used) DG_CUDA(cudaStreamWaitEvent(hp->h2d, sl.cmp, 0));
-  DG_CUDA(cudaMemcpyAsync(sl.q, q, qe * 2, cudaMemcpyHostToDevice, hp->h2d));
+  // Q: the whole block from this rank's host memory, or (dg_p2p_set_share_q) only this rank's row slice, the
+  // other slices arriving from the peers over NVLink
+  __nv_bfloat16* q_dev = nullptr;
+  r = p2p_share_q(x, uint32_t(hp->next % hp->depth), q, hp->h2d, &q_dev);
+  if (r != DG_OK) return r;
+  if (q_dev == nullptr) {
+    DG_CUDA(cudaMemcpyAsync(sl.q, q, qe * 2, cudaMemcpyHostToDevice, hp->h2d));
+    q_dev = sl.q;
+  }
   const bool stores_canvas = include_canvas != 0 || !kv->shard;
   if (stores_canvas) {
     DG_CUDA(cudaMemcpyAsync(sl.k, k, ke * 2, cudaMemcpyHostToDevice, hp->h2d));
@@ -1301,7 +1312,7 @@ extern "C" int32_t dg_host_pipe_submit_split(dg_host_pipe* hp, const dg_layer_de
   {
     const int saved = c->inputs_stable;   // as in dg_host_pipe_submit
     c->inputs_stable = 1;
-    r = dg_attn_denoise_split_p2p(c, d, kv, kv_len, t0, t1, include_canvas, x, sl.q, sl.k, sl.v, qw, kw, sl.o);
+    r = dg_attn_denoise_split_p2p(c, d, kv, kv_len, t0, t1, include_canvas, x, q_dev, sl.k, sl.v, qw, kw, sl.o);
     c->inputs_stable = saved;
   }
   if (r != DG_OK) return r;
@@ -1328,7 +1339,7 @@ extern "C" int32_t dg_attn_denoise_bitmap(dg_ctx* c, const dg_layer_desc* d, dg_
   c->last_launches = 0;
   AttnCall a;
   a.out = out;
-  return denoise_one(c, *d, kv, kv_len, 0, q, k, v, qw, kw, attend, a);
+  return denoise_one(c, *d, kv, kv_len, q, k, v, qw, kw, attend, a);
 }
 
 extern "C" int32_t dg_attn_partial(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint32_t kv_len, uint32_t t0, uint32_t t1,
@@ -1349,7 +1360,7 @@ extern "C" int32_t dg_attn_partial(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv,
   a.t0 = t0;
   a.t1 = t1;
   a.include_canvas = include_canvas ? 1 : 0;
-  return denoise_one(c, *d, kv, kv_len, 0, q, k, v, qw, kw, nullptr, a);
+  return denoise_one(c, *d, kv, kv_len, q, k, v, qw, kw, nullptr, a);
 }
 
 extern "C" int32_t dg_attn_merge_local(dg_ctx* c, uint32_t n_parts, uint32_t rows, uint32_t head_dim, const float* o,
@@ -1625,6 +1636,9 @@ struct dg_p2p {
   bool pend = false;
   uint32_t pend_slot = 0, pend_uses = 0;
   void* pend_out = nullptr;
+  // host pipeline: every rank copies in its own row slice of Q and the slices are exchanged over peer memory
+  bool share_q = false;
+  uint32_t q_uses[8] = {};
   int32_t mode = 0;          // 0 automatic (all rows with two ranks, slices otherwise), 1 slices, 2 all rows, 3 push
   bool poisoned = false;     // a launch failed half-way through a step: the ranks may disagree until dg_p2p_reset
   unsigned long long* stamps = nullptr;   // caller-owned device buffer for the merge kernel's stamps
@@ -1636,6 +1650,23 @@ static void p2p_slice_bytes(const dg_p2p* x, size_t* off, size_t* bytes) {
   const size_t r0 = (size_t(x->rank) * x->rows) / x->world, r1 = (size_t(x->rank + 1) * x->rows) / x->world;
   *off = r0 * x->D * 2;
   *bytes = (r1 - r0) * x->D * 2;
+}
+
+static int32_t p2p_share_q(dg_p2p* x, uint32_t slot, const void* q_host, cudaStream_t st, __nv_bfloat16** q_dev) {
+  *q_dev = nullptr;
+  if (!x->share_q || x->world < 2 || slot >= 8) return DG_OK;
+  size_t off = 0, bytes = 0;
+  p2p_slice_bytes(x, &off, &bytes);
+  uint8_t* stage = x->local + x->layout.off_qstage[slot];
+  DG_CUDA(cudaMemcpyAsync(stage + off, static_cast<const uint8_t*>(q_host) + off, bytes, cudaMemcpyHostToDevice, st));
+  x->q_uses[slot] += 1u;
+  const cudaError_t e = launch_p2p_qgather(x->layout, slot, x->q_uses[slot], st);
+  if (e != cudaSuccess) {
+    x->poisoned = true;
+    return fail_cuda(e, "launch_p2p_qgather");
+  }
+  *q_dev = reinterpret_cast<__nv_bfloat16*>(stage);
+  return DG_OK;
 }
 
 static void p2p_layout(dg_p2p* x) {
@@ -1654,10 +1685,12 @@ static void p2p_layout(dg_p2p* x) {
     L.off_recv[p] = take(size_t(x->world) * L.slice_cap * x->D * 2);
     L.off_rml[p] = take(size_t(x->world) * L.slice_cap * 16);
   }
+  for (int p = 0; p < 8; ++p) L.off_qstage[p] = take(size_t(x->rows) * x->D * 2);
   L.off_pflag = take(2 * 8 * 4);
   L.off_rflag = take(2 * 8 * 4);
   L.off_done = take(2 * 4);
   L.off_cnt = take(3 * 4);
+  L.off_qcnt = take(8 * 4);
   x->bytes = off;
   L.world = x->world;
   L.rank = x->rank;
@@ -1717,6 +1750,12 @@ extern "C" int32_t dg_p2p_slice(const dg_p2p* x, uint32_t* row0, uint32_t* n_row
   return DG_OK;
 }
 
+extern "C" int32_t dg_p2p_set_share_q(dg_p2p* x, int32_t on) {
+  if (!x) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  x->share_q = on != 0;
+  return DG_OK;
+}
+
 extern "C" int32_t dg_p2p_flush(dg_p2p* x) {
   if (!x) return fail(DG_ERR_INVALID_ARG, "NULL argument");
   if (!x->pend) return DG_OK;
@@ -1753,6 +1792,7 @@ extern "C" int32_t dg_p2p_reset(dg_p2p* x) {
   DG_CUDA(cudaMemset(x->local + L.off_pflag, 0, x->bytes - L.off_pflag));
   x->step = 0;
   x->push_uses[0] = x->push_uses[1] = x->push_uses[2] = 0;
+  for (uint32_t& u : x->q_uses) u = 0;
   x->pend = false;
   x->poisoned = false;
   return DG_OK;
@@ -1828,7 +1868,7 @@ extern "C" int32_t dg_attn_denoise_split_p2p(dg_ctx* c, const dg_layer_desc* d, 
   pp.step = step;
   pp.parity = par;
   pp.stamps = x->stamps;
-  r = denoise_one(c, *d, kv, kv_len, 0, q, k, v, qw, kw, nullptr, a);
+  r = denoise_one(c, *d, kv, kv_len, q, k, v, qw, kw, nullptr, a);
   if (r != DG_OK) {
     if (c->last_launches != 0) x->poisoned = true;   // part of the step is already queued
     return r;

@@ -206,6 +206,10 @@ struct P2pParams {
   // push form: per slot (step mod 3) a receive area [world][slice_cap][D] fp16 rows, their [world][slice_cap]
   // (m, l, 1 / scale, -) records, and one arrival counter (rows received since the last reset)
   size_t off_recv[3], off_rml[3], off_cnt;
+  // shared query staging of the host pipeline: per pipe slot a full [rows][D] bf16 query block that every rank
+  // fills with its own row slice (copied from host memory) and its peers' slices (pushed over NVLink), and one
+  // arrival counter per slot (rows received from peers since the last reset)
+  size_t off_qstage[8], off_qcnt;
   DevStatus* status;
   long long wait_limit;    // cycles
   uint32_t world, rank, rows, D, step, parity;

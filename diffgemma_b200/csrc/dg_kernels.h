@@ -20,6 +20,8 @@ void launch_p2p_merge(const P2pParams& q, void* out, int num_sms, cudaStream_t s
 // push form: every rank sends each row of its partial to the rank that owns the row, the owner merges;
 // `out` receives this rank's row slice only (rows [rank * rows / world, (rank + 1) * rows / world))
 cudaError_t launch_p2p_push_merge(const P2pParams& q, void* out, int num_sms, cudaStream_t st);
+// host pipeline: push this rank's row slice of the staged queries (slot) to every peer and wait for theirs
+cudaError_t launch_p2p_qgather(const P2pParams& q, uint32_t slot, uint32_t uses, cudaStream_t st);
 void launch_selftest_wait(uint32_t* flag, long long limit_cycles, DevStatus* status, cudaStream_t st);
 
 // Tensor-core kernel (head_dim 256).  tm_k / tm_v: 3-D tensor maps {D, cap, Hkv}, box {64, 128, 1},

@@ -416,6 +416,42 @@ cudaError_t launch_p2p_push_merge(const P2pParams& q, void* out, int num_sms, cu
   return cudaLaunchKernelEx(&cfg, dg_p2p_push_merge_kernel, q, static_cast<__nv_bfloat16*>(out));
 }
 
+// ------------------------------------------------------------------------------------------
+// Query all-gather of the host pipeline: split-KV replicates Q on every rank, but N copies of it from host memory
+// share the host's PCIe links.  Every rank copies in only its own row slice; this kernel stores that slice into the
+// same slot of every peer's query staging (posted stores over NVLink), publishes the row count with a system-scope
+// release per peer, and waits (bounded, on this rank's own memory) until the other ranks' slices have landed here.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) dg_p2p_qgather_kernel(const P2pParams q, uint32_t slot, uint32_t uses) {
+  const uint32_t tid = threadIdx.x, W = q.world;
+  const uint32_t r0 = uint32_t((uint64_t(q.rank) * q.rows) / W), r1 = uint32_t((uint64_t(q.rank + 1) * q.rows) / W);
+  const size_t row_units = size_t(q.D) * 2 / 16;                       // 16-byte units per row
+  const uint4* src = reinterpret_cast<const uint4*>(q.peer[q.rank] + q.off_qstage[slot]) + size_t(r0) * row_units;
+  // this CTA's share of the slice, whole rows
+  const uint32_t n_rows = r1 - r0;
+  const uint32_t per = (n_rows + gridDim.x - 1) / gridDim.x;
+  const uint32_t a = blockIdx.x * per < n_rows ? blockIdx.x * per : n_rows;
+  const uint32_t b = a + per < n_rows ? a + per : n_rows;
+  for (uint32_t w = 1; w < W; ++w) {
+    const uint32_t peer = (q.rank + w) % W;
+    uint4* dst = reinterpret_cast<uint4*>(q.peer[peer] + q.off_qstage[slot]) + size_t(r0) * row_units;
+    for (size_t i = size_t(a) * row_units + tid; i < size_t(b) * row_units; i += 256) dst[i] = src[i];
+  }
+  __syncthreads();
+  if (tid < W && tid != q.rank && b > a)
+    red_release_sys_add(reinterpret_cast<uint32_t*>(q.peer[tid] + q.off_qcnt) + slot, b - a);
+  if (blockIdx.x == 0 && tid == 0) {
+    const uint32_t want = uses * (q.rows - n_rows);
+    if (!wait_flag(reinterpret_cast<const uint32_t*>(q.peer[q.rank] + q.off_qcnt) + slot, want, q.wait_limit))
+      dev_status_set(q.status, DG_DEV_WAIT_TIMEOUT, KID_MERGE, blockIdx.x, 300u + slot);
+  }
+}
+
+cudaError_t launch_p2p_qgather(const P2pParams& q, uint32_t slot, uint32_t uses, cudaStream_t st) {
+  dg_p2p_qgather_kernel<<<16, 256, 0, st>>>(q, slot, uses);
+  return cudaGetLastError();
+}
+
 void launch_p2p_merge(const P2pParams& q, void* out, int num_sms, cudaStream_t st) {
   const uint32_t slice = q.all_rows ? q.rows : (q.rows + q.world - 1) / q.world;
   uint32_t grid = (slice + 7) / 8;

@@ -71,6 +71,7 @@ class SplitKvGroup:
         self.att = CanvasAttention(ctx, layer)
         self.comm = None
         self.p2p = None
+        self._bounds = {}             # kv_len -> this rank's (t0, t1): steps repeat at the same positions
         lib = ctx.lib
         on_gpu = dist.get_backend(group) == "nccl"
         xdev = torch.device("cuda", ctx.device) if on_gpu else torch.device("cpu")
@@ -93,8 +94,11 @@ class SplitKvGroup:
         self.comm = _nccl_comm(ctx, group)
 
     def shard_bounds(self, kv_len: int):
-        b = plan_shards(kv_len, self.world, canvas=self.layer.canvas)
-        return b[self.rank], b[self.rank + 1]
+        hit = self._bounds.get(kv_len)
+        if hit is None:
+            b = plan_shards(kv_len, self.world, canvas=self.layer.canvas)
+            hit = self._bounds[kv_len] = (b[self.rank], b[self.rank + 1])
+        return hit
 
     @property
     def owns_canvas(self) -> bool:
@@ -117,6 +121,10 @@ class SplitKvGroup:
         """Switch the exchange form (every rank, between steps; a pipelined step must have been flushed)."""
         check(self.ctx.lib.dg_p2p_set_mode(self.p2p, p2p_mode), "dg_p2p_set_mode")
         self.p2p_mode = p2p_mode
+
+    def set_share_q(self, on: bool) -> None:
+        """Host pipeline: every rank copies in only its row slice of Q, the ranks exchange the slices over NVLink."""
+        check(self.ctx.lib.dg_p2p_set_share_q(self.p2p, int(on)), "dg_p2p_set_share_q")
 
     def flush(self) -> None:
         """p2p_mode 4: merge the slice of the last step into the `out` that was given with it."""

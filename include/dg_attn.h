@@ -312,6 +312,11 @@ int32_t dg_p2p_handle(dg_p2p* x, uint8_t handle_out[64]);
  *       therefore written by the NEXT call on the group (or by dg_p2p_flush); keep each `out` valid until then, and
  *       give consecutive calls different `out` buffers.                                                          */
 int32_t dg_p2p_set_mode(dg_p2p* x, int32_t mode);
+/* For dg_host_pipe_submit_split: with on = 1 a rank copies in only ITS row slice of the host's Q (the same rows it
+ * owns of the output) and the ranks exchange the slices over peer memory, instead of every rank copying the whole
+ * replicated Q over the host's PCIe links.  Every rank must use the same setting, the same pipe depth, and host
+ * buffers q that hold the same values on every rank.  Off by default.                                            */
+int32_t dg_p2p_set_share_q(dg_p2p* x, int32_t on);
 /* Mode 4: merge the slice of the last step into its `out` (the call that a next step would have made).           */
 int32_t dg_p2p_flush(dg_p2p* x);
 /* The rows of the output this rank owns in modes 3 and 4: [*row0, *row0 + *n_rows) of the canvas * n_q_heads rows.    */

@@ -164,6 +164,69 @@ def test_push_exchange_timeout_is_reported_and_group_recovers():
             assert mx <= r["tol"] and mean <= 2e-3, (rank, key, mx, mean)
 
 
+def _pipe_main(rank, world, port, share_q, ret):
+    """The host-buffer pipeline of one rank under split-KV: several steps in flight, each with its own host inputs;
+    every rank ends with its row slice of every step's output in host memory."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import util
+    from diffgemma_b200.split_kv import SplitKvGroup
+    from diffgemma_b200.step_attn import AttnLayer, Context, HostPipe
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        ctx = Context(rank)
+        layer = AttnLayer(n_kv_heads=2)
+        P = 4000
+        cases = [util.make_case(layer, P, seed=600 + i) for i in range(7)]     # same seeds on every rank
+        dev = f"cuda:{rank}"
+        grp = SplitKvGroup(ctx, layer, exchange="p2p", p2p_mode=3)
+        grp.set_share_q(share_q)
+        kv = grp.make_shard_cache(P)
+        t0, t1 = grp.shard_bounds(P)
+        kv.load_prefix(cases[0]["kp"][t0:t1].contiguous().to(dev), cases[0]["vp"][t0:t1].contiguous().to(dev), t0)
+        pipe = HostPipe(ctx, layer, 1, 3)
+        hosts = [tuple(c[n].contiguous().pin_memory() for n in ("q", "kc", "vc")) + (torch.zeros_like(c["q"]).pin_memory(),)
+                 for c in cases]
+        tickets = [pipe.submit_split(kv, P, t0, t1, grp.owns_canvas, grp.p2p, q, k, v, o) for q, k, v, o in hosts]
+        for t in tickets:
+            pipe.wait(t)
+        ctx.synchronize()
+        r0, n = grp.row_slice()
+        worst = (0.0, 0.0)
+        for c, (_, _, _, o) in zip(cases, hosts):
+            cc = dict(c)
+            cc["kp"], cc["vp"] = cases[0]["kp"], cases[0]["vp"]
+            ref = util.run_oracle(cc).reshape(-1, layer.head_dim)[r0:r0 + n]
+            got = util.t2f(o).reshape(-1, layer.head_dim)
+            assert not got[:r0].any() and not got[r0 + n:].any()          # only this rank's slice is copied back
+            e = util.errors(got[r0:r0 + n], ref)
+            worst = (max(worst[0], e[0]), max(worst[1], e[1]))
+        ret[rank] = worst
+        pipe.close()
+        grp.close()
+        kv.close()
+        ctx.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("share_q,port", [(False, 29771), (True, 29772)])
+def test_host_pipe_split_step(share_q, port):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_pipe_main, args=(2, port, share_q, ret), nprocs=2, join=True)
+    assert len(ret) == 2
+    for rank in range(2):
+        mx, mean = ret[rank]
+        assert mx <= 2e-2 and mean <= 2e-3, (rank, mx, mean)
+
+
 def _head_shard_main(rank, world, port, P, W, mode, ret):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
