@@ -399,7 +399,7 @@ class Workload:
             self.drain()
             self.two_lanes = False
             self.group.set_mode(3)
-        if self.group is not None and self.args.exchange == "p2p" and not self.args.no_share_q:
+        if self.group is not None and self.args.exchange == "p2p" and self.args.share_q:
             self.group.set_share_q(True)       # every rank copies in its row slice of Q; the slices cross NVLink
         self.PIPE_DEPTH = 3 if self.world == 1 else 6
         self.pipe = HostPipe(self.ctx, self.lay, 1, self.PIPE_DEPTH)
@@ -410,7 +410,7 @@ class Workload:
         owner = self.group is None or self.group.owns_canvas
         stores_canvas = owner or self.args.exchange != "p2p"
         q_bytes = q0.numel() * 2
-        if self.group is not None and self.args.exchange == "p2p" and not self.args.no_share_q:
+        if self.group is not None and self.args.exchange == "p2p" and self.args.share_q:
             q_bytes = self.group.row_slice()[1] * self.lay.head_dim * 2
         self.h2d_bytes = q_bytes + (kc0.numel() * 2 + vc0.numel() * 2 if stores_canvas else 0)
         if self.group is not None and self.args.exchange == "p2p":
@@ -1024,8 +1024,9 @@ def main():
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="multi-GPU partial exchange")
     ap.add_argument("--exchange-timeline", action="store_true",
                     help="multi-GPU: add in-kernel time stamps of one split-KV step on every rank to the line")
-    ap.add_argument("--no-share-q", action="store_true",
-                    help="multi-GPU end-to-end arm: every rank copies the whole Q from host memory")
+    ap.add_argument("--share-q", action="store_true",
+                    help="multi-GPU end-to-end arm: every rank copies in only its row slice of Q and the ranks "
+                         "exchange the slices over NVLink (for hosts whose PCIe links are the bottleneck)")
     ap.add_argument("--one-lane", action="store_true",
                     help="multi-GPU: one context per rank instead of two that take alternate steps")
     ap.add_argument("--no-pipelined-exchange", action="store_true",
