@@ -966,7 +966,8 @@ def run_ours(args):
                          "peak_sustained": peaks["bf16_tflops_sustained"],
                          "frac_of_sustained": (achieved / peaks["bf16_tflops_sustained"])
                          if (achieved and peaks["bf16_tflops_sustained"]) else None,
-                         "kernel": "dg_attn_sm100_hd512_kernel" if lay.head_dim == 512 else "dg_attn_sm100_kernel",
+                         "kernel": ("dg_attn_sm100_hd512_kernel" if args.kernel_form == "single" else "dg_attn_sm100_hd512x_kernel")
+                         if lay.head_dim == 512 else "dg_attn_sm100_kernel",
                          "kernel_ms": k_avg_ms, "kernel_launches_timed": k_n, "kernel_ms_how": k_how, "sustained": sustained},
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e,
                     "how": (f"dg_host_pipe, {wl.PIPE_DEPTH} steps in flight on every rank: every step copies its inputs "

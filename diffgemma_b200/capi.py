@@ -42,6 +42,12 @@ _i32 = C.c_int32
 _u64 = C.c_uint64
 _pd = C.POINTER(LayerDesc)
 
+
+class BlockWeights(C.Structure):
+    """dg_block_weights of include/dg_attn.h (field for field)."""
+    _fields_ = [("input_ln", C.c_void_p), ("w_qkv", C.c_void_p), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
+                ("w_o", C.c_void_p), ("post_attn_ln", C.c_void_p), ("hidden", C.c_uint32), ("v_from_k", C.c_uint32)]
+
 # name -> (restype, argtypes); must list every symbol of include/dg_attn.h
 SIGNATURES = {
     "dg_ctx_create": (_i32, [_i32, C.POINTER(_vp)]),
@@ -61,6 +67,7 @@ SIGNATURES = {
     "dg_ctx_set_inputs_stable": (_i32, [_vp, _i32]),
     "dg_ctx_set_pair_mode": (_i32, [_vp, _i32]),
     "dg_ctx_max_active_clusters": (_i32, [_vp, _i32, _u32]),
+    "dg_attn_block": (_i32, [_vp, _pd, C.POINTER(BlockWeights), _vp, _u32, _vp, _vp]),
     "dg_kv_create": (_i32, [_vp, _pd, _u64, C.POINTER(_vp)]),
     "dg_kv_create_ring": (_i32, [_vp, _pd, _u32, C.POINTER(_vp)]),
     "dg_kv_create_shard": (_i32, [_vp, _pd, _u64, _u64, C.POINTER(_vp)]),

@@ -65,6 +65,23 @@ struct dg_ctx {
   float* nccl_pay = nullptr;           // [rows][D+1] payload of the cross-rank merge
   float* nccl_mg = nullptr;            // [rows]
   size_t nccl_rows = 0, nccl_d = 0;
+  // dg_attn_block: activations between its kernels (normed input, Q, K, V, O, projected O, row sums of squares)
+  __nv_bfloat16* blk_xn = nullptr;
+  __nv_bfloat16* blk_q = nullptr;
+  __nv_bfloat16* blk_k = nullptr;
+  __nv_bfloat16* blk_v = nullptr;
+  __nv_bfloat16* blk_o = nullptr;
+  __nv_bfloat16* blk_t = nullptr;
+  float* blk_sq = nullptr;
+  size_t blk_rows = 0, blk_hidden = 0, blk_qe = 0, blk_ke = 0;
+  CUtensorMap blk_tm_xn, blk_tm_o;
+  struct WMap {
+    const void* w;
+    uint32_t n, k, bn;
+    CUtensorMap tm;
+  };
+  std::vector<WMap> blk_wmaps;         // tensor maps of the weight matrices seen so far
+  int q_from_prev_kernel = 0;          // 1 while dg_attn_block runs: Q is written by the kernel queued just ahead
   int force_general = 0;
   int fused_append = 1;                // 1: the canvas append runs inside the attention launch where it can
   int inputs_stable = 0;               // 1: the caller's q/k/v are not written by work queued ahead of a call
@@ -304,6 +321,8 @@ extern "C" int32_t dg_ctx_create(int32_t device, dg_ctx** out) {
   if (e == cudaSuccess) e = sm100_attn_configure();
   if (e == cudaSuccess) e = sm100_pair_configure();
   if (e == cudaSuccess) e = sm100_hd512_configure();
+  if (e == cudaSuccess) e = sm100_hd512x_configure();
+  if (e == cudaSuccess) e = sm100_gemm_configure();
   if (e != cudaSuccess) {
     dg_ctx_destroy(c);
     return fail_cuda(e, "dg_ctx_create");
@@ -327,6 +346,13 @@ extern "C" int32_t dg_ctx_destroy(dg_ctx* c) {
   cudaFree(c->stage_o);
   cudaFree(c->nccl_pay);
   cudaFree(c->nccl_mg);
+  cudaFree(c->blk_xn);
+  cudaFree(c->blk_q);
+  cudaFree(c->blk_k);
+  cudaFree(c->blk_v);
+  cudaFree(c->blk_o);
+  cudaFree(c->blk_t);
+  cudaFree(c->blk_sq);
   for (cudaEvent_t e : c->ev) cudaEventDestroy(e);
   if (c->own_stream) cudaStreamDestroy(c->own_stream);
   delete c;
@@ -820,7 +846,9 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
     if (!a.q_prenormed) return fail(DG_ERR_UNSUPPORTED, "head_dim 512 tensor path needs a prenormed Q");
     const uint32_t q_tiles5 = sm100_query_tiles(p.C, p.G, p.Hkv);
     if (q_tiles5 * 2 > (fixed ? fixed->n_counters : kMaxQueryTiles)) return fail(DG_ERR_UNSUPPORTED, "too many query tiles");
-    p.n_splits = choose_splits(c, q_tiles5 * 2, sm100_hd512_key_tiles(p.mask));
+    // CTA-pair form (the two halves split the score work and exchange P) unless the single form is asked for
+    const bool pair5 = !fixed && c->pair_mode != 0;
+    p.n_splits = choose_splits(c, q_tiles5 * 2, pair5 ? sm100_hd512x_key_steps(p.mask) : sm100_hd512_key_tiles(p.mask));
     p.cluster_splits = 1;
     if (fixed) {
       // as many splits as the fixed arrays hold: [splits][rows][512] partial O, [2 splits][rows] (m, l) pairs
@@ -841,7 +869,8 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
     }
     const bool timed5 = c->timing && c->ev_used + 2 <= c->ev.size();
     if (timed5) DG_CUDA(cudaEventRecord(c->ev[c->ev_used], c->stream));
-    const cudaError_t e5 = launch_attn_sm100_hd512(p, kv->tm_k, kv->tm_v, launch_stream(c));
+    const cudaError_t e5 = pair5 ? launch_attn_sm100_hd512x(p, kv->tm_k, kv->tm_v, launch_stream(c))
+                                 : launch_attn_sm100_hd512(p, kv->tm_k, kv->tm_v, launch_stream(c));
     if (e5 != cudaSuccess) return fail_cuda(e5, "launch_attn_sm100_hd512");
     if (timed5) {
       DG_CUDA(cudaEventRecord(c->ev[c->ev_used + 1], c->stream));
@@ -981,7 +1010,7 @@ static int32_t denoise_one(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, uint32_
     // (Q, its weight, the table) comes from that kernel: the stand-alone append kernel is known not to
     // write them; with the append inside the launch the kernel ahead is the caller's, so the caller must
     // have said that its inputs are stable
-    a.early_q = in_launch ? (c->inputs_stable != 0) : cached;
+    a.early_q = !c->q_from_prev_kernel && (in_launch ? (c->inputs_stable != 0) : cached);
   }
   a.kv_len = kv_len;
   a.attend = attend;
@@ -1917,5 +1946,136 @@ extern "C" int32_t dg_attn_denoise_split_p2p(dg_ctx* c, const dg_layer_desc* d, 
   }
   x->step = step;
   c->last_launches += 1;
+  return DG_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// the attention stage with its neighbours: input norm -> Q|K|V projection -> attention -> output projection
+// -> post-attention norm + residual (reference: encode_layer_qkv_gemm, encode_layer_qk_rope_kv_dispatch,
+// encode_layer_attention_dispatch, encode_layer_o_proj_post_attn of src/metal/step_kernel/enc.rs:852-911,1560-1629)
+// ------------------------------------------------------------------------------------------
+static int32_t ensure_block_ws(dg_ctx* c, size_t rows, size_t hidden, size_t qe, size_t ke) {
+  if (rows <= c->blk_rows && hidden <= c->blk_hidden && qe <= c->blk_qe && ke <= c->blk_ke) return DG_OK;
+  DG_CUDA(cudaStreamSynchronize(c->stream));
+  const size_t R = rows > c->blk_rows ? rows : c->blk_rows, H = hidden > c->blk_hidden ? hidden : c->blk_hidden;
+  const size_t Q = qe > c->blk_qe ? qe : c->blk_qe, K = ke > c->blk_ke ? ke : c->blk_ke;
+  for (void* ptr : {(void*)c->blk_xn, (void*)c->blk_q, (void*)c->blk_k, (void*)c->blk_v, (void*)c->blk_o, (void*)c->blk_t,
+                    (void*)c->blk_sq})
+    cudaFree(ptr);
+  c->blk_xn = c->blk_q = c->blk_k = c->blk_v = c->blk_o = c->blk_t = nullptr;
+  c->blk_sq = nullptr;
+  c->blk_rows = c->blk_hidden = c->blk_qe = c->blk_ke = 0;
+  // rows are padded to whole 128-row tiles: the projections' loads of a ragged last tile stay inside the buffers
+  const size_t Rp = (R + 127) / 128 * 128;
+  DG_CUDA(cudaMalloc(&c->blk_xn, Rp * H * 2));
+  DG_CUDA(cudaMalloc(&c->blk_q, Rp * Q * 2));
+  DG_CUDA(cudaMalloc(&c->blk_k, Rp * K * 2));
+  DG_CUDA(cudaMalloc(&c->blk_v, Rp * K * 2));
+  DG_CUDA(cudaMalloc(&c->blk_o, Rp * Q * 2));
+  DG_CUDA(cudaMalloc(&c->blk_t, Rp * H * 2));
+  DG_CUDA(cudaMalloc(&c->blk_sq, Rp * (H / 64 + 1) * sizeof(float)));
+  DG_CUDA(cudaMemset(c->blk_xn, 0, Rp * H * 2));
+  DG_CUDA(cudaMemset(c->blk_o, 0, Rp * Q * 2));
+  c->blk_rows = R;
+  c->blk_hidden = H;
+  c->blk_qe = Q;
+  c->blk_ke = K;
+  return DG_OK;
+}
+
+static int32_t weight_map(dg_ctx* c, const void* w, uint32_t n, uint32_t k, uint32_t bn, const CUtensorMap** out) {
+  for (const dg_ctx::WMap& m : c->blk_wmaps)
+    if (m.w == w && m.n == n && m.k == k && m.bn == bn) {
+      *out = &m.tm;
+      return DG_OK;
+    }
+  if (c->blk_wmaps.size() >= 4096) c->blk_wmaps.clear();
+  dg_ctx::WMap m;
+  m.w = w;
+  m.n = n;
+  m.k = k;
+  m.bn = bn;
+  const int32_t r = make_kv_tmap(&m.tm, const_cast<void*>(w), n, 1, bn, k);
+  if (r != DG_OK) return r;
+  c->blk_wmaps.push_back(m);
+  *out = &c->blk_wmaps.back().tm;
+  return DG_OK;
+}
+
+extern "C" int32_t dg_attn_block(dg_ctx* c, const dg_layer_desc* d, const dg_block_weights* w, dg_kv* kv, uint32_t kv_len,
+                                 const void* hidden_in, void* stream_out) {
+  if (!c || !w || !kv || !hidden_in || !stream_out || !w->w_qkv || !w->w_o) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  int32_t r = check_desc(d);
+  if (r != DG_OK) return r;
+  r = check_ptrs16({hidden_in, stream_out, w->w_qkv, w->w_o, w->input_ln, w->post_attn_ln, w->q_norm, w->k_norm});
+  if (r != DG_OK) return r;
+  const uint32_t H = w->hidden, C = d->canvas;
+  const uint32_t nq = d->n_q_heads * d->head_dim, nk = d->n_kv_heads * d->head_dim;
+  const uint32_t n_qkv = nq + nk + (w->v_from_k ? 0u : nk);
+  // tile widths: 128 output columns for the stacked projection, 64 for the output projection (more CTAs)
+  if (H == 0 || H % 64 != 0 || nq % 128 != 0 || nk % 128 != 0)
+    return fail(DG_ERR_UNSUPPORTED, "dg_attn_block: hidden must be a multiple of 64, n_heads * head_dim of 128");
+  DG_CUDA(cudaSetDevice(c->device));
+  const size_t old_rows = c->blk_rows, old_h = c->blk_hidden, old_q = c->blk_qe;
+  const __nv_bfloat16* old_xn = c->blk_xn;
+  r = ensure_block_ws(c, C, H, nq, nk);
+  if (r != DG_OK) return r;
+  if (c->blk_xn != old_xn || old_rows != c->blk_rows || old_h != c->blk_hidden || old_q != c->blk_qe || old_xn == nullptr) {
+    // maps of the two activations the projections read, over whole 128-row tiles
+    const size_t Rp = (c->blk_rows + 127) / 128 * 128;
+    r = make_kv_tmap(&c->blk_tm_xn, c->blk_xn, Rp, 1, 128, uint32_t(c->blk_hidden));
+    if (r == DG_OK) r = make_kv_tmap(&c->blk_tm_o, c->blk_o, Rp, 1, 128, uint32_t(c->blk_qe));
+    if (r != DG_OK) return r;
+  }
+  // the maps above span the buffers' full width: this call's width must be the buffers'
+  if (H != c->blk_hidden || nq != c->blk_qe)
+    return fail(DG_ERR_UNSUPPORTED, "dg_attn_block: one context serves one (hidden, n_q_heads * head_dim) geometry");
+  const CUtensorMap *tm_wqkv = nullptr, *tm_wo = nullptr;
+  r = weight_map(c, w->w_qkv, n_qkv, H, 128, &tm_wqkv);
+  if (r == DG_OK) r = weight_map(c, w->w_o, H, nq, 64, &tm_wo);
+  if (r != DG_OK) return r;
+  cudaStream_t st = launch_stream(c);
+  uint32_t launches = 0;
+  // 1. input norm
+  cudaError_t e = launch_rmsnorm_rows(hidden_in, w->input_ln, c->blk_xn, C, H, st);
+  if (e != cudaSuccess) return fail_cuda(e, "launch_rmsnorm_rows");
+  // 2. stacked projection: Q, K and V leave as three dense tensors
+  GemmParams g = {};
+  g.M = C;
+  g.N = n_qkv;
+  g.K = H;
+  g.n_seg = w->v_from_k ? 2u : 3u;
+  g.seg[0] = GemmSeg{c->blk_q, 0u, nq};
+  g.seg[1] = GemmSeg{c->blk_k, nq, nk};
+  g.seg[2] = GemmSeg{c->blk_v, nq + nk, nk};
+  g.rowsq = nullptr;
+  g.status = c->d_status;
+  e = launch_gemm_sm100(g, c->blk_tm_xn, *tm_wqkv, 128, st);
+  if (e != cudaSuccess) return fail_cuda(e, "launch_gemm_sm100 (qkv)");
+  launches += 2;
+  // 3. per-head norm + RoPE + cache write + attention.  Q comes from the kernel queued just ahead, so the
+  // attention kernel must not read it before its stream dependency has resolved.
+  c->q_from_prev_kernel = 1;
+  dg_kv* kvs[1] = {kv};
+  const uint32_t lens[1] = {kv_len};
+  r = dg_attn_denoise(c, d, kvs, lens, 1, c->blk_q, c->blk_k, w->v_from_k ? c->blk_k : c->blk_v, w->q_norm, w->k_norm, c->blk_o);
+  c->q_from_prev_kernel = 0;
+  if (r != DG_OK) return r;
+  launches += c->last_launches;
+  // 4. output projection, with every row's sum of squares per 64-column tile
+  GemmParams go = {};
+  go.M = C;
+  go.N = H;
+  go.K = nq;
+  go.n_seg = 1;
+  go.seg[0] = GemmSeg{c->blk_t, 0u, H};
+  go.rowsq = c->blk_sq;
+  go.status = c->d_status;
+  e = launch_gemm_sm100(go, c->blk_tm_o, *tm_wo, 64, st);
+  if (e != cudaSuccess) return fail_cuda(e, "launch_gemm_sm100 (o_proj)");
+  // 5. post-attention norm + residual
+  e = launch_norm_residual(c->blk_t, c->blk_sq, H / 64, w->post_attn_ln, hidden_in, stream_out, C, H, st);
+  if (e != cudaSuccess) return fail_cuda(e, "launch_norm_residual");
+  c->last_launches = launches + 2;
   return DG_OK;
 }

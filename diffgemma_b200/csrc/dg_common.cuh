@@ -110,7 +110,7 @@ __device__ inline void dev_status_set(DevStatus* s, uint32_t code, uint32_t kern
   }
 }
 
-enum : uint32_t { KID_APPEND = 1, KID_GENERAL = 2, KID_SM100 = 3, KID_MERGE = 4, KID_VIS = 5, KID_SELFTEST = 6 };
+enum : uint32_t { KID_APPEND = 1, KID_GENERAL = 2, KID_SM100 = 3, KID_MERGE = 4, KID_VIS = 5, KID_SELFTEST = 6, KID_GEMM = 7 };
 
 // ----------------------------------------------------------------------------------------
 // Launch parameter blocks
@@ -225,5 +225,19 @@ struct P2pParams {
 };
 
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(uint32_t(b) << 16); }
+
+// D[M][N] = A[M][K] . W[N][K]^T of the projections either side of the attention stage (csrc/dg_gemm_sm100.cu).
+// Output columns [col_begin, next segment's col_begin) go to dst with row stride ld (elements).
+struct GemmSeg {
+  void* dst;
+  uint32_t col_begin;
+  uint32_t ld;
+};
+struct GemmParams {
+  uint32_t M, N, K, n_seg;
+  GemmSeg seg[3];
+  float* rowsq;        // optional [M][N / tile width]: sum of squares of each row's rounded outputs per tile
+  DevStatus* status;
+};
 
 }  // namespace dg

@@ -170,7 +170,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const void* tmap,
       : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
-
 // ---------------------------------------------------------------- tcgen05 / TMEM
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t n_cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot),
@@ -326,6 +325,18 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
       return false;
     }
   }
+}
+// Asynchronous stores into another CTA's shared memory (shared::cluster addresses of the data and of a barrier of
+// the same CTA): the bytes are counted on that barrier when they have landed, so the receiver needs no flag and
+// the sender no fence.
+__device__ __forceinline__ void dsmem_st_async_f32(uint32_t addr, float v, uint32_t cluster_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];" ::"r"(addr), "f"(v), "r"(cluster_bar)
+               : "memory");
+}
+__device__ __forceinline__ void dsmem_st_async_u4(uint32_t addr, uint4 v, uint32_t cluster_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(addr),
+               "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"(cluster_bar)
+               : "memory");
 }
 // tiled load into this CTA's shared memory whose bytes are counted on a barrier of the pair's
 // leader (cluster address); no multicast

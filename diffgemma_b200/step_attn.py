@@ -291,6 +291,31 @@ class CanvasAttention:
         return out
 
 
+class AttnBlock:
+    """One layer's attention block with its neighbours (dg_attn_block): input RMS norm, stacked Q|K|V projection,
+    attention, output projection, post-attention norm + residual; the reference's encode_layer up to the dense
+    FFN (src/metal/step_kernel/enc.rs:852-911).  Weights are bf16 device tensors [out_features, in_features];
+    the object keeps them alive, the library caches their TMA descriptors by address."""
+
+    def __init__(self, ctx: Context, layer: AttnLayer, w_qkv, w_o, input_ln=None, post_attn_ln=None, q_norm=None,
+                 k_norm=None, v_from_k: bool = False):
+        self.ctx, self.layer, self.lib = ctx, layer, ctx.lib
+        self.desc = layer.c_desc()
+        self.tensors = [t for t in (w_qkv, w_o, input_ln, post_attn_ln, q_norm, k_norm) if t is not None]
+        for t in self.tensors:
+            assert t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous()
+        self.hidden = int(w_qkv.shape[1])
+        self.w = capi.BlockWeights(_ptr(input_ln), _ptr(w_qkv), _ptr(q_norm), _ptr(k_norm), _ptr(w_o), _ptr(post_attn_ln),
+                                   self.hidden, int(v_from_k))
+
+    def step(self, kv: KvCache, kv_len: int, hidden_in, out=None):
+        """hidden_in: [canvas, hidden] bf16 device tensor; returns the residual stream after the block."""
+        out = torch.empty_like(hidden_in) if out is None else out
+        check(self.lib.dg_attn_block(self.ctx.h, C.byref(self.desc), C.byref(self.w), kv.h, kv_len, _ptr(hidden_in),
+                                     _ptr(out)), "dg_attn_block")
+        return out
+
+
 class HostPipe:
     """dg_host_pipe: pipelined host-buffer steps (copies of neighbouring steps overlap the kernels)."""
 

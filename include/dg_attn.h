@@ -251,6 +251,39 @@ int32_t dg_attn_denoise_bitmap(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* kv
                                const void* q, const void* k, const void* v, const void* qw, const void* kw,
                                const uint8_t* attend, void* out);
 
+/* ---- the attention stage with its neighbours ------------------------------------------------
+ * One decoder layer's attention block for the canvas rows of a denoise step, as the reference encodes it
+ * (src/metal/step_kernel/enc.rs:852-911 encode_layer: encode_layer_qkv_gemm :1560-1629,
+ * encode_layer_qk_rope_kv_dispatch, encode_layer_attention_dispatch, encode_layer_o_proj_post_attn :862-911):
+ *   xn     = rms_norm(hidden) * input_ln                   (rms_norm_rows_tiled.metal:16-78, eps 1e-6)
+ *   Q|K|V  = xn . w_qkv^T                                   (the stacked projection, one GEMM)
+ *   O      = dg_attn_denoise(Q, K, V, q_norm, k_norm)       (per-head norm, RoPE, cache write, attention)
+ *   t      = O . w_o^T
+ *   stream = hidden + rms_norm(t) * post_attn_ln            (residual_half.metal:9-22 with no scalar)
+ * every intermediate rounded to bf16 where the reference stores it in its activation arena.
+ * Weights are row-major bf16 device tensors [out_features][in_features], 16-byte aligned, and must stay
+ * valid and unchanged at their addresses while the context may use them (their TMA descriptors are
+ * cached by address).  w_qkv rows: n_q_heads*head_dim of Q, then n_kv_heads*head_dim of K, then the same of V;
+ * with v_from_k != 0 there are no V rows and V is the K projection before its norm (the reference's full
+ * layers, v_proj == 0: src/shaders/attn/cpu.rs:110-121).  hidden must be a multiple of 64 and
+ * n_kv_heads*head_dim of 128.  One context serves one (hidden, n_q_heads*head_dim) geometry.
+ * The activations between the kernels live in buffers the context owns; the Q|K|V GEMM writes Q, K and V
+ * as the three dense tensors the attention stage reads, the output projection's epilogue leaves each row's
+ * sum of squares for the norm behind it, and every kernel is launched programmatically behind the one
+ * before it.                                                                                      */
+typedef struct dg_block_weights {
+  const void* input_ln;     /* [hidden] or NULL (= unit) */
+  const void* w_qkv;        /* [n_q*D + n_kv*D (+ n_kv*D)][hidden] */
+  const void* q_norm;       /* [D] or NULL: per-head norm weights, as qw / kw of dg_attn_denoise */
+  const void* k_norm;
+  const void* w_o;          /* [hidden][n_q*D] */
+  const void* post_attn_ln; /* [hidden] or NULL */
+  uint32_t hidden;
+  uint32_t v_from_k;
+} dg_block_weights;
+int32_t dg_attn_block(dg_ctx* ctx, const dg_layer_desc* desc, const dg_block_weights* w, dg_kv* kv, uint32_t kv_len,
+                      const void* hidden_in, void* stream_out);
+
 /* ---- split-KV building blocks (multi-GPU, and the block-continuation state of the reference:
  * AttnBlockRange / attn_state, src/shaders/include/attention_device.metal:154-165) ------------ */
 /* Partial attention over prefix keys [t0, t1) (clipped to kv_len and to the layer's window)

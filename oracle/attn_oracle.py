@@ -278,6 +278,47 @@ def denoise_attention(q, k, v, k_prefix, v_prefix, desc: LayerDesc, kv_len: int,
     return attention(qn, K, V, attend, desc)
 
 
+# ----------------------------------------------------------------------------
+# the neighbours of the attention stage: input norm, stacked Q|K|V projection, output projection,
+# post-attention norm + residual (src/metal/step_kernel/enc.rs:852-911, 1560-1629 of the reference)
+# ----------------------------------------------------------------------------
+def rms_norm_rows(x: np.ndarray, w: np.ndarray | None, eps: float = 1e-6) -> np.ndarray:
+    """Row-wise RMS norm of the reference's activation planes
+    (src/shaders/elementwise/rms_norm_rows/rms_norm_rows_tiled.metal:16-78): f32 sum of squares,
+    inv = rsqrt(sum / dim + 1e-6), y = (x * inv) * w.  Not rounded here."""
+    x = x.astype(np.float32)
+    ss = np.sum(x.astype(np.float64) ** 2, axis=-1, keepdims=True)
+    inv = (1.0 / np.sqrt(ss / x.shape[-1] + eps)).astype(np.float32)
+    y = x * inv
+    if w is not None:
+        y = y * w.astype(np.float32)
+    return y.astype(np.float32)
+
+
+def linear_bf16(x: np.ndarray, w: np.ndarray) -> np.ndarray:
+    """x [M,K] . w[N,K]^T on bf16-representable inputs, accumulated exactly, rounded once to bf16 (the
+    reference's bf16 GEMMs accumulate in f32 and store to the bf16 arena)."""
+    return round_bf16((x.astype(np.float64) @ w.astype(np.float64).T).astype(np.float32))
+
+
+def attn_block(hidden, input_ln, w_qkv, qw, kw, w_o, post_ln, k_prefix, v_prefix, desc: LayerDesc, kv_len: int,
+               v_from_k: bool = False):
+    """One layer's attention block for the canvas rows of a step (enc.rs:852-911):
+    stream = hidden + rms_norm(o_proj(attention(qkv_proj(rms_norm(hidden))))), every stored intermediate
+    rounded to bf16.  hidden: [C, H]; w_qkv: [n_q*D + n_kv*D (+ n_kv*D), H]; w_o: [H, n_q*D]."""
+    C, D = desc.canvas, desc.head_dim
+    nq, nk = desc.n_q_heads * D, desc.n_kv_heads * D
+    xn = round_bf16(rms_norm_rows(hidden, input_ln))
+    qkv = linear_bf16(xn, w_qkv)
+    q = qkv[:, :nq].reshape(C, desc.n_q_heads, D)
+    k = qkv[:, nq:nq + nk].reshape(C, desc.n_kv_heads, D)
+    v = k if v_from_k else qkv[:, nq + nk:nq + 2 * nk].reshape(C, desc.n_kv_heads, D)
+    o = round_bf16(denoise_attention(q, k, v, k_prefix, v_prefix, desc, kv_len, qw, kw))
+    t = linear_bf16(o.reshape(C, nq), w_o)
+    tn = round_bf16(rms_norm_rows(t, post_ln))
+    return round_bf16(hidden.astype(np.float32) + tn)
+
+
 def algorithmic_flops(desc: LayerDesc, kv_len: int) -> float:
     """4*D flops per visible (row, q-head, key) triple."""
     vis = visibility(desc, kv_len).sum()

@@ -532,19 +532,28 @@ def test_gpu_matches_reference_shader_vectors(ctx, name):
     (3000, 8, 8, 100, 0, 0, 1 / 16, 1),     # no GQA stacking, ragged canvas
     (5000, 16, 4, 256, 1024, 1, 1 / 16, 1), # sliding window on a 512-wide head (not a reference layer; mask logic)
     (700, 16, 2, 256, 0, 3, 1.0, 1),        # causal re-prefill of a block on a full layer
+    (8192 + 64, 16, 2, 256, 0, 0, 1.0, 1),  # odd number of 64-key tiles, unscaled logits: the reference moves often
+    (1, 16, 2, 256, 0, 0, 1.0, 1),          # one prefix key: the canvas tiles carry everything
 ])
 def test_hd512_tensor_path_parity(ctx, P, Hq, Hkv, canvas, W, mode, scale, vnorm):
+    """Both tensor forms: one CTA per value half with the scores computed twice (pair mode off), and the CTA pair
+    that splits the score work and exchanges P (the default)."""
     layer = AttnLayer(n_q_heads=Hq, n_kv_heads=Hkv, head_dim=512, canvas=canvas, rotary_dim=128, rope_theta=1e6,
                       softmax_scale=scale, window=W, mask_mode=mode, v_norm=vnorm, rope_pairing=capi.ROPE_PROPORTIONAL)
     case = util.make_case(layer, P, seed=P + Hq, weights=True)
     ref = util.run_oracle(case)
     assert CanvasAttention(ctx, layer).uses_tensor_path
     try:
-        for splits in (0, 1, 2, 5):
-            ctx.set_splits(splits)
-            util.assert_close(util.run_gpu(ctx, case), ref, f"hd512 tensor path splits={splits}", stress=(scale == 1.0))
+        for pair in (None, False):
+            ctx.set_pair_mode(pair)
+            for splits in (0, 1, 2, 5):
+                ctx.set_splits(splits)
+                util.assert_close(util.run_gpu(ctx, case), ref, f"hd512 tensor path pair={pair} splits={splits}",
+                                  stress=(scale == 1.0))
+                assert ctx.device_status()[0] == 0
     finally:
         ctx.set_splits(0)
+        ctx.set_pair_mode(None)
     ctx.force_general(True)
     got = util.run_gpu(ctx, case)
     ctx.force_general(False)
