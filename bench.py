@@ -617,6 +617,96 @@ def measure_block(ctx, cfg_idx, world, rank, args, steps, timed, peaks, redraw=1
         wl.close()
 
 
+BLOCK_HIDDEN = 2816        # the reference's model width (enc.rs:1560-1629: 256 x 2816 -> 4096 + 2048 + 2048)
+
+
+def measure_attn_block(cfg_idx, args, timed_of, peaks, steps=200, v_from_k=False):
+    """One layer's attention block with its neighbours (dg_attn_block: input norm, stacked Q|K|V projection,
+    attention, output projection, post-attention norm + residual) on the geometry of a configuration, beside the
+    attention stage alone on the same caches.  Three weight sets (207 MB at the sliding geometry, more than L2) and
+    three caches rotate, as the layers of a model would; parity of the first canvas rows against the CPU restatement."""
+    import numpy as np
+    import torch
+    from diffgemma_b200 import synthetic
+    from diffgemma_b200.step_attn import AttnBlock, CanvasAttention, Context, KvCache
+    from oracle import attn_oracle as ao
+    log(f"extra block: attention block with neighbours, cfg {cfg_idx}")
+    cfg = _cfg(cfg_idx)
+    lay, P, H = cfg.layer, cfg.prefix, BLOCK_HIDDEN
+    C, D = lay.canvas, lay.head_dim
+    nq, nk = lay.n_q_heads * D, lay.n_kv_heads * D
+    n_qkv = nq + nk * (1 if v_from_k else 2)
+    ctx = Context(0)
+    ctx.set_inputs_stable(True)
+    dev = torch.device("cuda", 0)
+    timed = timed_of(ctx)
+    try:
+        g = torch.Generator().manual_seed(synthetic.config_seed(cfg_idx) + 9)
+        bf = lambda t: t.to(torch.bfloat16)
+        def wset():
+            return dict(w_qkv=bf(torch.randn(n_qkv, H, generator=g) / H ** 0.5), w_o=bf(torch.randn(H, nq, generator=g) / nq ** 0.5),
+                        input_ln=bf(1 + 0.1 * torch.randn(H, generator=g)), post_attn_ln=bf(1 + 0.1 * torch.randn(H, generator=g)))
+        w0 = wset()
+        blocks = [AttnBlock(ctx, lay, **{k: t.to(dev) for k, t in w0.items()}, v_from_k=v_from_k)]
+        for _ in range(2):
+            blocks.append(AttnBlock(ctx, lay, **{k: t.to(dev) for k, t in wset().items()}, v_from_k=v_from_k))
+        hidden = bf(torch.randn(C, H, generator=g))
+        _, _, _, kp, vp = synthetic.draw(lay, P, synthetic.config_seed(cfg_idx))
+        kvs = []
+        for j in range(3):
+            kv = KvCache(ctx, lay, P + C)
+            if j == 0:
+                kv.load_prefix(kp.to(dev), vp.to(dev), 0)
+            else:
+                gd = torch.Generator(device=dev).manual_seed(100 + j)
+                kv.load_prefix(torch.randn(P, lay.n_kv_heads, D, generator=gd, device=dev).to(torch.bfloat16),
+                               torch.randn(P, lay.n_kv_heads, D, generator=gd, device=dev).to(torch.bfloat16), 0)
+            kvs.append(kv)
+        h_dev = hidden.to(dev)
+        out = torch.empty_like(h_dev)
+        # parity: the first rows of the seeded case
+        R = 4
+        f = lambda t: t.to(torch.float32).numpy()
+        xn = ao.round_bf16(ao.rms_norm_rows(f(hidden), f(w0["input_ln"])))
+        qkv = ao.linear_bf16(xn, f(w0["w_qkv"]))
+        tq = torch.from_numpy(qkv[:, :nq].reshape(C, lay.n_q_heads, D).copy()).to(torch.bfloat16)
+        tk = torch.from_numpy(qkv[:, nq:nq + nk].reshape(C, lay.n_kv_heads, D).copy()).to(torch.bfloat16)
+        tv = tk if v_from_k else torch.from_numpy(qkv[:, nq + nk:].reshape(C, lay.n_kv_heads, D).copy()).to(torch.bfloat16)
+        orc = CpuOracle(None, n_threads=0, case=(tq, tk, tv, kp, vp), layer=lay, prefix=P)
+        o_rows = ao.round_bf16(orc.rows(0, R).reshape(R, nq))
+        t_rows = ao.linear_bf16(o_rows, f(w0["w_o"]))
+        ref = ao.round_bf16(f(hidden)[:R] + ao.round_bf16(ao.rms_norm_rows(t_rows, f(w0["post_attn_ln"]))))
+        blocks[0].step(kvs[0], P, h_dev, out=out)
+        ctx.synchronize()
+        err = np.abs(f(out.cpu())[:R] - ref)
+        gate = {"max_abs": 6.3e-2, "mean_abs": 4e-3}
+        par = {"max_abs": float(err.max()), "mean_abs": float(err.mean()), "rows": f"{R} canvas rows x {H} columns",
+               "vs": "CPU restatement of the block's stages (attention rows by the C++ port)", "gate": gate,
+               "ok": bool(err.max() <= gate["max_abs"] and err.mean() <= gate["mean_abs"])}
+        att = CanvasAttention(ctx, lay)
+        q4, k4, v4 = (t.to(dev)[None].contiguous() for t in (tq, tk, tv))
+        o4 = torch.empty_like(q4)
+        ms_blk = timed(lambda i: blocks[i % 3].step(kvs[i % 3], P, h_dev, out=out), steps, 5)
+        launches = ctx.last_launch_count
+        ms_att = timed(lambda i: att.denoise([kvs[i % 3]], [P], q4, k4, v4, out=o4), steps, 5)
+        st = ctx.device_status()
+        assert st[0] == 0, f"device status {st}"
+        fl_att = ao.algorithmic_flops(orc.d, P)
+        fl_gemm = 2.0 * C * H * (n_qkv + nq)
+        w_bytes = 2.0 * H * (n_qkv + nq)
+        nb = max(ms_blk - ms_att, 1e-6)
+        return {"workload": f"{cfg.name}: rms norm + Q|K|V projection ({C}x{H} -> {n_qkv}) + attention + output projection "
+                            f"({nq} -> {H}) + norm + residual", "ms_per_step": ms_blk, "ms_attention_alone": ms_att,
+                "ms_neighbours": ms_blk - ms_att, "launches_per_step": launches, "steps": steps,
+                "value": (fl_att + fl_gemm) / (ms_blk * 1e-3) / 1e12, "unit": UNIT,
+                "projection_flops": fl_gemm, "weight_bytes": w_bytes,
+                "neighbours_tflops": fl_gemm / (nb * 1e-3) / 1e12,
+                "neighbours_weight_gbs": w_bytes / (nb * 1e-3) / 1e9,
+                "neighbours_frac_of_measured_hbm_peak": w_bytes / (nb * 1e-3) / 1e9 / peaks["hbm_gbs"], "parity": par}
+    finally:
+        ctx.close()
+
+
 def stack_units(n_kv_heads: int, n_canvases: int, world: int, rank: int):
     """KV-head sharding of one layer of the stack over `world` ranks.  The sharded unit is the KV head; where a
     layer has fewer KV heads than there are ranks (the global layers: 2), the (canvas, KV head) pairs are the
@@ -938,6 +1028,11 @@ def run_ours(args):
                 extra[name] = measure_block(ctx, idx, world, rank, args, short, timed, peaks)
             extra["ref_full_layer_hd512_p32768"] = measure_block(ctx, 5, world, rank, args, min(short, 100), timed, peaks)
         extra["cfg4_global_p131072"] = measure_block(ctx, 4, world, rank, args, 48, timed, peaks, redraw=48)
+        if world == 1:
+            timed_of = lambda c: _timer(1, dev, c.torch_stream)
+            extra["attn_block_cfg1_sliding"] = measure_attn_block(1, args, timed_of, peaks)
+            extra["attn_block_cfg2_global"] = measure_attn_block(2, args, timed_of, peaks)
+            extra["attn_block_ref_full_layer_hd512"] = measure_attn_block(5, args, timed_of, peaks, steps=100, v_from_k=True)
 
     if rank == 0:
         value = flops / (ms_dev * 1e-3) / 1e12
