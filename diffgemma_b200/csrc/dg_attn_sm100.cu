@@ -67,9 +67,10 @@ enum : uint32_t {
   B_V_FULL = 3,    // +stage
   B_V_EMPTY = 7,   // +(tile & 1): PV of the tile complete -> its V stage is free, O may be rescaled
   B_S_FULL = 9,    // +(tile & 1): QK of the tile complete -> S is ready, its K stage is free
-  B_P_FULL = 11,   // +buffer
+  B_P_FULL = 11,   // +buffer: P of the tile's keys [0, 64)
   B_O_FINAL = 14,  // single phase: every PV of this CTA has completed
-  B_COUNT = 15
+  B_P2_FULL = 15,  // +buffer: P of the tile's keys [64, 128)
+  B_COUNT = 17
 };
 }  // namespace one
 
@@ -175,6 +176,7 @@ dg_attn_sm100_kernel(const __grid_constant__ AttnBatch bat) {
       mbar_init(bar_addr(bar_base, B_V_EMPTY + st), 1);
       mbar_init(bar_addr(bar_base, B_S_FULL + st), 1);
       mbar_init(bar_addr(bar_base, B_P_FULL + st), (PAIR ? 2u : 1u) * SM_WARPS);
+      mbar_init(bar_addr(bar_base, B_P2_FULL + st), (PAIR ? 2u : 1u) * SM_WARPS);
     }
     mbar_init(bar_addr(bar_base, B_O_FINAL), 1);
     ctl[1] = 0u;
@@ -379,6 +381,8 @@ dg_attn_sm100_kernel(const __grid_constant__ AttnBatch bat) {
     const float sc = p.scale_log2;
     const uint32_t p_full0 = PAIR ? lead_bar(B_P_FULL) : bar_addr(bar_base, B_P_FULL);
     const uint32_t p_full1 = PAIR ? lead_bar(B_P_FULL + 1) : bar_addr(bar_base, B_P_FULL + 1);
+    const uint32_t p2_full0 = PAIR ? lead_bar(B_P2_FULL) : bar_addr(bar_base, B_P2_FULL);
+    const uint32_t p2_full1 = PAIR ? lead_bar(B_P2_FULL + 1) : bar_addr(bar_base, B_P2_FULL + 1);
 
     for (uint32_t n = 0; n < n_local; ++n) {
       const uint32_t v = v_begin + n;
@@ -388,14 +392,18 @@ dg_attn_sm100_kernel(const __grid_constant__ AttnBatch bat) {
       // warp-uniform outcome: the TMEM instructions below need the whole warp
       if (!__all_sync(0xffffffffu, timed_wait(prof, w_s, [&] { return wait_bar(B_S_FULL + b, (n >> 1) & 1u, abort_flag); }))) break;
       tc_fence_after();
+      // This thread's 32 score columns are keys [16 qd, 16 qd + 16) and [64 + 16 qd, 64 + 16 qd + 16) of the tile:
+      // every thread then finishes its share of the tile's first 64 keys first, and the PV MMAs over those keys
+      // run while the exponentials of the other 64 are still being computed.
       uint32_t sraw[32];
-      tmem_ld32(t_lane + TM_S + b * 128u + qd * CPT, sraw);
+      tmem_ld16(t_lane + TM_S + b * 128u + qd * (CPT / 2), *reinterpret_cast<uint32_t(*)[16]>(&sraw[0]));
+      tmem_ld16(t_lane + TM_S + b * 128u + 64u + qd * (CPT / 2), *reinterpret_cast<uint32_t(*)[16]>(&sraw[16]));
       tmem_wait_ld();
 
       if (!mask_range_full(mk, rv, k0, BN)) {
 #pragma unroll
         for (int e = 0; e < 32; ++e)
-          if (!mask_visible_row(mk, rv, k0 + qd * CPT + e)) sraw[e] = 0xff800000u;  // -inf
+          if (!mask_visible_row(mk, rv, k0 + (e < 16 ? 0u : 48u) + qd * (CPT / 2) + e)) sraw[e] = 0xff800000u;  // -inf
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -433,30 +441,34 @@ dg_attn_sm100_kernel(const __grid_constant__ AttnBatch bat) {
       if (need) m_used = m_new;
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
       const float neg_m = -m_eff;
-      // P column j (32 bit) = keys (2j, 2j+1) as bf16x2: this thread's 32 keys are 16 columns.
+      // P column j (32 bit) = keys (2j, 2j+1) as bf16x2: each run of 16 keys is 8 columns.
       // Scale/shift and row sums run on packed fp32 pairs.
       const uint64_t sc2 = pack_f32x2(sc, sc), nm2 = pack_f32x2(neg_m, neg_m);
       uint64_t ls2[2] = {0ull, 0ull};   // (0.f, 0.f)
-      uint32_t pk[16];
 #pragma unroll
-      for (int e = 0; e < 32; e += 2) {
-        float x0, x1;
-        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sraw[e]), __uint_as_float(sraw[e + 1])), sc2, nm2), x0, x1);
-        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-        ls2[(e >> 1) & 1] = add_f32x2(ls2[(e >> 1) & 1], pack_f32x2(p0, p1));
-        pk[e >> 1] = pack_bf16x2(p0, p1);
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t pk[8];
+#pragma unroll
+        for (int e = 0; e < 16; e += 2) {
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sraw[hf * 16 + e]), __uint_as_float(sraw[hf * 16 + e + 1])), sc2, nm2), x0, x1);
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          ls2[(e >> 1) & 1] = add_f32x2(ls2[(e >> 1) & 1], pack_f32x2(p0, p1));
+          pk[e >> 1] = pack_bf16x2(p0, p1);
+        }
+        tmem_st8(t_lane + TM_S + b * 128u + uint32_t(hf) * 32u + qd * (CPT / 4), pk);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          const uint32_t bar = hf == 0 ? (b ? p_full1 : p_full0) : (b ? p2_full1 : p2_full0);
+          if (PAIR) mbar_arrive_remote(bar); else mbar_arrive(bar);
+        }
       }
       {
         float s0, s1;
         unpack_f32x2(add_f32x2(ls2[0], ls2[1]), s0, s1);
         l_run += s0 + s1;
-      }
-      tmem_st16(t_lane + TM_S + b * 128u + qd * (CPT / 2), pk);
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if (PAIR) mbar_arrive_remote(b ? p_full1 : p_full0); else mbar_arrive(b ? p_full1 : p_full0);
       }
     }
     if (prof && tid == 0) {
@@ -598,26 +610,34 @@ dg_attn_sm100_kernel(const __grid_constant__ AttnBatch bat) {
         if (!v_ready && !uni(timed_wait(prof, w_v, [&] { return wait_bar(B_V_FULL + st, ph, abort_flag); }))) break;
         p_ready = v_ready = false;
         tc_fence_after();
-        if (elect_one()) {
-          uint32_t p_tmem = tmem + TM_S + (n & 1u) * 128u;
-          uint32_t vb = v_lo0 + (PAIR ? st * (V_STAGE >> 4) : 0u);
+        uint32_t p_tmem = tmem + TM_S + (n & 1u) * 128u;
+        uint32_t vb = v_lo0 + (PAIR ? st * (V_STAGE >> 4) : 0u);
+        // keys [0, 64) of the tile, then, once the rest of P is there, keys [64, 128)
 #pragma unroll 1
-          for (uint32_t ks = 0; ks < 8; ks += 2) {
-#pragma unroll
-            for (uint32_t j = 0; j < 2; ++j) {
-              const uint64_t db = mkdesc(vb + j * (2048u >> 4), HI_MNMAJ);
-              if (PAIR) umma_ts_pair(tmem + TM_O, p_tmem + j * 8u, db, IDESC_PV, (n | ks | j) != 0u);
-              else umma_ts(tmem + TM_O, p_tmem + j * 8u, db, IDESC_PV, (n | ks | j) != 0u);
-            }
-            vb += 2u * (2048u >> 4);
-            p_tmem += 16u;
+        for (uint32_t hf = 0; hf < 2; ++hf) {
+          if (hf == 1) {
+            if (!uni(timed_wait(prof, w_p, [&] { return wait_bar(B_P2_FULL + (n & 1u), (n >> 1) & 1u, abort_flag); }))) { ok = false; break; }
+            tc_fence_after();
           }
-          commit(B_V_EMPTY + (n & 1u));
-          // The epilogue must not reuse B_V_EMPTY: when the last S tile is ready only PV(n-3) is
-          // known to be complete, so a parity wait on that barrier could alias by two phases.
-          if (n + 1 == n_local) commit(B_O_FINAL);
+          if (elect_one()) {
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+              const uint64_t db = mkdesc(vb + j * (2048u >> 4), HI_MNMAJ);
+              if (PAIR) umma_ts_pair(tmem + TM_O, p_tmem + j * 8u, db, IDESC_PV, (n | hf | j) != 0u);
+              else umma_ts(tmem + TM_O, p_tmem + j * 8u, db, IDESC_PV, (n | hf | j) != 0u);
+            }
+            if (hf == 1) {
+              commit(B_V_EMPTY + (n & 1u));
+              // The epilogue must not reuse B_V_EMPTY: when the last S tile is ready only PV(n-3) is
+              // known to be complete, so a parity wait on that barrier could alias by two phases.
+              if (n + 1 == n_local) commit(B_O_FINAL);
+            }
+          }
+          __syncwarp();
+          vb += 4u * (2048u >> 4);
+          p_tmem += 32u;
         }
-        __syncwarp();
+        if (!ok) break;
       }
       if (prof && lane == 0) {
         stamp_cycles(p, 6, w_k);
