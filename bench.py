@@ -1129,7 +1129,21 @@ def main():
                     help="multi-GPU: merge every step's slice inside that step instead of one step later")
     ap.add_argument("--kernel-form", default="auto", choices=["auto", "pair", "single"],
                     help="tensor-kernel form: CTA pairs, one CTA per query tile, or the library's choice")
+    ap.add_argument("--attn-block", type=int, default=None, choices=[1, 2, 5],
+                    help="only the attention block with its neighbours (dg_attn_block) on this configuration's geometry, "
+                         "1 GPU; prints that block's record, not the benchmark line")
     args = ap.parse_args()
+    if args.attn_block is not None:
+        import torch
+        from diffgemma_b200 import build as _build
+        _build.build()
+        dev = torch.device("cuda", 0)
+        blk = measure_attn_block(args.attn_block, args, lambda c: _timer(1, dev, c.torch_stream), _peaks(),
+                                 steps=min(args.steps, 200), v_from_k=args.attn_block == 5)
+        print(json.dumps(blk), flush=True)
+        if not blk["parity"]["ok"]:
+            sys.exit("parity gate failed: " + json.dumps(blk["parity"]))
+        return
     if args.impl == "reference":
         if args.cfg == 3:
             args.cfg = 2      # the CPU arm times the headline workload

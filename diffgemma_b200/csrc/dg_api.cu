@@ -13,6 +13,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <deque>
 #include <mutex>
 #include <new>
 #include <string>
@@ -71,8 +72,7 @@ struct dg_ctx {
   __nv_bfloat16* blk_k = nullptr;
   __nv_bfloat16* blk_v = nullptr;
   __nv_bfloat16* blk_o = nullptr;
-  __nv_bfloat16* blk_t = nullptr;
-  float* blk_sq = nullptr;
+  float* blk_part = nullptr;           // fp32 partial planes of the output projection, [4][rows][hidden]
   size_t blk_rows = 0, blk_hidden = 0, blk_qe = 0, blk_ke = 0;
   CUtensorMap blk_tm_xn, blk_tm_o;
   struct WMap {
@@ -80,7 +80,8 @@ struct dg_ctx {
     uint32_t n, k, bn;
     CUtensorMap tm;
   };
-  std::vector<WMap> blk_wmaps;         // tensor maps of the weight matrices seen so far
+  std::deque<WMap> blk_wmaps;          // tensor maps of the weight matrices seen so far (a deque: growing it leaves
+                                       // the addresses of its elements, which a call holds across two look-ups, alone)
   int q_from_prev_kernel = 0;          // 1 while dg_attn_block runs: Q is written by the kernel queued just ahead
   int force_general = 0;
   int fused_append = 1;                // 1: the canvas append runs inside the attention launch where it can
@@ -123,7 +124,7 @@ struct dg_kv {
   uint32_t Hkv = 0, D = 0;
   bool has_tmap = false;
   CUtensorMap tm_k, tm_v;
-  CUtensorMap tm_k64;   // K with 64-key boxes (CTA-pair kernel: each CTA stages half of a key tile)
+  CUtensorMap tm_k64;   // K with half-tile boxes (64 keys at head_dim 256, 32 at 512): each CTA of a cta_group::2 pair stages half of a key tile
 };
 
 constexpr uint32_t kMaxQueryTiles = 4096;
@@ -322,6 +323,7 @@ extern "C" int32_t dg_ctx_create(int32_t device, dg_ctx** out) {
   if (e == cudaSuccess) e = sm100_pair_configure();
   if (e == cudaSuccess) e = sm100_hd512_configure();
   if (e == cudaSuccess) e = sm100_hd512x_configure();
+  if (e == cudaSuccess) e = sm100_hd512q_configure();
   if (e == cudaSuccess) e = sm100_gemm_configure();
   if (e != cudaSuccess) {
     dg_ctx_destroy(c);
@@ -351,8 +353,7 @@ extern "C" int32_t dg_ctx_destroy(dg_ctx* c) {
   cudaFree(c->blk_k);
   cudaFree(c->blk_v);
   cudaFree(c->blk_o);
-  cudaFree(c->blk_t);
-  cudaFree(c->blk_sq);
+  cudaFree(c->blk_part);
   for (cudaEvent_t e : c->ev) cudaEventDestroy(e);
   if (c->own_stream) cudaStreamDestroy(c->own_stream);
   delete c;
@@ -526,6 +527,7 @@ static int32_t kv_create(dg_ctx* c, const dg_layer_desc* d, uint64_t capacity_to
     // head_dim-512 kernel: key tiles of 64 keys for both K and V
     r = make_kv_tmap(&kv->tm_k, kv->k, kv->cap, kv->Hkv, 64, 512);
     if (r == DG_OK) r = make_kv_tmap(&kv->tm_v, kv->v, kv->cap, kv->Hkv, 64, 512);
+    if (r == DG_OK) r = make_kv_tmap(&kv->tm_k64, kv->k, kv->cap, kv->Hkv, 32, 512);   // half of a key tile per CTA of a pair
     if (r != DG_OK) {
       dg_kv_destroy(kv);
       return r;
@@ -846,8 +848,11 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
     if (!a.q_prenormed) return fail(DG_ERR_UNSUPPORTED, "head_dim 512 tensor path needs a prenormed Q");
     const uint32_t q_tiles5 = sm100_query_tiles(p.C, p.G, p.Hkv);
     if (q_tiles5 * 2 > (fixed ? fixed->n_counters : kMaxQueryTiles)) return fail(DG_ERR_UNSUPPORTED, "too many query tiles");
-    // CTA-pair form (the two halves split the score work and exchange P) unless the single form is asked for
+    // The two value halves split the score work and exchange P unless the single form is asked for; on top of
+    // that, pairs of query tiles of one KV head share their K and V stages (cta_group::2) when the head has an
+    // even number of tiles (pair mode 1 = the exchange alone, 2 = automatic)
     const bool pair5 = !fixed && c->pair_mode != 0;
+    const bool quad5 = pair5 && c->pair_mode == 2 && sm100_query_tiles(p.C, p.G, 1) % 2 == 0;
     p.n_splits = choose_splits(c, q_tiles5 * 2, pair5 ? sm100_hd512x_key_steps(p.mask) : sm100_hd512_key_tiles(p.mask));
     p.cluster_splits = 1;
     if (fixed) {
@@ -869,8 +874,9 @@ static int32_t do_attention(dg_ctx* c, const dg_layer_desc& d, dg_kv* kv, const 
     }
     const bool timed5 = c->timing && c->ev_used + 2 <= c->ev.size();
     if (timed5) DG_CUDA(cudaEventRecord(c->ev[c->ev_used], c->stream));
-    const cudaError_t e5 = pair5 ? launch_attn_sm100_hd512x(p, kv->tm_k, kv->tm_v, launch_stream(c))
-                                 : launch_attn_sm100_hd512(p, kv->tm_k, kv->tm_v, launch_stream(c));
+    const cudaError_t e5 = quad5   ? launch_attn_sm100_hd512q(p, kv->tm_k64, kv->tm_v, launch_stream(c))
+                           : pair5 ? launch_attn_sm100_hd512x(p, kv->tm_k, kv->tm_v, launch_stream(c))
+                                   : launch_attn_sm100_hd512(p, kv->tm_k, kv->tm_v, launch_stream(c));
     if (e5 != cudaSuccess) return fail_cuda(e5, "launch_attn_sm100_hd512");
     if (timed5) {
       DG_CUDA(cudaEventRecord(c->ev[c->ev_used + 1], c->stream));
@@ -1954,16 +1960,17 @@ extern "C" int32_t dg_attn_denoise_split_p2p(dg_ctx* c, const dg_layer_desc* d, 
 // -> post-attention norm + residual (reference: encode_layer_qkv_gemm, encode_layer_qk_rope_kv_dispatch,
 // encode_layer_attention_dispatch, encode_layer_o_proj_post_attn of src/metal/step_kernel/enc.rs:852-911,1560-1629)
 // ------------------------------------------------------------------------------------------
+constexpr uint32_t kBlockMaxSlices = 4;   // split-K slices of the output projection
+
 static int32_t ensure_block_ws(dg_ctx* c, size_t rows, size_t hidden, size_t qe, size_t ke) {
   if (rows <= c->blk_rows && hidden <= c->blk_hidden && qe <= c->blk_qe && ke <= c->blk_ke) return DG_OK;
   DG_CUDA(cudaStreamSynchronize(c->stream));
   const size_t R = rows > c->blk_rows ? rows : c->blk_rows, H = hidden > c->blk_hidden ? hidden : c->blk_hidden;
   const size_t Q = qe > c->blk_qe ? qe : c->blk_qe, K = ke > c->blk_ke ? ke : c->blk_ke;
-  for (void* ptr : {(void*)c->blk_xn, (void*)c->blk_q, (void*)c->blk_k, (void*)c->blk_v, (void*)c->blk_o, (void*)c->blk_t,
-                    (void*)c->blk_sq})
+  for (void* ptr : {(void*)c->blk_xn, (void*)c->blk_q, (void*)c->blk_k, (void*)c->blk_v, (void*)c->blk_o, (void*)c->blk_part})
     cudaFree(ptr);
-  c->blk_xn = c->blk_q = c->blk_k = c->blk_v = c->blk_o = c->blk_t = nullptr;
-  c->blk_sq = nullptr;
+  c->blk_xn = c->blk_q = c->blk_k = c->blk_v = c->blk_o = nullptr;
+  c->blk_part = nullptr;
   c->blk_rows = c->blk_hidden = c->blk_qe = c->blk_ke = 0;
   // rows are padded to whole 128-row tiles: the projections' loads of a ragged last tile stay inside the buffers
   const size_t Rp = (R + 127) / 128 * 128;
@@ -1972,8 +1979,7 @@ static int32_t ensure_block_ws(dg_ctx* c, size_t rows, size_t hidden, size_t qe,
   DG_CUDA(cudaMalloc(&c->blk_k, Rp * K * 2));
   DG_CUDA(cudaMalloc(&c->blk_v, Rp * K * 2));
   DG_CUDA(cudaMalloc(&c->blk_o, Rp * Q * 2));
-  DG_CUDA(cudaMalloc(&c->blk_t, Rp * H * 2));
-  DG_CUDA(cudaMalloc(&c->blk_sq, Rp * (H / 64 + 1) * sizeof(float)));
+  DG_CUDA(cudaMalloc(&c->blk_part, kBlockMaxSlices * Rp * H * sizeof(float)));
   DG_CUDA(cudaMemset(c->blk_xn, 0, Rp * H * 2));
   DG_CUDA(cudaMemset(c->blk_o, 0, Rp * Q * 2));
   c->blk_rows = R;
@@ -1989,7 +1995,6 @@ static int32_t weight_map(dg_ctx* c, const void* w, uint32_t n, uint32_t k, uint
       *out = &m.tm;
       return DG_OK;
     }
-  if (c->blk_wmaps.size() >= 4096) c->blk_wmaps.clear();
   dg_ctx::WMap m;
   m.w = w;
   m.n = n;
@@ -2012,9 +2017,8 @@ extern "C" int32_t dg_attn_block(dg_ctx* c, const dg_layer_desc* d, const dg_blo
   const uint32_t H = w->hidden, C = d->canvas;
   const uint32_t nq = d->n_q_heads * d->head_dim, nk = d->n_kv_heads * d->head_dim;
   const uint32_t n_qkv = nq + nk + (w->v_from_k ? 0u : nk);
-  // tile widths: 128 output columns for the stacked projection, 64 for the output projection (more CTAs)
-  if (H == 0 || H % 64 != 0 || nq % 128 != 0 || nk % 128 != 0)
-    return fail(DG_ERR_UNSUPPORTED, "dg_attn_block: hidden must be a multiple of 64, n_heads * head_dim of 128");
+  if (H == 0 || H % 64 != 0 || H > 8192 || nq % 128 != 0 || nk % 128 != 0)
+    return fail(DG_ERR_UNSUPPORTED, "dg_attn_block: hidden must be a multiple of 64 up to 8192, n_heads * head_dim a multiple of 128");
   DG_CUDA(cudaSetDevice(c->device));
   const size_t old_rows = c->blk_rows, old_h = c->blk_hidden, old_q = c->blk_qe;
   const __nv_bfloat16* old_xn = c->blk_xn;
@@ -2031,8 +2035,16 @@ extern "C" int32_t dg_attn_block(dg_ctx* c, const dg_layer_desc* d, const dg_blo
   if (H != c->blk_hidden || nq != c->blk_qe)
     return fail(DG_ERR_UNSUPPORTED, "dg_attn_block: one context serves one (hidden, n_q_heads * head_dim) geometry");
   const CUtensorMap *tm_wqkv = nullptr, *tm_wo = nullptr;
+  if (c->blk_wmaps.size() >= 4096) c->blk_wmaps.clear();   // before the look-ups of this call, never between them
   r = weight_map(c, w->w_qkv, n_qkv, H, 128, &tm_wqkv);
-  if (r == DG_OK) r = weight_map(c, w->w_o, H, nq, 64, &tm_wo);
+  // output projection: 128 output columns per tile where hidden allows it, and as many slices of the contraction
+  // as bring the grid to about one CTA per SM (hidden 2816, 256 rows: 22 x 2 tiles x 3 slices = 132 CTAs)
+  const uint32_t bn_o = H % 128 == 0 ? 128u : 64u;
+  const uint32_t tiles_o = (H / bn_o) * ((C + 127) / 128);
+  uint32_t slices = (c->num_sms > 0 ? uint32_t(c->num_sms) : 148u) / tiles_o;
+  slices = slices < 1 ? 1 : slices > kBlockMaxSlices ? kBlockMaxSlices : slices;
+  if (slices > nq / 64) slices = nq / 64;
+  if (r == DG_OK) r = weight_map(c, w->w_o, H, nq, bn_o, &tm_wo);
   if (r != DG_OK) return r;
   cudaStream_t st = launch_stream(c);
   uint32_t launches = 0;
@@ -2062,19 +2074,20 @@ extern "C" int32_t dg_attn_block(dg_ctx* c, const dg_layer_desc* d, const dg_blo
   c->q_from_prev_kernel = 0;
   if (r != DG_OK) return r;
   launches += c->last_launches;
-  // 4. output projection, with every row's sum of squares per 64-column tile
+  // 4. output projection: fp32 partial planes, one per slice of the contraction
   GemmParams go = {};
   go.M = C;
   go.N = H;
   go.K = nq;
-  go.n_seg = 1;
-  go.seg[0] = GemmSeg{c->blk_t, 0u, H};
-  go.rowsq = c->blk_sq;
+  go.n_seg = 0;
+  go.rowsq = nullptr;
+  go.part = c->blk_part;
+  go.k_slices = slices;
   go.status = c->d_status;
-  e = launch_gemm_sm100(go, c->blk_tm_o, *tm_wo, 64, st);
+  e = launch_gemm_sm100(go, c->blk_tm_o, *tm_wo, bn_o, st);
   if (e != cudaSuccess) return fail_cuda(e, "launch_gemm_sm100 (o_proj)");
-  // 5. post-attention norm + residual
-  e = launch_norm_residual(c->blk_t, c->blk_sq, H / 64, w->post_attn_ln, hidden_in, stream_out, C, H, st);
+  // 5. planes added and stored as bf16, post-attention norm, residual
+  e = launch_norm_residual(c->blk_part, slices, w->post_attn_ln, hidden_in, stream_out, C, H, st);
   if (e != cudaSuccess) return fail_cuda(e, "launch_norm_residual");
   c->last_launches = launches + 2;
   return DG_OK;

@@ -237,6 +237,8 @@ struct GemmParams {
   uint32_t M, N, K, n_seg;
   GemmSeg seg[3];
   float* rowsq;        // optional [M][N / tile width]: sum of squares of each row's rounded outputs per tile
+  float* part;         // split-K: fp32 partial sums [k_slices][M][N] instead of the bf16 output
+  uint32_t k_slices;
   DevStatus* status;
 };
 

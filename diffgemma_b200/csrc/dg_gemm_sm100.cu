@@ -44,7 +44,10 @@ dg_gemm_sm100_kernel(const GemmParams g, const __grid_constant__ CUtensorMap tm_
   const uint32_t bar_base = smem_base + ST * STAGE;
   volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + ST * STAGE + B_COUNT * 8);
   const uint32_t n0 = blockIdx.x * BN, m0 = blockIdx.y * GM;
-  const uint32_t n_kb = g.K / BK;
+  // split-K: slice blockIdx.z of the contraction; its fp32 partial tile goes to plane blockIdx.z of g.part
+  const uint32_t kb_all = g.K / BK;
+  const uint32_t kb0 = uint32_t((uint64_t(blockIdx.z) * kb_all) / gridDim.z);
+  const uint32_t n_kb = uint32_t((uint64_t(blockIdx.z + 1) * kb_all) / gridDim.z) - kb0;
 
   if (tid == 0) {
     for (uint32_t s = 0; s < ST; ++s) {
@@ -79,8 +82,8 @@ dg_gemm_sm100_kernel(const GemmParams g, const __grid_constant__ CUtensorMap tm_
         if (use > 0 && !mbar_wait(bar_addr(bar_base, B_EMPTY + s), (use - 1u) & 1u, abort_flag)) break;
         const uint32_t full = bar_addr(bar_base, B_FULL + s);
         mbar_expect_tx(full, STAGE);
-        tma_load_3d(smem_base + s * STAGE, &tm_a, full, int32_t(kb * BK), int32_t(m0), 0);
-        tma_load_3d(smem_base + s * STAGE + A_STAGE, &tm_w, full, int32_t(kb * BK), int32_t(n0), 0);
+        tma_load_3d(smem_base + s * STAGE, &tm_a, full, int32_t((kb0 + kb) * BK), int32_t(m0), 0);
+        tma_load_3d(smem_base + s * STAGE + A_STAGE, &tm_w, full, int32_t((kb0 + kb) * BK), int32_t(n0), 0);
       }
     }
   } else if (warp == 1) {
@@ -114,6 +117,21 @@ dg_gemm_sm100_kernel(const GemmParams g, const __grid_constant__ CUtensorMap tm_
     if (g.n_seg > 1 && n0 >= g.seg[1].col_begin) sg = 1;
     if (g.n_seg > 2 && n0 >= g.seg[2].col_begin) sg = 2;
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g.seg[sg].dst) + size_t(row) * g.seg[sg].ld + (n0 - g.seg[sg].col_begin);
+    if (g.part != nullptr) {
+      // fp32 partial sums of this slice of the contraction, row-major [slice][M][N]
+      float* dp = g.part + (size_t(blockIdx.z) * g.M + row) * g.N + n0;
+#pragma unroll 1
+      for (uint32_t c = 0; ok && c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem + ((q4 * 32u) << 16) + c * 32u, v);
+        tmem_wait_ld();
+        if (row < g.M) {
+#pragma unroll
+          for (uint32_t j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(dp + c * 32u + j * 4u) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        }
+      }
+    } else {
     float ss = 0.f;
     if (ok) {
 #pragma unroll 1
@@ -144,6 +162,7 @@ dg_gemm_sm100_kernel(const GemmParams g, const __grid_constant__ CUtensorMap tm_
       }
     }
     if (g.rowsq != nullptr && row < g.M) g.rowsq[size_t(row) * gridDim.x + blockIdx.x] = ok ? ss : 0.f;
+    }
   }
 
   if (*abort_flag) {
@@ -158,19 +177,11 @@ dg_gemm_sm100_kernel(const GemmParams g, const __grid_constant__ CUtensorMap tm_
   if (warp == 1) tmem_dealloc(tmem, BN < 32 ? 32 : BN);
 }
 
-// y[row] = bf16(x[row] * rsqrt(mean(x[row]^2) + 1e-6) * w), one block per row
-// (rms_norm_rows_tiled.metal:16-78: f32 sum of squares, v * inv, then * weight).
-__global__ void __launch_bounds__(256) dg_rmsnorm_rows_kernel(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* y,
-                                                              uint32_t dim) {
-  __shared__ float red[8];
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  const size_t base = size_t(blockIdx.x) * dim;
-  float acc = 0.f;
-  for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) {
-    const float v = __bfloat162float(x[base + i]);
-    acc = fmaf(v, v, acc);
-  }
+// Row-wise kernels: one block of 256 threads per row, a thread holds up to ROW_VEC 8-element vectors of the row in
+// registers, so the row crosses memory once.
+constexpr uint32_t ROW_VEC = 4;        // rows of up to 256 * 4 * 8 = 8192 elements
+
+__device__ __forceinline__ float block_sum_256(float acc, float* red) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
@@ -178,30 +189,110 @@ __global__ void __launch_bounds__(256) dg_rmsnorm_rows_kernel(const __nv_bfloat1
   float t = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) t += red[i];
-  const float inv = rsqrtf(t / float(dim) + 1e-6f);
-  for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) {
-    float v = __bfloat162float(x[base + i]) * inv;
-    if (w != nullptr) v *= __bfloat162float(w[i]);
-    y[base + i] = __float2bfloat16(v);
+  return t;
+}
+
+// y[row] = bf16(x[row] * rsqrt(mean(x[row]^2) + 1e-6) * w)
+// (rms_norm_rows_tiled.metal:16-78: f32 sum of squares, v * inv, then * weight).
+__global__ void __launch_bounds__(256) dg_rmsnorm_rows_kernel(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* y,
+                                                              uint32_t dim) {
+  __shared__ float red[8];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const uint32_t n_vec = dim / 8;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + size_t(blockIdx.x) * dim);
+  uint4 v[ROW_VEC];
+  float acc = 0.f;
+#pragma unroll
+  for (uint32_t j = 0; j < ROW_VEC; ++j) {
+    const uint32_t i = threadIdx.x + j * 256u;
+    v[j] = i < n_vec ? xr[i] : make_uint4(0u, 0u, 0u, 0u);
+    const uint32_t ws[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+    for (uint32_t e = 0; e < 4; ++e) {
+      const float lo = __uint_as_float(ws[e] << 16), hi = __uint_as_float(ws[e] & 0xffff0000u);
+      acc = fmaf(lo, lo, acc);
+      acc = fmaf(hi, hi, acc);
+    }
+  }
+  const float inv = rsqrtf(block_sum_256(acc, red) / float(dim) + 1e-6f);
+  uint4* yr = reinterpret_cast<uint4*>(y + size_t(blockIdx.x) * dim);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+#pragma unroll
+  for (uint32_t j = 0; j < ROW_VEC; ++j) {
+    const uint32_t i = threadIdx.x + j * 256u;
+    if (i >= n_vec) continue;
+    const uint4 w4 = w != nullptr ? wr[i] : make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+    const uint32_t xs[4] = {v[j].x, v[j].y, v[j].z, v[j].w}, ws[4] = {w4.x, w4.y, w4.z, w4.w};
+    uint32_t o[4];
+#pragma unroll
+    for (uint32_t e = 0; e < 4; ++e) {
+      float lo = __uint_as_float(xs[e] << 16) * inv, hi = __uint_as_float(xs[e] & 0xffff0000u) * inv;
+      if (w != nullptr) {
+        lo *= __uint_as_float(ws[e] << 16);
+        hi *= __uint_as_float(ws[e] & 0xffff0000u);
+      }
+      o[e] = pack_bf16x2(lo, hi);
+    }
+    yr[i] = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 
-// out[row] = bf16(hidden[row] + bf16(t[row] * inv * w)), inv from the per-tile sums of squares the output
-// projection left (enc.rs:888-911: RMS norm of the projection in place, then the residual add).
-__global__ void __launch_bounds__(256) dg_norm_residual_kernel(const __nv_bfloat16* t, const float* rowsq, uint32_t n_part,
+// out[row] = bf16(hidden[row] + bf16(t[row] * inv * w)) with t[row] = bf16(sum over the n_part fp32 partial planes of
+// the output projection), inv = rsqrt(mean(t[row]^2) + 1e-6)
+// (enc.rs:888-911: the projection stored to the bf16 arena, its RMS norm in place, then the residual add).
+// The planes are added in a fixed order: same bits every run.
+__global__ void __launch_bounds__(256) dg_norm_residual_kernel(const float* part, uint32_t n_part, size_t plane,
                                                                const __nv_bfloat16* w, const __nv_bfloat16* hidden,
                                                                __nv_bfloat16* out, uint32_t dim) {
+  __shared__ float red[8];
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  const size_t base = size_t(blockIdx.x) * dim;
-  float s = 0.f;
-  for (uint32_t i = 0; i < n_part; ++i) s += rowsq[size_t(blockIdx.x) * n_part + i];   // fixed order: same bits every run
-  const float inv = rsqrtf(s / float(dim) + 1e-6f);
-  for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) {
-    float v = __bfloat162float(t[base + i]) * inv;
-    if (w != nullptr) v *= __bfloat162float(w[i]);
-    const float nv = __bfloat162float(__float2bfloat16(v));
-    out[base + i] = __float2bfloat16(__bfloat162float(hidden[base + i]) + nv);
+  const uint32_t n_vec = dim / 8;
+  float t[ROW_VEC][8];
+  float acc = 0.f;
+#pragma unroll
+  for (uint32_t j = 0; j < ROW_VEC; ++j) {
+    const uint32_t i = threadIdx.x + j * 256u;
+#pragma unroll
+    for (uint32_t e = 0; e < 8; ++e) t[j][e] = 0.f;
+    if (i >= n_vec) continue;
+    for (uint32_t s = 0; s < n_part; ++s) {
+      const float4* pr = reinterpret_cast<const float4*>(part + s * plane + size_t(blockIdx.x) * dim) + 2 * i;
+      const float4 a = pr[0], b = pr[1];
+      t[j][0] += a.x; t[j][1] += a.y; t[j][2] += a.z; t[j][3] += a.w;
+      t[j][4] += b.x; t[j][5] += b.y; t[j][6] += b.z; t[j][7] += b.w;
+    }
+#pragma unroll
+    for (uint32_t e = 0; e < 8; ++e) {
+      t[j][e] = __bfloat162float(__float2bfloat16(t[j][e]));      // the projection as stored
+      acc = fmaf(t[j][e], t[j][e], acc);
+    }
+  }
+  const float inv = rsqrtf(block_sum_256(acc, red) / float(dim) + 1e-6f);
+  const uint4* hr = reinterpret_cast<const uint4*>(hidden + size_t(blockIdx.x) * dim);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* orow = reinterpret_cast<uint4*>(out + size_t(blockIdx.x) * dim);
+#pragma unroll
+  for (uint32_t j = 0; j < ROW_VEC; ++j) {
+    const uint32_t i = threadIdx.x + j * 256u;
+    if (i >= n_vec) continue;
+    const uint4 h4 = hr[i];
+    const uint4 w4 = w != nullptr ? wr[i] : make_uint4(0u, 0u, 0u, 0u);
+    const uint32_t hs[4] = {h4.x, h4.y, h4.z, h4.w}, ws[4] = {w4.x, w4.y, w4.z, w4.w};
+    uint32_t o[4];
+#pragma unroll
+    for (uint32_t e = 0; e < 4; ++e) {
+      float lo = t[j][2 * e] * inv, hi = t[j][2 * e + 1] * inv;
+      if (w != nullptr) {
+        lo *= __uint_as_float(ws[e] << 16);
+        hi *= __uint_as_float(ws[e] & 0xffff0000u);
+      }
+      lo = __bfloat162float(__float2bfloat16(lo));               // the normed projection as stored
+      hi = __bfloat162float(__float2bfloat16(hi));
+      o[e] = pack_bf16x2(__uint_as_float(hs[e] << 16) + lo, __uint_as_float(hs[e] & 0xffff0000u) + hi);
+    }
+    orow[i] = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 
@@ -229,7 +320,7 @@ cudaError_t launch_gemm_sm100(const GemmParams& g, const CUtensorMap& tm_a, cons
                               cudaStream_t st) {
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[1];
-  const dim3 grid(g.N / bn, (g.M + gm::GM - 1) / gm::GM);
+  const dim3 grid(g.N / bn, (g.M + gm::GM - 1) / gm::GM, g.part != nullptr ? g.k_slices : 1u);
   pdl_cfg(cfg, attr, grid, dim3(gm::THREADS), gm::smem_bytes(bn), st);
   if (bn == 128) return cudaLaunchKernelEx(&cfg, dg_gemm_sm100_kernel<128>, g, tm_a, tm_w);
   return cudaLaunchKernelEx(&cfg, dg_gemm_sm100_kernel<64>, g, tm_a, tm_w);
@@ -243,12 +334,12 @@ cudaError_t launch_rmsnorm_rows(const void* x, const void* w, void* y, uint32_t 
                             static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), dim);
 }
 
-cudaError_t launch_norm_residual(const void* t, const float* rowsq, uint32_t n_part, const void* w, const void* hidden,
-                                 void* out, uint32_t rows, uint32_t dim, cudaStream_t st) {
+cudaError_t launch_norm_residual(const float* part, uint32_t n_part, const void* w, const void* hidden, void* out,
+                                 uint32_t rows, uint32_t dim, cudaStream_t st) {
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[1];
   pdl_cfg(cfg, attr, dim3(rows), dim3(256), 0, st);
-  return cudaLaunchKernelEx(&cfg, dg_norm_residual_kernel, static_cast<const __nv_bfloat16*>(t), rowsq, n_part,
+  return cudaLaunchKernelEx(&cfg, dg_norm_residual_kernel, part, n_part, size_t(rows) * dim,
                             static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(hidden),
                             static_cast<__nv_bfloat16*>(out), dim);
 }

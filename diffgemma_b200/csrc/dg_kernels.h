@@ -51,13 +51,18 @@ cudaError_t sm100_hd512x_configure();
 cudaError_t launch_attn_sm100_hd512x(const AttnParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
                                      cudaStream_t st);
 uint32_t sm100_hd512x_key_steps(const MaskParams& mk);            // pairs of 64-key tiles per cluster
+// head_dim 512, four CTAs per cluster (csrc/dg_attn_sm100_hd512q.cu): the exchange above plus cta_group::2 MMAs over
+// two query tiles; tm_k has boxes {64, 32, 1} (each CTA stages half of a key tile), tm_v as above
+cudaError_t sm100_hd512q_configure();
+cudaError_t launch_attn_sm100_hd512q(const AttnParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
+                                     cudaStream_t st);
 uint32_t sm100_key_tiles(const MaskParams& mk);                     // upper bound of key tiles per CTA
 // projections and row-wise kernels either side of the attention stage (csrc/dg_gemm_sm100.cu)
 cudaError_t sm100_gemm_configure();
 cudaError_t launch_gemm_sm100(const GemmParams& g, const CUtensorMap& tm_a, const CUtensorMap& tm_w, uint32_t bn,
                               cudaStream_t st);
 cudaError_t launch_rmsnorm_rows(const void* x, const void* w, void* y, uint32_t rows, uint32_t dim, cudaStream_t st);
-cudaError_t launch_norm_residual(const void* t, const float* rowsq, uint32_t n_part, const void* w, const void* hidden,
-                                 void* out, uint32_t rows, uint32_t dim, cudaStream_t st);
+cudaError_t launch_norm_residual(const float* part, uint32_t n_part, const void* w, const void* hidden, void* out,
+                                 uint32_t rows, uint32_t dim, cudaStream_t st);
 
 }  // namespace dg

@@ -536,15 +536,16 @@ def test_gpu_matches_reference_shader_vectors(ctx, name):
     (1, 16, 2, 256, 0, 0, 1.0, 1),          # one prefix key: the canvas tiles carry everything
 ])
 def test_hd512_tensor_path_parity(ctx, P, Hq, Hkv, canvas, W, mode, scale, vnorm):
-    """Both tensor forms: one CTA per value half with the scores computed twice (pair mode off), and the CTA pair
-    that splits the score work and exchanges P (the default)."""
+    """All three tensor forms: one CTA per value half with the scores computed twice (pair mode off), the two-CTA
+    cluster that splits the score work and exchanges P (pair mode on), and the four-CTA cluster that also shares the
+    K and V stages between two query tiles (automatic, taken when a KV head has an even number of query tiles)."""
     layer = AttnLayer(n_q_heads=Hq, n_kv_heads=Hkv, head_dim=512, canvas=canvas, rotary_dim=128, rope_theta=1e6,
                       softmax_scale=scale, window=W, mask_mode=mode, v_norm=vnorm, rope_pairing=capi.ROPE_PROPORTIONAL)
     case = util.make_case(layer, P, seed=P + Hq, weights=True)
     ref = util.run_oracle(case)
     assert CanvasAttention(ctx, layer).uses_tensor_path
     try:
-        for pair in (None, False):
+        for pair in (None, True, False):
             ctx.set_pair_mode(pair)
             for splits in (0, 1, 2, 5):
                 ctx.set_splits(splits)
