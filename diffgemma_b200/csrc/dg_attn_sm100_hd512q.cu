@@ -248,13 +248,22 @@ dg_attn_sm100_hd512q_kernel(const AttnParams p, const __grid_constant__ CUtensor
       const uint64_t sc2 = pack_f32x2(sc, sc), nm2 = pack_f32x2(neg_m, neg_m);
       uint64_t ls2[2] = {0ull, 0ull};
       uint32_t pk[32];
+      // Every 8 keys (one 16-byte chunk of the row) leave for the peer as soon as they are computed, so that the
+      // transfer of the row runs under the exponentials of its later keys: chunk j = keys [8j, 8j + 8) at chunk
+      // position j ^ (r & 7).  The buffer is free: the peer read its step n - 2 before it sent the row maxima of step
+      // n, which this thread has waited for.
 #pragma unroll
-      for (int e = 0; e < 64; e += 2) {
-        float x0, x1;
-        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sraw[e]), __uint_as_float(sraw[e + 1])), sc2, nm2), x0, x1);
-        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-        ls2[(e >> 1) & 1] = add_f32x2(ls2[(e >> 1) & 1], pack_f32x2(p0, p1));
-        pk[e >> 1] = pack_bf16x2(p0, p1);
+      for (uint32_t j = 0; j < 8; ++j) {
+#pragma unroll
+        for (int e = int(j) * 8; e < int(j) * 8 + 8; e += 2) {
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sraw[e]), __uint_as_float(sraw[e + 1])), sc2, nm2), x0, x1);
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          ls2[(e >> 1) & 1] = add_f32x2(ls2[(e >> 1) & 1], pack_f32x2(p0, p1));
+          pk[e >> 1] = pack_bf16x2(p0, p1);
+        }
+        dsmem_st_async_u4(peer_pr + ((j ^ (r & 7u)) << 4), make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]),
+                          peer_bar_pr);
       }
       {
         float s0, s1;
@@ -266,13 +275,6 @@ dg_attn_sm100_hd512q_kernel(const AttnParams p, const __grid_constant__ CUtensor
         c_exp += t_b - t_a;
         t_a = t_b;
       }
-      // the peer's copy first (it travels while the own copy is stored): row r, 16-byte chunk j = keys [8j, 8j + 8)
-      // at chunk position j ^ (r & 7).  The buffer is free: the peer read its step n - 2 before it sent the row
-      // maxima of step n, which this thread has waited for.
-#pragma unroll
-      for (uint32_t j = 0; j < 8; ++j)
-        dsmem_st_async_u4(peer_pr + ((j ^ (r & 7u)) << 4), make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]),
-                          peer_bar_pr);
       // own copy: P column j = keys (2j, 2j + 1), over the first 32 columns of the S buffer
       tmem_st32(t_lane + T_S + b * TN, pk);
       tmem_wait_st();
