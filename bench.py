@@ -39,8 +39,8 @@ L2_BYTES = 126e6
 MAX_ABS_GATE, MEAN_ABS_GATE = 2e-2, 2e-3
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention-kernel launch of the headline
-# workload on one GPU, from an ncu capture of this kernel (read 70.26 MB + write 4.29 MB)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {2: 74.55e6}
+# workload on one GPU, from an ncu capture of this kernel (read 70.32 MB + write 4.32 MB)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {2: 74.64e6}
 
 
 def _peaks():
@@ -403,6 +403,9 @@ class Workload:
             self.group.set_share_q(True)       # every rank copies in its row slice of Q; the slices cross NVLink
         self.PIPE_DEPTH = 3 if self.world == 1 else 6
         self.pipe = HostPipe(self.ctx, self.lay, 1, self.PIPE_DEPTH)
+        if self.group is None and not self.args.no_deferred_launch:
+            # a step's kernel is launched one submit after its copies: no event wait between consecutive kernels
+            self.pipe.set_deferred_launch(True)
         self.pending = []
         q0, kc0, vc0 = (t[None].contiguous() for t in self.case[:3])
         self.host_sets = [tuple(t.clone().pin_memory() for t in (q0, kc0, vc0, torch.zeros_like(q0)))
@@ -1123,6 +1126,8 @@ def main():
     ap.add_argument("--share-q", action="store_true",
                     help="multi-GPU end-to-end arm: every rank copies in only its row slice of Q and the ranks "
                          "exchange the slices over NVLink (for hosts whose PCIe links are the bottleneck)")
+    ap.add_argument("--no-deferred-launch", action="store_true",
+                    help="end-to-end arm on one GPU: launch every step's kernels inside its own submit")
     ap.add_argument("--one-lane", action="store_true",
                     help="multi-GPU: one context per rank instead of two that take alternate steps")
     ap.add_argument("--no-pipelined-exchange", action="store_true",

@@ -89,6 +89,7 @@ SIGNATURES = {
                                    C.POINTER(_u64)]),
     "dg_host_pipe_wait": (_i32, [_vp, _u64]),
     "dg_host_pipe_destroy": (_i32, [_vp]),
+    "dg_host_pipe_set_deferred_launch": (_i32, [_vp, _i32]),
     "dg_attn_denoise_bitmap": (_i32, [_vp, _pd, _vp, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dg_attn_partial": (_i32, [_vp, _pd, _vp, _u32, _u32, _u32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dg_attn_merge_local": (_i32, [_vp, _u32, _u32, _u32, _vp, _vp, _vp, _vp]),

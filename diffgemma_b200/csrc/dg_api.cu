@@ -1179,13 +1179,58 @@ struct dg_host_pipe {
     cudaEvent_t in = nullptr, cmp = nullptr, out = nullptr;
     bool used = false;      // the events have been recorded at least once
     bool pending = false;   // submitted and not yet waited for
+    // dg_host_pipe_submit: the step's copies in are queued at once, its kernels one submit later (pipe_launch)
+    bool launched = true;
+    dg_layer_desc d;
+    std::vector<dg_kv*> kv;
+    std::vector<uint32_t> len;
+    uint32_t batch = 0;
+    const void *qw = nullptr, *kw = nullptr;
+    void* out_host = nullptr;
+    size_t qe = 0;
   } slot[8];
   uint64_t next = 0;        // ticket of the next submit
+  bool deferred = false;    // dg_host_pipe_set_deferred_launch
 };
+
+// Kernels and copy out of a submitted step whose copies in have been queued.  Deferred form: the HOST waits for those
+// copies here (they were queued a whole submit ago, so this normally returns at once) instead of making the compute
+// stream wait for their event: with nothing between this step's kernel and the previous step's on the stream the
+// launch stays programmatic, and the kernel's set-up and Q prologue overlap the tail of the kernel before it.
+static int32_t pipe_launch(dg_host_pipe* hp, dg_host_pipe::Slot& sl) {
+  if (sl.launched) return DG_OK;
+  sl.launched = true;
+  dg_ctx* c = hp->ctx;
+  if (hp->deferred) DG_CUDA(cudaEventSynchronize(sl.in));
+  else DG_CUDA(cudaStreamWaitEvent(c->stream, sl.in, 0));
+  // the slot's staging buffers are complete and are not rewritten before sl.cmp: the Q prologue may read them as
+  // early as it likes.  (The slot's previous output left long ago: its submitter or a wait synchronised on sl.out.)
+  const int saved = c->inputs_stable;
+  c->inputs_stable = 1;
+  const int32_t r = dg_attn_denoise(c, &sl.d, sl.kv.data(), sl.len.data(), sl.batch, sl.q, sl.k, sl.v, sl.qw, sl.kw, sl.o);
+  c->inputs_stable = saved;
+  if (r != DG_OK) return r;
+  DG_CUDA(cudaEventRecord(sl.cmp, c->stream));
+  DG_CUDA(cudaStreamWaitEvent(hp->d2h, sl.cmp, 0));
+  DG_CUDA(cudaMemcpyAsync(sl.out_host, sl.o, sl.qe * 2, cudaMemcpyDeviceToHost, hp->d2h));
+  DG_CUDA(cudaEventRecord(sl.out, hp->d2h));
+  sl.used = true;
+  return DG_OK;
+}
+// every submitted step up to and including `upto`, in submission order
+static int32_t pipe_launch_upto(dg_host_pipe* hp, uint64_t upto) {
+  const uint64_t first = hp->next > hp->depth ? hp->next - hp->depth : 0;
+  for (uint64_t t = first; t <= upto && t < hp->next; ++t) {
+    const int32_t r = pipe_launch(hp, hp->slot[t % hp->depth]);
+    if (r != DG_OK) return r;
+  }
+  return DG_OK;
+}
 
 extern "C" int32_t dg_host_pipe_destroy(dg_host_pipe* hp) {
   if (!hp) return DG_OK;
   cudaSetDevice(hp->ctx->device);
+  if (hp->next > 0) pipe_launch_upto(hp, hp->next - 1);
   cudaStreamSynchronize(hp->ctx->stream);
   if (hp->h2d) cudaStreamSynchronize(hp->h2d);
   if (hp->d2h) cudaStreamSynchronize(hp->d2h);
@@ -1246,6 +1291,8 @@ extern "C" int32_t dg_host_pipe_wait(dg_host_pipe* hp, uint64_t ticket) {
   dg_host_pipe::Slot& sl = hp->slot[ticket % hp->depth];
   if (!sl.pending) return DG_OK;
   DG_CUDA(cudaSetDevice(hp->ctx->device));
+  const int32_t r = pipe_launch_upto(hp, ticket);
+  if (r != DG_OK) return r;
   DG_CUDA(cudaEventSynchronize(sl.out));
   sl.pending = false;
   return DG_OK;
@@ -1262,6 +1309,11 @@ extern "C" int32_t dg_host_pipe_submit(dg_host_pipe* hp, const dg_layer_desc* d,
   const size_t ke = size_t(batch) * d->canvas * d->n_kv_heads * d->head_dim;
   if (qe > hp->q_elems || ke > hp->kv_elems) return fail(DG_ERR_CAPACITY, "batch / geometry larger than the pipe was created for");
   DG_CUDA(cudaSetDevice(c->device));
+  // the steps submitted before this one: their copies in were queued a submit ago
+  if (hp->next > 0) {
+    r = pipe_launch_upto(hp, hp->next - 1);
+    if (r != DG_OK) return r;
+  }
   dg_host_pipe::Slot& sl = hp->slot[hp->next % hp->depth];
   if (sl.pending) {   // the caller has not collected this slot's previous result: finish it first
     DG_CUDA(cudaEventSynchronize(sl.out));
@@ -1273,26 +1325,29 @@ extern "C" int32_t dg_host_pipe_submit(dg_host_pipe* hp, const dg_layer_desc* d,
   DG_CUDA(cudaMemcpyAsync(sl.k, k, ke * 2, cudaMemcpyHostToDevice, hp->h2d));
   DG_CUDA(cudaMemcpyAsync(sl.v, v, ke * 2, cudaMemcpyHostToDevice, hp->h2d));
   DG_CUDA(cudaEventRecord(sl.in, hp->h2d));
-  // kernels: after this slot's inputs have landed and its previous output has left
-  DG_CUDA(cudaStreamWaitEvent(c->stream, sl.in, 0));
-  if (sl.used) DG_CUDA(cudaStreamWaitEvent(c->stream, sl.out, 0));
-  {
-    // the slot's staging buffers are complete before the kernels may start (they wait for sl.in) and are
-    // not rewritten before sl.cmp: the Q prologue may read them as early as it likes
-    const int saved = c->inputs_stable;
-    c->inputs_stable = 1;
-    r = dg_attn_denoise(c, d, kv, kv_len, batch, sl.q, sl.k, sl.v, qw, kw, sl.o);
-    c->inputs_stable = saved;
-  }
-  if (r != DG_OK) return r;
-  DG_CUDA(cudaEventRecord(sl.cmp, c->stream));
-  // copy out
-  DG_CUDA(cudaStreamWaitEvent(hp->d2h, sl.cmp, 0));
-  DG_CUDA(cudaMemcpyAsync(out, sl.o, qe * 2, cudaMemcpyDeviceToHost, hp->d2h));
-  DG_CUDA(cudaEventRecord(sl.out, hp->d2h));
-  sl.used = true;
+  sl.d = *d;
+  sl.kv.assign(kv, kv + batch);
+  sl.len.assign(kv_len, kv_len + batch);
+  sl.batch = batch;
+  sl.qw = qw;
+  sl.kw = kw;
+  sl.out_host = out;
+  sl.qe = qe;
+  sl.launched = false;
   sl.pending = true;
   *ticket = hp->next++;
+  // deferred form: the kernels follow at the next submit, or at the wait for this step, whichever comes first
+  return hp->deferred ? DG_OK : pipe_launch(hp, sl);
+}
+
+extern "C" int32_t dg_host_pipe_set_deferred_launch(dg_host_pipe* hp, int32_t on) {
+  if (!hp) return fail(DG_ERR_INVALID_ARG, "pipe is NULL");
+  if (hp->next > 0) {
+    DG_CUDA(cudaSetDevice(hp->ctx->device));
+    const int32_t r = pipe_launch_upto(hp, hp->next - 1);
+    if (r != DG_OK) return r;
+  }
+  hp->deferred = on != 0;
   return DG_OK;
 }
 
@@ -1321,6 +1376,10 @@ extern "C" int32_t dg_host_pipe_submit_split(dg_host_pipe* hp, const dg_layer_de
   const size_t ke = size_t(d->canvas) * d->n_kv_heads * d->head_dim;
   if (qe > hp->q_elems || ke > hp->kv_elems) return fail(DG_ERR_CAPACITY, "geometry larger than the pipe was created for");
   DG_CUDA(cudaSetDevice(c->device));
+  if (hp->next > 0) {
+    r = pipe_launch_upto(hp, hp->next - 1);
+    if (r != DG_OK) return r;
+  }
   dg_host_pipe::Slot& sl = hp->slot[hp->next % hp->depth];
   if (sl.pending) {
     DG_CUDA(cudaEventSynchronize(sl.out));

@@ -350,6 +350,10 @@ class HostPipe:
     def wait(self, ticket: int) -> None:
         check(self.ctx.lib.dg_host_pipe_wait(self.h, ticket), "dg_host_pipe_wait")
 
+    def set_deferred_launch(self, on: bool) -> None:
+        """submit() queues a step's copies at once and its kernels at the next submit (dg_host_pipe_set_deferred_launch)."""
+        check(self.ctx.lib.dg_host_pipe_set_deferred_launch(self.h, int(bool(on))), "dg_host_pipe_set_deferred_launch")
+
     def close(self) -> None:
         if self.h:
             self.ctx.lib.dg_host_pipe_destroy(self.h)

@@ -565,7 +565,9 @@ def test_hd512_tensor_path_parity(ctx, P, Hq, Hkv, canvas, W, mode, scale, vnorm
 # ------------------------------------------------------------------------------------------
 # host-buffer pipeline
 # ------------------------------------------------------------------------------------------
-def test_host_pipe_matches_the_synchronous_host_call(ctx):
+@pytest.mark.parametrize("deferred", [False, True])
+def test_host_pipe_matches_the_synchronous_host_call(ctx, deferred):
+    """Also with the deferred launch: a step's kernels are queued one submit after its copies, or at its wait."""
     from diffgemma_b200.step_attn import HostPipe
     layer = AttnLayer(n_kv_heads=2)
     cases = [util.make_case(layer, 3000, seed=400 + i) for i in range(7)]
@@ -578,6 +580,7 @@ def test_host_pipe_matches_the_synchronous_host_call(ctx):
         att.denoise_host([kv], [3000], q, k, v, o)
         want.append(o.clone())
     pipe = HostPipe(ctx, layer, 1, depth=3)
+    pipe.set_deferred_launch(deferred)
     outs = [torch.empty_like(ins[0][0]).pin_memory() for _ in cases]
     tickets = [pipe.submit([kv], [3000], q, k, v, o) for (q, k, v), o in zip(ins, outs)]   # more submits than slots
     for t in reversed(tickets):                           # collected out of order
