@@ -749,6 +749,8 @@ def run_stack(args, as_block=False):
     assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
     dev = torch.device("cuda", local)
     ctx = Context(local)
+    if args.kernel_form != "auto":
+        ctx.set_pair_mode(args.kernel_form == "pair")
     ctx.set_inputs_stable(True)        # resident inputs, written before the timed region
     comm = _nccl_comm(ctx, None) if world > 1 else None
     P, B = 16384, 4
@@ -1064,7 +1066,7 @@ def run_ours(args):
                          "peak_sustained": peaks["bf16_tflops_sustained"],
                          "frac_of_sustained": (achieved / peaks["bf16_tflops_sustained"])
                          if (achieved and peaks["bf16_tflops_sustained"]) else None,
-                         "kernel": ("dg_attn_sm100_hd512_kernel" if args.kernel_form == "single" else "dg_attn_sm100_hd512x_kernel")
+                         "kernel": {"single": "dg_attn_sm100_hd512_kernel", "pair": "dg_attn_sm100_hd512x_kernel"}.get(args.kernel_form, "dg_attn_sm100_hd512q_kernel")
                          if lay.head_dim == 512 else "dg_attn_sm100_kernel",
                          "kernel_ms": k_avg_ms, "kernel_launches_timed": k_n, "kernel_ms_how": k_how, "sustained": sustained},
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e,
