@@ -403,7 +403,7 @@ class Workload:
             self.group.set_share_q(True)       # every rank copies in its row slice of Q; the slices cross NVLink
         self.PIPE_DEPTH = 3 if self.world == 1 else 6
         self.pipe = HostPipe(self.ctx, self.lay, 1, self.PIPE_DEPTH)
-        if self.group is None and not self.args.no_deferred_launch:
+        if self.group is None and not self.args.no_deferred_launch:   # measured slower on a split-KV rank (host-bound)
             # a step's kernel is launched one submit after its copies: no event wait between consecutive kernels
             self.pipe.set_deferred_launch(True)
         self.pending = []

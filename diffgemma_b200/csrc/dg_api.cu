@@ -73,6 +73,8 @@ struct dg_ctx {
   __nv_bfloat16* blk_v = nullptr;
   __nv_bfloat16* blk_o = nullptr;
   float* blk_part = nullptr;           // fp32 partial planes of the output projection, [4][rows][hidden]
+  uint16_t* topk_scores = nullptr;     // dg_attn_denoise_topk: bf16 score plane [Hkv][canvas * G][ld]
+  size_t topk_elems = 0;
   size_t blk_rows = 0, blk_hidden = 0, blk_qe = 0, blk_ke = 0;
   CUtensorMap blk_tm_xn, blk_tm_o;
   struct WMap {
@@ -354,6 +356,7 @@ extern "C" int32_t dg_ctx_destroy(dg_ctx* c) {
   cudaFree(c->blk_v);
   cudaFree(c->blk_o);
   cudaFree(c->blk_part);
+  cudaFree(c->topk_scores);
   for (cudaEvent_t e : c->ev) cudaEventDestroy(e);
   if (c->own_stream) cudaStreamDestroy(c->own_stream);
   delete c;
@@ -1169,6 +1172,13 @@ extern "C" int32_t dg_attn_denoise_host(dg_ctx* c, const dg_layer_desc* d, dg_kv
 // ------------------------------------------------------------------------------------------
 // Host-buffer pipeline: the copies of step i+1 and i-1 overlap the kernels of step i
 // ------------------------------------------------------------------------------------------
+struct dg_p2p;
+static bool p2p_is_push(const dg_p2p* x);
+static void p2p_slice_bytes(const dg_p2p* x, size_t* off, size_t* bytes);
+extern "C" int32_t dg_attn_denoise_split_p2p(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint32_t kv_len, uint32_t t0,
+                                             uint32_t t1, int32_t include_canvas, dg_p2p* x, const void* q, const void* k,
+                                             const void* v, const void* qw, const void* kw, void* out);
+
 struct dg_host_pipe {
   dg_ctx* ctx = nullptr;
   uint32_t depth = 0;
@@ -1188,6 +1198,12 @@ struct dg_host_pipe {
     const void *qw = nullptr, *kw = nullptr;
     void* out_host = nullptr;
     size_t qe = 0;
+    // dg_host_pipe_submit_split: the step of one rank of a split-KV group
+    bool split = false;
+    uint32_t t0 = 0, t1 = 0;
+    int32_t include_canvas = 0;
+    struct dg_p2p* x = nullptr;
+    const void* q_dev = nullptr;
   } slot[8];
   uint64_t next = 0;        // ticket of the next submit
   bool deferred = false;    // dg_host_pipe_set_deferred_launch
@@ -1207,12 +1223,18 @@ static int32_t pipe_launch(dg_host_pipe* hp, dg_host_pipe::Slot& sl) {
   // early as it likes.  (The slot's previous output left long ago: its submitter or a wait synchronised on sl.out.)
   const int saved = c->inputs_stable;
   c->inputs_stable = 1;
-  const int32_t r = dg_attn_denoise(c, &sl.d, sl.kv.data(), sl.len.data(), sl.batch, sl.q, sl.k, sl.v, sl.qw, sl.kw, sl.o);
+  const int32_t r = sl.split ? dg_attn_denoise_split_p2p(c, &sl.d, sl.kv[0], sl.len[0], sl.t0, sl.t1, sl.include_canvas, sl.x,
+                                                         sl.q_dev, sl.k, sl.v, sl.qw, sl.kw, sl.o)
+                             : dg_attn_denoise(c, &sl.d, sl.kv.data(), sl.len.data(), sl.batch, sl.q, sl.k, sl.v, sl.qw, sl.kw, sl.o);
   c->inputs_stable = saved;
   if (r != DG_OK) return r;
   DG_CUDA(cudaEventRecord(sl.cmp, c->stream));
   DG_CUDA(cudaStreamWaitEvent(hp->d2h, sl.cmp, 0));
-  DG_CUDA(cudaMemcpyAsync(sl.out_host, sl.o, sl.qe * 2, cudaMemcpyDeviceToHost, hp->d2h));
+  // a split-KV step in the push form of the exchange leaves only this rank's row slice
+  size_t off = 0, bytes = sl.qe * 2;
+  if (sl.split && p2p_is_push(sl.x)) p2p_slice_bytes(sl.x, &off, &bytes);
+  DG_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(sl.out_host) + off, reinterpret_cast<uint8_t*>(sl.o) + off, bytes,
+                          cudaMemcpyDeviceToHost, hp->d2h));
   DG_CUDA(cudaEventRecord(sl.out, hp->d2h));
   sl.used = true;
   return DG_OK;
@@ -1333,6 +1355,7 @@ extern "C" int32_t dg_host_pipe_submit(dg_host_pipe* hp, const dg_layer_desc* d,
   sl.kw = kw;
   sl.out_host = out;
   sl.qe = qe;
+  sl.split = false;
   sl.launched = false;
   sl.pending = true;
   *ticket = hp->next++;
@@ -1355,15 +1378,9 @@ extern "C" int32_t dg_host_pipe_set_deferred_launch(dg_host_pipe* hp, int32_t on
 // dg_attn_denoise_split_p2p.  A rank that does not count the canvas keys and whose cache is a shard
 // never stores the canvas K/V, so their host-to-device copies are left out; in the push form of the
 // exchange only this rank's row slice of the output is copied back.
-struct dg_p2p;
-static bool p2p_is_push(const dg_p2p* x);
-static void p2p_slice_bytes(const dg_p2p* x, size_t* off, size_t* bytes);
 // shared query staging: null when the group does not share Q; else the slot's device buffer, after the slice
 // exchange has been queued on `st`
 static int32_t p2p_share_q(dg_p2p* x, uint32_t slot, const void* q_host, cudaStream_t st, __nv_bfloat16** q_dev);
-extern "C" int32_t dg_attn_denoise_split_p2p(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint32_t kv_len, uint32_t t0,
-                                             uint32_t t1, int32_t include_canvas, dg_p2p* x, const void* q, const void* k,
-                                             const void* v, const void* qw, const void* kw, void* out);
 extern "C" int32_t dg_host_pipe_submit_split(dg_host_pipe* hp, const dg_layer_desc* d, dg_kv* kv, uint32_t kv_len,
                                              uint32_t t0, uint32_t t1, int32_t include_canvas, dg_p2p* x, const void* q,
                                              const void* k, const void* v, const void* qw, const void* kw, void* out,
@@ -1401,26 +1418,24 @@ extern "C" int32_t dg_host_pipe_submit_split(dg_host_pipe* hp, const dg_layer_de
     DG_CUDA(cudaMemcpyAsync(sl.v, v, ke * 2, cudaMemcpyHostToDevice, hp->h2d));
   }
   DG_CUDA(cudaEventRecord(sl.in, hp->h2d));
-  DG_CUDA(cudaStreamWaitEvent(c->stream, sl.in, 0));
-  if (sl.used) DG_CUDA(cudaStreamWaitEvent(c->stream, sl.out, 0));
-  {
-    const int saved = c->inputs_stable;   // as in dg_host_pipe_submit
-    c->inputs_stable = 1;
-    r = dg_attn_denoise_split_p2p(c, d, kv, kv_len, t0, t1, include_canvas, x, q_dev, sl.k, sl.v, qw, kw, sl.o);
-    c->inputs_stable = saved;
-  }
-  if (r != DG_OK) return r;
-  DG_CUDA(cudaEventRecord(sl.cmp, c->stream));
-  DG_CUDA(cudaStreamWaitEvent(hp->d2h, sl.cmp, 0));
-  size_t off = 0, bytes = qe * 2;
-  if (p2p_is_push(x)) p2p_slice_bytes(x, &off, &bytes);
-  DG_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(out) + off, reinterpret_cast<uint8_t*>(sl.o) + off, bytes,
-                          cudaMemcpyDeviceToHost, hp->d2h));
-  DG_CUDA(cudaEventRecord(sl.out, hp->d2h));
-  sl.used = true;
+  sl.d = *d;
+  sl.kv.assign(1, kv);
+  sl.len.assign(1, kv_len);
+  sl.batch = 1;
+  sl.qw = qw;
+  sl.kw = kw;
+  sl.out_host = out;
+  sl.qe = qe;
+  sl.split = true;
+  sl.t0 = t0;
+  sl.t1 = t1;
+  sl.include_canvas = include_canvas;
+  sl.x = x;
+  sl.q_dev = q_dev;
+  sl.launched = false;
   sl.pending = true;
   *ticket = hp->next++;
-  return DG_OK;
+  return hp->deferred ? DG_OK : pipe_launch(hp, sl);
 }
 
 extern "C" int32_t dg_attn_denoise_bitmap(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint32_t kv_len, const void* q,
@@ -2149,5 +2164,100 @@ extern "C" int32_t dg_attn_block(dg_ctx* c, const dg_layer_desc* d, const dg_blo
   e = launch_norm_residual(c->blk_part, slices, w->post_attn_ln, hidden_in, stream_out, C, H, st);
   if (e != cudaSuccess) return fail_cuda(e, "launch_norm_residual");
   c->last_launches = launches + 2;
+  return DG_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// top-k sparse attention of the reference's full layers (src/shaders/attn/attention_topk/, enc.rs:2125-2135):
+// stage 1 -> score GEMM per KV head -> selection + gathered PV
+// ------------------------------------------------------------------------------------------
+extern "C" int32_t dg_attn_denoise_topk(dg_ctx* c, const dg_layer_desc* d, dg_kv* kv, uint32_t kv_len, const void* q,
+                                        const void* k, const void* v, const void* qw, const void* kw, const dg_topk_cfg* cfg,
+                                        void* out) {
+  if (!c || !q || !k || !v || !out || !cfg) return fail(DG_ERR_INVALID_ARG, "NULL argument");
+  int32_t r = check_desc(d);
+  if (r != DG_OK) return r;
+  r = check_kv(*d, kv, uint64_t(kv_len) + d->canvas);
+  if (r != DG_OK) return r;
+  r = check_ptrs16({q, k, v, qw, kw, out});
+  if (r != DG_OK) return r;
+  if (kv->ring_mask != 0 || kv->shard || !kv->has_tmap)
+    return fail(DG_ERR_UNSUPPORTED, "dg_attn_denoise_topk: a linear, unsharded cache of head_dim 256 or 512");
+  const uint32_t G = d->n_q_heads / d->n_kv_heads, D = d->head_dim, C = d->canvas;
+  if (G > 128 || 128 % G != 0) return fail(DG_ERR_UNSUPPORTED, "dg_attn_denoise_topk: the GQA group must divide 128");
+  if (cfg->k_div == 0 ? cfg->k_fixed == 0 : cfg->k_min > cfg->k_max)
+    return fail(DG_ERR_INVALID_ARG, "dg_attn_denoise_topk: k_fixed >= 1, or k_min <= k_max with k_div");
+  if ((cfg->k_div == 0 ? cfg->k_fixed : cfg->k_max) > 1024) return fail(DG_ERR_UNSUPPORTED, "dg_attn_denoise_topk: at most 1024 keys per row");
+  DG_CUDA(cudaSetDevice(c->device));
+  c->last_launches = 0;
+  const size_t qe = size_t(C) * d->n_q_heads * D;
+  r = ensure_stage(c, qe, 0);
+  if (r != DG_OK) return r;
+  // the score plane: keys padded to whole tiles of the score GEMM (128 keys at head_dim 256, 64 at 512)
+  const uint32_t bn = D == 256 ? 128u : 64u;
+  const uint32_t T = kv_len + C, ld = (T + bn - 1) / bn * bn;
+  const size_t rows = size_t(C) * G, need = size_t(d->n_kv_heads) * ((rows + 127) / 128 * 128) * ld;
+  if (need > c->topk_elems) {
+    DG_CUDA(cudaStreamSynchronize(c->stream));
+    cudaFree(c->topk_scores);
+    c->topk_scores = nullptr;
+    c->topk_elems = 0;
+    DG_CUDA(cudaMalloc(&c->topk_scores, need * 2));
+    c->topk_elems = need;
+  }
+  cudaStream_t st = launch_stream(c);
+  // 1. stage 1: Q normed + roped into the staging tensor, canvas K/V into the cache
+  r = do_append(c, *d, kv, kv_len, C, q, c->stage_q, k, nullptr, v, nullptr, qw, kw, nullptr);
+  if (r != DG_OK) return r;
+  // 2. scores of every (row, key) of one KV head: rows (i, g) of the staged Q against the cache's K
+  CUtensorMap tm_q;
+  {
+    PFN_encodeTiled enc = get_encode_fn();
+    if (!enc) return fail(DG_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    for (uint32_t h = 0; h < d->n_kv_heads; ++h) {
+      const cuuint64_t dims[3] = {D, G, C};
+      const cuuint64_t strides[2] = {cuuint64_t(D) * 2, cuuint64_t(d->n_q_heads) * D * 2};
+      const cuuint32_t box[3] = {64, G, 128 / G};
+      const cuuint32_t estr[3] = {1, 1, 1};
+      const CUresult cr = enc(&tm_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, c->stage_q + size_t(h) * G * D, dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (cr != CUDA_SUCCESS) return fail(DG_ERR_CUDA, "cuTensorMapEncodeTiled failed for the staged Q");
+      GemmParams g = {};
+      g.M = uint32_t(rows);
+      g.N = ld;
+      g.K = D;
+      g.n_seg = 1;
+      g.seg[0] = GemmSeg{c->topk_scores + size_t(h) * ((rows + 127) / 128 * 128) * ld, 0u, ld};
+      g.a_inner = G;
+      g.w_z = h;
+      g.status = c->d_status;
+      const cudaError_t e = launch_gemm_sm100(g, tm_q, kv->tm_k, bn, st);
+      if (e != cudaSuccess) return fail_cuda(e, "launch_gemm_sm100 (scores)");
+      c->last_launches += 1;
+    }
+  }
+  // 3. selection + softmax over the kept keys + gathered PV
+  TopkParams tp = {};
+  tp.scores = c->topk_scores;
+  tp.ld = ld;
+  tp.q = c->stage_q;
+  tp.k = kv->k;
+  tp.v = kv->v;
+  tp.out = static_cast<__nv_bfloat16*>(out);
+  tp.C = C;
+  tp.Hq = d->n_q_heads;
+  tp.G = G;
+  tp.D = D;
+  tp.cap = kv->cap;
+  tp.mask = make_mask(*d, kv_len, 0, 0xffffffffu, 1);
+  tp.k_fixed = cfg->k_fixed;
+  tp.k_div = cfg->k_div;
+  tp.k_min = cfg->k_min;
+  tp.k_max = cfg->k_max;
+  tp.scale_log2 = d->softmax_scale * 1.4426950408889634f;
+  const cudaError_t e = launch_topk_select_pv(tp, st);
+  if (e != cudaSuccess) return fail_cuda(e, "launch_topk_select_pv");
+  c->last_launches += 1;
   return DG_OK;
 }

@@ -239,7 +239,25 @@ struct GemmParams {
   float* rowsq;        // optional [M][N / tile width]: sum of squares of each row's rounded outputs per tile
   float* part;         // split-K: fp32 partial sums [k_slices][M][N] instead of the bf16 output
   uint32_t k_slices;
+  uint32_t a_inner;    // 0: A is a {K, M} map.  G > 0: A is a {K, G, M / G} map (rows (i, g) of one KV head of a
+                       // [C][Hq][D] tensor) with boxes {64, G, 128 / G}
+  uint32_t w_z;        // third coordinate of the W map (the KV head of a cache map), else 0
   DevStatus* status;
+};
+
+// top-k selection + gathered PV over a plane of 16-bit scores (csrc/dg_topk.cu)
+struct TopkParams {
+  const uint16_t* scores;        // bf16 [Hkv][C * G][ld]: row i * G + g of KV head h, key t
+  uint32_t ld;
+  const __nv_bfloat16* q;        // normed + roped Q [C][Hq][D]
+  const __nv_bfloat16* k;        // caches [Hkv][cap][D]
+  const __nv_bfloat16* v;
+  __nv_bfloat16* out;            // [C][Hq][D]
+  uint32_t C, Hq, G, D;
+  uint64_t cap;
+  MaskParams mask;
+  uint32_t k_fixed, k_div, k_min, k_max;   // k = k_div ? clamp(n_visible / k_div, k_min, k_max) : k_fixed, at most n_visible
+  float scale_log2;
 };
 
 }  // namespace dg

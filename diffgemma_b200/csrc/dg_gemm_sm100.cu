@@ -82,8 +82,9 @@ dg_gemm_sm100_kernel(const GemmParams g, const __grid_constant__ CUtensorMap tm_
         if (use > 0 && !mbar_wait(bar_addr(bar_base, B_EMPTY + s), (use - 1u) & 1u, abort_flag)) break;
         const uint32_t full = bar_addr(bar_base, B_FULL + s);
         mbar_expect_tx(full, STAGE);
-        tma_load_3d(smem_base + s * STAGE, &tm_a, full, int32_t((kb0 + kb) * BK), int32_t(m0), 0);
-        tma_load_3d(smem_base + s * STAGE + A_STAGE, &tm_w, full, int32_t((kb0 + kb) * BK), int32_t(n0), 0);
+        if (g.a_inner == 0u) tma_load_3d(smem_base + s * STAGE, &tm_a, full, int32_t((kb0 + kb) * BK), int32_t(m0), 0);
+        else tma_load_3d(smem_base + s * STAGE, &tm_a, full, int32_t((kb0 + kb) * BK), 0, int32_t(m0 / g.a_inner));
+        tma_load_3d(smem_base + s * STAGE + A_STAGE, &tm_w, full, int32_t((kb0 + kb) * BK), int32_t(n0), int32_t(g.w_z));
       }
     }
   } else if (warp == 1) {

@@ -292,6 +292,26 @@ typedef struct dg_block_weights {
 int32_t dg_attn_block(dg_ctx* ctx, const dg_layer_desc* desc, const dg_block_weights* w, dg_kv* kv, uint32_t kv_len,
                       const void* hidden_in, void* stream_out);
 
+/* ---- top-k sparse attention (the reference's default on its full layers) ---------------------
+ * The reference's DGQ_ATTN_TOPK_DECODE path (src/metal/step_kernel/enc.rs:2125-2135,
+ * src/shaders/attn/attention_topk/, oracle attention_topk/cpu.rs:39-120): per (canvas row, query head) only the k
+ * highest-scoring visible keys are kept (equal scores: lower index first), the softmax is renormalised over them and
+ * O = sum_j p_j V[idx_j].  Its outputs differ from dense attention by construction; this call exists for hosts that
+ * need the reference's default numerics, not for speed (on this GPU the exact dense step is faster).
+ * k per row: with k_div != 0, k = clamp(n_visible / k_div, k_min, k_max) (the reference's kv-adaptive rule:
+ * k_div 128, k_min 64, k_max 512), else k_fixed; never more than the row's visible keys, at most 1024.
+ * Same q / k / v / qw / kw / out as dg_attn_denoise for one canvas; linear unsharded caches of head_dim 256 or 512,
+ * GQA groups that divide 128.  Three stages: stage 1 as in dg_qk_rope_kv, a tensor-core GEMM that writes the scores
+ * of every (row, key) as a 16-bit plane (the reference's u16 key plane), and a selection kernel: two 256-bin radix
+ * levels find the k-th largest 16-bit score, keys that share it are ranked by their exact fp32 score, the winners'
+ * exact scores are recomputed, softmax, gathered V.                                                              */
+typedef struct dg_topk_cfg {
+  uint32_t k_fixed, k_div, k_min, k_max;
+} dg_topk_cfg;
+int32_t dg_attn_denoise_topk(dg_ctx* ctx, const dg_layer_desc* desc, dg_kv* kv, uint32_t kv_len, const void* q,
+                             const void* k, const void* v, const void* qw, const void* kw, const dg_topk_cfg* cfg,
+                             void* out);
+
 /* ---- split-KV building blocks (multi-GPU, and the block-continuation state of the reference:
  * AttnBlockRange / attn_state, src/shaders/include/attention_device.metal:154-165) ------------ */
 /* Partial attention over prefix keys [t0, t1) (clipped to kv_len and to the layer's window)

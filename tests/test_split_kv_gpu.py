@@ -164,7 +164,7 @@ def test_push_exchange_timeout_is_reported_and_group_recovers():
             assert mx <= r["tol"] and mean <= 2e-3, (rank, key, mx, mean)
 
 
-def _pipe_main(rank, world, port, share_q, ret):
+def _pipe_main(rank, world, port, share_q, deferred, ret):
     """The host-buffer pipeline of one rank under split-KV: several steps in flight, each with its own host inputs;
     every rank ends with its row slice of every step's output in host memory."""
     sys.path.insert(0, ROOT)
@@ -189,6 +189,7 @@ def _pipe_main(rank, world, port, share_q, ret):
         t0, t1 = grp.shard_bounds(P)
         kv.load_prefix(cases[0]["kp"][t0:t1].contiguous().to(dev), cases[0]["vp"][t0:t1].contiguous().to(dev), t0)
         pipe = HostPipe(ctx, layer, 1, 3)
+        pipe.set_deferred_launch(deferred)
         hosts = [tuple(c[n].contiguous().pin_memory() for n in ("q", "kc", "vc")) + (torch.zeros_like(c["q"]).pin_memory(),)
                  for c in cases]
         tickets = [pipe.submit_split(kv, P, t0, t1, grp.owns_canvas, grp.p2p, q, k, v, o) for q, k, v, o in hosts]
@@ -214,13 +215,13 @@ def _pipe_main(rank, world, port, share_q, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("share_q,port", [(False, 29771), (True, 29772)])
-def test_host_pipe_split_step(share_q, port):
+@pytest.mark.parametrize("share_q,deferred,port", [(False, False, 29771), (True, False, 29772), (False, True, 29773)])
+def test_host_pipe_split_step(share_q, deferred, port):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs at least 2 GPUs")
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_pipe_main, args=(2, port, share_q, ret), nprocs=2, join=True)
+    mp.spawn(_pipe_main, args=(2, port, share_q, deferred, ret), nprocs=2, join=True)
     assert len(ret) == 2
     for rank in range(2):
         mx, mean = ret[rank]
