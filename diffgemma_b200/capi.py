@@ -43,6 +43,11 @@ _u64 = C.c_uint64
 _pd = C.POINTER(LayerDesc)
 
 
+class TopkCfg(C.Structure):
+    """dg_topk_cfg"""
+    _fields_ = [("k_fixed", C.c_uint32), ("k_div", C.c_uint32), ("k_min", C.c_uint32), ("k_max", C.c_uint32)]
+
+
 class BlockWeights(C.Structure):
     """dg_block_weights of include/dg_attn.h (field for field)."""
     _fields_ = [("input_ln", C.c_void_p), ("w_qkv", C.c_void_p), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
@@ -67,6 +72,7 @@ SIGNATURES = {
     "dg_ctx_set_inputs_stable": (_i32, [_vp, _i32]),
     "dg_ctx_set_pair_mode": (_i32, [_vp, _i32]),
     "dg_ctx_max_active_clusters": (_i32, [_vp, _i32, _u32]),
+    "dg_attn_denoise_topk": (_i32, [_vp, _pd, _vp, _u32, _vp, _vp, _vp, _vp, _vp, C.POINTER(TopkCfg), _vp]),
     "dg_attn_block": (_i32, [_vp, _pd, C.POINTER(BlockWeights), _vp, _u32, _vp, _vp]),
     "dg_kv_create": (_i32, [_vp, _pd, _u64, C.POINTER(_vp)]),
     "dg_kv_create_ring": (_i32, [_vp, _pd, _u32, C.POINTER(_vp)]),

@@ -2241,6 +2241,7 @@ extern "C" int32_t dg_attn_denoise_topk(dg_ctx* c, const dg_layer_desc* d, dg_kv
   TopkParams tp = {};
   tp.scores = c->topk_scores;
   tp.ld = ld;
+  tp.head_rows = uint32_t((rows + 127) / 128 * 128);
   tp.q = c->stage_q;
   tp.k = kv->k;
   tp.v = kv->v;

@@ -247,8 +247,8 @@ struct GemmParams {
 
 // top-k selection + gathered PV over a plane of 16-bit scores (csrc/dg_topk.cu)
 struct TopkParams {
-  const uint16_t* scores;        // bf16 [Hkv][C * G][ld]: row i * G + g of KV head h, key t
-  uint32_t ld;
+  const uint16_t* scores;        // bf16 [Hkv][head_rows][ld]: row i * G + g of KV head h, key t
+  uint32_t ld, head_rows;        // head_rows = C * G rounded up to whole 128-row tiles
   const __nv_bfloat16* q;        // normed + roped Q [C][Hq][D]
   const __nv_bfloat16* k;        // caches [Hkv][cap][D]
   const __nv_bfloat16* v;

@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(tk::THREADS) dg_topk_select_pv_kernel(const To
   const uint32_t kvh = h / p.G, g = h % p.G;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  const uint16_t* srow = p.scores + (size_t(kvh) * p.C * p.G + size_t(i) * p.G + g) * p.ld;
+  const uint16_t* srow = p.scores + (size_t(kvh) * p.head_rows + size_t(i) * p.G + g) * p.ld;
   const MaskParams mk = p.mask;
   const RowVis rv = mask_row(mk, i);
   const uint32_t T = mk.can_hi;

@@ -238,6 +238,16 @@ class CanvasAttention:
               "dg_attention")
         return out
 
+    def denoise_topk(self, kv: KvCache, kv_len: int, q, k, v, qw=None, kw=None, out=None, k_fixed: int = 0,
+                     k_div: int = 128, k_min: int = 64, k_max: int = 512):
+        """Top-k sparse attention of the reference's full layers for one canvas (dg_attn_denoise_topk).
+        q: [C,Hq,D], k, v: [C,Hkv,D] pre-norm bf16 device tensors."""
+        out = torch.empty_like(q) if out is None else out
+        cfg = capi.TopkCfg(k_fixed, k_div, k_min, k_max)
+        check(self.lib.dg_attn_denoise_topk(self.ctx.h, C.byref(self.desc), kv.h, kv_len, _ptr(q), _ptr(k), _ptr(v),
+                                            _ptr(qw), _ptr(kw), C.byref(cfg), _ptr(out)), "dg_attn_denoise_topk")
+        return out
+
     def denoise(self, kvs, kv_lens, q, k, v, qw=None, kw=None, out=None):
         """q: [B,C,Hq,D], k,v: [B,C,Hkv,D] pre-norm bf16 device tensors; kvs: list of KvCache."""
         B = len(kvs)

@@ -279,6 +279,50 @@ def denoise_attention(q, k, v, k_prefix, v_prefix, desc: LayerDesc, kv_len: int,
 
 
 # ----------------------------------------------------------------------------
+# top-k sparse attention (src/shaders/attn/attention_topk/cpu.rs:39-120 of the reference)
+# ----------------------------------------------------------------------------
+def topk_k(n_valid: int, k_fixed: int = 0, k_div: int = 128, k_min: int = 64, k_max: int = 512) -> int:
+    """Keys kept for a row with n_valid visible keys: the kv-adaptive rule of
+    src/shaders/attn/attention_topk/attention_topk.metal:176-185 (k = clamp(n / k_div, k_min, k_max)) or a
+    fixed k when k_div == 0; never more than n_valid."""
+    k_req = int(np.clip(n_valid // k_div, k_min, k_max)) if k_div else max(int(k_fixed), 1)
+    return min(k_req, n_valid)
+
+
+def attention_topk(qn, K, V, attend, desc: LayerDesc, k_fixed: int = 0, k_div: int = 128, k_min: int = 64,
+                   k_max: int = 512):
+    """Per (row, head): scores over the visible keys, the top k by (score descending, index ascending)
+    (cpu.rs:84-95), softmax renormalised over those (cpu.rs:96-106), O = sum p_j V[idx_j] (cpu.rs:107-115).
+    qn: [C,Hq,D] normed+roped queries, K/V: [T,Hkv,D] as stored, attend: [C,T] bool."""
+    C, Hq, D = qn.shape
+    G = Hq // desc.n_kv_heads
+    out = np.zeros((C, Hq, D), np.float32)
+    scale = np.float32(desc.softmax_scale)
+    for h in range(Hq):
+        kvh = h // G
+        s_all = (qn[:, h, :].astype(np.float32) @ K[:, kvh, :].astype(np.float32).T).astype(np.float32)   # [C, T]
+        for i in range(C):
+            vis = np.nonzero(attend[i])[0]
+            k = topk_k(len(vis), k_fixed, k_div, k_min, k_max)
+            if k == 0:
+                continue
+            sc = s_all[i, vis]
+            order = np.argsort(-sc, kind="stable")[:k]          # equal scores: lower index first
+            idx, s = vis[order], sc[order] * scale
+            p = np.exp(s - s.max()).astype(np.float32)
+            out[i, h] = (p[:, None] * V[idx, kvh, :].astype(np.float32)).sum(axis=0) / p.sum()
+    return out
+
+
+def denoise_attention_topk(q, k, v, k_prefix, v_prefix, desc: LayerDesc, kv_len: int, qw=None, kw=None, **kcfg):
+    """The hot path with the top-k stage 2: qk_rope_kv, append, top-k attention."""
+    qn, kn, vn = qk_rope_kv(q, k, v, qw, kw, desc, kv_len)
+    K = np.concatenate([k_prefix[:kv_len], kn], axis=0)
+    V = np.concatenate([v_prefix[:kv_len], vn], axis=0)
+    return attention_topk(qn, K, V, visibility(desc, kv_len), desc, **kcfg)
+
+
+# ----------------------------------------------------------------------------
 # the neighbours of the attention stage: input norm, stacked Q|K|V projection, output projection,
 # post-attention norm + residual (src/metal/step_kernel/enc.rs:852-911, 1560-1629 of the reference)
 # ----------------------------------------------------------------------------
