@@ -710,6 +710,67 @@ def measure_attn_block(cfg_idx, args, timed_of, peaks, steps=200, v_from_k=False
         ctx.close()
 
 
+def measure_topk(cfg_idx, args, timed_of, peaks, steps=50):
+    """The reference's top-k sparse attention (dg_attn_denoise_topk, kv-adaptive k = clamp(T / 128, 64, 512)) on the
+    geometry of a configuration, beside the exact dense step on the same caches; parity of the first canvas rows
+    against the CPU restatement of the reference's top-k oracle."""
+    import numpy as np
+    import torch
+    from diffgemma_b200 import synthetic
+    from diffgemma_b200.step_attn import CanvasAttention, Context, KvCache
+    from oracle import attn_oracle as ao
+    log(f"extra block: top-k sparse attention, cfg {cfg_idx}")
+    cfg = _cfg(cfg_idx)
+    lay, P = cfg.layer, cfg.prefix
+    ctx = Context(0)
+    ctx.set_inputs_stable(True)
+    dev = torch.device("cuda", 0)
+    timed = timed_of(ctx)
+    try:
+        q, kc, vc, kp, vp = synthetic.draw(lay, P, synthetic.config_seed(cfg_idx))
+        kvs = []
+        for j in range(2):
+            kv = KvCache(ctx, lay, P + lay.canvas)
+            if j == 0:
+                kv.load_prefix(kp.to(dev), vp.to(dev), 0)
+            else:
+                gd = torch.Generator(device=dev).manual_seed(200 + j)
+                kv.load_prefix(torch.randn(P, lay.n_kv_heads, lay.head_dim, generator=gd, device=dev).to(torch.bfloat16),
+                               torch.randn(P, lay.n_kv_heads, lay.head_dim, generator=gd, device=dev).to(torch.bfloat16), 0)
+            kvs.append(kv)
+        att = CanvasAttention(ctx, lay)
+        qd, kd, vd = q.to(dev), kc.to(dev), vc.to(dev)
+        out = torch.empty_like(qd)
+        att.denoise_topk(kvs[0], P, qd, kd, vd, out=out)
+        ctx.synchronize()
+        R = 2
+        f = lambda t: t.to(torch.float32).numpy()
+        d = ao.LayerDesc(lay.n_q_heads, lay.n_kv_heads, lay.head_dim, lay.canvas, lay.rotary_dim, lay.rope_theta, lay.rms_eps,
+                         lay.softmax_scale, lay.window, lay.mask_mode, lay.v_norm, lay.rope_pairing)
+        qn, kn, vn = ao.qk_rope_kv(f(q), f(kc), f(vc), None, None, d, P)
+        K = np.concatenate([f(kp), kn], axis=0)
+        V = np.concatenate([f(vp), vn], axis=0)
+        ref = ao.attention_topk(qn[:R], K, V, ao.visibility(d, P)[:R], d)
+        err = np.abs(f(out.cpu())[:R] - ref)
+        par = {"max_abs": float(err.max()), "mean_abs": float(err.mean()), "rows": f"{R} canvas rows x {lay.n_q_heads} heads",
+               "vs": "CPU restatement of the reference's top-k oracle", "gate": {"max_abs": MAX_ABS_GATE, "mean_abs": MEAN_ABS_GATE},
+               "ok": bool(err.max() <= MAX_ABS_GATE and err.mean() <= MEAN_ABS_GATE)}
+        ms_topk = timed(lambda i: att.denoise_topk(kvs[i % 2], P, qd, kd, vd, out=out), steps, 3)
+        launches = ctx.last_launch_count
+        q4, k4, v4 = qd[None].contiguous(), kd[None].contiguous(), vd[None].contiguous()
+        o4 = torch.empty_like(q4)
+        ms_dense = timed(lambda i: att.denoise([kvs[i % 2]], [P], q4, k4, v4, out=o4), steps, 3)
+        st = ctx.device_status()
+        assert st[0] == 0, f"device status {st}"
+        T = P + lay.canvas
+        rows = lay.canvas * lay.n_q_heads
+        return {"workload": f"{cfg.name}: top-k sparse attention, k = {ao.topk_k(T)} of {T} keys per row", "ms_per_step": ms_topk,
+                "ms_dense_attention": ms_dense, "launches_per_step": launches, "steps": steps,
+                "score_plane_bytes": 2.0 * rows * T, "score_gemm_flops": 2.0 * rows * T * lay.head_dim, "parity": par}
+    finally:
+        ctx.close()
+
+
 def stack_units(n_kv_heads: int, n_canvases: int, world: int, rank: int):
     """KV-head sharding of one layer of the stack over `world` ranks.  The sharded unit is the KV head; where a
     layer has fewer KV heads than there are ranks (the global layers: 2), the (canvas, KV head) pairs are the
@@ -1038,6 +1099,8 @@ def run_ours(args):
             extra["attn_block_cfg1_sliding"] = measure_attn_block(1, args, timed_of, peaks)
             extra["attn_block_cfg2_global"] = measure_attn_block(2, args, timed_of, peaks)
             extra["attn_block_ref_full_layer_hd512"] = measure_attn_block(5, args, timed_of, peaks, steps=100, v_from_k=True)
+            extra["topk_cfg2_global"] = measure_topk(2, args, timed_of, peaks)
+            extra["topk_ref_full_layer_hd512"] = measure_topk(5, args, timed_of, peaks)
 
     if rank == 0:
         value = flops / (ms_dev * 1e-3) / 1e12
@@ -1136,10 +1199,23 @@ def main():
                     help="multi-GPU: merge every step's slice inside that step instead of one step later")
     ap.add_argument("--kernel-form", default="auto", choices=["auto", "pair", "single"],
                     help="tensor-kernel form: CTA pairs, one CTA per query tile, or the library's choice")
+    ap.add_argument("--topk", type=int, default=None, choices=[2, 5],
+                    help="only the top-k sparse attention (dg_attn_denoise_topk) on this configuration's geometry, 1 GPU; "
+                         "prints that block's record, not the benchmark line")
     ap.add_argument("--attn-block", type=int, default=None, choices=[1, 2, 5],
                     help="only the attention block with its neighbours (dg_attn_block) on this configuration's geometry, "
                          "1 GPU; prints that block's record, not the benchmark line")
     args = ap.parse_args()
+    if args.topk is not None:
+        import torch
+        from diffgemma_b200 import build as _build
+        _build.build()
+        dev = torch.device("cuda", 0)
+        blk = measure_topk(args.topk, args, lambda c: _timer(1, dev, c.torch_stream), _peaks(), steps=min(args.steps, 50))
+        print(json.dumps(blk), flush=True)
+        if not blk["parity"]["ok"]:
+            sys.exit("parity gate failed: " + json.dumps(blk["parity"]))
+        return
     if args.attn_block is not None:
         import torch
         from diffgemma_b200 import build as _build

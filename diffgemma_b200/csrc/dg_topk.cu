@@ -50,6 +50,8 @@ __device__ __forceinline__ float dot_row_bf16(const __nv_bfloat16* a, const __nv
 __global__ void __launch_bounds__(tk::THREADS) dg_topk_select_pv_kernel(const TopkParams p) {
   using namespace tk;
   __shared__ uint32_t hist[256];
+  __shared__ uint32_t whist[THREADS / 32][256];   // one histogram per warp, added up into hist
+  __shared__ float o_part[THREADS / 32][512];     // the warps' partial output rows
   __shared__ uint32_t s_idx[K_CAP];      // winners
   __shared__ float s_sc[K_CAP];          // their exact scores, then their probabilities
   __shared__ uint32_t c_idx[CAND_CAP];   // keys that share the threshold value
@@ -66,17 +68,46 @@ __global__ void __launch_bounds__(tk::THREADS) dg_topk_select_pv_kernel(const To
   const MaskParams mk = p.mask;
   const RowVis rv = mask_row(mk, i);
   const uint32_t T = mk.can_hi;
-  auto visible = [&](uint32_t t) { return mask_visible_row(mk, rv, t); };
+  const bool all_vis = mask_range_full(mk, rv, 0u, T);       // every key below T is visible to this row
+  auto visible = [&](uint32_t t) { return all_vis || mask_visible_row(mk, rv, t); };
+  // every visible key of the row, eight per 16-byte load (the row of the plane starts on a 16-byte boundary and is
+  // padded to whole tiles), two loads in flight per thread: f(t, key)
+  const uint4* row4 = reinterpret_cast<const uint4*>(srow);
+  const uint32_t n8 = (T + 7u) / 8u;
+  auto for_keys = [&](auto f) {
+#pragma unroll 2
+    for (uint32_t c = tid; c < n8; c += THREADS) {
+      const uint4 x = row4[c];
+      const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+      for (uint32_t e = 0; e < 8; ++e) {
+        const uint32_t t = c * 8u + e;
+        if (t < T && visible(t)) f(t, bf16_order_key(uint16_t(xs[e >> 1] >> ((e & 1u) * 16u))));
+      }
+    }
+  };
+  auto zero_whist = [&]() {
+    for (uint32_t b = tid; b < (THREADS / 32) * 256; b += THREADS) (&whist[0][0])[b] = 0u;
+  };
+  auto fold_whist = [&]() {
+    for (uint32_t b = tid; b < 256; b += THREADS) {
+      uint32_t c = 0;
+#pragma unroll
+      for (uint32_t w = 0; w < THREADS / 32; ++w) c += whist[w][b];
+      hist[b] = c;
+    }
+  };
 
   // ---- visible keys and k
   uint32_t nv = 0;
-  for (uint32_t t = tid; t < T; t += THREADS) nv += visible(t) ? 1u : 0u;
+  if (!all_vis)
+    for (uint32_t t = tid; t < T; t += THREADS) nv += visible(t) ? 1u : 0u;
   if (tid < 8) sh[tid] = 0u;
-  for (uint32_t b = tid; b < 256; b += THREADS) hist[b] = 0u;
+  zero_whist();
   __syncthreads();
-  atomicAdd(&sh[5], nv);
+  if (!all_vis) atomicAdd(&sh[5], nv);
   __syncthreads();
-  const uint32_t n_valid = sh[5];
+  const uint32_t n_valid = all_vis ? T : sh[5];
   uint32_t k_req = p.k_fixed;
   if (p.k_div != 0u) {
     k_req = n_valid / p.k_div;
@@ -92,8 +123,10 @@ __global__ void __launch_bounds__(tk::THREADS) dg_topk_select_pv_kernel(const To
   }
 
   // ---- level 1: top byte of the key
-  for (uint32_t t = tid; t < T; t += THREADS)
-    if (visible(t)) atomicAdd(&hist[bf16_order_key(srow[t]) >> 8], 1u);
+  // (one histogram per warp: scores cluster on a few exponent values, a single one would serialise on a few bins)
+  for_keys([&](uint32_t, uint32_t key) { atomicAdd(&whist[warp][key >> 8], 1u); });
+  __syncthreads();
+  fold_whist();
   __syncthreads();
   if (tid == 0) {
     uint32_t cum = 0, b1 = 0;
@@ -111,14 +144,14 @@ __global__ void __launch_bounds__(tk::THREADS) dg_topk_select_pv_kernel(const To
   const uint32_t bin1 = sh[2];
   uint32_t above = sh[4];
   __syncthreads();
-  for (uint32_t b = tid; b < 256; b += THREADS) hist[b] = 0u;
+  zero_whist();
   __syncthreads();
   // ---- level 2: low byte inside that bin
-  for (uint32_t t = tid; t < T; t += THREADS) {
-    if (!visible(t)) continue;
-    const uint32_t key = bf16_order_key(srow[t]);
-    if ((key >> 8) == bin1) atomicAdd(&hist[key & 0xffu], 1u);
-  }
+  for_keys([&](uint32_t, uint32_t key) {
+    if ((key >> 8) == bin1) atomicAdd(&whist[warp][key & 0xffu], 1u);
+  });
+  __syncthreads();
+  fold_whist();
   __syncthreads();
   if (tid == 0) {
     uint32_t cum = above, b2 = 0;
@@ -146,12 +179,10 @@ __global__ void __launch_bounds__(tk::THREADS) dg_topk_select_pv_kernel(const To
   uint32_t my_cand = 0;
   const uint32_t per = (T + THREADS - 1) / THREADS;          // contiguous index ranges, for the index-ordered path
   if (ranked) {
-    for (uint32_t t = tid; t < T; t += THREADS) {
-      if (!visible(t)) continue;
-      const uint32_t key = bf16_order_key(srow[t]);
+    for_keys([&](uint32_t t, uint32_t key) {
       if (key > thr) s_idx[atomicAdd(&sh[0], 1u)] = t;
       else if (key == thr) c_idx[atomicAdd(&sh[1], 1u)] = t;
-    }
+    });
   } else {
     const uint32_t t_lo = tid * per, t_hi = (t_lo + per < T) ? t_lo + per : T;
     for (uint32_t t = t_lo; t < t_hi; ++t) {
@@ -219,6 +250,7 @@ __global__ void __launch_bounds__(tk::THREADS) dg_topk_select_pv_kernel(const To
   __syncthreads();
 
   // ---- exact scores of the winners, softmax over them
+#pragma unroll 2
   for (uint32_t j = warp; j < k; j += THREADS / 32) {
     const float s = dot_row_bf16(qrow, kbase + size_t(s_idx[j]) * p.D, p.D, lane);
     if (lane == 0) s_sc[j] = s * p.scale_log2;
@@ -249,14 +281,42 @@ __global__ void __launch_bounds__(tk::THREADS) dg_topk_select_pv_kernel(const To
   for (int w = 0; w < 8; ++w) l += red[w];
   const float inv_l = l > 0.f ? 1.0f / l : 0.f;
 
-  // ---- O = sum_j p_j V[idx_j]: a thread owns two adjacent value columns
+  // ---- O = sum_j p_j V[idx_j]: a warp takes every eighth kept key, its lanes cover the value row with 16-byte
+  // loads (several rows in flight), and the eight partial rows meet in shared memory
+  __syncthreads();
+  const uint32_t n_chunk = p.D / 256;            // 16-byte chunks per lane: 1 at head_dim 256, 2 at 512
+  float acc[16];
+#pragma unroll
+  for (int e = 0; e < 16; ++e) acc[e] = 0.f;
+#pragma unroll 4
+  for (uint32_t j = warp; j < k; j += THREADS / 32) {
+    const uint4* vr = reinterpret_cast<const uint4*>(vbase + size_t(s_idx[j]) * p.D);
+    const float pj = s_sc[j];
+#pragma unroll
+    for (uint32_t c = 0; c < 2; ++c) {
+      if (c >= n_chunk) break;
+      const uint4 x = vr[c * 32u + lane];
+      const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        acc[c * 8 + 2 * e] = fmaf(pj, __uint_as_float(xs[e] << 16), acc[c * 8 + 2 * e]);
+        acc[c * 8 + 2 * e + 1] = fmaf(pj, __uint_as_float(xs[e] & 0xffff0000u), acc[c * 8 + 2 * e + 1]);
+      }
+    }
+  }
+#pragma unroll
+  for (uint32_t c = 0; c < 2; ++c) {
+    if (c >= n_chunk) break;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o_part[warp][(c * 32u + lane) * 8u + e] = acc[c * 8 + e];
+  }
+  __syncthreads();
   for (uint32_t d2 = tid; d2 < p.D / 2; d2 += THREADS) {
     float a0 = 0.f, a1 = 0.f;
-    for (uint32_t j = 0; j < k; ++j) {
-      const uint32_t w = reinterpret_cast<const uint32_t*>(vbase + size_t(s_idx[j]) * p.D)[d2];
-      const float pj = s_sc[j];
-      a0 = fmaf(pj, __uint_as_float(w << 16), a0);
-      a1 = fmaf(pj, __uint_as_float(w & 0xffff0000u), a1);
+#pragma unroll
+    for (uint32_t w = 0; w < THREADS / 32; ++w) {      // fixed order: same bits every run
+      a0 += o_part[w][2 * d2];
+      a1 += o_part[w][2 * d2 + 1];
     }
     reinterpret_cast<uint32_t*>(orow)[d2] = pack_bf16x2(a0 * inv_l, a1 * inv_l);
   }
