@@ -27,15 +27,20 @@ namespace gm {
 constexpr uint32_t GM = 128, BK = 64;   // rows of a tile, contraction elements per stage
 constexpr uint32_t THREADS = 192;
 constexpr uint32_t A_STAGE = GM * BK * 2;   // 16 KB
-__host__ __device__ constexpr uint32_t stages(uint32_t bn) { return bn >= 128 ? 6u : 8u; }
-__host__ __device__ constexpr uint32_t smem_bytes(uint32_t bn) { return stages(bn) * (A_STAGE + bn * BK * 2) + 256 + 1024; }
+// stages of the ring: deep for the projections (44-128 contraction blocks per CTA); two for the score GEMM of the
+// top-k path, whose contraction is four or eight blocks, so that three CTAs share an SM and one's epilogue overlaps
+// another's loads
+__host__ __device__ constexpr uint32_t stages(uint32_t bn, bool shallow) { return shallow ? 2u : bn >= 128 ? 6u : 8u; }
+__host__ __device__ constexpr uint32_t smem_bytes(uint32_t bn, bool shallow) {
+  return stages(bn, shallow) * (A_STAGE + bn * BK * 2) + 256 + 1024;
+}
 }  // namespace gm
 
-template <uint32_t BN>
+template <uint32_t BN, bool SHALLOW>
 __global__ void __launch_bounds__(gm::THREADS, 1)
 dg_gemm_sm100_kernel(const GemmParams g, const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w) {
   using namespace gm;
-  constexpr uint32_t ST = stages(BN), B_STAGE = BN * BK * 2, STAGE = A_STAGE + B_STAGE;
+  constexpr uint32_t ST = stages(BN, SHALLOW), B_STAGE = BN * BK * 2, STAGE = A_STAGE + B_STAGE;
   enum : uint32_t { B_FULL = 0, B_EMPTY = ST, B_ACC = 2 * ST, B_COUNT = 2 * ST + 1 };
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -298,9 +303,14 @@ __global__ void __launch_bounds__(256) dg_norm_residual_kernel(const float* part
 }
 
 cudaError_t sm100_gemm_configure() {
-  cudaError_t e = cudaFuncSetAttribute(dg_gemm_sm100_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gm::smem_bytes(128)));
+  cudaError_t e = cudaFuncSetAttribute(dg_gemm_sm100_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       int(gm::smem_bytes(128, false)));
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(dg_gemm_sm100_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gm::smem_bytes(64)));
+    e = cudaFuncSetAttribute(dg_gemm_sm100_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gm::smem_bytes(64, false)));
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(dg_gemm_sm100_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gm::smem_bytes(128, true)));
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(dg_gemm_sm100_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gm::smem_bytes(64, true)));
   return e;
 }
 
@@ -322,9 +332,14 @@ cudaError_t launch_gemm_sm100(const GemmParams& g, const CUtensorMap& tm_a, cons
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[1];
   const dim3 grid(g.N / bn, (g.M + gm::GM - 1) / gm::GM, g.part != nullptr ? g.k_slices : 1u);
-  pdl_cfg(cfg, attr, grid, dim3(gm::THREADS), gm::smem_bytes(bn), st);
-  if (bn == 128) return cudaLaunchKernelEx(&cfg, dg_gemm_sm100_kernel<128>, g, tm_a, tm_w);
-  return cudaLaunchKernelEx(&cfg, dg_gemm_sm100_kernel<64>, g, tm_a, tm_w);
+  const bool shallow = g.K / gm::BK <= 8;
+  pdl_cfg(cfg, attr, grid, dim3(gm::THREADS), gm::smem_bytes(bn, shallow), st);
+  if (shallow) {
+    if (bn == 128) return cudaLaunchKernelEx(&cfg, dg_gemm_sm100_kernel<128, true>, g, tm_a, tm_w);
+    return cudaLaunchKernelEx(&cfg, dg_gemm_sm100_kernel<64, true>, g, tm_a, tm_w);
+  }
+  if (bn == 128) return cudaLaunchKernelEx(&cfg, dg_gemm_sm100_kernel<128, false>, g, tm_a, tm_w);
+  return cudaLaunchKernelEx(&cfg, dg_gemm_sm100_kernel<64, false>, g, tm_a, tm_w);
 }
 
 cudaError_t launch_rmsnorm_rows(const void* x, const void* w, void* y, uint32_t rows, uint32_t dim, cudaStream_t st) {

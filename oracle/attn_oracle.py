@@ -290,13 +290,17 @@ def topk_k(n_valid: int, k_fixed: int = 0, k_div: int = 128, k_min: int = 64, k_
 
 
 def attention_topk(qn, K, V, attend, desc: LayerDesc, k_fixed: int = 0, k_div: int = 128, k_min: int = 64,
-                   k_max: int = 512):
+                   k_max: int = 512, return_gap: bool = False):
     """Per (row, head): scores over the visible keys, the top k by (score descending, index ascending)
     (cpu.rs:84-95), softmax renormalised over those (cpu.rs:96-106), O = sum p_j V[idx_j] (cpu.rs:107-115).
-    qn: [C,Hq,D] normed+roped queries, K/V: [T,Hkv,D] as stored, attend: [C,T] bool."""
+    qn: [C,Hq,D] normed+roped queries, K/V: [T,Hkv,D] as stored, attend: [C,T] bool.
+    With return_gap also [C,Hq]: how far the last kept score lies above the first dropped one, relative to its
+    magnitude (inf when every visible key is kept) - a row whose gap is within fp32 summation noise has no unique
+    top-k set, and an implementation that sums the dot products in another order may keep the other key."""
     C, Hq, D = qn.shape
     G = Hq // desc.n_kv_heads
     out = np.zeros((C, Hq, D), np.float32)
+    gap = np.full((C, Hq), np.inf, np.float32)
     scale = np.float32(desc.softmax_scale)
     for h in range(Hq):
         kvh = h // G
@@ -307,11 +311,29 @@ def attention_topk(qn, K, V, attend, desc: LayerDesc, k_fixed: int = 0, k_div: i
             if k == 0:
                 continue
             sc = s_all[i, vis]
-            order = np.argsort(-sc, kind="stable")[:k]          # equal scores: lower index first
+            full = np.argsort(-sc, kind="stable")               # equal scores: lower index first
+            order = full[:k]
+            if k < len(vis):
+                gap[i, h] = (sc[full[k - 1]] - sc[full[k]]) / max(abs(float(sc[full[k - 1]])), 1e-30)
             idx, s = vis[order], sc[order] * scale
             p = np.exp(s - s.max()).astype(np.float32)
             out[i, h] = (p[:, None] * V[idx, kvh, :].astype(np.float32)).sum(axis=0) / p.sum()
-    return out
+    return (out, gap) if return_gap else out
+
+
+TOPK_TIE_GAP = 5e-6      # relative score gap below which two fp32 summation orders may rank two keys differently
+
+
+def topk_errors(got, ref, gap):
+    """(max-abs over the (row, head) pairs whose kept set is unique, mean-abs over everything, share of pairs
+    whose kept set is not unique).  A pair counts as not unique when its last kept and first dropped scores lie
+    within TOPK_TIE_GAP of each other: either key may then be kept, and the outputs differ by that key's weight
+    times the difference of two value rows (the reference's own GPU-vs-CPU test says the same of its kernels:
+    src/shaders/attn/attention_topk/mod.rs:495-510)."""
+    err = np.abs(np.asarray(got, np.float32) - ref)
+    unique = gap >= TOPK_TIE_GAP
+    mx = float(err[unique].max()) if unique.any() else 0.0
+    return mx, float(err.mean()), float(1.0 - unique.mean())
 
 
 def denoise_attention_topk(q, k, v, k_prefix, v_prefix, desc: LayerDesc, kv_len: int, qw=None, kw=None, **kcfg):

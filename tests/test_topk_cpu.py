@@ -47,3 +47,15 @@ def test_ties_go_to_the_lower_index():
 def test_adaptive_k_rule():
     assert ao.topk_k(33024) == 258 and ao.topk_k(100256) == 512 and ao.topk_k(2000) == 64 and ao.topk_k(40) == 40
     assert ao.topk_k(500, k_fixed=64, k_div=0) == 64 and ao.topk_k(10, k_fixed=64, k_div=0) == 10
+
+
+# a row whose last kept and first dropped scores coincide has no unique kept set: the comparison helper says so
+def test_near_tie_rows_are_reported():
+    d, q, k, v, kp, vp, P = _case(seed=8)
+    qn, kn, vn = ao.qk_rope_kv(q, k, v, None, None, d, P)
+    K, V = np.concatenate([kp, kn]), np.concatenate([vp, vn])
+    K[3] = K[7]                                         # two identical keys: identical scores
+    out, gap = ao.attention_topk(qn, K, V, ao.visibility(d, P), d, k_fixed=5, k_div=0, return_gap=True)
+    assert gap.shape == (d.canvas, d.n_q_heads) and (gap >= 0).all()
+    mx, mean, ties = ao.topk_errors(out, out, gap)
+    assert mx == 0.0 and mean == 0.0 and 0.0 <= ties <= 1.0

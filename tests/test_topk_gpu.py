@@ -46,8 +46,13 @@ CASES = [
 def test_topk_matches_oracle(ctx, name, lk, P, kcfg):
     layer = AttnLayer(**lk)
     case = util.make_case(layer, P, seed=P, weights=True)
-    got, ref = _run(ctx, case, **kcfg), _oracle(case, **kcfg)
-    util.assert_close(got, ref, f"top-k {name}", stress=(layer.softmax_scale == 1.0))
+    got = _run(ctx, case, **kcfg)
+    ref, gap = _oracle(case, return_gap=True, **kcfg)
+    # rows whose k-th and (k+1)-th scores coincide to fp32 summation noise have no unique kept set: they are left
+    # out of the max-abs gate (there may only be a handful) and stay inside the mean-abs gate
+    mx, mean, ties = ao.topk_errors(got, ref, gap)
+    tol = util.max_abs_tol(ref) if layer.softmax_scale == 1.0 else util.MAX_ABS_TOL
+    assert mx <= tol and mean <= util.MEAN_ABS_TOL and ties <= 0.02, (name, mx, mean, ties)
     assert ctx.device_status()[0] == 0
     # same bits on a second run: the kept keys are summed in index order
     assert np.array_equal(got, _run(ctx, case, **kcfg))
