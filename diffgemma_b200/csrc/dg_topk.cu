@@ -79,10 +79,17 @@ __global__ void __launch_bounds__(tk::THREADS) dg_topk_select_pv_kernel(const To
     for (uint32_t c = tid; c < n8; c += THREADS) {
       const uint4 x = row4[c];
       const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
+      const uint32_t base = c * 8u;
+      const bool whole = all_vis && base + 8u <= T;      // no key of the chunk needs a bounds or mask test
 #pragma unroll
-      for (uint32_t e = 0; e < 8; ++e) {
-        const uint32_t t = c * 8u + e;
-        if (t < T && visible(t)) f(t, bf16_order_key(uint16_t(xs[e >> 1] >> ((e & 1u) * 16u))));
+      for (uint32_t w = 0; w < 4; ++w) {
+        // both order-preserving keys of the word at once: a negative value is complemented, a positive one gets
+        // its sign bit set
+        const uint32_t sg = (xs[w] >> 15) & 0x00010001u;
+        const uint32_t k2 = xs[w] ^ ((sg * 0xffffu) | 0x80008000u);
+        const uint32_t t = base + 2u * w;
+        if (whole || (t < T && visible(t))) f(t, k2 & 0xffffu);
+        if (whole || (t + 1u < T && visible(t + 1u))) f(t + 1u, k2 >> 16);
       }
     }
   };
