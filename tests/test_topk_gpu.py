@@ -39,6 +39,11 @@ CASES = [
                                softmax_scale=1.0, v_norm=1, rope_pairing=capi.ROPE_PROPORTIONAL), 2000, {}),
     ("Hkv 8, ragged canvas, ragged keys", dict(n_q_heads=16, n_kv_heads=8, head_dim=256, canvas=100, rope_theta=1e4), 1111,
      dict(k_div=16, k_min=8, k_max=100)),
+    # masked rows: only the window's keys are candidates, and k follows each row's own visible count
+    ("sliding window, per row", dict(n_q_heads=16, n_kv_heads=8, head_dim=256, canvas=128, rope_theta=1e4, window=512,
+                                     mask_mode=capi.MASK_WINDOW_PER_ROW), 2000, dict(k_div=8, k_min=16, k_max=128)),
+    ("causal block", dict(n_q_heads=8, n_kv_heads=2, head_dim=256, canvas=64, rope_theta=1e6, mask_mode=capi.MASK_CAUSAL), 500,
+     dict(k_fixed=48, k_div=0)),
 ]
 
 
