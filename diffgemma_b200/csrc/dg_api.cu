@@ -2110,7 +2110,10 @@ extern "C" int32_t dg_attn_block(dg_ctx* c, const dg_layer_desc* d, const dg_blo
     return fail(DG_ERR_UNSUPPORTED, "dg_attn_block: one context serves one (hidden, n_q_heads * head_dim) geometry");
   const CUtensorMap *tm_wqkv = nullptr, *tm_wo = nullptr;
   if (c->blk_wmaps.size() >= 4096) c->blk_wmaps.clear();   // before the look-ups of this call, never between them
-  r = weight_map(c, w->w_qkv, n_qkv, H, 128, &tm_wqkv);
+  // Two row tiles (129..256 canvas rows) run as CTA pairs: each CTA stages half of every 128-column weight tile,
+  // so the weight map then has 64-row boxes.
+  const bool gemm_pair = c->pair_mode != 0 && C > 128 && C <= 256;
+  r = weight_map(c, w->w_qkv, n_qkv, H, gemm_pair ? 64 : 128, &tm_wqkv);
   // output projection: 128 output columns per tile where hidden allows it, and as many slices of the contraction
   // as bring the grid to about one CTA per SM (hidden 2816, 256 rows: 22 x 2 tiles x 3 slices = 132 CTAs)
   const uint32_t bn_o = H % 128 == 0 ? 128u : 64u;
@@ -2118,7 +2121,8 @@ extern "C" int32_t dg_attn_block(dg_ctx* c, const dg_layer_desc* d, const dg_blo
   uint32_t slices = (c->num_sms > 0 ? uint32_t(c->num_sms) : 148u) / tiles_o;
   slices = slices < 1 ? 1 : slices > kBlockMaxSlices ? kBlockMaxSlices : slices;
   if (slices > nq / 64) slices = nq / 64;
-  if (r == DG_OK) r = weight_map(c, w->w_o, H, nq, bn_o, &tm_wo);
+  const bool pair_o = gemm_pair && bn_o == 128;
+  if (r == DG_OK) r = weight_map(c, w->w_o, H, nq, pair_o ? 64 : bn_o, &tm_wo);
   if (r != DG_OK) return r;
   cudaStream_t st = launch_stream(c);
   uint32_t launches = 0;
@@ -2136,7 +2140,7 @@ extern "C" int32_t dg_attn_block(dg_ctx* c, const dg_layer_desc* d, const dg_blo
   g.seg[2] = GemmSeg{c->blk_v, nq + nk, nk};
   g.rowsq = nullptr;
   g.status = c->d_status;
-  e = launch_gemm_sm100(g, c->blk_tm_xn, *tm_wqkv, 128, st);
+  e = gemm_pair ? launch_gemm_sm100_pair(g, c->blk_tm_xn, *tm_wqkv, st) : launch_gemm_sm100(g, c->blk_tm_xn, *tm_wqkv, 128, st);
   if (e != cudaSuccess) return fail_cuda(e, "launch_gemm_sm100 (qkv)");
   launches += 2;
   // 3. per-head norm + RoPE + cache write + attention.  Q comes from the kernel queued just ahead, so the
@@ -2158,7 +2162,7 @@ extern "C" int32_t dg_attn_block(dg_ctx* c, const dg_layer_desc* d, const dg_blo
   go.part = c->blk_part;
   go.k_slices = slices;
   go.status = c->d_status;
-  e = launch_gemm_sm100(go, c->blk_tm_o, *tm_wo, bn_o, st);
+  e = pair_o ? launch_gemm_sm100_pair(go, c->blk_tm_o, *tm_wo, st) : launch_gemm_sm100(go, c->blk_tm_o, *tm_wo, bn_o, st);
   if (e != cudaSuccess) return fail_cuda(e, "launch_gemm_sm100 (o_proj)");
   // 5. planes added and stored as bf16, post-attention norm, residual
   e = launch_norm_residual(c->blk_part, slices, w->post_attn_ln, hidden_in, stream_out, C, H, st);

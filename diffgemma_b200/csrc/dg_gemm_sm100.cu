@@ -34,13 +34,21 @@ __host__ __device__ constexpr uint32_t stages(uint32_t bn, bool shallow) { retur
 __host__ __device__ constexpr uint32_t smem_bytes(uint32_t bn, bool shallow) {
   return stages(bn, shallow) * (A_STAGE + bn * BK * 2) + 256 + 1024;
 }
+// pair form: every CTA stages its own 128 rows of A and HALF of the W tile
+constexpr uint32_t PAIR_STAGES = 8;
+__host__ __device__ constexpr uint32_t smem_bytes_pair(uint32_t bn) { return PAIR_STAGES * (A_STAGE + bn / 2 * BK * 2) + 256 + 1024; }
 }  // namespace gm
 
-template <uint32_t BN, bool SHALLOW>
+// PAIR: the two row tiles of a 256-row problem form a cta_group::2 pair (cluster (2, 1, 1)): one lane of the leader's
+// MMA warp issues M = 256 MMAs over both CTAs, each CTA supplies its own 128 rows of A and half of the N extent of W
+// (tm_w then has boxes {64, BN / 2}), so a weight tile is staged once per pair instead of once per CTA: 24 KB instead
+// of 32 KB cross L2 -> SM per CTA and contraction block.
+template <uint32_t BN, bool SHALLOW, bool PAIR>
 __global__ void __launch_bounds__(gm::THREADS, 1)
 dg_gemm_sm100_kernel(const GemmParams g, const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w) {
   using namespace gm;
-  constexpr uint32_t ST = stages(BN, SHALLOW), B_STAGE = BN * BK * 2, STAGE = A_STAGE + B_STAGE;
+  constexpr uint32_t ST = PAIR ? PAIR_STAGES : stages(BN, SHALLOW), B_STAGE = (PAIR ? BN / 2 : BN) * BK * 2,
+                     STAGE = A_STAGE + B_STAGE;
   enum : uint32_t { B_FULL = 0, B_EMPTY = ST, B_ACC = 2 * ST, B_COUNT = 2 * ST + 1 };
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -48,7 +56,13 @@ dg_gemm_sm100_kernel(const GemmParams g, const __grid_constant__ CUtensorMap tm_
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t bar_base = smem_base + ST * STAGE;
   volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + ST * STAGE + B_COUNT * 8);
-  const uint32_t n0 = blockIdx.x * BN, m0 = blockIdx.y * GM;
+  // pair form: blockIdx.x is the row tile (= the rank inside the cluster of (2, 1, 1)), blockIdx.y the column tile
+  const uint32_t n_tile = PAIR ? blockIdx.y : blockIdx.x, n_tiles = PAIR ? gridDim.y : gridDim.x;
+  const uint32_t n0 = n_tile * BN, m0 = (PAIR ? blockIdx.x : blockIdx.y) * GM;
+  const uint32_t xi = PAIR ? cluster_ctarank() : 0u;       // position inside the pair = the row tile
+  const bool is_leader = xi == 0u;
+  auto lead_bar = [&](uint32_t idx) { return dsmem_addr(bar_addr(bar_base, idx), 0u); };
+  auto pair_bar = [&](uint32_t idx) { return dsmem_addr(bar_addr(bar_base, idx), 1u); };
   // split-K: slice blockIdx.z of the contraction; its fp32 partial tile goes to plane blockIdx.z of g.part
   const uint32_t kb_all = g.K / BK;
   const uint32_t kb0 = uint32_t((uint64_t(blockIdx.z) * kb_all) / gridDim.z);
@@ -64,8 +78,13 @@ dg_gemm_sm100_kernel(const GemmParams g, const __grid_constant__ CUtensorMap tm_
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(const_cast<uint32_t*>(&ctl[0])), BN < 32 ? 32 : BN);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(&ctl[0])), BN);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(const_cast<uint32_t*>(&ctl[0])), BN < 32 ? 32 : BN);
+      tmem_relinquish();
+    }
   }
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tm_a);
@@ -73,6 +92,7 @@ dg_gemm_sm100_kernel(const GemmParams g, const __grid_constant__ CUtensorMap tm_
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();      // the other CTA's barriers exist before anything of ours can signal them
   tc_fence_after();
   const uint32_t tmem = ctl[0];
   volatile uint32_t* abort_flag = &ctl[1];
@@ -85,6 +105,15 @@ dg_gemm_sm100_kernel(const GemmParams g, const __grid_constant__ CUtensorMap tm_
       for (uint32_t kb = 0; kb < n_kb; ++kb) {
         const uint32_t s = kb % ST, use = kb / ST;
         if (use > 0 && !mbar_wait(bar_addr(bar_base, B_EMPTY + s), (use - 1u) & 1u, abort_flag)) break;
+        if (PAIR) {
+          // both CTAs' bytes are counted on the leader's barrier
+          if (is_leader) mbar_expect_tx(bar_addr(bar_base, B_FULL + s), 2 * STAGE);
+          const uint32_t full = lead_bar(B_FULL + s);
+          tma_load_3d_pair(smem_base + s * STAGE, &tm_a, full, int32_t((kb0 + kb) * BK), int32_t(m0), 0);
+          tma_load_3d_pair(smem_base + s * STAGE + A_STAGE, &tm_w, full, int32_t((kb0 + kb) * BK), int32_t(n0 + xi * (BN / 2)),
+                           int32_t(g.w_z));
+          continue;
+        }
         const uint32_t full = bar_addr(bar_base, B_FULL + s);
         mbar_expect_tx(full, STAGE);
         if (g.a_inner == 0u) tma_load_3d(smem_base + s * STAGE, &tm_a, full, int32_t((kb0 + kb) * BK), int32_t(m0), 0);
@@ -94,10 +123,10 @@ dg_gemm_sm100_kernel(const GemmParams g, const __grid_constant__ CUtensorMap tm_
     }
   } else if (warp == 1) {
     // the whole warp waits, one elected lane issues
-    constexpr uint32_t IDESC = umma_idesc_bf16(GM, BN, 0, 0);
+    constexpr uint32_t IDESC = umma_idesc_bf16(PAIR ? 2 * GM : GM, BN, 0, 0);
     constexpr uint32_t HI = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024, version 1, 128-byte swizzle
     auto mkdesc = [](uint32_t lo, uint32_t hi) { return (uint64_t(hi) << 32) | uint64_t(lo); };
-    for (uint32_t kb = 0; kb < n_kb; ++kb) {
+    for (uint32_t kb = 0; kb < n_kb && (!PAIR || is_leader); ++kb) {
       const uint32_t s = kb % ST, use = kb / ST;
       if (!__all_sync(0xffffffffu, mbar_wait(bar_addr(bar_base, B_FULL + s), use & 1u, abort_flag))) break;
       tc_fence_after();
@@ -105,10 +134,22 @@ dg_gemm_sm100_kernel(const GemmParams g, const __grid_constant__ CUtensorMap tm_
         const uint32_t a_lo = (((smem_base + s * STAGE) >> 4) & 0x3FFFu) | ((16u >> 4) << 16);
         const uint32_t b_lo = (((smem_base + s * STAGE + A_STAGE) >> 4) & 0x3FFFu) | ((16u >> 4) << 16);
 #pragma unroll
-        for (uint32_t kk = 0; kk < BK / 16; ++kk)
-          umma_ss(tmem, mkdesc(a_lo + kk * 2u, HI), mkdesc(b_lo + kk * 2u, HI), IDESC, (kb | kk) != 0u);
-        umma_commit(bar_addr(bar_base, B_EMPTY + s));
-        if (kb + 1 == n_kb) umma_commit(bar_addr(bar_base, B_ACC));
+        for (uint32_t kk = 0; kk < BK / 16; ++kk) {
+          if (PAIR) umma_ss_pair(tmem, mkdesc(a_lo + kk * 2u, HI), mkdesc(b_lo + kk * 2u, HI), IDESC, (kb | kk) != 0u);
+          else umma_ss(tmem, mkdesc(a_lo + kk * 2u, HI), mkdesc(b_lo + kk * 2u, HI), IDESC, (kb | kk) != 0u);
+        }
+        if (PAIR) {
+          // the stage is free, and at the end the accumulator complete, in both CTAs
+          umma_commit_pair(lead_bar(B_EMPTY + s));
+          umma_commit_pair(pair_bar(B_EMPTY + s));
+          if (kb + 1 == n_kb) {
+            umma_commit_pair(lead_bar(B_ACC));
+            umma_commit_pair(pair_bar(B_ACC));
+          }
+        } else {
+          umma_commit(bar_addr(bar_base, B_EMPTY + s));
+          if (kb + 1 == n_kb) umma_commit(bar_addr(bar_base, B_ACC));
+        }
       }
       __syncwarp();
     }
@@ -167,7 +208,7 @@ dg_gemm_sm100_kernel(const GemmParams g, const __grid_constant__ CUtensorMap tm_
         }
       }
     }
-    if (g.rowsq != nullptr && row < g.M) g.rowsq[size_t(row) * gridDim.x + blockIdx.x] = ok ? ss : 0.f;
+    if (g.rowsq != nullptr && row < g.M) g.rowsq[size_t(row) * n_tiles + n_tile] = ok ? ss : 0.f;
     }
   }
 
@@ -180,7 +221,13 @@ dg_gemm_sm100_kernel(const GemmParams g, const __grid_constant__ CUtensorMap tm_
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, BN < 32 ? 32 : BN);
+  if (PAIR) {
+    // neither CTA frees tensor memory or leaves while the other can still be the target of a pair-wide MMA or commit
+    cluster_sync_all();
+    if (warp == 1) tmem_dealloc_pair(tmem, BN);
+  } else if (warp == 1) {
+    tmem_dealloc(tmem, BN < 32 ? 32 : BN);
+  }
 }
 
 // Row-wise kernels: one block of 256 threads per row, a thread holds up to ROW_VEC 8-element vectors of the row in
@@ -303,14 +350,20 @@ __global__ void __launch_bounds__(256) dg_norm_residual_kernel(const float* part
 }
 
 cudaError_t sm100_gemm_configure() {
-  cudaError_t e = cudaFuncSetAttribute(dg_gemm_sm100_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(dg_gemm_sm100_kernel<128, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        int(gm::smem_bytes(128, false)));
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(dg_gemm_sm100_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gm::smem_bytes(64, false)));
+    e = cudaFuncSetAttribute(dg_gemm_sm100_kernel<64, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             int(gm::smem_bytes(64, false)));
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(dg_gemm_sm100_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gm::smem_bytes(128, true)));
+    e = cudaFuncSetAttribute(dg_gemm_sm100_kernel<128, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             int(gm::smem_bytes(128, true)));
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(dg_gemm_sm100_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gm::smem_bytes(64, true)));
+    e = cudaFuncSetAttribute(dg_gemm_sm100_kernel<64, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             int(gm::smem_bytes(64, true)));
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(dg_gemm_sm100_kernel<128, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             int(gm::smem_bytes_pair(128)));
   return e;
 }
 
@@ -335,11 +388,30 @@ cudaError_t launch_gemm_sm100(const GemmParams& g, const CUtensorMap& tm_a, cons
   const bool shallow = g.K / gm::BK <= 8;
   pdl_cfg(cfg, attr, grid, dim3(gm::THREADS), gm::smem_bytes(bn, shallow), st);
   if (shallow) {
-    if (bn == 128) return cudaLaunchKernelEx(&cfg, dg_gemm_sm100_kernel<128, true>, g, tm_a, tm_w);
-    return cudaLaunchKernelEx(&cfg, dg_gemm_sm100_kernel<64, true>, g, tm_a, tm_w);
+    if (bn == 128) return cudaLaunchKernelEx(&cfg, dg_gemm_sm100_kernel<128, true, false>, g, tm_a, tm_w);
+    return cudaLaunchKernelEx(&cfg, dg_gemm_sm100_kernel<64, true, false>, g, tm_a, tm_w);
   }
-  if (bn == 128) return cudaLaunchKernelEx(&cfg, dg_gemm_sm100_kernel<128, false>, g, tm_a, tm_w);
-  return cudaLaunchKernelEx(&cfg, dg_gemm_sm100_kernel<64, false>, g, tm_a, tm_w);
+  if (bn == 128) return cudaLaunchKernelEx(&cfg, dg_gemm_sm100_kernel<128, false, false>, g, tm_a, tm_w);
+  return cudaLaunchKernelEx(&cfg, dg_gemm_sm100_kernel<64, false, false>, g, tm_a, tm_w);
+}
+
+// Pair form: exactly two row tiles (128 < M <= 256), 128 output columns per tile; tm_w has boxes {64, 64, 1}.
+cudaError_t launch_gemm_sm100_pair(const GemmParams& g, const CUtensorMap& tm_a, const CUtensorMap& tm_w, cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2, g.N / 128, g.part != nullptr ? g.k_slices : 1u);
+  cfg.blockDim = dim3(gm::THREADS);
+  cfg.dynamicSmemBytes = gm::smem_bytes_pair(128);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = 2;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return cudaLaunchKernelEx(&cfg, dg_gemm_sm100_kernel<128, false, true>, g, tm_a, tm_w);
 }
 
 cudaError_t launch_rmsnorm_rows(const void* x, const void* w, void* y, uint32_t rows, uint32_t dim, cudaStream_t st) {

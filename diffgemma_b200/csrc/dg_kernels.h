@@ -63,6 +63,7 @@ cudaError_t launch_gemm_sm100(const GemmParams& g, const CUtensorMap& tm_a, cons
                               cudaStream_t st);
 // top-k selection + gathered PV (csrc/dg_topk.cu)
 cudaError_t launch_topk_select_pv(const TopkParams& p, cudaStream_t st);
+cudaError_t launch_gemm_sm100_pair(const GemmParams& g, const CUtensorMap& tm_a, const CUtensorMap& tm_w, cudaStream_t st);
 cudaError_t launch_rmsnorm_rows(const void* x, const void* w, void* y, uint32_t rows, uint32_t dim, cudaStream_t st);
 cudaError_t launch_norm_residual(const float* part, uint32_t n_part, const void* w, const void* hidden, void* out,
                                  uint32_t rows, uint32_t dim, cudaStream_t st);

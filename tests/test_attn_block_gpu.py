@@ -41,6 +41,8 @@ CASES = [
                      softmax_scale=1.0, v_norm=1, rope_pairing=capi.ROPE_PROPORTIONAL), 2816, 1500, True),
     # ragged: 100 canvas rows (one partial 128-row tile), a narrow model
     ("ragged", dict(n_q_heads=4, n_kv_heads=2, head_dim=256, canvas=100, rope_theta=1e4), 256, 300, False),
+    # 200 canvas rows: two row tiles, the second partial (the projections run as CTA pairs)
+    ("ragged_pair", dict(n_q_heads=4, n_kv_heads=2, head_dim=256, canvas=200, rope_theta=1e4), 512, 700, False),
 ]
 
 
@@ -72,5 +74,13 @@ def test_attn_block_matches_oracle(name, lk, hidden, P, v_from_k):
     out2 = blk.step(kv, P, hd)
     ctx.synchronize()
     assert torch.equal(out, out2)
+    if 128 < layer.canvas <= 256:
+        # the same step with the projections as single-CTA tiles: split-K planes and bf16 rounding are the same
+        ctx.set_pair_mode(False)
+        out3 = blk.step(kv, P, hd)
+        ctx.synchronize()
+        ctx.set_pair_mode(None)
+        err3 = np.abs(f(out3) - ref)
+        assert err3.max() <= BLOCK_MAX_ABS and err3.mean() <= BLOCK_MEAN_ABS, (name, "single", float(err3.max()))
     kv.close()
     ctx.close()
