@@ -1137,8 +1137,9 @@ def run_ours(args):
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e,
                     "how": (f"dg_host_pipe, {wl.PIPE_DEPTH} steps in flight on every rank: every step copies its inputs "
                             "from pinned host memory and its result back; copies of neighbouring steps overlap the kernels"
-                            + ("; a rank copies in its row slice of Q (the ranks exchange the slices over NVLink) and the canvas "
-                               "K/V only where they are stored, and copies back its own row slice of the output"
+                            + (("; a rank copies in " + ("its row slice of Q (the ranks exchange the slices over NVLink)"
+                                                         if args.share_q else "all of Q (every rank needs every row)")
+                                + " and the canvas K/V only where they are stored, and copies back its own row slice of the output")
                                if world > 1 and args.exchange == "p2p" else "")),
                     "h2d_bytes_per_step": h2d_total, "d2h_bytes_per_step": d2h_total},
             "gpu_launches": int(launches_per_step * args.steps),
