@@ -328,7 +328,8 @@ dg_attn_sm100_kernel(const __grid_constant__ AttnBatch bat) {
     stamp(p, 2);
 
     // ---------------------------------------------------------------- canvas append inside the launch
-    // The 2 C Hkv head vectors of canvas K / V are cut into shares of one vector per softmax warp.  Every CTA
+    // The 2 C Hkv head vectors of canvas K / V are cut into units of up to four heads of one token's K or V (the
+    // token's rotation is prepared once per unit) and the units into shares of one unit per softmax warp.  Every CTA
     // that gets here keeps taking shares from a counter until none is left, so all shares are taken by CTAs
     // that are running - also when part of the grid has not been scheduled yet (more clusters than fit) - and
     // none of them needs anything from anybody to finish its shares.  Whoever waits for the append (the
@@ -352,7 +353,11 @@ dg_attn_sm100_kernel(const __grid_constant__ AttnBatch bat) {
       av.write_end = p.ap_write_end;
       av.pos_base = p.pos_base;
       av.eps = p.eps;
-      const uint32_t n_shares = (p.ap_vectors + SM_WARPS - 1u) / SM_WARPS;
+      // a share = one unit (up to four heads of one token's K or V) for every softmax warp
+      const uint32_t n_units = append_unit_count(p.ap_vectors / (2u * p.Hkv), p.Hkv);
+      const uint32_t n_shares = (n_units + SM_WARPS - 1u) / SM_WARPS;
+      uint4 kw_own, kw_partner;
+      append_norm_weight(av, lane, kw_own, kw_partner);
       uint32_t mine = 0;
       for (uint32_t it = 0;; ++it) {
         // two slots in turn: a slot is rewritten only after the barrier that follows everybody's read of it
@@ -360,11 +365,8 @@ dg_attn_sm100_kernel(const __grid_constant__ AttnBatch bat) {
         asm volatile("bar.sync 5, %0;" ::"n"(SM_WARPS * 32) : "memory");
         const uint32_t share = ctl[3u + (it & 1u)];
         if (share >= n_shares) break;
-        const uint32_t v = share * SM_WARPS + warp;
-        if (v < p.ap_vectors) {
-          append_table_vector(av, v, lane);
-          ++mine;
-        }
+        const uint32_t u = share * SM_WARPS + warp;
+        if (u < n_units) mine += append_table_unit(av, u, lane, kw_own, kw_partner);
       }
       if (mine != 0u) {
         __threadfence();

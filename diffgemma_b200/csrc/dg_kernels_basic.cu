@@ -74,22 +74,34 @@ __global__ void __launch_bounds__(32) dg_append_kernel(const AppendParams p, con
   }
   ss = warp_sum(ss);
   const bool norm = is_q || is_k || p.v_norm;
+  const float inv = norm ? 1.0f / sqrtf(ss / float(D) + p.eps) : 1.0f;
+  const __nv_bfloat16* w = is_q ? p.qw : (is_k ? p.kw : nullptr);
   if (norm) {
-    const float inv = 1.0f / sqrtf(ss / float(D) + p.eps);
-    const __nv_bfloat16* w = is_q ? p.qw : (is_k ? p.kw : nullptr);
     for (uint32_t d = lane; d < D; d += 32) {
+      // the rotated elements of K get their norm inside the rotation (rope_norm_rotate)
+      if (is_k && ((d < rp.rot_half) || (d >= rp.pair_off && d < rp.pair_off + rp.rot_half))) continue;
       const float wv = w ? __bfloat162float(w[d]) : 1.0f;
       xs[d] = xs[d] * (inv * wv);
     }
   }
   __syncwarp();
-  if (is_q || is_k) {
+  if (is_q) {
     for (uint32_t i = lane; i < rp.rot_half; i += 32) {
       const float a = fpos * rp.inv_freq[i];
       const float c = cosf(a), s = sinf(a);
       const float x0 = xs[i], x1 = xs[rp.pair_off + i];
       xs[i] = rope_rotate_lo(x0, x1, c, s);
       xs[rp.pair_off + i] = rope_rotate_hi(x0, x1, c, s);
+    }
+    __syncwarp();
+  } else if (is_k) {
+    for (uint32_t i = lane; i < rp.rot_half; i += 32) {
+      const float a = fpos * rp.inv_freq[i];
+      const float c = cosf(a), s = sinf(a);
+      const float x0 = xs[i], x1 = xs[rp.pair_off + i];
+      const float w0 = w ? __bfloat162float(w[i]) : 1.0f, w1 = w ? __bfloat162float(w[rp.pair_off + i]) : 1.0f;
+      xs[i] = rope_norm_rotate(x0, x1, rope_coef_a(w0, c), rope_coef_b(w1, s, true), inv);
+      xs[rp.pair_off + i] = rope_norm_rotate(x1, x0, rope_coef_a(w1, c), rope_coef_b(w0, s, false), inv);
     }
     __syncwarp();
   }
