@@ -358,15 +358,23 @@ dg_attn_sm100_kernel(const __grid_constant__ AttnBatch bat) {
       const uint32_t n_shares = (n_units + SM_WARPS - 1u) / SM_WARPS;
       uint4 kw_own, kw_partner;
       append_norm_weight(av, lane, kw_own, kw_partner);
+      // In a share the K units (norm, rotation) and the V units (a copy unless V is normed) of a token alternate
+      // in runs of `groups`; odd shares shift the warps by one run, so that no warp gets the K units every time.
+      const uint32_t groups = (p.Hkv + APPEND_UNIT_HEADS - 1u) / APPEND_UNIT_HEADS;
       uint32_t mine = 0;
+      // the next share number is asked for before the work on this one starts: its round trip through the counter
+      // (about 500 cycles) then runs beside the work
+      if (tid == 0) ctl[3u] = atomicAdd(p.ap_ctl, 1u);
       for (uint32_t it = 0;; ++it) {
         // two slots in turn: a slot is rewritten only after the barrier that follows everybody's read of it
-        if (tid == 0) ctl[3u + (it & 1u)] = atomicAdd(p.ap_ctl, 1u);
         asm volatile("bar.sync 5, %0;" ::"n"(SM_WARPS * 32) : "memory");
         const uint32_t share = ctl[3u + (it & 1u)];
         if (share >= n_shares) break;
-        const uint32_t u = share * SM_WARPS + warp;
+        uint32_t next = 0;
+        if (tid == 0) next = atomicAdd(p.ap_ctl, 1u);
+        const uint32_t u = share * SM_WARPS + ((warp + (share & 1u) * groups) % SM_WARPS);
         if (u < n_units) mine += append_table_unit(av, u, lane, kw_own, kw_partner);
+        if (tid == 0) ctl[3u + ((it + 1u) & 1u)] = next;
       }
       if (mine != 0u) {
         __threadfence();
