@@ -293,3 +293,36 @@ def test_decoder_bitmap_sparse_fixture_properties():
             p = np.exp(s - s.max())
             p /= p.sum()
             np.testing.assert_allclose(got[qi, h], p @ V[:, h // 2, :], atol=1e-5)
+
+
+# --- the append kernels fold the K norm into the rotation: fma(x, w cos, x_partner (-/+ w_partner sin)) inv instead of
+# the reference's (x inv w) rotated afterwards (src/shaders/attn/qk_rope_kv/qk_rope_kv.metal:58-149).  Restated here
+# in fp32 (an fma = the exactly computed product-sum rounded once, taken through float64) the two orders must give
+# the same bf16 value except where the exact result lies at a rounding boundary, and never differ by more than one
+# bf16 step there.
+def test_folded_k_rotation_matches_reference_order():
+    rng = np.random.default_rng(11)
+    C, H, D = 64, 4, 256
+    half = D // 2
+    x = ao.round_bf16(rng.standard_normal((C, H, D)).astype(np.float32))
+    w = ao.round_bf16((1 + 0.1 * rng.standard_normal(D)).astype(np.float32))
+    cos, sin = ao.rope_tables(np.arange(16384, 16384 + C), D, D, 1e4)
+    ref = ao.round_bf16(ao.apply_rope(ao.rms_norm_heads(x, w, 1e-6), cos, sin, D))
+
+    f32 = np.float32
+    ss = np.sum(x * x, axis=-1, keepdims=True, dtype=np.float32)
+    inv = (f32(1.0) / np.sqrt(ss / f32(D) + f32(1e-6))).astype(f32)
+    c, s = cos[:, None, :], sin[:, None, :]
+    x0, x1, w0, w1 = x[..., :half], x[..., half:], w[:half], w[half:]
+
+    def fma(a, b, cc):
+        return (a.astype(np.float64) * b.astype(np.float64) + cc.astype(np.float64)).astype(f32)
+
+    lo = (fma(x0, (w0 * c).astype(f32), (x1 * (-(w1 * s).astype(f32))).astype(f32)) * inv).astype(f32)
+    hi = (fma(x1, (w1 * c).astype(f32), (x0 * (w0 * s).astype(f32)).astype(f32)) * inv).astype(f32)
+    got = ao.round_bf16(np.concatenate([lo, hi], axis=-1))
+
+    differ = got != ref
+    assert differ.mean() < 0.02, differ.mean()
+    step = np.maximum(np.abs(ref), 2.0 ** -20) * 2.0 ** -7        # one bf16 step at the value's magnitude, at most
+    assert np.all(np.abs(got - ref)[differ] <= step[differ])
